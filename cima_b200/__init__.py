@@ -1,0 +1,102 @@
+"""cima_b200: a small generation library for one GPU (NVIDIA B200, sm_100a).
+
+    import cima_b200
+    lm = cima_b200.load("model_dir", dtype="bfloat16", max_tokens=8192)
+    results = lm.generate([[1, 2, 3], [4, 5]], temperature=0, max_tokens=32)
+
+A model folder holds ``config.json`` and ``model.safetensors``; the model class is chosen by
+config.json through the architecture registry.  ``cima_b200.write_random_model`` makes such a folder
+from a configuration and a seed.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Union
+
+from .config import (ArchitectureEntry, ConfigError, Qwen2Config, lookup_architecture, read_config_json,
+                     register_architecture, registered_architectures)
+from .sampling import GenOptions, OptionError
+
+register_architecture(ArchitectureEntry(name=Qwen2Config.ARCHITECTURE, model_type="qwen2",
+                                        parse=Qwen2Config.from_dict, spec=Qwen2Config.model_spec))
+
+__version__ = "0.1.0"
+
+
+class LM:
+    """A loaded model with its cache, stepper and generation loop."""
+
+    def __init__(self, model, eos_ids: Sequence[int] = (), max_batch: int = 64):
+        from .engine import GenerationLoop, ModelStepper
+        self.model = model
+        self.stepper = ModelStepper(model, max_batch=max_batch)
+        self.loop = GenerationLoop(self.stepper, eos_ids)
+
+    @property
+    def spec(self):
+        return self.model.spec
+
+    def generate(self, prompts: Sequence[Sequence[int]], options: Union[GenOptions, Sequence[GenOptions], None] = None,
+                 **named):
+        """Token ids in, ``GenResult`` per prompt out.  Options by the reference's names
+        (temperature, top_k, top_p, repeat_penalty, seed, max_tokens, stop, ignore_eos), either as a
+        ``GenOptions`` (one for all prompts or one per prompt) or as keyword arguments."""
+        if named:
+            if options is not None and not isinstance(options, GenOptions):
+                raise ValueError("keyword options go with at most one GenOptions")
+            o = options or GenOptions()
+            for k, v in named.items():
+                if k == "stop" and not isinstance(v, (int, str)):
+                    for s in v:
+                        o = o.set("stop", s)
+                else:
+                    o = o.set(k, v)
+            options = o
+        return self.loop.generate(prompts, options)
+
+    @property
+    def stats(self):
+        return self.loop.stats
+
+
+def eos_ids_of(folder: str) -> List[int]:
+    """Stop ids a model folder declares (generation_config.json, then config.json), as the reference
+    gathers them (src/tokenizer.rs:704-749)."""
+    import json, os
+    out: List[int] = []
+    for name in ("generation_config.json", "config.json"):
+        p = os.path.join(folder, name)
+        if os.path.exists(p):
+            try:
+                with open(p) as f:
+                    v = json.load(f).get("eos_token_id")
+            except (OSError, ValueError):
+                continue
+            for t in (v if isinstance(v, list) else [v]):
+                if isinstance(t, int) and not isinstance(t, bool) and t not in out:
+                    out.append(t)
+    return out
+
+
+def load(folder: str, dtype: str = "bfloat16", max_tokens: int = 8192, max_seqs: Optional[int] = None,
+         max_batch: int = 64, device: str = "cuda:0", verbose: bool = True) -> LM:
+    from .engine import load_model
+    model = load_model(folder, dtype=dtype, max_tokens=max_tokens, max_seqs=max_seqs, device=device, verbose=verbose)
+    return LM(model, eos_ids_of(folder), max_batch=max_batch)
+
+
+def write_random_model(folder: str, config: Union[dict, Qwen2Config], seed: int = 0) -> None:
+    """A model folder (config.json, model.safetensors in bfloat16) from a configuration and a seed."""
+    from .engine import build_plan
+    from .weights import write_random_model as _write
+    raw = config.to_dict() if hasattr(config, "to_dict") else dict(config)
+    entry = lookup_architecture(raw)
+    typed = entry.parse(raw)
+    out = typed.to_dict() if hasattr(typed, "to_dict") else raw
+    for k, v in raw.items():
+        out.setdefault(k, v)
+    _write(folder, out, build_plan(entry.spec(typed)), seed)
+
+
+__all__ = ["LM", "load", "write_random_model", "eos_ids_of", "GenOptions", "OptionError", "ConfigError",
+           "Qwen2Config", "register_architecture", "registered_architectures", "lookup_architecture",
+           "read_config_json", "ArchitectureEntry"]

@@ -1,0 +1,98 @@
+"""Descriptions of a model as data: one spec per part, one per block, one per model.
+
+An architecture's typed configuration (``qwen2.py``) turns its ``config.json``
+keys into these specs; the parts (``cima_b200/parts``) are built from them and
+know nothing else about the model they sit in.  Every size and constant is a
+field here; none stands in the parts' code.
+
+``kind`` selects the implementation from the part registries
+(``cima_b200/parts/registry.py``); ``params`` carries what a kind needs beyond
+the common fields, so that a kind defined outside the package needs no change
+to these classes.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional
+
+
+@dataclass(frozen=True)
+class NormSpec:
+    kind: str                    # "rmsnorm"
+    size: int
+    eps: float
+    params: Dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class PositionSpec:
+    kind: str                    # "rope" | "none"
+    head_dim: int
+    rotary_dim: int              # how many leading dims of a head rotate (<= head_dim, even)
+    theta: float
+    params: Dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class MixerSpec:
+    kind: str                    # "attention"
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    qkv_bias: bool
+    out_bias: bool
+    window: int                  # 0 = every earlier key; w > 0 = the last w keys
+    scale: float                 # factor of q.k before the softmax
+    position: PositionSpec
+    # Index (in ModelSpec.layers) of the layer whose cache this one reads instead of
+    # writing its own; None = own cache.
+    cache_from: Optional[int] = None
+    params: Dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class FeedForwardSpec:
+    kind: str                    # "gated_mlp"
+    hidden: int
+    intermediate: int
+    activation: str              # "silu"
+    bias: bool = False
+    params: Dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class BlockSpec:
+    kind: str                    # "prenorm": x += mixer(norm(x)); x += ffn(norm(x))
+    mixer: MixerSpec
+    feed_forward: FeedForwardSpec
+    mixer_norm: NormSpec
+    ffn_norm: NormSpec
+    prefix: str                  # tensor-name prefix of the layer, e.g. "model.layers.3."
+    # tensor-name stems under the prefix, owned by the architecture's naming
+    names: Dict[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    architecture: str
+    vocab: int
+    hidden: int
+    max_position: int
+    layers: List[BlockSpec]
+    # The order in which layers run: indices into ``layers``.  A layer may be named
+    # twice; default is each layer once, in order.
+    schedule: List[int]
+    final_norm: NormSpec
+    tie_head: bool
+    embed_name: str
+    final_norm_name: str
+    head_name: str
+    embed_scale: float = 1.0
+
+    def describe(self) -> str:
+        kinds = [f"{self.layers[i].mixer.kind}"
+                 f"{'(w=%d)' % self.layers[i].mixer.window if self.layers[i].mixer.window else ''}"
+                 f"+{self.layers[i].feed_forward.kind}" for i in self.schedule]
+        return (f"{self.architecture}: vocab {self.vocab}, hidden {self.hidden}, "
+                f"{len(self.layers)} layers, schedule {kinds}")

@@ -1,0 +1,109 @@
+// Embedding gather, RMSNorm, gated activation, residual add, row gather.
+//
+// The residual stream is float32 in both precisions; what the matrix products read and write
+// ("activations") is float32 or bfloat16.  Norm weights and biases are float32 vectors.
+//
+// Counterparts in the reference (f16 storage, f32 arithmetic): k_gather_* src/kernels.cu:10-21,
+// k_rmsnorm :37-50, k_swiglu :81-84, k_add :75-78.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding: x[t,:] = scale * E[ids[t],:]
+template <typename TW>
+__global__ void k_embed(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ x,
+                        int H, int V, float scale) {
+  const int row = blockIdx.x;
+  int id = ids[row];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);    // ids are checked on the host; never read outside the table
+  const TW* src = table + (size_t)id * H;
+  float* dst = x + (size_t)row * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = cima_to_f32<TW>(src[i]) * scale;
+}
+
+extern "C" int cima_embed(const int* ids, const void* table, int table_dtype, float* x, int T, int H, int V,
+                          float scale, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || V <= 0) return cima_fail(CIMA_E_SIZE, "embed: hidden %d and vocab %d must be positive", H, V);
+  if (table_dtype == CIMA_F32) k_embed<float><<<T, 256, 0, stream>>>(ids, (const float*)table, x, H, V, scale);
+  else if (table_dtype == CIMA_BF16) k_embed<__nv_bfloat16><<<T, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, x, H, V, scale);
+  else return cima_fail(CIMA_E_DTYPE, "embed: table dtype code %d is neither float32 nor bfloat16", table_dtype);
+  return cima_launch_result();
+}
+
+// ---------------------------------------------------------------- RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w
+// One block per row.  Sum of squares, reciprocal root and the products are float32; one rounding
+// at the store.  1/sqrtf rather than rsqrtf: the latter is an approximation.
+template <typename TO>
+__global__ void k_rmsnorm(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ y,
+                          int H, float eps) {
+  __shared__ float red[32];
+  const float* xi = x + (size_t)blockIdx.x * H;
+  TO* yo = y + (size_t)blockIdx.x * H;
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = xi[i]; acc += v * v; }
+  const float total = cima_block_sum(acc, red);
+  const float inv = 1.0f / sqrtf(total / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) yo[i] = cima_from_f32<TO>(xi[i] * inv * w[i]);
+}
+
+extern "C" int cima_rmsnorm(const float* x, const float* w, void* y, int y_dtype, int T, int H, float eps,
+                            cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0) return cima_fail(CIMA_E_SIZE, "rmsnorm: width %d must be positive", H);
+  if (y_dtype == CIMA_F32) k_rmsnorm<float><<<T, 256, 0, stream>>>(x, w, (float*)y, H, eps);
+  else if (y_dtype == CIMA_BF16) k_rmsnorm<__nv_bfloat16><<<T, 256, 0, stream>>>(x, w, (__nv_bfloat16*)y, H, eps);
+  else return cima_fail(CIMA_E_DTYPE, "rmsnorm: output dtype code %d is neither float32 nor bfloat16", y_dtype);
+  return cima_launch_result();
+}
+
+// ---------------------------------------------------------------- gated activation: a = silu(g) * u
+// gu is [T, 2I] with the gate in columns [0, I) and the up projection in [I, 2I).
+template <typename TA>
+__global__ void k_swiglu(const TA* __restrict__ gu, TA* __restrict__ a, size_t total, int I) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = idx / I;
+    const int c = (int)(idx - row * I);
+    const float g = cima_to_f32<TA>(gu[row * 2 * I + c]);
+    const float u = cima_to_f32<TA>(gu[row * 2 * I + I + c]);
+    a[idx] = cima_from_f32<TA>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+extern "C" int cima_swiglu(const void* gu, void* a, int dtype, int T, int I, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (I <= 0) return cima_fail(CIMA_E_SIZE, "swiglu: intermediate width %d must be positive", I);
+  const size_t total = (size_t)T * I;
+  const int grid = (int)((total + 255) / 256 > 148 * 32 ? 148 * 32 : (total + 255) / 256);
+  if (dtype == CIMA_F32) k_swiglu<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)a, total, I);
+  else if (dtype == CIMA_BF16) k_swiglu<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)a, total, I);
+  else return cima_fail(CIMA_E_DTYPE, "swiglu: dtype code %d is neither float32 nor bfloat16", dtype);
+  return cima_launch_result();
+}
+
+// ---------------------------------------------------------------- residual: x += d  (sum in float32)
+template <typename TA>
+__global__ void k_add_residual(float* __restrict__ x, const TA* __restrict__ d, size_t total) {
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+    x[idx] += cima_to_f32<TA>(d[idx]);
+}
+
+extern "C" int cima_add_residual(float* x, const void* d, int d_dtype, size_t total, cudaStream_t stream) {
+  if (total == 0) return 0;
+  const int grid = (int)((total + 255) / 256 > 148 * 32 ? 148 * 32 : (total + 255) / 256);
+  if (d_dtype == CIMA_F32) k_add_residual<float><<<grid, 256, 0, stream>>>(x, (const float*)d, total);
+  else if (d_dtype == CIMA_BF16) k_add_residual<__nv_bfloat16><<<grid, 256, 0, stream>>>(x, (const __nv_bfloat16*)d, total);
+  else return cima_fail(CIMA_E_DTYPE, "add_residual: dtype code %d is neither float32 nor bfloat16", d_dtype);
+  return cima_launch_result();
+}
+
+// ---------------------------------------------------------------- row gather: out[i,:] = x[rows[i],:]
+__global__ void k_gather_rows(const float* __restrict__ x, const int* __restrict__ rows, float* __restrict__ out, int H) {
+  const float* src = x + (size_t)rows[blockIdx.x] * H;
+  float* dst = out + (size_t)blockIdx.x * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+}
+
+extern "C" int cima_gather_rows(const float* x, const int* rows, float* out, int n, int H, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  k_gather_rows<<<n, 256, 0, stream>>>(x, rows, out, H);
+  return cima_launch_result();
+}

@@ -1,0 +1,106 @@
+// Plain matrix product for the true 32-bit path and for weights that are stored in 32-bit:
+//   out[m,n] = sum_k A[m,k] * W[n,k] (+ bias[n])        weights are [out, in], as in the checkpoint
+// FFMA only, no tensor cores and no reduced-precision mode.  Each output element is accumulated
+// by one thread over k = 0..K-1 in ascending order, so its value depends on its own row of A and
+// row of W only: the same bits whether the row comes alone, in a prompt or in a batch.
+//
+// Counterpart in the reference: k_gemm_f16 (src/kernels.cu:1410-1431; 16x16 tiles, one output per
+// thread, f32 accumulate) with k_bias (:390-393) and k_add (:75-78) behind it.
+#include "common.cuh"
+
+enum { LIN_STORE = 0, LIN_ACCUM = 1 };
+
+template <typename TA, typename TW, typename TO, int MODE>
+__global__ void __launch_bounds__(256)
+k_linear_plain(const TA* __restrict__ A, const TW* __restrict__ W, const float* __restrict__ bias,
+               TO* __restrict__ out, int M, int N, int K, int lda, int ldo) {
+  constexpr int BM = 64, BN = 64, BK = 16;
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Ws[BK][BN + 4];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // 16 x 16 threads, 4 x 4 outputs each
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+
+  for (int k0 = 0; k0 < K; k0 += BK) {
+    // 64 x 16 elements of each operand, 4 per thread: thread -> (row = idx / 16, k = idx % 16)
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+      const int idx = threadIdx.x + r * 256;
+      const int row = idx >> 4, kk = idx & 15;
+      const int k = k0 + kk;
+      float a = 0.f, w = 0.f;
+      if (k < K) {
+        if (m0 + row < M) a = cima_to_f32<TA>(A[(size_t)(m0 + row) * lda + k]);
+        if (n0 + row < N) w = cima_to_f32<TW>(W[(size_t)(n0 + row) * K + k]);
+      }
+      As[kk][row] = a;
+      Ws[kk][row] = w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; kk++) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; j++) w[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      float v = acc[i][j];
+      if (bias) v += bias[n];
+      TO* o = out + (size_t)m * ldo + n;
+      if (MODE == LIN_ACCUM) *o = cima_from_f32<TO>(cima_to_f32<TO>(*o) + v);
+      else *o = cima_from_f32<TO>(v);
+    }
+  }
+}
+
+template <typename TA, typename TW, typename TO>
+static int launch_plain(const void* A, const void* W, const float* bias, void* out, int mode, int M, int N, int K,
+                        int lda, int ldo, cudaStream_t stream) {
+  dim3 grid((N + 63) / 64, (M + 63) / 64);
+  if (mode == LIN_STORE)
+    k_linear_plain<TA, TW, TO, LIN_STORE><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, bias, (TO*)out, M, N, K, lda, ldo);
+  else
+    k_linear_plain<TA, TW, TO, LIN_ACCUM><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, bias, (TO*)out, M, N, K, lda, ldo);
+  return cima_launch_result();
+}
+
+// mode 0: out = A W^T (+ bias), stored as out_dtype.  mode 1: out += A W^T (+ bias); out must be float32.
+extern "C" int cima_linear_plain(const void* A, int a_dtype, const void* W, int w_dtype, const float* bias,
+                                 void* out, int out_dtype, int mode, int M, int N, int K, int lda, int ldo,
+                                 cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (N <= 0 || K <= 0) return cima_fail(CIMA_E_SIZE, "linear_plain: N %d and K %d must be positive", N, K);
+  if (lda < K || ldo < N) return cima_fail(CIMA_E_SIZE, "linear_plain: leading dimensions (%d, %d) are smaller than the rows (%d, %d)", lda, ldo, K, N);
+  if (mode != LIN_STORE && mode != LIN_ACCUM) return cima_fail(CIMA_E_ARG, "linear_plain: mode %d is neither store (0) nor accumulate (1)", mode);
+  if (mode == LIN_ACCUM && out_dtype != CIMA_F32) return cima_fail(CIMA_E_DTYPE, "linear_plain: accumulation needs a float32 output");
+  if ((long long)((M + 63) / 64) > 65535) return cima_fail(CIMA_E_SIZE, "linear_plain: %d rows exceed one launch; the caller cuts them", M);
+  const int key = a_dtype * 4 + w_dtype * 2 + out_dtype;
+  switch (key) {
+    case 0: return launch_plain<float, float, float>(A, W, bias, out, mode, M, N, K, lda, ldo, stream);
+    case 4 + 0 + 0: return launch_plain<__nv_bfloat16, float, float>(A, W, bias, out, mode, M, N, K, lda, ldo, stream);
+    case 4 + 0 + 1: return launch_plain<__nv_bfloat16, float, __nv_bfloat16>(A, W, bias, out, mode, M, N, K, lda, ldo, stream);
+    case 4 + 2 + 0: return launch_plain<__nv_bfloat16, __nv_bfloat16, float>(A, W, bias, out, mode, M, N, K, lda, ldo, stream);
+    case 4 + 2 + 1: return launch_plain<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(A, W, bias, out, mode, M, N, K, lda, ldo, stream);
+    default:
+      return cima_fail(CIMA_E_DTYPE, "linear_plain: dtypes (A %d, W %d, out %d) are not a supported combination", a_dtype, w_dtype, out_dtype);
+  }
+}

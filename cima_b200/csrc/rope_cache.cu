@@ -1,0 +1,79 @@
+// Rotary position encoding of q and k, and the append of k and v to the paged cache, in one pass
+// over a step's rows.
+//
+// qkv is [T, ld]: q heads, then k heads, then v heads of each row.  q and k are rotated in place
+// (prefill attention reads them from this buffer); the rotated k and the v are also written to the
+// position's place in the layer's pages.  The angle p * inv_freq[i] and its sine and cosine are
+// float32 (sincosf, not the fast approximations); inv_freq[i] = theta^(-2i / rotary_dim) comes from
+// the host, computed in float64.  Pair (i, i + rotary_dim/2) of a head rotates:
+//   u_i' = u_i cos a - u_j sin a,   u_j' = u_i sin a + u_j cos a        (src/kernels.cu:397-414)
+// Dimensions from rotary_dim on pass through.  Append: src/kernels.cu:440-454 (one sequence,
+// [kv_heads, max_seq, dim]); here the place comes from the slot's block table.
+#include "common.cuh"
+
+template <typename TA>
+__global__ void __launch_bounds__(256)
+k_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, int rotary_dim,
+              const int* __restrict__ row_pos, const int* __restrict__ row_seq, const int* __restrict__ seq_slot,
+              TA* __restrict__ cache, CimaPaged pg, int nh, int nkv, int hd) {
+  __shared__ float cs[128], sn[128];
+  const int row = blockIdx.x;
+  const int pos = row_pos[row];
+  const int half = rotary_dim >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float s, c;
+    sincosf((float)pos * inv_freq[i], &s, &c);
+    cs[i] = c;
+    sn[i] = s;
+  }
+  __syncthreads();
+  TA* base = qkv + (size_t)row * ld;
+  const int slot = cache ? seq_slot[row_seq[row]] : 0;
+  // rotation pairs of q heads [0, nh) and k heads [nh, nh + nkv)
+  const int npairs = (nh + nkv) * half;
+  for (int idx = threadIdx.x; idx < npairs; idx += blockDim.x) {
+    const int head = idx / half, i = idx - head * half;
+    TA* u = base + (size_t)head * hd;
+    const float a = cima_to_f32<TA>(u[i]), b = cima_to_f32<TA>(u[i + half]);
+    const TA ra = cima_from_f32<TA>(a * cs[i] - b * sn[i]);
+    const TA rb = cima_from_f32<TA>(a * sn[i] + b * cs[i]);
+    u[i] = ra;
+    u[i + half] = rb;
+    if (cache && head >= nh) {
+      TA* dst = cache + pg.offset(slot, pos, 0, head - nh);
+      dst[i] = ra;
+      dst[i + half] = rb;
+    }
+  }
+  if (!cache) return;
+  // k dimensions that do not rotate
+  const int rest = hd - rotary_dim;
+  for (int idx = threadIdx.x; idx < nkv * rest; idx += blockDim.x) {
+    const int head = idx / rest, d = rotary_dim + (idx - head * rest);
+    cache[pg.offset(slot, pos, 0, head) + d] = base[(size_t)(nh + head) * hd + d];
+  }
+  // v
+  for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+    const int head = idx / hd, d = idx - head * hd;
+    cache[pg.offset(slot, pos, 1, head) + d] = base[(size_t)(nh + nkv + head) * hd + d];
+  }
+}
+
+// cache may be null (a layer that reads another layer's keys and values writes none).
+extern "C" int cima_rope_append(void* qkv, int dtype, int ld, const float* inv_freq, int rotary_dim,
+                                const int* row_pos, const int* row_seq, const int* seq_slot,
+                                void* cache, const int* table, int table_width, int ring, int page_size,
+                                int T, int nh, int nkv, int hd, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (hd <= 0 || hd > 256 || rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1))
+    return cima_fail(CIMA_E_SIZE, "rope_append: head_dim %d (at most 256) and an even rotary_dim %d <= head_dim are needed", hd, rotary_dim);
+  if (ld < (nh + 2 * nkv) * hd) return cima_fail(CIMA_E_SIZE, "rope_append: row stride %d is smaller than (heads + 2 kv heads) * head_dim = %d", ld, (nh + 2 * nkv) * hd);
+  if (cache && (page_size <= 0 || table_width <= 0)) return cima_fail(CIMA_E_SIZE, "rope_append: page size %d and table width %d must be positive", page_size, table_width);
+  CimaPaged pg{table, table_width, ring, page_size, nkv, hd};
+  if (dtype == CIMA_F32)
+    k_rope_append<float><<<T, 256, 0, stream>>>((float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, (float*)cache, pg, nh, nkv, hd);
+  else if (dtype == CIMA_BF16)
+    k_rope_append<__nv_bfloat16><<<T, 256, 0, stream>>>((__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, (__nv_bfloat16*)cache, pg, nh, nkv, hd);
+  else return cima_fail(CIMA_E_DTYPE, "rope_append: dtype code %d is neither float32 nor bfloat16", dtype);
+  return cima_launch_result();
+}

@@ -1,0 +1,217 @@
+// Token selection on the device.
+//
+// argmax: one block per row of float32 logits; ties go to the higher index, the order the
+// reference gets from packing (orderable float bits << 32 | index) into one u64 maximum
+// (src/kernels.cu:244-262).
+#include "common.cuh"
+
+__device__ __forceinline__ unsigned long long cima_pack_key(float v, int i) {
+  unsigned int b = __float_as_uint(v);
+  b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+  return ((unsigned long long)b << 32) | (unsigned int)i;
+}
+
+__device__ __forceinline__ unsigned long long cima_block_max_u64(unsigned long long v, unsigned long long* red) {
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long w = __shfl_xor_sync(0xffffffffu, v, o);
+    v = w > v ? w : v;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = (blockDim.x + 31) >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  unsigned long long t = lane < nwarp ? red[lane] : 0ULL;
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long w = __shfl_xor_sync(0xffffffffu, t, o);
+    t = w > t ? w : t;
+  }
+  return t;
+}
+
+__global__ void __launch_bounds__(1024)
+k_argmax(const float* __restrict__ logits, int ld, int V, int* __restrict__ tokens) {
+  __shared__ unsigned long long red[32];
+  const float* x = logits + (size_t)blockIdx.x * ld;
+  unsigned long long best = 0ULL;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const unsigned long long k = cima_pack_key(x[i], i);
+    best = k > best ? k : best;
+  }
+  best = cima_block_max_u64(best, red);
+  if (threadIdx.x == 0) tokens[blockIdx.x] = (int)(unsigned int)best;
+}
+
+extern "C" int cima_argmax(const float* logits, int ld, int n, int V, int* tokens, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (V <= 0 || ld < V) return cima_fail(CIMA_E_SIZE, "argmax: vocabulary %d must be positive and fit the row stride %d", V, ld);
+  k_argmax<<<n, 1024, 0, stream>>>(logits, ld, V, tokens);
+  return cima_launch_result();
+}
+
+// ---------------------------------------------------------------------------------------------
+// The sampling chain of the reference's DefaultSampler (src/models/mod.rs:86-201), whole, on the
+// device, one block per row:
+//   1. repeat penalty over the last 64 tokens of the sequence's history, once per occurrence:
+//      l > 0 ? l / rp : l * rp                                                    (:149-160)
+//   2. temperature <= 0 -> argmax, ties to the higher index                        (:163-169)
+//   3. top-k (0 = all) in the order (value descending, index descending)           (:171-194)
+//   4. p = exp((l - max) / max(T, 1e-4)), normalised over the kept                 (:104-109)
+//   5. top-p: the shortest prefix of that order whose mass reaches top_p           (:110-119)
+//   6. r = u * mass(kept); the first token of the order whose cumulated mass reaches r (:121-130)
+//      u from xorshift64* (state max(seed, 1)), u = (x * 0x2545F4914F6CDD1D >> 40) / 2^24 (:69-78)
+// The reference sorts on the host.  Here nothing is sorted: every token has the 64-bit key
+// (orderable value bits << 32 | index), whose order is the order above, and steps 3, 5 and 6 are
+// each a search for the largest key T such that {tokens with key >= T} has at least k members, or
+// at least the wanted mass.  A search fixes T bit by bit from the top; each bit is one pass over
+// the row.  Sums of masses run in a fixed order, so a row's draw is the same whatever else is in
+// the batch; they differ from the host's sequential sums by rounding only.
+//
+// Per-sequence state (by slot): rng state, the ring of the last 64 tokens and the count of tokens
+// pushed so far.  The drawn token is pushed into the ring before the kernel ends.
+// ---------------------------------------------------------------------------------------------
+
+constexpr int SAMPLE_THREADS = 1024;
+constexpr int SAMPLE_RING = 64;
+
+struct SampleRow {
+  const float* l;     // penalised logits of the row
+  int V;
+  float maxl, inv_t;
+};
+
+// number of tokens with key >= T
+__device__ int sample_count(const SampleRow& r, unsigned long long T, float* redf) {
+  int c = 0;
+  for (int i = threadIdx.x; i < r.V; i += blockDim.x) c += cima_pack_key(r.l[i], i) >= T ? 1 : 0;
+  return (int)(cima_block_sum((float)c, redf) + 0.5f);     // counts below 2^24 are exact in float32
+}
+
+// mass of the tokens with key in [T, ...) that are also kept (key >= floor)
+__device__ float sample_mass(const SampleRow& r, unsigned long long T, float* redf) {
+  float s = 0.f;
+  for (int i = threadIdx.x; i < r.V; i += blockDim.x) {
+    const float v = r.l[i];
+    if (cima_pack_key(v, i) >= T) s += expf((v - r.maxl) * r.inv_t);
+  }
+  return cima_block_sum(s, redf);
+}
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+k_sample(const float* __restrict__ logits, int ld, int V, const int* __restrict__ row_slot,
+         const float* __restrict__ params, unsigned long long* __restrict__ rng, int* __restrict__ ring,
+         int* __restrict__ ring_count, float* __restrict__ work, int* __restrict__ tokens) {
+  __shared__ float redf[32];
+  __shared__ unsigned long long redk[32];
+  __shared__ float s_u;
+  const int row = blockIdx.x;
+  const int slot = row_slot[row];
+  const float temperature = params[row * 4 + 0];
+  const int top_k = (int)params[row * 4 + 1];
+  const float top_p = params[row * 4 + 2];
+  const float rp = params[row * 4 + 3];
+  const float* x = logits + (size_t)row * ld;
+  float* l = work + (size_t)row * V;
+  int* myring = ring + (size_t)slot * SAMPLE_RING;
+
+  // 1. working copy, then the penalty, entry by entry as the host loop does
+  for (int i = threadIdx.x; i < V; i += blockDim.x) l[i] = x[i];
+  __syncthreads();
+  const int pushed = ring_count[slot];
+  if (threadIdx.x == 0 && rp != 1.0f) {
+    const int n = pushed < SAMPLE_RING ? pushed : SAMPLE_RING;
+    for (int j = 0; j < n; j++) {
+      // oldest first, as a history slice is walked
+      const int t = myring[(pushed - n + j) % SAMPLE_RING];
+      if (t >= 0 && t < V) l[t] = l[t] > 0.f ? l[t] / rp : l[t] * rp;
+    }
+  }
+  __syncthreads();
+
+  // the largest key (needed by both the greedy and the sampled way)
+  unsigned long long best = 0ULL;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const unsigned long long k = cima_pack_key(l[i], i);
+    best = k > best ? k : best;
+  }
+  best = cima_block_max_u64(best, redk);
+  int token = (int)(unsigned int)best;
+
+  if (temperature > 0.f) {
+    SampleRow r;
+    r.l = l; r.V = V;
+    r.maxl = l[token];
+    r.inv_t = 1.0f / fmaxf(temperature, 1e-4f);
+    int idx_bits = 1;
+    while ((1 << idx_bits) < V) idx_bits++;
+
+    // 3. floor of the kept keys: the k-th largest key
+    unsigned long long floor_key = 0ULL;
+    if (top_k > 0 && top_k < V) {
+      for (int b = 63; b >= 0; b--) {
+        if (b < 32 && b >= idx_bits) continue;               // index bits that no token has
+        const unsigned long long cand = floor_key | (1ULL << b);
+        const int c = sample_count(r, cand, redf);
+        if (c >= top_k) floor_key = cand;
+        if (c == top_k) break;                                // the kept set is settled
+      }
+    }
+    // 4./5. mass of the kept, then the top-p floor.  A search builds, bit by bit from the top, the
+    // largest T for which "T <= floor, or the tokens with key >= T are some and weigh enough" holds.
+    const float total = sample_mass(r, floor_key, redf);
+    if (top_p < 1.0f) {
+      unsigned long long T = 0ULL;
+      for (int b = 63; b >= 0; b--) {
+        if (b < 32 && b >= idx_bits) continue;
+        const unsigned long long cand = T | (1ULL << b);
+        if (cand <= floor_key) { T = cand; continue; }
+        if (cand > best) continue;
+        if (sample_mass(r, cand, redf) / total >= top_p) T = cand;
+      }
+      floor_key = T > floor_key ? T : floor_key;
+    }
+    const float kept = sample_mass(r, floor_key, redf) / total;
+    // 6. the draw
+    if (threadIdx.x == 0) {
+      unsigned long long s = rng[slot];
+      s ^= s >> 12; s ^= s << 25; s ^= s >> 27;
+      rng[slot] = s;
+      s_u = (float)((s * 0x2545F4914F6CDD1DULL) >> 40) / 16777216.0f;
+    }
+    __syncthreads();
+    const float target = s_u * kept;
+    unsigned long long T = 0ULL;
+    for (int b = 63; b >= 0; b--) {
+      if (b < 32 && b >= idx_bits) continue;
+      const unsigned long long cand = T | (1ULL << b);
+      if (cand <= floor_key) { T = cand; continue; }
+      if (cand > best) continue;
+      if (sample_mass(r, cand, redf) / total >= target) T = cand;
+    }
+    if (T < floor_key) T = floor_key;
+    // the token is the one with the smallest key >= T (T itself whenever T is a token's key)
+    unsigned long long m = 0ULL;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      const unsigned long long k = cima_pack_key(l[i], i);
+      if (k >= T) { const unsigned long long c = ~k; m = c > m ? c : m; }
+    }
+    m = cima_block_max_u64(m, redk);
+    token = (int)(unsigned int)(~m);
+  }
+  if (threadIdx.x == 0) {
+    tokens[row] = token;
+    myring[pushed % SAMPLE_RING] = token;
+    ring_count[slot] = pushed + 1;
+  }
+}
+
+// logits [n, V] float32 (row stride ld); row_slot [n]; params [n, 4] = temperature, top_k, top_p,
+// repeat_penalty; rng [slots] u64; ring [slots, 64]; ring_count [slots]; work [n, V] float32 scratch.
+extern "C" int cima_sample(const float* logits, int ld, int n, int V, const int* row_slot, const float* params,
+                           unsigned long long* rng, int* ring, int* ring_count, float* work, int* tokens,
+                           cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (V <= 0 || ld < V) return cima_fail(CIMA_E_SIZE, "sample: vocabulary %d must be positive and fit the row stride %d", V, ld);
+  if (V >= (1 << 24)) return cima_fail(CIMA_E_SIZE, "sample: vocabulary %d exceeds 2^24 (counts are summed in float32)", V);
+  k_sample<<<n, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, row_slot, params, rng, ring, ring_count, work, tokens);
+  return cima_launch_result();
+}

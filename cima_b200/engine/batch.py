@@ -1,0 +1,91 @@
+"""A step's batch: the tokens it brings and where they belong, as the kernels want them.
+
+Rows are flat and ragged: the tokens of all sequences one after another, no padding.  Per row its
+absolute position and the index of its sequence in the batch; per sequence its slot, its first row
+and its length after the step.  All of it travels to the device in one copy from pinned memory.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()          # places among ``tokens`` whose logits are wanted
+
+
+@dataclass
+class StepBatch:
+    prefill: bool                     # True: every sequence starts at position 0; False: one token each
+    n_rows: int
+    n_seqs: int
+    n_want: int
+    max_len: int                      # longest sequence after the step (host copy, sizes launches)
+    want_all_in_order: bool
+    tokens: torch.Tensor              # int32 [rows]
+    row_pos: torch.Tensor             # int32 [rows]
+    row_seq: torch.Tensor             # int32 [rows]
+    seq_slot: torch.Tensor            # int32 [seqs]
+    seq_first_row: torch.Tensor       # int32 [seqs + 1]
+    seq_len: torch.Tensor             # int32 [seqs]
+    want_rows: torch.Tensor           # int32 [wanted]
+    host_seq_first_row: np.ndarray = None
+    host_seq_len: np.ndarray = None
+
+
+def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, device) -> StepBatch:
+    """Validate and pack.  ``starts[i]`` is how many positions entry i's slot already holds."""
+    if not entries:
+        raise ValueError("a step needs at least one entry")
+    if len({e.slot for e in entries}) != len(entries):
+        raise ValueError("a slot appears twice in one step")
+    counts = [len(e.tokens) for e in entries]
+    if any(c <= 0 for c in counts):
+        raise ValueError("every entry of a step brings at least one token")
+    if all(c == 1 for c in counts):
+        prefill = False                   # one token each: attention over the cache, also at position 0
+    elif all(s == 0 for s in starts):
+        prefill = True
+    else:
+        raise ValueError("the sequences of a step either all start at their first token or all go on by one "
+                         f"token (token counts {counts}, positions held {list(starts)})")
+    B, T = len(entries), sum(counts)
+    W = sum(len(e.want) for e in entries)
+    buf = np.empty(3 * T + 3 * B + 1 + W, dtype=np.int32)
+    tokens, row_pos, row_seq = buf[0:T], buf[T:2 * T], buf[2 * T:3 * T]
+    o = 3 * T
+    seq_slot, seq_first, seq_len, want_rows = buf[o:o + B], buf[o + B:o + 2 * B + 1], buf[o + 2 * B + 1:o + 3 * B + 1], buf[o + 3 * B + 1:]
+    r = w = 0
+    for i, (e, s, c) in enumerate(zip(entries, starts, counts)):
+        tk = np.asarray(e.tokens, dtype=np.int64)
+        if tk.min() < 0 or tk.max() >= vocab:
+            raise ValueError(f"entry {i}: token ids must lie in [0, {vocab})")
+        tokens[r:r + c] = tk
+        row_pos[r:r + c] = np.arange(s, s + c)
+        row_seq[r:r + c] = i
+        seq_slot[i], seq_first[i], seq_len[i] = e.slot, r, s + c
+        for p in e.want:
+            if not (0 <= p < c):
+                raise ValueError(f"entry {i}: wanted place {p} is outside its {c} tokens")
+            want_rows[w] = r + p
+            w += 1
+        r += c
+    seq_first[B] = T
+    host = torch.from_numpy(buf)
+    if torch.device(device).type == "cuda":
+        dev = host.pin_memory().to(device, non_blocking=True)
+    else:
+        dev = host.clone()
+    all_in_order = W == T and bool(np.array_equal(want_rows, np.arange(T)))
+    return StepBatch(prefill=prefill, n_rows=T, n_seqs=B, n_want=W, max_len=int(seq_len.max()),
+                     want_all_in_order=all_in_order,
+                     tokens=dev[0:T], row_pos=dev[T:2 * T], row_seq=dev[2 * T:3 * T],
+                     seq_slot=dev[o:o + B], seq_first_row=dev[o + B:o + 2 * B + 1],
+                     seq_len=dev[o + 2 * B + 1:o + 3 * B + 1], want_rows=dev[o + 3 * B + 1:],
+                     host_seq_first_row=seq_first.copy(), host_seq_len=seq_len.copy())

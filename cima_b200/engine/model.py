@@ -1,0 +1,145 @@
+"""A model put together from a ModelSpec: embedding, the blocks in the order of the schedule, final
+norm and head; its cache; and the one step function that prefill, decoding, generation and trace
+replay all go through.
+
+The reference's counterparts: ``Transformer::build`` (src/models/transformer.rs:778-1002),
+``forward_chunk_at`` (:1012-1321), ``project_logits`` (:1631-1652); one sequence there, a ragged
+batch of sequences here.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..cache.kv import KVCache, StateRequest
+from ..config.registry import lookup_architecture, read_config_json
+from ..config.specs import ModelSpec
+from ..parts import Linear, Runtime, build_block, build_norm
+from ..weights.loader import TensorSpec, load_tensors
+from .batch import StepBatch, StepEntry, build_batch
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def parse_dtype(d) -> torch.dtype:
+    if d not in _DTYPES:
+        raise ValueError(f"dtype {d!r} is not one of bfloat16, float32")
+    return _DTYPES[d]
+
+
+def build_plan(spec: ModelSpec, rt: Optional[Runtime] = None) -> Dict[str, TensorSpec]:
+    """Every tensor the model reads, by name (needs no GPU: parts are built but not loaded)."""
+    rt = rt or Runtime(kernels=None, dtype=torch.bfloat16, device="cpu")
+    return Model(spec, rt).plan()
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, rt: Runtime):
+        self.spec, self.rt = spec, rt
+        for i in spec.schedule:
+            if not (0 <= i < len(spec.layers)):
+                raise ValueError(f"the schedule names layer {i}; the model has {len(spec.layers)}")
+        self.blocks = [build_block(b, i, rt) for i, b in enumerate(spec.layers)]
+        self.final_norm = build_norm(spec.final_norm, rt)
+        self.embedding: Optional[torch.Tensor] = None
+        self.head: Optional[Linear] = None
+        self.cache: Optional[KVCache] = None
+
+    # ------------------------------------------------------------------ weights
+    def plan(self) -> Dict[str, TensorSpec]:
+        s = self.spec
+        p: Dict[str, TensorSpec] = {s.embed_name: TensorSpec((s.vocab, s.hidden))}
+        for b in self.blocks:
+            p.update(b.plan())
+        p.update(self.final_norm.plan(s.final_norm_name))
+        if not s.tie_head:
+            p[s.head_name] = TensorSpec((s.vocab, s.hidden))
+        return p
+
+    def ignorable(self) -> List[str]:
+        """Names a checkpoint may hold without the model reading them."""
+        pats = ["*.rotary_emb.inv_freq"]
+        if self.spec.tie_head:
+            pats.append(self.spec.head_name)
+        return pats
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        self.embedding = self.rt.matrix(tensors[s.embed_name])
+        for b in self.blocks:
+            b.load(tensors)
+        self.final_norm.load(tensors, s.final_norm_name)
+        self.head = Linear(tensors[s.embed_name] if s.tie_head else tensors[s.head_name], None, self.rt)
+        if s.tie_head and self.head.weight.dtype == self.embedding.dtype:
+            self.head.weight = self.embedding                 # one copy on the device
+
+    def weight_bytes(self) -> int:
+        """Bytes a decode step reads of the weights: every block, final norm and head once
+        (embedding rows excluded unless the head shares the table)."""
+        return sum(b.nbytes() for b in self.blocks) + self.final_norm.nbytes() + self.head.nbytes()
+
+    # ------------------------------------------------------------------ cache
+    def make_cache(self, max_tokens: int, max_seqs: Optional[int] = None, page_size: int = 64,
+                   extra_state: Sequence[StateRequest] = ()) -> KVCache:
+        shares = {i: b.mixer.cache_from for i, b in enumerate(self.spec.layers) if b.mixer.cache_from is not None}
+        self.cache = KVCache([b.cache_requests() for b in self.blocks], max_tokens, self.spec.max_position,
+                             self.rt.dtype, self.rt.device, page_size=page_size, max_seqs=max_seqs,
+                             shares=shares, extra_state=extra_state)
+        return self.cache
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the tokens the entries bring, from the cache earlier steps left; float32 logits
+        ``[wanted, vocab]`` in the order of the entries and of their ``want``."""
+        cache = self.cache
+        if cache is None:
+            raise RuntimeError("the model has no cache yet: call make_cache first")
+        entries = list(entries)
+        for e in entries:
+            if not cache.slots.is_held(e.slot):
+                raise ValueError(f"slot {e.slot} is not open")
+        starts = [cache.length(e.slot) for e in entries]
+        batch = build_batch(entries, starts, self.spec.vocab, self.rt.device)
+        for e, s in zip(entries, starts):
+            cache.reserve(e.slot, s + len(e.tokens))
+        cache.flush()
+        logits = self.forward(batch)
+        for e, s in zip(entries, starts):
+            cache.commit(e.slot, s + len(e.tokens))
+        return logits
+
+    def forward(self, batch: StepBatch) -> torch.Tensor:
+        K_, s = self.rt.kernels, self.spec
+        x = self.rt.empty(batch.n_rows, s.hidden, dtype=torch.float32)
+        K_.embed(batch.tokens, self.embedding, x, s.embed_scale)
+        for i in s.schedule:
+            self.blocks[i].forward(x, batch, self.cache)
+        return self.project(x, batch)
+
+    def project(self, x: torch.Tensor, batch: StepBatch) -> torch.Tensor:
+        """Final norm and head at the wanted rows only."""
+        if batch.n_want == 0:
+            return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=self.rt.device)
+        if not batch.want_all_in_order:
+            picked = self.rt.empty(batch.n_want, self.spec.hidden, dtype=torch.float32)
+            self.rt.kernels.gather_rows(x, batch.want_rows, picked)
+            x = picked
+        return self.head.logits(self.final_norm(x))
+
+
+def load_model(folder: str, dtype="bfloat16", max_tokens: int = 4096, max_seqs: Optional[int] = None,
+               device="cuda:0", kernels=None, verbose: bool = True) -> Model:
+    """A model from a folder with config.json and model.safetensors, its class chosen by config.json."""
+    from ..kernels import Kernels
+    raw = read_config_json(folder)
+    entry = lookup_architecture(raw)
+    spec = entry.spec(entry.parse(raw))
+    rt = Runtime(kernels=kernels if kernels is not None else Kernels(verbose=verbose),
+                 dtype=parse_dtype(dtype), device=device)
+    model = Model(spec, rt)
+    model.load(load_tensors(folder, model.plan(), ignore=model.ignorable()))
+    from ..sampling.sampler import sampler_state
+    model.make_cache(max_tokens, max_seqs, extra_state=sampler_state())
+    return model

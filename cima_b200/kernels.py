@@ -1,0 +1,260 @@
+"""The kernel library as Python calls: one method per entry point of ``csrc``.
+
+Arguments are torch tensors on the GPU; the methods check dtypes, shapes and contiguity, pass raw
+pointers and the current CUDA stream to the C entry points, and turn a refusal into an exception
+with the library's own sentence.  There is no CPU path and no substitute: if the library cannot be
+built or loaded, ``Kernels()`` raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc.build import BuildError, library_path
+
+F32, BF16 = 0, 1
+ABI_VERSION = 3
+
+# epilogues of the skinny product
+SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt is torch.float32:
+        return F32
+    if dt is torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {dt} is neither float32 nor bfloat16")
+
+
+_vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+
+_SIGNATURES = {
+    "cima_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp],
+    "cima_rmsnorm": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
+    "cima_swiglu": [_vp, _vp, _i, _i, _i, _vp],
+    "cima_add_residual": [_vp, _vp, _i, _sz, _vp],
+    "cima_gather_rows": [_vp, _vp, _vp, _i, _i, _vp],
+    "cima_linear_plain": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_linear_skinny": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_attention_plain": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+                             _f, _i, _i, _vp],
+    "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
+    "cima_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+}
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class Kernels:
+    """Loads (building first if needed) the CUDA library; fails loudly when it cannot."""
+
+    def __init__(self, verbose: bool = True):
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device is visible: this library runs on the GPU only")
+        try:
+            path = library_path(build=True, verbose=verbose)
+        except BuildError as e:
+            raise KernelError(f"the CUDA kernel library is missing and could not be built: {e}") from e
+        try:
+            self.lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load {path}: {e}") from e
+        self.path = path
+        self.lib.cima_last_error.restype = ctypes.c_char_p
+        self.lib.cima_abi_version.restype = ctypes.c_int
+        if self.lib.cima_abi_version() != ABI_VERSION:
+            raise KernelError(f"{path} has ABI {self.lib.cima_abi_version()}, this package wants {ABI_VERSION}")
+        for name, sig in _SIGNATURES.items():
+            fn = getattr(self.lib, name)
+            fn.argtypes = sig
+            fn.restype = ctypes.c_int
+        self.launches = 0
+
+    # ------------------------------------------------------------------ plumbing
+    def _check(self, code: int, what: str) -> None:
+        self.launches += 1
+        if code != 0:
+            raise KernelError(f"{what}: {self.lib.cima_last_error().decode()} (code {code})")
+
+    @staticmethod
+    def _stream() -> int:
+        return torch.cuda.current_stream().cuda_stream
+
+    @staticmethod
+    def _need(t: torch.Tensor, name: str, dtype=None, dims=None) -> None:
+        if not t.is_cuda:
+            raise KernelError(f"{name} is on {t.device}; the kernels take GPU tensors only")
+        if dtype is not None and t.dtype is not dtype:
+            raise KernelError(f"{name} is {t.dtype}, expected {dtype}")
+        if dims is not None and t.dim() != dims:
+            raise KernelError(f"{name} has {t.dim()} dimensions, expected {dims}")
+        if not t.is_contiguous():
+            raise KernelError(f"{name} is not contiguous")
+
+    # ------------------------------------------------------------------ elementwise
+    def embed(self, ids: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: float = 1.0) -> None:
+        self._need(ids, "ids", torch.int32, 1); self._need(table, "table", None, 2); self._need(x, "x", torch.float32, 2)
+        T, (V, H) = ids.numel(), table.shape
+        if tuple(x.shape) != (T, H):
+            raise KernelError(f"embed: x is {tuple(x.shape)}, expected {(T, H)}")
+        self._check(self.lib.cima_embed(ids.data_ptr(), table.data_ptr(), dtype_code(table.dtype), x.data_ptr(),
+                                        T, H, V, scale, self._stream()), "embed")
+
+    def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+        self._need(x, "x", torch.float32, 2); self._need(w, "w", torch.float32, 1); self._need(out, "out", None, 2)
+        T, H = x.shape
+        if w.numel() != H or tuple(out.shape) != (T, H):
+            raise KernelError(f"rmsnorm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+        self._check(self.lib.cima_rmsnorm(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
+                                          T, H, eps, self._stream()), "rmsnorm")
+
+    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
+        self._need(gate_up, "gate_up", None, 2); self._need(out, "out", gate_up.dtype, 2)
+        T, I2 = gate_up.shape
+        if I2 % 2 or tuple(out.shape) != (T, I2 // 2):
+            raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} and out {tuple(out.shape)} do not agree")
+        self._check(self.lib.cima_swiglu(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), T, I2 // 2,
+                                         self._stream()), "swiglu")
+
+    def add_residual(self, x: torch.Tensor, delta: torch.Tensor) -> None:
+        self._need(x, "x", torch.float32); self._need(delta, "delta")
+        if x.shape != delta.shape:
+            raise KernelError(f"add_residual: x {tuple(x.shape)} and delta {tuple(delta.shape)} differ")
+        self._check(self.lib.cima_add_residual(x.data_ptr(), delta.data_ptr(), dtype_code(delta.dtype),
+                                               x.numel(), self._stream()), "add_residual")
+
+    def gather_rows(self, x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+        self._need(x, "x", torch.float32, 2); self._need(rows, "rows", torch.int32, 1); self._need(out, "out", torch.float32, 2)
+        if tuple(out.shape) != (rows.numel(), x.shape[1]):
+            raise KernelError(f"gather_rows: out is {tuple(out.shape)}, expected {(rows.numel(), x.shape[1])}")
+        self._check(self.lib.cima_gather_rows(x.data_ptr(), rows.data_ptr(), out.data_ptr(), rows.numel(),
+                                              x.shape[1], self._stream()), "gather_rows")
+
+    # ------------------------------------------------------------------ matrix products
+    def linear_plain(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                     accumulate: bool = False) -> None:
+        """out = a @ w.T (+ bias), or out += ... when ``accumulate`` (out float32)."""
+        self._need(a, "a", None, 2); self._need(w, "w", None, 2); self._need(out, "out", None, 2)
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or tuple(out.shape) != (M, N):
+            raise KernelError(f"linear_plain: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+        if bias is not None:
+            self._need(bias, "bias", torch.float32, 1)
+            if bias.numel() != N:
+                raise KernelError(f"linear_plain: bias has {bias.numel()} entries, expected {N}")
+        # one launch takes up to 65535 * 64 rows; cut above that
+        step = 65535 * 64
+        for m0 in range(0, M, step):
+            m1 = min(M, m0 + step)
+            self._check(self.lib.cima_linear_plain(a[m0:m1].data_ptr(), dtype_code(a.dtype), w.data_ptr(),
+                                                   dtype_code(w.dtype), _ptr(bias), out[m0:m1].data_ptr(),
+                                                   dtype_code(out.dtype), 1 if accumulate else 0, m1 - m0, N, K,
+                                                   K, N, self._stream()), "linear_plain")
+
+    def linear_skinny(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                      mode: int) -> None:
+        """Few rows (<= 64), bf16 operands; ``mode`` is one of SK_*.  For SK_SWIGLU ``w`` is [2N, K]."""
+        self._need(a, "a", torch.bfloat16, 2); self._need(w, "w", torch.bfloat16, 2); self._need(out, "out", None, 2)
+        M, K = a.shape
+        N = w.shape[0] // 2 if mode == SK_SWIGLU else w.shape[0]
+        want = torch.float32 if mode in (SK_ACCUM, SK_STORE_F32) else torch.bfloat16
+        if w.shape[1] != K or tuple(out.shape) != (M, N) or out.dtype is not want:
+            raise KernelError(f"linear_skinny(mode {mode}): a {tuple(a.shape)}, w {tuple(w.shape)}, "
+                              f"out {tuple(out.shape)} {out.dtype} do not agree")
+        if bias is not None:
+            self._need(bias, "bias", torch.float32, 1)
+            if bias.numel() != N:
+                raise KernelError(f"linear_skinny: bias has {bias.numel()} entries, expected {N}")
+        self._check(self.lib.cima_linear_skinny(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode,
+                                                M, N, K, K, N, self._stream()), "linear_skinny")
+
+    # ------------------------------------------------------------------ attention
+    def rope_append(self, qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, row_pos, row_seq, seq_slot,
+                    kv, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+        """Rotate q and k of ``qkv`` in place and append k, v to the layer's pages (``kv`` a LayerKV or None)."""
+        self._need(qkv, "qkv", None, 2); self._need(inv_freq, "inv_freq", torch.float32, 1)
+        for n, t in (("row_pos", row_pos), ("row_seq", row_seq), ("seq_slot", seq_slot)):
+            self._need(t, n, torch.int32, 1)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError(f"rope_append: inv_freq has {inv_freq.numel()} entries, expected {rotary_dim // 2}")
+        T = qkv.shape[0]
+        if row_pos.numel() < T or row_seq.numel() < T:
+            raise KernelError("rope_append: the rows' positions do not cover the rows")
+        if kv is not None:
+            self._need(kv.storage, "cache", qkv.dtype, 5); self._need(kv.block_table, "block_table", torch.int32, 2)
+            if tuple(kv.storage.shape[1:]) != (2, n_kv_heads, kv.page_size, head_dim):
+                raise KernelError(f"rope_append: cache pages are {tuple(kv.storage.shape)}, expected "
+                                  f"[*, 2, {n_kv_heads}, {kv.page_size}, {head_dim}]")
+            args = (kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1], kv.ring_pages, kv.page_size)
+        else:
+            args = (None, None, 0, 0, 0)
+        self._check(self.lib.cima_rope_append(qkv.data_ptr(), dtype_code(qkv.dtype), qkv.shape[1], inv_freq.data_ptr(),
+                                              rotary_dim, row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
+                                              *args, T, n_heads, n_kv_heads, head_dim, self._stream()), "rope_append")
+
+    def attention_plain(self, qkv: torch.Tensor, kv, row_pos, row_seq, seq_slot, seq_first_row, out: torch.Tensor,
+                        n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int,
+                        from_cache: bool) -> None:
+        self._need(qkv, "qkv", None, 2); self._need(out, "out", qkv.dtype, 2)
+        T = qkv.shape[0]
+        if tuple(out.shape) != (T, n_heads * head_dim):
+            raise KernelError(f"attention: out is {tuple(out.shape)}, expected {(T, n_heads * head_dim)}")
+        if from_cache:
+            if kv is None:
+                raise KernelError("attention: decoding needs the layer's cache")
+            self._need(kv.storage, "cache", qkv.dtype, 5)
+            args = (kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1], kv.ring_pages, kv.page_size)
+        else:
+            args = (None, None, 0, 0, 1)
+        self._check(self.lib.cima_attention_plain(qkv.data_ptr(), dtype_code(qkv.dtype), qkv.shape[1], *args,
+                                                  row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
+                                                  seq_first_row.data_ptr(), out.data_ptr(), out.shape[1], T,
+                                                  n_heads, n_kv_heads, head_dim, scale, window,
+                                                  1 if from_cache else 0, self._stream()), "attention_plain")
+
+    def attention(self, qkv: torch.Tensor, kv, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
+                  head_dim: int, scale: float, window: int, from_cache: bool) -> None:
+        """Attention of a step's rows: over the step's own keys (a prompt from position 0) or over the
+        cache.  Chooses the kernel; every choice computes the same function."""
+        self.attention_plain(qkv, kv, batch.row_pos, batch.row_seq, batch.seq_slot, batch.seq_first_row, out,
+                             n_heads, n_kv_heads, head_dim, scale, window, from_cache)
+
+    # ------------------------------------------------------------------ sampling
+    def argmax(self, logits: torch.Tensor, tokens: torch.Tensor) -> None:
+        self._need(logits, "logits", torch.float32, 2); self._need(tokens, "tokens", torch.int32, 1)
+        n, V = logits.shape
+        if tokens.numel() < n:
+            raise KernelError(f"argmax: {tokens.numel()} token places for {n} rows")
+        self._check(self.lib.cima_argmax(logits.data_ptr(), V, n, V, tokens.data_ptr(), self._stream()), "argmax")
+
+    def sample(self, logits: torch.Tensor, row_slot: torch.Tensor, params: torch.Tensor, rng: torch.Tensor,
+               ring: torch.Tensor, count: torch.Tensor, work: torch.Tensor, tokens: torch.Tensor,
+               all_greedy: bool = False) -> None:
+        """The whole sampling chain per row; per-slot state (rng, ring, count) is read and advanced.
+        ``all_greedy`` (no row penalises or draws) takes the argmax kernel and leaves the state alone."""
+        self._need(logits, "logits", torch.float32, 2); self._need(tokens, "tokens", torch.int32, 1)
+        n, V = logits.shape
+        if tokens.numel() < n:
+            raise KernelError(f"sample: {tokens.numel()} token places for {n} rows")
+        if all_greedy:
+            self._check(self.lib.cima_argmax(logits.data_ptr(), V, n, V, tokens.data_ptr(), self._stream()), "argmax")
+            return
+        self._need(row_slot, "row_slot", torch.int32, 1); self._need(params, "params", torch.float32, 2)
+        self._need(rng, "rng", torch.int64); self._need(ring, "ring", torch.int32, 2); self._need(count, "count", torch.int32)
+        self._need(work, "work", torch.float32, 2)
+        if params.shape != (n, 4) or ring.shape[1] != 64 or work.shape[0] < n or work.shape[1] != V:
+            raise KernelError("sample: params must be [rows, 4], the ring [slots, 64], the scratch [>= rows, vocab]")
+        self._check(self.lib.cima_sample(logits.data_ptr(), V, n, V, row_slot.data_ptr(), params.data_ptr(),
+                                         rng.data_ptr(), ring.data_ptr(), count.data_ptr(), work.data_ptr(),
+                                         tokens.data_ptr(), self._stream()), "sample")

@@ -1,0 +1,84 @@
+"""Grouped-query causal attention over the paged cache, with optional window.
+
+forward: qkv = h Wqkv^T + b  ->  rotate q, k and append k, v to the layer's pages  ->
+attention (prefill: over the step's own keys; decode: over the cache)  ->  x += att Wo^T.
+Formulas and order as the reference's layer loop, steps 2-7 (src/models/transformer.rs:1039-1264):
+bias before rotation, rotation before caching, scale = spec.scale, head h reads kv head
+h / (heads / kv_heads), no output bias unless the spec says so.
+
+Every size (heads, kv heads, head_dim, window, scale, bias flags) is a field of the spec.
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..cache.kv import KVRequest
+from ..weights.loader import TensorSpec
+from .linear import Linear
+from .registry import build_position, register_mixer
+
+
+class Attention:
+    def __init__(self, spec, layer: int, rt):
+        if spec.head_dim % 16 or spec.head_dim > 256:
+            raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 16, at most 256")
+        if spec.n_heads % spec.n_kv_heads:
+            raise ValueError(f"attention: {spec.n_heads} heads are not a multiple of {spec.n_kv_heads} kv heads")
+        self.spec, self.layer, self.rt = spec, layer, rt
+        self.position = build_position(spec.position, rt)
+        self.qd = spec.n_heads * spec.head_dim
+        self.kvd = spec.n_kv_heads * spec.head_dim
+        self.qkv = None
+        self.out = None
+
+    # ------------------------------------------------------------------ weights
+    def plan(self, prefix: str, names: Dict[str, str]) -> Dict[str, TensorSpec]:
+        s = self.spec
+        p: Dict[str, TensorSpec] = {}
+        for key, rows in (("q", self.qd), ("k", self.kvd), ("v", self.kvd)):
+            p[f"{prefix}{names[key]}.weight"] = TensorSpec((rows, s.hidden))
+            if s.qkv_bias:
+                p[f"{prefix}{names[key]}.bias"] = TensorSpec((rows,))
+        p[f"{prefix}{names['o']}.weight"] = TensorSpec((s.hidden, self.qd))
+        if s.out_bias:
+            p[f"{prefix}{names['o']}.bias"] = TensorSpec((s.hidden,))
+        return p
+
+    def load(self, tensors: Dict[str, torch.Tensor], prefix: str, names: Dict[str, str]) -> None:
+        s = self.spec
+        ws = [tensors[f"{prefix}{names[k]}.weight"] for k in ("q", "k", "v")]
+        if len({w.dtype for w in ws}) > 1:
+            ws = [w.float() for w in ws]
+        bias = None
+        if s.qkv_bias:
+            bias = torch.cat([tensors[f"{prefix}{names[k]}.bias"].float() for k in ("q", "k", "v")])
+        self.qkv = Linear(torch.cat(ws, dim=0), bias, self.rt)
+        ob = tensors[f"{prefix}{names['o']}.bias"] if s.out_bias else None
+        self.out = Linear(tensors[f"{prefix}{names['o']}.weight"], ob, self.rt)
+
+    def nbytes(self) -> int:
+        return self.qkv.nbytes() + self.out.nbytes()
+
+    # ------------------------------------------------------------------ cache
+    def cache_requests(self) -> List[object]:
+        if self.spec.cache_from is not None:
+            return []
+        return [KVRequest(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)]
+
+    # ------------------------------------------------------------------ step
+    def forward(self, h: torch.Tensor, x: torch.Tensor, batch, cache) -> None:
+        s, K_ = self.spec, self.rt.kernels
+        kv = cache.layer_kv(self.layer)
+        writes = s.cache_from is None
+        qkv = self.qkv.store(h)
+        K_.rope_append(qkv, self.position.inv_freq, self.position.rotary_dim, batch.row_pos, batch.row_seq,
+                       batch.seq_slot, kv if writes else None, s.n_heads, s.n_kv_heads, s.head_dim)
+        att = self.rt.empty(h.shape[0], self.qd)
+        from_cache = (not batch.prefill) or not writes
+        K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, from_cache)
+        self.out.accumulate(att, x)
+
+
+register_mixer("attention", Attention)

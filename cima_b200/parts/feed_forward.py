@@ -1,0 +1,49 @@
+"""Gated feed-forward: x += (act(h Wg^T) * (h Wu^T)) Wd^T, act = SiLU g / (1 + exp(-g)) in float32
+(src/kernels.cu:81-84; src/models/transformer.rs:1219-1229 and :1273-1291).  Rows are independent,
+so a long step is cut into row chunks that bound the [rows, 2I] scratch."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..weights.loader import TensorSpec
+from .linear import GatedLinearPair, Linear
+from .registry import register_feed_forward
+
+_SCRATCH_ELEMS = 1 << 29          # elements of the [rows, 2I] gate|up scratch per chunk
+
+
+class GatedMLP:
+    def __init__(self, spec, layer: int, rt):
+        if spec.activation != "silu":
+            raise ValueError(f"gated_mlp: activation '{spec.activation}' is not implemented (only 'silu')")
+        if spec.bias:
+            raise ValueError("gated_mlp: biases are not implemented")
+        self.spec, self.layer, self.rt = spec, layer, rt
+        self.gate_up = None
+        self.down = None
+
+    def plan(self, prefix: str, names: Dict[str, str]) -> Dict[str, TensorSpec]:
+        s = self.spec
+        return {f"{prefix}{names['gate']}.weight": TensorSpec((s.intermediate, s.hidden)),
+                f"{prefix}{names['up']}.weight": TensorSpec((s.intermediate, s.hidden)),
+                f"{prefix}{names['down']}.weight": TensorSpec((s.hidden, s.intermediate))}
+
+    def load(self, tensors: Dict[str, torch.Tensor], prefix: str, names: Dict[str, str]) -> None:
+        self.gate_up = GatedLinearPair(tensors[f"{prefix}{names['gate']}.weight"],
+                                       tensors[f"{prefix}{names['up']}.weight"], self.rt)
+        self.down = Linear(tensors[f"{prefix}{names['down']}.weight"], None, self.rt)
+
+    def nbytes(self) -> int:
+        return self.gate_up.nbytes() + self.down.nbytes()
+
+    def forward(self, h: torch.Tensor, x: torch.Tensor, batch) -> None:
+        rows = h.shape[0]
+        chunk = max(64, _SCRATCH_ELEMS // (2 * self.spec.intermediate))
+        for r0 in range(0, rows, chunk):
+            r1 = min(rows, r0 + chunk)
+            self.down.accumulate(self.gate_up.activated(h[r0:r1]), x[r0:r1])
+
+
+register_feed_forward("gated_mlp", GatedMLP)

@@ -1,0 +1,118 @@
+"""y = a W^T (+ bias): the one place that chooses how a matrix product runs.
+
+* 32-bit path, or a weight that is stored in 32-bit: the plain FFMA kernel (``linear_plain``).
+* bfloat16, at most 64 rows, K a multiple of 8: the hand-written skinny kernel with its fused
+  epilogues (bias, residual accumulate, gated activation, float32 store).
+* bfloat16, more rows: the library matrix product (cuBLAS through ``torch.mm``), where the reference
+  also calls its library (``cublasGemmEx`` for rows > 1, src/models/transformer.rs:1068-1084,
+  src/cuda.rs:2484-2541), followed by the bias / residual kernels.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
+
+SKINNY_ROWS = 64
+
+
+class Linear:
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor], rt):
+        self.rt = rt
+        self.weight = rt.matrix(weight)                    # [N, K]
+        self.bias = rt.vector(bias) if bias is not None else None
+        self.N, self.K = self.weight.shape
+        self._bias_act = None
+
+    # ------------------------------------------------------------------ choices
+    def _plain(self) -> bool:
+        return self.rt.full_precision or self.weight.dtype is torch.float32
+
+    def _skinny(self, rows: int) -> bool:
+        return (not self._plain()) and rows <= SKINNY_ROWS and self.K % 8 == 0
+
+    def nbytes(self) -> int:
+        n = self.weight.numel() * self.weight.element_size()
+        return n + (self.bias.numel() * 4 if self.bias is not None else 0)
+
+    # ------------------------------------------------------------------ products
+    def store(self, a: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """a W^T + bias in the activation dtype."""
+        K_ = self.rt.kernels
+        M = a.shape[0]
+        if out is None:
+            out = self.rt.empty(M, self.N)
+        if M == 0:
+            return out
+        if self._plain():
+            K_.linear_plain(a, self.weight, self.bias, out)
+        elif self._skinny(M):
+            K_.linear_skinny(a, self.weight, self.bias, out, SK_STORE)
+        else:
+            if self.bias is not None:
+                if self._bias_act is None:
+                    self._bias_act = self.bias.to(self.rt.dtype)
+                torch.addmm(self._bias_act, a, self.weight.t(), out=out)
+            else:
+                torch.mm(a, self.weight.t(), out=out)
+        return out
+
+    def accumulate(self, a: torch.Tensor, x: torch.Tensor) -> None:
+        """x += a W^T (+ bias), x being the float32 residual stream."""
+        K_ = self.rt.kernels
+        M = a.shape[0]
+        if M == 0:
+            return
+        if self._plain():
+            K_.linear_plain(a, self.weight, self.bias, x, accumulate=True)
+        elif self._skinny(M):
+            K_.linear_skinny(a, self.weight, self.bias, x, SK_ACCUM)
+        else:
+            K_.add_residual(x, self.store(a))
+
+    def logits(self, a: torch.Tensor) -> torch.Tensor:
+        """a W^T + bias in float32 whatever the path (the head)."""
+        K_ = self.rt.kernels
+        M = a.shape[0]
+        out = self.rt.empty(M, self.N, dtype=torch.float32)
+        if M == 0:
+            return out
+        if self._plain() or self.K % 8:
+            K_.linear_plain(a, self.weight, self.bias, out)
+        else:
+            for m0 in range(0, M, SKINNY_ROWS):
+                m1 = min(M, m0 + SKINNY_ROWS)
+                K_.linear_skinny(a[m0:m1], self.weight, self.bias, out[m0:m1], SK_STORE_F32)
+        return out
+
+
+class GatedLinearPair:
+    """gate and up projections kept as one [2I, K] matrix (gate rows first), so that one product
+    gives both and the skinny kernel can apply act(gate) * up before anything is stored
+    (the reference fuses the same way at load, src/models/transformer.rs:864-873, and in its
+    decode GEMV mode 2, src/kernels.cu:533-537)."""
+
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor, rt):
+        if gate.dtype != up.dtype:
+            gate, up = gate.float(), up.float()
+        self.lin = Linear(torch.cat([gate, up], dim=0), None, rt)
+        self.rt = rt
+        self.I = gate.shape[0]
+
+    def nbytes(self) -> int:
+        return self.lin.nbytes()
+
+    def activated(self, a: torch.Tensor) -> torch.Tensor:
+        """silu(a Wg^T) * (a Wu^T) in the activation dtype, [M, I]."""
+        K_ = self.rt.kernels
+        M = a.shape[0]
+        out = self.rt.empty(M, self.I)
+        if M == 0:
+            return out
+        if self.lin._skinny(M):
+            K_.linear_skinny(a, self.lin.weight, None, out, SK_SWIGLU)
+        else:
+            K_.swiglu(self.lin.store(a), out)
+        return out
