@@ -118,9 +118,9 @@ class KVGroup:
 class KVCache:
     """Slots, pages and per-sequence state of one model.
 
-    ``requests[i]`` is what layer ``i``'s mixer asks for: a list of ``KVRequest`` /
-    ``StateRequest`` (possibly empty).  ``shares[i] = j`` lets layer ``i`` read layer ``j``'s
-    keys and values instead of holding its own.  ``max_tokens`` is the most positions that live
+    ``requests[i]`` is what the mixer at site ``i`` (the i-th entry of the model's schedule; "layer"
+    below) asks for: a list of ``KVRequest`` / ``StateRequest`` (possibly empty).  ``shares[i] = j``
+    lets site ``i`` read site ``j``'s keys and values instead of holding its own.  ``max_tokens`` is the most positions that live
     sequences hold at any time, each sequence's count rounded up to ``page_size``.
     """
 

@@ -45,7 +45,7 @@ class MixerSpec:
     window: int                  # 0 = every earlier key; w > 0 = the last w keys
     scale: float                 # factor of q.k before the softmax
     position: PositionSpec
-    # Index (in ModelSpec.layers) of the layer whose cache this one reads instead of
+    # Site (index into ModelSpec.schedule) whose keys and values this layer reads instead of
     # writing its own; None = own cache.
     cache_from: Optional[int] = None
     params: Dict[str, Any] = field(default_factory=dict)

@@ -107,3 +107,23 @@ extern "C" int cima_gather_rows(const float* x, const int* rows, float* out, int
   k_gather_rows<<<n, 256, 0, stream>>>(x, rows, out, H);
   return cima_launch_result();
 }
+
+// ---------------------------------------------------------------- end of a decode step on the device
+// The chosen tokens become the next step's input and every sequence moves on by one position, so
+// that a captured step replays without the host touching its inputs (the reference closes its
+// captured step the same way: k_argmax_extract and k_pos_bump, src/kernels.cu:309-318).
+__global__ void k_decode_advance(const int* __restrict__ chosen, int* __restrict__ tokens, int* __restrict__ row_pos,
+                                 int* __restrict__ seq_len, int B) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < B) {
+    tokens[i] = chosen[i];
+    row_pos[i] += 1;
+    seq_len[i] += 1;
+  }
+}
+
+extern "C" int cima_decode_advance(const int* chosen, int* tokens, int* row_pos, int* seq_len, int B, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  k_decode_advance<<<(B + 127) / 128, 128, 0, stream>>>(chosen, tokens, row_pos, seq_len, B);
+  return cima_launch_result();
+}

@@ -77,29 +77,35 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
       wrow[a][h] = W + (size_t)((wok[a][h] ? r : 0) + a * up_offset) * K;
     }
 
-  constexpr int CHUNK = 32 * U;
+  // A warp owns chunks of 128 consecutive k, interleaved with the other warps' chunks; this split,
+  // and so the order of summation, is the same for every instantiation.  U only says how many of a
+  // chunk's four 32-wide steps are loaded before they are multiplied.
+  constexpr int CHUNK = 128;
   for (int k0 = warp * CHUNK; k0 < K; k0 += SK_WARPS * CHUNK) {
-    uint4 w[MT][2][U];
 #pragma unroll
-    for (int s = 0; s < U; s++) {
-      const int k = k0 + s * 32 + 8 * t;
+    for (int sub = 0; sub < 4; sub += U) {
+      uint4 w[MT][2][U];
 #pragma unroll
-      for (int a = 0; a < MT; a++)
+      for (int s = 0; s < U; s++) {
+        const int k = k0 + (sub + s) * 32 + 8 * t;
 #pragma unroll
-        for (int h = 0; h < 2; h++)
-          w[a][h][s] = (wok[a][h] && k < K) ? ld_stream16(wrow[a][h] + k) : make_uint4(0u, 0u, 0u, 0u);
-    }
+        for (int a = 0; a < MT; a++)
 #pragma unroll
-    for (int s = 0; s < U; s++) {
-      const int k = k0 + s * 32 + 8 * t;
+          for (int h = 0; h < 2; h++)
+            w[a][h][s] = (wok[a][h] && k < K) ? ld_stream16(wrow[a][h] + k) : make_uint4(0u, 0u, 0u, 0u);
+      }
 #pragma unroll
-      for (int j = 0; j < NT; j++) {
-        const int m = j * 8 + g;
-        const uint4 x = (m < M && k < K) ? ld_cached16(X + (size_t)m * ldx + k) : make_uint4(0u, 0u, 0u, 0u);
+      for (int s = 0; s < U; s++) {
+        const int k = k0 + (sub + s) * 32 + 8 * t;
 #pragma unroll
-        for (int a = 0; a < MT; a++) {
-          mma_16816(acc[a][j], w[a][0][s].x, w[a][1][s].x, w[a][0][s].y, w[a][1][s].y, x.x, x.y);
-          mma_16816(acc[a][j], w[a][0][s].z, w[a][1][s].z, w[a][0][s].w, w[a][1][s].w, x.z, x.w);
+        for (int j = 0; j < NT; j++) {
+          const int m = j * 8 + g;
+          const uint4 x = (m < M && k < K) ? ld_cached16(X + (size_t)m * ldx + k) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+          for (int a = 0; a < MT; a++) {
+            mma_16816(acc[a][j], w[a][0][s].x, w[a][1][s].x, w[a][0][s].y, w[a][1][s].y, x.x, x.y);
+            mma_16816(acc[a][j], w[a][0][s].z, w[a][1][s].z, w[a][0][s].w, w[a][1][s].w, x.z, x.w);
+          }
         }
       }
     }

@@ -15,7 +15,7 @@ template <typename TA>
 __global__ void __launch_bounds__(256)
 k_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, int rotary_dim,
               const int* __restrict__ row_pos, const int* __restrict__ row_seq, const int* __restrict__ seq_slot,
-              TA* __restrict__ cache, CimaPaged pg, int nh, int nkv, int hd) {
+              const int* __restrict__ seq_len, TA* __restrict__ cache_in, CimaPaged pg, int nh, int nkv, int hd) {
   __shared__ float cs[128], sn[128];
   const int row = blockIdx.x;
   const int pos = row_pos[row];
@@ -28,6 +28,10 @@ k_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, 
   }
   __syncthreads();
   TA* base = qkv + (size_t)row * ld;
+  // In a ring of pages a long prompt wraps: a position whose place a later position of the same
+  // step takes is not written at all (two rows of one launch must not write one place).
+  TA* cache = cache_in;
+  if (cache && pg.ring && pos + pg.ring * pg.page_size < seq_len[row_seq[row]]) cache = nullptr;
   const int slot = cache ? seq_slot[row_seq[row]] : 0;
   // rotation pairs of q heads [0, nh) and k heads [nh, nh + nkv)
   const int npairs = (nh + nkv) * half;
@@ -60,8 +64,9 @@ k_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, 
 }
 
 // cache may be null (a layer that reads another layer's keys and values writes none).
+// seq_len[i] is the length of sequence i after this step.
 extern "C" int cima_rope_append(void* qkv, int dtype, int ld, const float* inv_freq, int rotary_dim,
-                                const int* row_pos, const int* row_seq, const int* seq_slot,
+                                const int* row_pos, const int* row_seq, const int* seq_slot, const int* seq_len,
                                 void* cache, const int* table, int table_width, int ring, int page_size,
                                 int T, int nh, int nkv, int hd, cudaStream_t stream) {
   if (T <= 0) return 0;
@@ -71,9 +76,9 @@ extern "C" int cima_rope_append(void* qkv, int dtype, int ld, const float* inv_f
   if (cache && (page_size <= 0 || table_width <= 0)) return cima_fail(CIMA_E_SIZE, "rope_append: page size %d and table width %d must be positive", page_size, table_width);
   CimaPaged pg{table, table_width, ring, page_size, nkv, hd};
   if (dtype == CIMA_F32)
-    k_rope_append<float><<<T, 256, 0, stream>>>((float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, (float*)cache, pg, nh, nkv, hd);
+    k_rope_append<float><<<T, 256, 0, stream>>>((float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, hd);
   else if (dtype == CIMA_BF16)
-    k_rope_append<__nv_bfloat16><<<T, 256, 0, stream>>>((__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, (__nv_bfloat16*)cache, pg, nh, nkv, hd);
+    k_rope_append<__nv_bfloat16><<<T, 256, 0, stream>>>((__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, hd);
   else return cima_fail(CIMA_E_DTYPE, "rope_append: dtype code %d is neither float32 nor bfloat16", dtype);
   return cima_launch_result();
 }

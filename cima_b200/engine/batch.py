@@ -35,6 +35,7 @@ class StepBatch:
     seq_first_row: torch.Tensor       # int32 [seqs + 1]
     seq_len: torch.Tensor             # int32 [seqs]
     want_rows: torch.Tensor           # int32 [wanted]
+    host_seq_slot: np.ndarray = None
     host_seq_first_row: np.ndarray = None
     host_seq_len: np.ndarray = None
 
@@ -88,4 +89,4 @@ def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, dev
                      tokens=dev[0:T], row_pos=dev[T:2 * T], row_seq=dev[2 * T:3 * T],
                      seq_slot=dev[o:o + B], seq_first_row=dev[o + B:o + 2 * B + 1],
                      seq_len=dev[o + 2 * B + 1:o + 3 * B + 1], want_rows=dev[o + 3 * B + 1:],
-                     host_seq_first_row=seq_first.copy(), host_seq_len=seq_len.copy())
+                     host_seq_slot=seq_slot.copy(), host_seq_first_row=seq_first.copy(), host_seq_len=seq_len.copy())

@@ -1,0 +1,76 @@
+"""A decode step captured as a CUDA graph: one launch per token instead of a few hundred.
+
+The step's inputs (tokens, positions, lengths, slots, sampling parameters) live in device buffers of
+fixed address; the captured step ends with a kernel that feeds the chosen tokens back and moves
+every sequence on by one, so replaying needs nothing from the host but the pages that the next
+positions need (block tables are updated outside the graph, before the replay).  The reference
+arms its decode graph the same way around a device position counter
+(src/models/transformer.rs:1467-1494, src/cuda.rs:1069-1097).
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from .batch import StepBatch
+
+
+class DecodeGraph:
+    """One batch size's captured step.  ``load`` sets its inputs for a set of sequences; ``run``
+    does one step (the first run after construction executes eagerly and captures)."""
+
+    def __init__(self, model, sampler, n_seqs: int, all_greedy: bool):
+        self.model, self.sampler = model, sampler
+        self.B = B = n_seqs
+        self.all_greedy = all_greedy
+        dev = model.rt.device
+        self.meta = torch.zeros(6 * B + 1, dtype=torch.int32, device=dev)
+        self.meta_host = torch.zeros(6 * B + 1, dtype=torch.int32).pin_memory()
+        m = self.meta
+        self.tokens, self.row_pos, self.row_seq = m[0:B], m[B:2 * B], m[2 * B:3 * B]
+        self.seq_slot, self.seq_first_row, self.seq_len = m[3 * B:4 * B], m[4 * B:5 * B + 1], m[5 * B + 1:6 * B + 1]
+        self.params = torch.zeros(B, 4, dtype=torch.float32, device=dev)
+        self.chosen = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.batch = StepBatch(prefill=False, n_rows=B, n_seqs=B, n_want=B, max_len=0, want_all_in_order=True,
+                               tokens=self.tokens, row_pos=self.row_pos, row_seq=self.row_seq,
+                               seq_slot=self.seq_slot, seq_first_row=self.seq_first_row, seq_len=self.seq_len,
+                               want_rows=self.row_seq)
+        self.graph = None
+        self.slots: List[int] = []
+
+    def load(self, slots: Sequence[int], tokens: Sequence[int], lengths: Sequence[int], params: np.ndarray) -> None:
+        """Inputs of the next step: sequence i sits in slots[i], holds lengths[i] positions and brings tokens[i]."""
+        B = self.B
+        h = self.meta_host.numpy()
+        h[0:B] = tokens
+        h[B:2 * B] = lengths                       # the new token's position
+        h[2 * B:3 * B] = np.arange(B)
+        h[3 * B:4 * B] = slots
+        h[4 * B:5 * B + 1] = np.arange(B + 1)
+        h[5 * B + 1:6 * B + 1] = np.asarray(lengths) + 1
+        self.meta.copy_(self.meta_host, non_blocking=True)
+        self.params.copy_(torch.from_numpy(params), non_blocking=False)
+        self.slots = list(slots)
+
+    def _step(self) -> None:
+        logits = self.model.forward(self.batch)
+        self.sampler.sample(logits, self.seq_slot, self.params, self.chosen, self.all_greedy)
+        self.model.rt.kernels.decode_advance(self.chosen, self.tokens, self.row_pos, self.seq_len)
+
+    def run(self) -> torch.Tensor:
+        """One decode step of the loaded sequences; returns the device tensor of chosen tokens."""
+        if self.graph is None:
+            self._step()                            # a real step, eagerly; it also warms every kernel up
+            torch.cuda.current_stream().synchronize()
+            g = torch.cuda.CUDAGraph()
+            k = self.model.rt.kernels
+            before = k.launches
+            with torch.cuda.graph(g):               # records the same step for the following ones; runs nothing
+                self._step()
+            self.launches_per_step = k.launches - before
+            self.graph = g
+        else:
+            self.graph.replay()
+        return self.chosen

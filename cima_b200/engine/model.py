@@ -83,8 +83,13 @@ class Model:
     # ------------------------------------------------------------------ cache
     def make_cache(self, max_tokens: int, max_seqs: Optional[int] = None, page_size: int = 64,
                    extra_state: Sequence[StateRequest] = ()) -> KVCache:
-        shares = {i: b.mixer.cache_from for i, b in enumerate(self.spec.layers) if b.mixer.cache_from is not None}
-        self.cache = KVCache([b.cache_requests() for b in self.blocks], max_tokens, self.spec.max_position,
+        # storage belongs to a *site* (an entry of the schedule), weights to a layer: a layer that
+        # runs twice keeps the keys and values of each run apart
+        sched = self.spec.schedule
+        shares = {site: self.spec.layers[layer].mixer.cache_from for site, layer in enumerate(sched)
+                  if self.spec.layers[layer].mixer.cache_from is not None}
+        self.cache = KVCache([self.blocks[layer].cache_requests(site) for site, layer in enumerate(sched)],
+                             max_tokens, self.spec.max_position,
                              self.rt.dtype, self.rt.device, page_size=page_size, max_seqs=max_seqs,
                              shares=shares, extra_state=extra_state)
         return self.cache
@@ -114,8 +119,8 @@ class Model:
         K_, s = self.rt.kernels, self.spec
         x = self.rt.empty(batch.n_rows, s.hidden, dtype=torch.float32)
         K_.embed(batch.tokens, self.embedding, x, s.embed_scale)
-        for i in s.schedule:
-            self.blocks[i].forward(x, batch, self.cache)
+        for site, layer in enumerate(s.schedule):
+            self.blocks[layer].forward(x, batch, self.cache, site)
         return self.project(x, batch)
 
     def project(self, x: torch.Tensor, batch: StepBatch) -> torch.Tensor:

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
@@ -41,9 +41,10 @@ _SIGNATURES = {
     "cima_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "cima_add_residual": [_vp, _vp, _i, _sz, _vp],
     "cima_gather_rows": [_vp, _vp, _vp, _i, _i, _vp],
+    "cima_decode_advance": [_vp, _vp, _vp, _vp, _i, _vp],
     "cima_linear_plain": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_linear_skinny": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
-    "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_attention_plain": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                              _f, _i, _i, _vp],
     "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
@@ -140,6 +141,16 @@ class Kernels:
         self._check(self.lib.cima_gather_rows(x.data_ptr(), rows.data_ptr(), out.data_ptr(), rows.numel(),
                                               x.shape[1], self._stream()), "gather_rows")
 
+    def decode_advance(self, chosen: torch.Tensor, tokens: torch.Tensor, row_pos: torch.Tensor, seq_len: torch.Tensor) -> None:
+        """tokens = chosen; every row's position and every sequence's length + 1 (one token per sequence)."""
+        B = tokens.numel()
+        for n, t in (("chosen", chosen), ("tokens", tokens), ("row_pos", row_pos), ("seq_len", seq_len)):
+            self._need(t, n, torch.int32, 1)
+            if t.numel() != B:
+                raise KernelError(f"decode_advance: {n} has {t.numel()} entries, expected {B}")
+        self._check(self.lib.cima_decode_advance(chosen.data_ptr(), tokens.data_ptr(), row_pos.data_ptr(),
+                                                 seq_len.data_ptr(), B, self._stream()), "decode_advance")
+
     # ------------------------------------------------------------------ matrix products
     def linear_plain(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
                      accumulate: bool = False) -> None:
@@ -181,10 +192,10 @@ class Kernels:
 
     # ------------------------------------------------------------------ attention
     def rope_append(self, qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, row_pos, row_seq, seq_slot,
-                    kv, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+                    seq_len, kv, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
         """Rotate q and k of ``qkv`` in place and append k, v to the layer's pages (``kv`` a LayerKV or None)."""
         self._need(qkv, "qkv", None, 2); self._need(inv_freq, "inv_freq", torch.float32, 1)
-        for n, t in (("row_pos", row_pos), ("row_seq", row_seq), ("seq_slot", seq_slot)):
+        for n, t in (("row_pos", row_pos), ("row_seq", row_seq), ("seq_slot", seq_slot), ("seq_len", seq_len)):
             self._need(t, n, torch.int32, 1)
         if inv_freq.numel() != rotary_dim // 2:
             raise KernelError(f"rope_append: inv_freq has {inv_freq.numel()} entries, expected {rotary_dim // 2}")
@@ -201,7 +212,7 @@ class Kernels:
             args = (None, None, 0, 0, 0)
         self._check(self.lib.cima_rope_append(qkv.data_ptr(), dtype_code(qkv.dtype), qkv.shape[1], inv_freq.data_ptr(),
                                               rotary_dim, row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
-                                              *args, T, n_heads, n_kv_heads, head_dim, self._stream()), "rope_append")
+                                              seq_len.data_ptr(), *args, T, n_heads, n_kv_heads, head_dim, self._stream()), "rope_append")
 
     def attention_plain(self, qkv: torch.Tensor, kv, row_pos, row_seq, seq_slot, seq_first_row, out: torch.Tensor,
                         n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int,

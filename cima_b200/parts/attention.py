@@ -62,19 +62,19 @@ class Attention:
         return self.qkv.nbytes() + self.out.nbytes()
 
     # ------------------------------------------------------------------ cache
-    def cache_requests(self) -> List[object]:
+    def cache_requests(self, site: int) -> List[object]:
         if self.spec.cache_from is not None:
             return []
         return [KVRequest(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)]
 
     # ------------------------------------------------------------------ step
-    def forward(self, h: torch.Tensor, x: torch.Tensor, batch, cache) -> None:
+    def forward(self, h: torch.Tensor, x: torch.Tensor, batch, cache, site: int) -> None:
         s, K_ = self.spec, self.rt.kernels
-        kv = cache.layer_kv(self.layer)
+        kv = cache.layer_kv(site)
         writes = s.cache_from is None
         qkv = self.qkv.store(h)
         K_.rope_append(qkv, self.position.inv_freq, self.position.rotary_dim, batch.row_pos, batch.row_seq,
-                       batch.seq_slot, kv if writes else None, s.n_heads, s.n_kv_heads, s.head_dim)
+                       batch.seq_slot, batch.seq_len, kv if writes else None, s.n_heads, s.n_kv_heads, s.head_dim)
         att = self.rt.empty(h.shape[0], self.qd)
         from_cache = (not batch.prefill) or not writes
         K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, from_cache)

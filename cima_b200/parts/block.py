@@ -3,7 +3,7 @@
 registries; it does not know which kinds they are, nor which model it is in.
 
 Interface of the parts it holds:
-  norm(x) -> h                      mixer.forward(h, x, batch, cache)   (adds into x)
+  norm(x) -> h                      mixer.forward(h, x, batch, cache, site)   (adds into x)
   feed_forward.forward(h, x, batch) (adds into x)
 """
 from __future__ import annotations
@@ -40,14 +40,14 @@ class PreNormBlock:
         self.ffn_norm.load(tensors, f"{s.prefix}{s.names['ffn_norm']}.weight")
         self.feed_forward.load(tensors, s.prefix, s.names)
 
-    def cache_requests(self) -> List[object]:
-        return list(self.mixer.cache_requests())
+    def cache_requests(self, site: int) -> List[object]:
+        return list(self.mixer.cache_requests(site))
 
     def nbytes(self) -> int:
         return self.mixer_norm.nbytes() + self.mixer.nbytes() + self.ffn_norm.nbytes() + self.feed_forward.nbytes()
 
-    def forward(self, x: torch.Tensor, batch, cache) -> None:
-        self.mixer.forward(self.mixer_norm(x), x, batch, cache)
+    def forward(self, x: torch.Tensor, batch, cache, site: int) -> None:
+        self.mixer.forward(self.mixer_norm(x), x, batch, cache, site)
         self.feed_forward.forward(self.ffn_norm(x), x, batch)
 
 

@@ -53,6 +53,11 @@ class ReferenceKernels:
     def gather_rows(self, x, rows, out):
         out.copy_(x[rows.long()])
 
+    def decode_advance(self, chosen, tokens, row_pos, seq_len):
+        tokens.copy_(chosen)
+        row_pos.add_(1)
+        seq_len.add_(1)
+
     # ------------------------------------------------------------------ matrix products
     def linear_plain(self, a, w, bias, out, accumulate=False):
         y = a.to(self.compute) @ w.to(self.compute).t()
@@ -78,7 +83,7 @@ class ReferenceKernels:
             out.copy_(y.to(out.dtype))
 
     # ------------------------------------------------------------------ attention
-    def rope_append(self, qkv, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, kv, n_heads, n_kv_heads, head_dim):
+    def rope_append(self, qkv, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, kv, n_heads, n_kv_heads, head_dim):
         T = qkv.shape[0]
         half = rotary_dim // 2
         heads = qkv[:, :(n_heads + 2 * n_kv_heads) * head_dim].view(T, n_heads + 2 * n_kv_heads, head_dim)
@@ -94,6 +99,8 @@ class ReferenceKernels:
             return
         for r in range(T):
             slot = int(seq_slot[int(row_seq[r])])
+            if kv.ring_pages and int(row_pos[r]) + kv.ring_pages * kv.page_size < int(seq_len[int(row_seq[r])]):
+                continue          # a later position of this step takes the place
             page, off = _page_offset(kv, slot, int(row_pos[r]))
             kv.storage[page, 0, :, off, :] = heads[r, n_heads:n_heads + n_kv_heads, :]
             kv.storage[page, 1, :, off, :] = heads[r, n_heads + n_kv_heads:, :]

@@ -1,0 +1,164 @@
+"""Generation through the Python entry point and trace replay through bin/trace_run, on the GPU."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import cima_b200
+from helpers import TINY, model_folder, random_tokens
+from qwen2_plain import PlainXorshift, plain_forward, plain_load, plain_sample
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def plain_generate(name, prompt, opts, n, stop=()):
+    cfg, W = plain_load(model_folder(name))
+    rng = PlainXorshift(opts.get("seed", 0xC0FFEE))
+    seq, out = list(prompt), []
+    for _ in range(n):
+        logits = plain_forward(W, cfg, seq)[-1].float()
+        t = plain_sample(logits.tolist(), seq, opts, rng)
+        if t in stop:
+            return out, "stop"
+        out.append(t)
+        seq.append(t)
+    return out, "length"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,lens,steps", [("A", [7, 1, 13], 10), ("B", [1, 9, 30, 64], 16)])
+def test_greedy_generation_matches_plain(name, lens, steps, dtype):
+    V = TINY[name]["vocab_size"]
+    prompts = [random_tokens(V, n, seed=40 + n) for n in lens]
+    lm = cima_b200.load(model_folder(name), dtype=dtype, max_tokens=1024, verbose=False)
+    got = lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=steps)
+    cfg, W = plain_load(model_folder(name))
+    for p, r in zip(prompts, got):
+        assert r.finish_reason == "length" and len(r.tokens) == steps
+        if dtype == "float32":
+            assert r.tokens == plain_generate(name, p, dict(temperature=0.0), steps)[0]
+        else:
+            # bfloat16 may pick another token where two logits are closer than its rounding: every
+            # chosen token must be within that of the plain maximum, given the same history
+            seq = list(p)
+            for t in r.tokens:
+                lg = plain_forward(W, cfg, seq)[-1]
+                assert lg[t] >= lg.max() - 4e-2
+                seq.append(t)
+    assert lm.model.cache.slots.held == 0
+
+
+@pytest.mark.parametrize("name,temp", [("A", 0.8), ("B", 1.0)])
+def test_sampled_generation_matches_plain_in_float32(name, temp):
+    V = TINY[name]["vocab_size"]
+    lens = [7, 1, 13] if name == "A" else [1, 9, 30, 64]
+    prompts = [random_tokens(V, n, seed=60 + n) for n in lens]
+    lm = cima_b200.load(model_folder(name), dtype="float32", max_tokens=1024, verbose=False)
+    opts = dict(temperature=temp, top_k=0, top_p=1.0, repeat_penalty=1.0, seed=1234)
+    got = lm.generate(prompts, max_tokens=10, **opts)
+    for p, r in zip(prompts, got):
+        assert r.tokens == plain_generate(name, p, opts, 10)[0]
+    # the reference's default chain too (top-k 40, top-p 0.9, penalty 1.1)
+    opts = dict(temperature=0.8, top_k=40, top_p=0.9, repeat_penalty=1.1, seed=7)
+    got = lm.generate(prompts[:2], max_tokens=8, **opts)
+    for p, r in zip(prompts[:2], got):
+        assert r.tokens == plain_generate(name, p, opts, 8)[0]
+
+
+def test_stop_tokens_early_finishers_and_many_batches():
+    """More requests than a batch holds; some stop early on a stop token; slots are used again."""
+    name = "A"
+    prompts = [random_tokens(512, 3 + (i % 5), seed=80 + i) for i in range(7)]
+    lm = cima_b200.load(model_folder(name), dtype="float32", max_tokens=64 * 3, max_seqs=3, max_batch=3, verbose=False)
+    free = lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=12)
+    assert lm.stats.batches == 3
+    # make the 4th token of request 2 and the 1st of request 5 stop tokens
+    stops = (free[2].tokens[3], free[5].tokens[0])
+    got = lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=12, stop=stops)
+    for i, (f, r) in enumerate(zip(free, got)):
+        cut = next((j for j, t in enumerate(f.tokens) if t in stops), None)
+        if cut is None:
+            assert r.tokens == f.tokens and r.finish_reason == "length"
+        else:
+            assert r.tokens == f.tokens[:cut] and r.finish_reason == "stop", i
+    assert got[5].tokens == []
+    ignored = lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=12, stop=stops, ignore_eos=True)
+    assert [r.tokens for r in ignored] == [f.tokens for f in free]
+    lm.model.cache.check()
+    assert lm.model.cache.slots.held == 0
+
+
+# ---------------------------------------------------------------------------- trace replay
+def run_trace(folder, dtype, steps, out_dir, max_tokens):
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype,
+                        "--out", str(out_dir), "--max-tokens", str(max_tokens)],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.split("\n") if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+
+
+def read_step(out_dir, step, V):
+    return torch.from_numpy(np.fromfile(os.path.join(out_dir, f"{step}.f32"), dtype="<f4").reshape(-1, V).copy())
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 2e-2)])
+def test_trace_run_three_ways(tmp_path, dtype, tol):
+    name = "C"
+    V = TINY[name]["vocab_size"]
+    folder = model_folder(name)
+    cfg, W = plain_load(folder)
+    reqs = {f"r{i}": random_tokens(V, n, seed=90 + i) for i, n in enumerate([150, 40, 97])}
+    want = {k: plain_forward(W, cfg, v).float() for k, v in reqs.items()}
+    # 1. each request alone and whole
+    steps = [{"step": i, "entries": [{"id": k, "tokens": v, "want": list(range(len(v)))}], "end": [k]}
+             for i, (k, v) in enumerate(reqs.items())]
+    run_trace(folder, dtype, steps, tmp_path / "whole", 192)
+    for i, k in enumerate(reqs):
+        assert (read_step(tmp_path / "whole", i, V) - want[k]).abs().max().item() <= tol
+    # 2. the last 32 tokens one by one
+    steps, n = [], 0
+    for k, v in reqs.items():
+        head = len(v) - 32
+        steps.append({"step": n, "entries": [{"id": k, "tokens": v[:head], "want": [head - 1]}], "end": []}); n += 1
+        for j in range(head, len(v)):
+            steps.append({"step": n, "entries": [{"id": k, "tokens": [v[j]], "want": [0]}],
+                          "end": [k] if j == len(v) - 1 else []}); n += 1
+    run_trace(folder, dtype, steps, tmp_path / "tail", 192)
+    n = 0
+    for k, v in reqs.items():
+        head = len(v) - 32
+        assert (read_step(tmp_path / "tail", n, V)[0] - want[k][head - 1]).abs().max().item() <= tol; n += 1
+        for j in range(head, len(v)):
+            assert (read_step(tmp_path / "tail", n, V)[0] - want[k][j]).abs().max().item() <= tol, (k, j); n += 1
+    # 3. one batch of unequal lengths; the shorter requests end earlier; then a second batch reuses the cache
+    steps, n = [], 0
+    for rnd in range(2):
+        ids = {k: f"{k}_{rnd}" for k in reqs}
+        heads = {k: len(v) - 20 for k, v in reqs.items()}
+        steps.append({"step": n, "entries": [{"id": ids[k], "tokens": v[:heads[k] + (5 if k == "r1" else 0)], "want": [0, heads[k] - 1]}
+                                             for k, v in reqs.items()], "end": []}); n += 1
+        pos = {k: heads[k] + (5 if k == "r1" else 0) for k in reqs}
+        while any(pos[k] < len(reqs[k]) for k in reqs):
+            live = [k for k in reqs if pos[k] < len(reqs[k])]
+            steps.append({"step": n, "entries": [{"id": ids[k], "tokens": [reqs[k][pos[k]]], "want": [0]} for k in live],
+                          "end": [ids[k] for k in live if pos[k] == len(reqs[k]) - 1]}); n += 1
+            for k in live:
+                pos[k] += 1
+    run_trace(folder, dtype, steps, tmp_path / "batch", 64 * 6)
+    # every wanted place against the plain logits at its position (tokens fed so far + place)
+    fed = {}
+    for s in steps:
+        got = read_step(tmp_path / "batch", s["step"], V)
+        r = 0
+        for e in s["entries"]:
+            k = e["id"].split("_")[0]
+            start = fed.get(e["id"], 0)
+            for w in e["want"]:
+                assert (got[r] - want[k][start + w]).abs().max().item() <= tol, (s["step"], e["id"], start + w)
+                r += 1
+            fed[e["id"]] = start + len(e["tokens"])

@@ -1,0 +1,349 @@
+"""Each CUDA kernel alone against its plain statement (tests/reference_kernels.py), at sizes other
+than the tiny models': widths and vocabularies that are no power of two, head sizes in steps of 16,
+odd group sizes, and inputs made so that a fault in an index shows (one key that stands out among
+hundreds, the window's edge, the slot of the cache)."""
+import math
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+from reference_kernels import ReferenceKernels
+from cima_b200.cache.kv import LayerKV
+
+pytestmark = pytest.mark.gpu
+
+REF = ReferenceKernels(compute=torch.float64)
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# one rounding to the output dtype of values of magnitude about 1, plus summation error
+TOL = {"float32": 2e-5, "bfloat16": 1.6e-2}
+
+
+@pytest.fixture(scope="module")
+def K():
+    from cima_b200.kernels import Kernels
+    return Kernels(verbose=False)
+
+
+def g(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    gen = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=gen) * scale).to(dtype)
+
+
+def err(a, b):
+    return (a.double().cpu() - b.double().cpu()).abs().max().item()
+
+
+# ---------------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("wdtype", ["float32", "bfloat16"])
+def test_embed(K, wdtype):
+    V, H = 777, 200
+    table = g(V, H, dtype=DT[wdtype])
+    ids = torch.tensor([0, 776, 5, 5, 300], dtype=torch.int32)
+    x = torch.full((5, H), -7.0, device="cuda")
+    K.embed(ids.cuda(), table.cuda(), x, 1.0)
+    assert torch.equal(x.cpu(), table[ids.long()].float())
+
+
+@pytest.mark.parametrize("odtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,eps", [(200, 3e-6), (3584, 1e-6), (1, 1e-5), (1000, 1e-2)])
+def test_rmsnorm(K, odtype, H, eps):
+    x, w = g(13, H, seed=1, scale=3.0), 1 + g(H, seed=2, scale=0.1)
+    out = torch.empty(13, H, dtype=DT[odtype], device="cuda")
+    K.rmsnorm(x.cuda(), w.cuda(), eps, out)
+    want = torch.empty(13, H, dtype=torch.float64)
+    REF.rmsnorm(x, w, eps, want)
+    assert err(out, want) <= TOL[odtype] * 4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu_and_residual_and_gather(K, dtype):
+    T, I = 37, 328
+    gu = g(T, 2 * I, dtype=DT[dtype], seed=3, scale=2.0)
+    out = torch.empty(T, I, dtype=DT[dtype], device="cuda")
+    K.swiglu(gu.cuda(), out)
+    want = torch.empty(T, I, dtype=torch.float64)
+    REF.swiglu(gu, want)
+    assert err(out, want) <= TOL[dtype] * 4
+    x, d = g(T, I, seed=4), g(T, I, dtype=DT[dtype], seed=5)
+    xg = x.cuda()
+    K.add_residual(xg, d.cuda())
+    assert torch.equal(xg.cpu(), x + d.float())
+    rows = torch.tensor([36, 0, 0, 17], dtype=torch.int32)
+    picked = torch.empty(4, I, device="cuda")
+    K.gather_rows(xg, rows.cuda(), picked)
+    assert torch.equal(picked.cpu(), xg.cpu()[rows.long()])
+
+
+# ---------------------------------------------------------------------------- matrix products
+@pytest.mark.parametrize("M,N,K_", [(1, 192, 448), (7, 1000, 333), (130, 65, 17), (64, 64, 64)])
+@pytest.mark.parametrize("combo", [("float32", "float32", "float32"), ("bfloat16", "float32", "bfloat16"),
+                                   ("bfloat16", "bfloat16", "float32")])
+def test_linear_plain(K, M, N, K_, combo):
+    a, w, b = g(M, K_, dtype=DT[combo[0]], seed=1), g(N, K_, dtype=DT[combo[1]], seed=2, scale=0.1), g(N, seed=3)
+    # guard columns around the output prove that nothing is written outside it
+    # (the reference's sentinel check, src/selftest.rs:803, :837-850)
+    out = torch.full((M, N), -777.0, dtype=DT[combo[2]], device="cuda")
+    K.linear_plain(a.cuda(), w.cuda(), b.cuda(), out)
+    want = a.double() @ w.double().t() + b.double()
+    assert err(out, want) <= TOL[combo[2]] * max(1.0, want.abs().max().item())
+    if combo[2] == "float32":
+        acc = torch.ones(M, N, device="cuda")
+        K.linear_plain(a.cuda(), w.cuda(), None, acc, accumulate=True)
+        assert err(acc, 1 + a.double() @ w.double().t()) <= 2e-5 * max(1.0, want.abs().max().item())
+
+
+def test_linear_plain_rows_are_independent(K):
+    a, w = g(70, 200, seed=1), g(300, 200, seed=2)
+    full = torch.empty(70, 300, device="cuda")
+    K.linear_plain(a.cuda(), w.cuda(), None, full)
+    one = torch.empty(1, 300, device="cuda")
+    K.linear_plain(a[33:34].contiguous().cuda(), w.cuda(), None, one)
+    assert torch.equal(full[33:34], one)
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 31, 64])
+@pytest.mark.parametrize("N,K_", [(200, 328), (1000, 192), (4608, 3584), (17, 8)])
+def test_linear_skinny_modes(K, M, N, K_):
+    from cima_b200.kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
+    a = g(M, K_, dtype=torch.bfloat16, seed=M)
+    w = g(N, K_, dtype=torch.bfloat16, seed=N, scale=1.0 / math.sqrt(K_))
+    b = g(N, seed=7)
+    want = a.double() @ w.double().t()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    K.linear_skinny(a.cuda(), w.cuda(), b.cuda(), out, SK_STORE)
+    assert err(out, want + b.double()) <= TOL["bfloat16"] * 4
+    out32 = torch.empty(M, N, device="cuda")
+    K.linear_skinny(a.cuda(), w.cuda(), None, out32, SK_STORE_F32)
+    assert err(out32, want) <= 1e-4
+    x = g(M, N, seed=9)
+    xg = x.cuda()
+    K.linear_skinny(a.cuda(), w.cuda(), None, xg, SK_ACCUM)
+    assert err(xg, x.double() + want) <= 1e-4
+    if N % 2 == 0:
+        I = N // 2
+        act = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+        K.linear_skinny(a.cuda(), w.cuda(), None, act, SK_SWIGLU)
+        gg, uu = want[:, :I], want[:, I:]
+        assert err(act, gg / (1 + torch.exp(-gg)) * uu) <= TOL["bfloat16"] * 4
+
+
+def test_linear_skinny_row_does_not_depend_on_batch(K):
+    from cima_b200.kernels import SK_STORE_F32
+    a, w = g(64, 448, dtype=torch.bfloat16, seed=1), g(1000, 448, dtype=torch.bfloat16, seed=2)
+    full = torch.empty(64, 1000, device="cuda")
+    K.linear_skinny(a.cuda(), w.cuda(), None, full, SK_STORE_F32)
+    for m in (1, 5, 16, 40):
+        part = torch.empty(m, 1000, device="cuda")
+        K.linear_skinny(a[:m].contiguous().cuda(), w.cuda(), None, part, SK_STORE_F32)
+        assert torch.equal(part, full[:m])
+
+
+def test_linear_skinny_refuses(K):
+    from cima_b200.kernels import KernelError, SK_STORE
+    a, w = g(65, 64, dtype=torch.bfloat16).cuda(), g(32, 64, dtype=torch.bfloat16).cuda()
+    with pytest.raises(KernelError, match="at most 64"):
+        K.linear_skinny(a, w, None, torch.empty(65, 32, dtype=torch.bfloat16, device="cuda"), SK_STORE)
+    a, w = g(2, 12, dtype=torch.bfloat16).cuda(), g(32, 12, dtype=torch.bfloat16).cuda()
+    with pytest.raises(KernelError, match="multiples of 8"):
+        K.linear_skinny(a, w, None, torch.empty(2, 32, dtype=torch.bfloat16, device="cuda"), SK_STORE)
+
+
+# ---------------------------------------------------------------------------- cache and attention
+def make_kv(n_pages, nkv, page, hd, n_slots, width, ring, window, dtype, tables):
+    """A layer's pages (filled with a large stale value) and block table, on the GPU and mirrored on the CPU."""
+    storage = torch.full((n_pages, 2, nkv, page, hd), 50.0, dtype=dtype)
+    table = torch.zeros(n_slots, width, dtype=torch.int32)
+    for slot, pages in tables.items():
+        table[slot, :len(pages)] = torch.tensor(pages, dtype=torch.int32)
+    cpu = LayerKV(storage, table, page, ring, window, 0)
+    gpu = LayerKV(storage.cuda(), table.cuda(), page, ring, window, 0)
+    return cpu, gpu
+
+
+def batch_of(seqs, device):
+    """seqs: list of (slot, start_pos, n_tokens) -> the arrays the kernels take."""
+    row_pos, row_seq, first = [], [], [0]
+    for i, (slot, start, n) in enumerate(seqs):
+        row_pos += list(range(start, start + n))
+        row_seq += [i] * n
+        first.append(first[-1] + n)
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+    return SimpleNamespace(row_pos=t(row_pos), row_seq=t(row_seq), seq_slot=t([s[0] for s in seqs]),
+                           seq_first_row=t(first), seq_len=t([s[1] + s[2] for s in seqs]),
+                           n_rows=len(row_pos), n_seqs=len(seqs), prefill=all(s[1] == 0 for s in seqs),
+                           max_len=max(s[1] + s[2] for s in seqs))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,rot", [(6, 2, 48, 48), (7, 7, 16, 16), (4, 1, 128, 64), (2, 2, 256, 256)])
+def test_rope_append(K, dtype, nh, nkv, hd, rot):
+    page = 16
+    seqs = [(2, 0, 21), (0, 37, 1), (3, 5, 9)]
+    tables = {2: [4, 1], 0: [7, 3, 9], 3: [0]}
+    cpu, gpu = make_kv(10, nkv, page, hd, 4, 3, 0, 0, DT[dtype], tables)
+    T = sum(s[2] for s in seqs)
+    qkv = g(T, (nh + 2 * nkv) * hd, dtype=DT[dtype], seed=hd)
+    inv = torch.pow(torch.tensor(12345.0, dtype=torch.float64), -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot).float()
+    bc, bg = batch_of(seqs, "cpu"), batch_of(seqs, "cuda")
+    want = qkv.clone()
+    REF.rope_append(want, inv, rot, bc.row_pos, bc.row_seq, bc.seq_slot, bc.seq_len, cpu, nh, nkv, hd)
+    got = qkv.cuda()
+    K.rope_append(got, inv.cuda(), rot, bg.row_pos, bg.row_seq, bg.seq_slot, bg.seq_len, gpu, nh, nkv, hd)
+    assert err(got, want) <= TOL[dtype]
+    assert err(gpu.storage, cpu.storage) <= TOL[dtype]
+    # pages of no sequence keep their stale contents
+    for p in (2, 5, 6, 8):
+        assert torch.all(gpu.storage[p].float() == 50.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rope_append_long_prompt_wraps_a_ring(K, dtype):
+    """A prompt longer than a windowed group's ring: every place must end up with its newest
+    position, whichever block of the launch ran last."""
+    nh, nkv, hd, page, window = 2, 2, 32, 16, 20
+    ring = -(-window // page) + 1                      # 3 pages = 48 positions
+    seqs = [(1, 0, 200), (0, 0, 30), (2, 0, 49)]
+    tables = {1: [5, 0, 7], 0: [3, 8, 1], 2: [2, 4, 6]}
+    cpu, gpu = make_kv(9, nkv, page, hd, 3, ring, ring, window, DT[dtype], tables)
+    T = sum(s[2] for s in seqs)
+    qkv = g(T, (nh + 2 * nkv) * hd, dtype=DT[dtype], seed=11)
+    inv = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd).float()
+    bc, bg = batch_of(seqs, "cpu"), batch_of(seqs, "cuda")
+    want = qkv.clone()
+    REF.rope_append(want, inv, hd, bc.row_pos, bc.row_seq, bc.seq_slot, bc.seq_len, cpu, nh, nkv, hd)
+    for _ in range(3):
+        got = qkv.cuda()
+        gpu.storage.fill_(50.0)
+        K.rope_append(got, inv.cuda(), hd, bg.row_pos, bg.row_seq, bg.seq_slot, bg.seq_len, gpu, nh, nkv, hd)
+        assert err(gpu.storage, cpu.storage) <= TOL[dtype]
+    # position 199 of the long prompt is where the ring says, holding the rotated key of row 199
+    e, off = (199 // page) % ring, 199 % page
+    assert err(gpu.storage[tables[1][e], 0, :, off], want[199].view(-1, hd)[nh:nh + nkv]) <= TOL[dtype]
+
+
+def test_rope_is_a_rotation_by_position_times_frequency(K):
+    """Independent check: pair (i, i + d/2) as a complex number is multiplied by exp(i * p * f_i)."""
+    nh, nkv, hd, theta = 2, 1, 32, 10000.0
+    T = 5
+    qkv = g(T, (nh + 2 * nkv) * hd, seed=1)
+    pos = torch.tensor([0, 1, 17, 255, 4000], dtype=torch.int32)
+    inv = torch.pow(torch.tensor(theta, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)
+    got = qkv.cuda()
+    z = torch.zeros(T, dtype=torch.int32, device="cuda")
+    K.rope_append(got, inv.float().cuda(), hd, pos.cuda(), z, z[:1], z[:1], None, nh, nkv, hd)
+    u = qkv.double().view(T, nh + 2 * nkv, hd)[:, :nh + nkv]
+    c = torch.complex(u[..., :hd // 2], u[..., hd // 2:]) * torch.polar(torch.ones(T, hd // 2, dtype=torch.float64),
+                                                                        pos.double()[:, None] * inv[None])[:, None, :]
+    want = torch.cat([c.real, c.imag], dim=-1)
+    gotq = got.cpu().double().view(T, nh + 2 * nkv, hd)
+    assert (gotq[:, :nh + nkv] - want).abs().max().item() <= 3e-3 * 1e-2 + 4000 * 1.2e-7 * 4   # angle rounding at p = 4000
+    assert torch.equal(gotq[:, nh + nkv:], qkv.double().view(T, -1, hd)[:, nh + nkv:])           # v untouched
+
+
+def fill_cache(cpu, gpu, slot, k, v):
+    """Write keys/values [n, nkv, hd] of positions 0..n-1 into a slot's pages (ring aware)."""
+    for j in range(k.shape[0]):
+        e = j // cpu.page_size
+        if cpu.ring_pages:
+            e %= cpu.ring_pages
+        page = int(cpu.block_table[slot, e])
+        cpu.storage[page, 0, :, j % cpu.page_size] = k[j]
+        cpu.storage[page, 1, :, j % cpu.page_size] = v[j]
+    gpu.storage.copy_(cpu.storage)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd", [(6, 2, 48), (7, 1, 128), (4, 4, 16), (28, 4, 128), (3, 3, 80)])
+def test_attention_decode_over_cache(K, dtype, nh, nkv, hd):
+    """Three sequences of unequal length in scattered pages; a far key stands out in one of them."""
+    page = 16
+    lens = [300, 1, 77]
+    tables = {1: list(range(39, 20, -1)), 3: [2], 0: [5, 6, 7, 8, 9]}
+    slots = [1, 3, 0]
+    cpu, gpu = make_kv(40, nkv, page, hd, 4, 19, 0, 0, DT[dtype], tables)
+    scale = 1.0 / math.sqrt(hd)
+    qkv = g(3, (nh + 2 * nkv) * hd, dtype=DT[dtype], seed=3)
+    for i, (slot, n) in enumerate(zip(slots, lens)):
+        k, v = g(n, nkv, hd, dtype=DT[dtype], seed=10 + i), g(n, nkv, hd, dtype=DT[dtype], seed=20 + i)
+        if i == 0:
+            # key 13 of 300 is the query of head 0 scaled up: nearly all the weight falls on it
+            k[13, 0] = qkv[0, :hd] * 6.0
+        fill_cache(cpu, gpu, slot, k, v)
+    seqs = [(slots[i], lens[i] - 1, 1) for i in range(3)]
+    bc, bg = batch_of(seqs, "cpu"), batch_of(seqs, "cuda")
+    want = torch.zeros(3, nh * hd, dtype=torch.float64)
+    REF.attention_plain(qkv, cpu, bc.row_pos, bc.row_seq, bc.seq_slot, bc.seq_first_row, want, nh, nkv, hd, scale, 0, True)
+    out = torch.empty(3, nh * hd, dtype=DT[dtype], device="cuda")
+    K.attention(qkv.cuda(), gpu, bg, out, nh, nkv, hd, scale, 0, True)
+    assert err(out, want) <= TOL[dtype]
+    plain = torch.empty_like(out)
+    K.attention_plain(qkv.cuda(), gpu, bg.row_pos, bg.row_seq, bg.seq_slot, bg.seq_first_row, plain, nh, nkv, hd, scale, 0, True)
+    assert err(plain, want) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,n", [(40, 200), (16, 17), (33, 33), (64, 500)])
+def test_attention_decode_window_edge(K, dtype, window, n):
+    """A ring of pages; the key just outside the window stands out and must not be seen, the one just
+    inside must."""
+    nh, nkv, hd, page = 4, 2, 32, 16
+    ring = -(-window // page) + 1
+    cpu, gpu = make_kv(12, nkv, page, hd, 2, ring, ring, window, DT[dtype], {1: list(range(11, 11 - ring, -1))})
+    scale = 1.0 / math.sqrt(hd)
+    qkv = g(1, (nh + 2 * nkv) * hd, dtype=DT[dtype], seed=4)
+    k, v = g(n, nkv, hd, dtype=DT[dtype], seed=5), g(n, nkv, hd, dtype=DT[dtype], seed=6)
+    inside, outside = n - window, n - window - 1
+    if outside >= 0:
+        k[outside, 0] = qkv[0, :hd] * 8.0          # would take all the weight of head 0 if it were seen
+    k[inside, 1] = qkv[0, 2 * hd:3 * hd] * 8.0     # head 2 reads kv head 1: must be seen
+    # only what a ring still holds: the newest positions
+    fill_cache(cpu, gpu, 1, k, v)
+    bc, bg = batch_of([(1, n - 1, 1)], "cpu"), batch_of([(1, n - 1, 1)], "cuda")
+    # the statement: plain softmax over the visible keys of the full, unwrapped sequence
+    want = torch.zeros(1, nh * hd, dtype=torch.float64)
+    for h in range(nh):
+        gk = h // (nh // nkv)
+        lo = max(0, n - window)
+        s = (k[lo:n, gk].double() @ qkv[0, h * hd:(h + 1) * hd].double()) * scale
+        want[0, h * hd:(h + 1) * hd] = torch.softmax(s, 0) @ v[lo:n, gk].double()
+    out = torch.empty(1, nh * hd, dtype=DT[dtype], device="cuda")
+    K.attention(qkv.cuda(), gpu, bg, out, nh, nkv, hd, scale, window, True)
+    assert err(out, want) <= TOL[dtype]
+    assert err(out[0, 2 * hd:3 * hd], v[inside, 1]) <= 5e-2      # head 2 is (nearly) that one value
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nh,nkv,hd,window", [(6, 2, 48, 0), (7, 1, 128, 0), (4, 2, 64, 50), (2, 2, 256, 0),
+                                              (28, 4, 128, 0), (5, 5, 16, 7)])
+def test_attention_prefill_over_the_step(K, dtype, nh, nkv, hd, window):
+    """Ragged prompts in one launch; keys and values come from the step's own rows."""
+    lens = [130, 1, 67, 300]
+    seqs = [(i, 0, n) for i, n in enumerate(lens)]
+    T = sum(lens)
+    scale = 1.0 / math.sqrt(hd)
+    qkv = g(T, (nh + 2 * nkv) * hd, dtype=DT[dtype], seed=hd + nh)
+    # in the last sequence, key 5 stands out for the last query of head 0 (a far key among hundreds)
+    last = T - 1
+    first4 = T - 300
+    qkv[first4 + 5, nh * hd:(nh + 1) * hd] = qkv[last, :hd] * 6.0
+    bc, bg = batch_of(seqs, "cpu"), batch_of(seqs, "cuda")
+    want = torch.zeros(T, nh * hd, dtype=torch.float64)
+    REF.attention_plain(qkv, None, bc.row_pos, bc.row_seq, bc.seq_slot, bc.seq_first_row, want, nh, nkv, hd, scale, window, False)
+    out = torch.empty(T, nh * hd, dtype=DT[dtype], device="cuda")
+    K.attention(qkv.cuda(), None, bg, out, nh, nkv, hd, scale, window, False)
+    assert err(out, want) <= TOL[dtype]
+
+
+# ---------------------------------------------------------------------------- sampling
+def test_argmax_ties_go_to_the_higher_index(K):
+    V = 1000
+    x = g(5, V, seed=1)
+    x[0, 17] = x[0, 900] = 9.0
+    x[1, :] = -3.0
+    x[2, 999] = 50.0
+    x[3, 0] = 50.0
+    tok = torch.empty(5, dtype=torch.int32, device="cuda")
+    K.argmax(x.cuda(), tok)
+    assert tok.tolist() == [900, 999, 999, 0, int(torch.nonzero(x[4] == x[4].max()).max())]

@@ -1,0 +1,159 @@
+"""The engine on the GPU against the plain implementation: every way of cutting the same requests,
+in 32-bit and in bfloat16, on three tiny configurations that differ in every size and option."""
+import pytest
+import torch
+
+from helpers import (TINY, gpu_model, model_folder, random_tokens, run_batched, run_tail_one_by_one, run_whole)
+from qwen2_plain import plain_forward, plain_load
+from cima_b200.engine import StepEntry
+
+pytestmark = pytest.mark.gpu
+
+# float32: rounding of float32 sums over a few hundred terms and a few layers, on logits of
+# magnitude about 1.  bfloat16: activations are rounded to 8 bits of mantissa (2^-8 relative)
+# several times per layer.
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+LENGTHS = {"A": 40, "B": 150, "C": 300}
+
+_models = {}
+
+
+def model_of(name, dtype, max_tokens=2048):
+    key = (name, dtype, max_tokens)
+    if key not in _models:
+        _models[key] = gpu_model(name, dtype, max_tokens=max_tokens)
+    return _models[key]
+
+
+_plain = {}
+
+
+def plain_logits(name, toks):
+    key = (name, tuple(toks))
+    if key not in _plain:
+        cfg, W = plain_load(model_folder(name))
+        _plain[key] = plain_forward(W, cfg, toks).float()
+    return _plain[key]
+
+
+def close(a, b, tol):
+    return (a - b).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_whole_request(name, dtype):
+    toks = random_tokens(TINY[name]["vocab_size"], LENGTHS[name], seed=3)
+    m = model_of(name, dtype)
+    got = run_whole(m, toks)
+    assert close(got, plain_logits(name, toks), TOL[dtype])
+    m.cache.check()
+    assert m.cache.slots.held == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_last_32_one_by_one(name, dtype):
+    toks = random_tokens(TINY[name]["vocab_size"], LENGTHS[name], seed=3)
+    m = model_of(name, dtype)
+    got = run_tail_one_by_one(m, toks, 32)
+    assert close(got, plain_logits(name, toks), TOL[dtype])
+    if dtype == "float32":
+        # the 32-bit kernels are row-independent with a fixed order of summation
+        assert torch.equal(got, run_whole(m, toks))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_unequal_batches_one_after_another(name, dtype):
+    """Batches of unequal lengths whose shorter requests end earlier, on a cache with so few slots
+    and pages that the second and third batch get slots and pages the first one used."""
+    V = TINY[name]["vocab_size"]
+    lens = {"A": [7, 1, 13, 40], "B": [1, 9, 30, 64], "C": [130, 3, 70, 41]}[name]
+    decode = {"A": 10, "B": 16, "C": 20}[name]
+    m = gpu_model(name, dtype, max_tokens=64 * 8, max_seqs=4)
+    for rnd in range(3):
+        seqs = [random_tokens(V, n + (decode if i != 1 else 2), seed=100 * rnd + i) for i, n in enumerate(lens)]
+        got = run_batched(m, seqs, lens)
+        for q, g in zip(seqs, got):
+            assert close(g, plain_logits(name, q), TOL[dtype]), (name, dtype, rnd, len(q))
+        m.cache.check()
+        assert m.cache.slots.held == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(dtype):
+    """A short prompt, then every further token one by one up to the model's last position."""
+    name = "B"
+    toks = random_tokens(TINY[name]["vocab_size"], 256, seed=9)
+    m = model_of(name, dtype)
+    got = run_tail_one_by_one(m, toks, 250)
+    assert close(got, plain_logits(name, toks), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_first_tokens(name, dtype):
+    """Positions 0, 1, 2 fed one by one from an empty slot, and a one-token prompt."""
+    toks = random_tokens(TINY[name]["vocab_size"], 3, seed=5)
+    m = model_of(name, dtype)
+    got = run_tail_one_by_one(m, toks, 3)
+    assert close(got, plain_logits(name, toks), TOL[dtype])
+    assert close(run_whole(m, toks[:1]), plain_logits(name, toks[:1]), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_batch_composition_does_not_change_a_row(dtype):
+    """The same request alone and among others, in another slot: float32 bit for bit."""
+    name = "C"
+    V = TINY[name]["vocab_size"]
+    m = model_of(name, dtype)
+    a = random_tokens(V, 90, seed=21)
+    alone = run_whole(m, a)
+    others = [random_tokens(V, n, seed=30 + n) for n in (5, 200, 64)]
+    slots = m.cache.open(4)
+    try:
+        entries = [StepEntry(slots[0], others[0], []), StepEntry(slots[1], others[1], []),
+                   StepEntry(slots[3], a, list(range(len(a)))), StepEntry(slots[2], others[2], [])]
+        among = m.step(entries).float().cpu()
+    finally:
+        m.cache.close(slots)
+    if dtype == "float32":
+        assert torch.equal(alone, among)
+    else:
+        assert close(alone, among, TOL[dtype])
+
+
+def test_wanted_rows_only():
+    m = model_of("B", "float32")
+    toks = random_tokens(1000, 50, seed=2)
+    full = run_whole(m, toks)
+    (slot,) = m.cache.open(1)
+    try:
+        some = m.step([StepEntry(slot, toks, [49, 0, 7])]).float().cpu()
+        none = m.step([StepEntry(slot, [1], [])])
+    finally:
+        m.cache.close([slot])
+    assert torch.equal(some, full[[49, 0, 7]])
+    assert tuple(none.shape) == (0, 1000)
+
+
+def test_step_refuses_mixed_batches_and_overflow():
+    from cima_b200.cache import CacheFull, CapacityError
+    m = gpu_model("A", "float32", max_tokens=128, max_seqs=2)
+    s = m.cache.open(2)
+    try:
+        m.step([StepEntry(s[0], [1, 2, 3], [])])
+        with pytest.raises(ValueError):
+            m.step([StepEntry(s[0], [4, 5], []), StepEntry(s[1], [1, 2], [])])   # one goes on by two
+        with pytest.raises(ValueError):
+            m.step([StepEntry(s[0], [600], [])])                                   # token id out of range
+        with pytest.raises(CacheFull):
+            m.step([StepEntry(s[1], list(range(100)), [])])                        # 2 pages wanted, 1 free
+        with pytest.raises(CapacityError):
+            m2 = gpu_model("A", "float32", max_tokens=1024)
+            (t,) = m2.cache.open(1)
+            m2.step([StepEntry(t, list(range(129)), [])])                          # beyond max_position 128
+    finally:
+        m.cache.close(s)
+    m.cache.check()
