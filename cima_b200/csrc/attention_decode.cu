@@ -1,0 +1,304 @@
+// Decode attention over the paged cache (bfloat16): one new query per sequence, grouped-query,
+// keys split across blocks ("split-KV") so that few sequences still fill the GPU.
+//
+// Grid (split, kv head x m-tile, sequence).  A block streams its share of the sequence's pages
+// through shared memory with cp.async (two pages in flight) and serves ALL query heads of the
+// kv head's group at once, so every key and value byte is read from HBM once per step: the group's
+// heads are the 16 rows of the tensor-core tile (mma.m16n8k16, bf16 in, f32 out), the page's 64 keys
+// are split over the 4 warps.  Scores, the running maximum, the exponentials and the sums are
+// float32; probabilities are rounded to bfloat16 only as the operand of P.V.  Each warp keeps
+// (max, sum, accumulator) of its keys; the warps, and then the splits, are merged by
+// log-sum-exp in a fixed order (warp 0..3, split 0..S-1).
+//
+// The reference's decode attention has the same shape without tensor cores or batches: a block
+// per (head, 128-key chunk) writing {m, l, acc[dim]} partials (k_attn_decode_split,
+// src/kernels.cu:547-611) and a merge per head (k_attn_reduce, :615-639).
+//
+// Accepts head_dim in {16, 32, ..., 128}, page_size 64, any group size (16 heads per m-tile), any
+// window; other sizes are refused with a sentence and the caller takes the plain kernel.
+#include "common.cuh"
+
+namespace {
+
+constexpr int PS = 64;            // keys per page
+constexpr int WARPS = 4;
+constexpr int KEYS_PER_WARP = PS / WARPS;   // 16
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfloat16* __restrict__ cache,
+                   CimaPaged pg, const int* __restrict__ seq_slot, const int* __restrict__ seq_len,
+                   float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int ldo,
+                   int nh, int nkv, int mtiles, float scale, int window, int n_splits) {
+  constexpr int ROW = HD + 8;                         // padded row of a tile, in elements (16 bytes of padding)
+  constexpr int TILE = PS * ROW;                      // elements of one K or V tile
+  constexpr int KSTEPS = HD / 16, NTILES = HD / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [2 stages][K|V][PS][ROW]
+
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y / mtiles, mt = blockIdx.y % mtiles;
+  const int b = blockIdx.z;
+  const int G = nh / nkv;
+  const int h0 = kvh * G + mt * 16;                   // first query head of this m-tile
+  const int rows = min(16, G - mt * 16);              // heads in this m-tile
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  const int len = seq_len[b];
+  const int slot = seq_slot[b];
+  const int lo = (window > 0 && len > window) ? len - window : 0;
+  const int pf = lo / PS, pl = (len - 1) / PS;
+  const int per = (pl - pf + 1 + n_splits - 1) / n_splits;
+  const int p0 = pf + split * per;
+  const int p1 = min(p0 + per, pl + 1);
+
+  // the group's queries as A fragments: row g and g + 8 of the m-tile, 16 dims per k-step
+  uint32_t q[KSTEPS][4];
+  {
+    const __nv_bfloat16* qb = qkv + (size_t)b * ld + (size_t)h0 * HD;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; kk++) {
+      const int d = kk * 16 + 2 * t;
+      q[kk][0] = g < rows ? *reinterpret_cast<const uint32_t*>(qb + (size_t)g * HD + d) : 0u;
+      q[kk][1] = g + 8 < rows ? *reinterpret_cast<const uint32_t*>(qb + (size_t)(g + 8) * HD + d) : 0u;
+      q[kk][2] = g < rows ? *reinterpret_cast<const uint32_t*>(qb + (size_t)g * HD + d + 8) : 0u;
+      q[kk][3] = g + 8 < rows ? *reinterpret_cast<const uint32_t*>(qb + (size_t)(g + 8) * HD + d + 8) : 0u;
+    }
+  }
+
+  float o[NTILES][4];
+#pragma unroll
+  for (int j = 0; j < NTILES; j++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) o[j][e] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  auto issue = [&](int page_index, int stage) {
+    // one page: K then V, each [PS][HD] contiguous in the cache -> padded rows in shared memory
+    int e = page_index;
+    if (pg.ring) e %= pg.ring;
+    const int page = pg.table[(size_t)slot * pg.width + e];
+    const __nv_bfloat16* src = cache + (((size_t)page * 2) * pg.kv_heads + kvh) * (size_t)(PS * HD);
+    const size_t vofs = (size_t)pg.kv_heads * PS * HD;
+    __nv_bfloat16* dst = tiles + (size_t)stage * 2 * TILE;
+    constexpr int CPR = HD / 8;                       // 16-byte chunks per row
+    for (int c = threadIdx.x; c < PS * CPR; c += WARPS * 32) {
+      const int r = c / CPR, cc = c % CPR;
+      cp_async16(dst + r * ROW + cc * 8, src + r * HD + cc * 8);
+      cp_async16(dst + TILE + r * ROW + cc * 8, src + vofs + r * HD + cc * 8);
+    }
+  };
+
+  if (p0 < p1) issue(p0, 0);
+  cp_async_commit();
+  for (int p = p0; p < p1; p++) {
+    const int stage = (p - p0) & 1;
+    if (p + 1 < p1) issue(p + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const __nv_bfloat16* Kt = tiles + (size_t)stage * 2 * TILE;
+    const __nv_bfloat16* Vt = Kt + TILE;
+    const int kw = warp * KEYS_PER_WARP;              // this warp's keys within the page
+
+    // S = Q K^T for 16 keys: two n-tiles of 8 keys
+    float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; kk++) {
+      uint32_t kb[4];
+      ldmatrix_x4(kb, Kt + (kw + (lane & 7) + 8 * (lane >> 4)) * ROW + kk * 16 + 8 * ((lane >> 3) & 1));
+      mma_bf16(s[0], q[kk][0], q[kk][1], q[kk][2], q[kk][3], kb[0], kb[1]);
+      mma_bf16(s[1], q[kk][0], q[kk][1], q[kk][2], q[kk][3], kb[2], kb[3]);
+    }
+    // scale, mask what lies outside [lo, len), running softmax per row (rows g and g + 8)
+    const int key0 = p * PS + kw;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 2; j++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int key = key0 + j * 8 + 2 * t + (e & 1);
+        const float v = (key >= lo && key < len) ? s[j][e] * scale : -INFINITY;
+        s[j][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    float corr[2], msafe[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float mnew = fmaxf(m_run[r], mx[r]);
+      msafe[r] = mnew == -INFINITY ? 0.f : mnew;
+      corr[r] = expf(m_run[r] - msafe[r]);            // exp(-inf) = 0 while nothing was seen
+      m_run[r] = mnew;
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < 2; j++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const float pv = expf(s[j][e] - msafe[e >> 1]);
+        s[j][e] = pv;
+        psum[e >> 1] += pv;
+      }
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 1);
+      psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
+      l_run[r] = l_run[r] * corr[r] + psum[r];
+    }
+#pragma unroll
+    for (int j = 0; j < NTILES; j++) {
+      o[j][0] *= corr[0]; o[j][1] *= corr[0];
+      o[j][2] *= corr[1]; o[j][3] *= corr[1];
+    }
+    // O += P V: P (16 x 16 keys) straight from the score registers
+    const uint32_t a0 = pack_bf16(s[0][0], s[0][1]), a1 = pack_bf16(s[0][2], s[0][3]);
+    const uint32_t a2 = pack_bf16(s[1][0], s[1][1]), a3 = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+    for (int j = 0; j < NTILES; j += 2) {
+      uint32_t vb[4];
+      ldmatrix_x4_trans(vb, Vt + (kw + (lane & 7) + 8 * ((lane >> 3) & 1)) * ROW + j * 8 + 8 * (lane >> 4));
+      mma_bf16(o[j], a0, a1, a2, a3, vb[0], vb[1]);
+      mma_bf16(o[j + 1], a0, a1, a2, a3, vb[2], vb[3]);
+    }
+    __syncthreads();                                   // the stage is free for the page after next
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // merge the 4 warps (fixed order) through shared memory, reusing the tiles' space
+  float* so = reinterpret_cast<float*>(smem_raw);      // [WARPS][16][HD]
+  float* sml = so + WARPS * 16 * HD;                   // [WARPS][16][2]
+#pragma unroll
+  for (int j = 0; j < NTILES; j++) {
+    float* base = so + ((size_t)warp * 16 + g) * HD + j * 8 + 2 * t;
+    base[0] = o[j][0]; base[1] = o[j][1];
+    base[8 * HD] = o[j][2]; base[8 * HD + 1] = o[j][3];
+  }
+  if (t == 0) {
+    sml[(warp * 16 + g) * 2] = m_run[0]; sml[(warp * 16 + g) * 2 + 1] = l_run[0];
+    sml[(warp * 16 + g + 8) * 2] = m_run[1]; sml[(warp * 16 + g + 8) * 2 + 1] = l_run[1];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < rows * HD; idx += WARPS * 32) {
+    const int r = idx / HD, d = idx - r * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; w++) M = fmaxf(M, sml[(w * 16 + r) * 2]);
+    const float Ms = M == -INFINITY ? 0.f : M;
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; w++) {
+      const float f = expf(sml[(w * 16 + r) * 2] - Ms);
+      acc += f * so[((size_t)w * 16 + r) * HD + d];
+      l += f * sml[(w * 16 + r) * 2 + 1];
+    }
+    const int h = h0 + r;
+    if (n_splits == 1) {
+      out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    } else {
+      const size_t pi = ((size_t)b * nh + h) * n_splits + split;
+      part_o[pi * HD + d] = acc;
+      if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = l; }
+    }
+  }
+}
+
+// out[b, h, :] = sum_s e^(m_s - M) o_s / sum_s e^(m_s - M) l_s, splits in order
+__global__ void k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    __nv_bfloat16* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
+  const int b = blockIdx.y, h = blockIdx.x;
+  const size_t base = ((size_t)b * nh + h) * n_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; s++) M = fmaxf(M, part_ml[(base + s) * 2]);
+  const float Ms = M == -INFINITY ? 0.f : M;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f, l = 0.f;
+    for (int s = 0; s < n_splits; s++) {
+      const float f = expf(part_ml[(base + s) * 2] - Ms);
+      acc += f * part_o[(base + s) * hd + d];
+      l += f * part_ml[(base + s) * 2 + 1];
+    }
+    out[(size_t)b * ldo + (size_t)h * hd + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+  }
+}
+
+template <int HD>
+int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, const int* seq_slot, const int* seq_len,
+                  float* part_o, float* part_ml, void* out, int ldo, int B, int nh, int nkv, float scale, int window,
+                  int n_splits, cudaStream_t stream) {
+  auto kern = k_attention_decode<HD>;
+  const size_t tiles = (size_t)2 * 2 * PS * (HD + 8) * sizeof(__nv_bfloat16);
+  const size_t merge = (size_t)WARPS * 16 * (HD + 2) * sizeof(float);
+  const size_t smem = tiles > merge ? tiles : merge;
+  static bool raised = false;
+  if (smem > 48 * 1024 && !raised) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cima_fail((int)e, "attention_decode: cannot raise shared memory to %zu bytes: %s", smem, cudaGetErrorString(e));
+    raised = true;
+  }
+  const int G = nh / nkv, mtiles = (G + 15) / 16;
+  dim3 grid(n_splits, nkv * mtiles, B);
+  kern<<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)qkv, ld, (const __nv_bfloat16*)cache, pg, seq_slot,
+                                           seq_len, part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, nkv, mtiles, scale,
+                                           window, n_splits);
+  int rc = cima_launch_result();
+  if (rc || n_splits == 1) return rc;
+  k_attention_combine<<<dim3(nh, B), HD >= 64 ? 64 : 32, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, HD, n_splits);
+  return cima_launch_result();
+}
+
+}  // namespace
+
+// One query row per sequence (row b of qkv belongs to sequence b).  part_o [B, nh, n_splits, hd] and
+// part_ml [B, nh, n_splits, 2] float32 are scratch, needed when n_splits > 1.
+extern "C" int cima_attention_decode(const void* qkv, int ld, const void* cache, const int* table, int table_width,
+                                     int ring, int page_size, const int* seq_slot, const int* seq_len, float* part_o,
+                                     float* part_ml, void* out, int ldo, int B, int nh, int nkv, int hd, float scale,
+                                     int window, int n_splits, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (page_size != PS) return cima_fail(CIMA_E_SIZE, "attention_decode: page size %d; this kernel takes 64", page_size);
+  if (hd % 16 || hd < 16 || hd > 128) return cima_fail(CIMA_E_SIZE, "attention_decode: head_dim %d; this kernel takes multiples of 16 up to 128", hd);
+  if (nh <= 0 || nkv <= 0 || nh % nkv) return cima_fail(CIMA_E_SIZE, "attention_decode: %d heads are not a multiple of %d kv heads", nh, nkv);
+  if (n_splits < 1 || n_splits > 65535 || B > 65535) return cima_fail(CIMA_E_SIZE, "attention_decode: %d splits / %d sequences exceed one launch", n_splits, B);
+  if (n_splits > 1 && (!part_o || !part_ml)) return cima_fail(CIMA_E_ARG, "attention_decode: more than one split needs the scratch buffers");
+  if (ld % 2 || ((uintptr_t)qkv & 3) || ((uintptr_t)cache & 15)) return cima_fail(CIMA_E_ARG, "attention_decode: qkv rows must be 4-byte and the cache 16-byte aligned");
+  CimaPaged pg{table, table_width, ring, page_size, nkv, hd};
+#define CASE(H) case H: return launch_decode<H>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, stream)
+  switch (hd) {
+    CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
+  }
+#undef CASE
+  return cima_fail(CIMA_E_SIZE, "attention_decode: head_dim %d is not instantiated", hd);
+}

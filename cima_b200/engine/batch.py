@@ -13,6 +13,9 @@ import numpy as np
 import torch
 
 
+Q_TILE = 64        # query rows per block of the prefill attention kernel
+
+
 @dataclass
 class StepEntry:
     slot: int
@@ -35,6 +38,9 @@ class StepBatch:
     seq_first_row: torch.Tensor       # int32 [seqs + 1]
     seq_len: torch.Tensor             # int32 [seqs]
     want_rows: torch.Tensor           # int32 [wanted]
+    n_q_tiles: int = 0                # prefill only: blocks of 64 query rows, heaviest first
+    q_tile_seq: torch.Tensor = None   # int32 [n_q_tiles] sequence of the block
+    q_tile_row0: torch.Tensor = None  # int32 [n_q_tiles] first query position of the block
     host_seq_slot: np.ndarray = None
     host_seq_first_row: np.ndarray = None
     host_seq_len: np.ndarray = None
@@ -58,10 +64,19 @@ def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, dev
                          f"token (token counts {counts}, positions held {list(starts)})")
     B, T = len(entries), sum(counts)
     W = sum(len(e.want) for e in entries)
-    buf = np.empty(3 * T + 3 * B + 1 + W, dtype=np.int32)
+    q_tiles = []
+    if prefill:
+        q_tiles = sorted(((i, r0) for i, c in enumerate(counts) for r0 in range(0, c, Q_TILE)), key=lambda t: -t[1])
+    NT = len(q_tiles)
+    buf = np.empty(3 * T + 3 * B + 1 + W + 2 * NT, dtype=np.int32)
     tokens, row_pos, row_seq = buf[0:T], buf[T:2 * T], buf[2 * T:3 * T]
     o = 3 * T
-    seq_slot, seq_first, seq_len, want_rows = buf[o:o + B], buf[o + B:o + 2 * B + 1], buf[o + 2 * B + 1:o + 3 * B + 1], buf[o + 3 * B + 1:]
+    seq_slot, seq_first, seq_len = buf[o:o + B], buf[o + B:o + 2 * B + 1], buf[o + 2 * B + 1:o + 3 * B + 1]
+    w0 = o + 3 * B + 1
+    want_rows = buf[w0:w0 + W]
+    if NT:
+        buf[w0 + W:w0 + W + NT] = [t[0] for t in q_tiles]
+        buf[w0 + W + NT:] = [t[1] for t in q_tiles]
     r = w = 0
     for i, (e, s, c) in enumerate(zip(entries, starts, counts)):
         tk = np.asarray(e.tokens, dtype=np.int64)
@@ -88,5 +103,6 @@ def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, dev
                      want_all_in_order=all_in_order,
                      tokens=dev[0:T], row_pos=dev[T:2 * T], row_seq=dev[2 * T:3 * T],
                      seq_slot=dev[o:o + B], seq_first_row=dev[o + B:o + 2 * B + 1],
-                     seq_len=dev[o + 2 * B + 1:o + 3 * B + 1], want_rows=dev[o + 3 * B + 1:],
+                     seq_len=dev[o + 2 * B + 1:o + 3 * B + 1], want_rows=dev[w0:w0 + W],
+                     n_q_tiles=NT, q_tile_seq=dev[w0 + W:w0 + W + NT], q_tile_row0=dev[w0 + W + NT:],
                      host_seq_slot=seq_slot.copy(), host_seq_first_row=seq_first.copy(), host_seq_len=seq_len.copy())

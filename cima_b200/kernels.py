@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 4
+ABI_VERSION = 6
 
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
@@ -47,6 +47,8 @@ _SIGNATURES = {
     "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_attention_plain": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                              _f, _i, _i, _vp],
+    "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
     "cima_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
@@ -80,6 +82,7 @@ class Kernels:
             fn.argtypes = sig
             fn.restype = ctypes.c_int
         self.launches = 0
+        self._scratch_bufs = {}
 
     # ------------------------------------------------------------------ plumbing
     def _check(self, code: int, what: str) -> None:
@@ -238,8 +241,67 @@ class Kernels:
                   head_dim: int, scale: float, window: int, from_cache: bool) -> None:
         """Attention of a step's rows: over the step's own keys (a prompt from position 0) or over the
         cache.  Chooses the kernel; every choice computes the same function."""
+        if (from_cache and qkv.dtype is torch.bfloat16 and kv.page_size == 64 and head_dim % 16 == 0
+                and head_dim <= 128 and batch.n_rows == batch.n_seqs):
+            return self.attention_decode(qkv, kv, batch.seq_slot, batch.seq_len, out, n_heads, n_kv_heads, head_dim,
+                                         scale, window, batch.max_len)
+        if (not from_cache and qkv.dtype is torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128
+                and qkv.shape[1] % 8 == 0 and getattr(batch, "n_q_tiles", 0) > 0):
+            return self.attention_prefill(qkv, batch.q_tile_seq, batch.q_tile_row0, batch.seq_first_row, out,
+                                          n_heads, n_kv_heads, head_dim, scale, window)
         self.attention_plain(qkv, kv, batch.row_pos, batch.row_seq, batch.seq_slot, batch.seq_first_row, out,
                              n_heads, n_kv_heads, head_dim, scale, window, from_cache)
+
+    def attention_prefill(self, qkv: torch.Tensor, tile_seq, tile_row0, seq_first_row, out: torch.Tensor,
+                          n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: int) -> None:
+        """Flash attention of ragged prompts that start at position 0 (bf16, head_dim <= 128);
+        ``tile_seq``/``tile_row0`` list the blocks of 64 query rows."""
+        self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)
+        for n, t in (("tile_seq", tile_seq), ("tile_row0", tile_row0), ("seq_first_row", seq_first_row)):
+            self._need(t, n, torch.int32, 1)
+        T = qkv.shape[0]
+        if tuple(out.shape) != (T, n_heads * head_dim) or tile_seq.numel() != tile_row0.numel():
+            raise KernelError(f"attention_prefill: out {tuple(out.shape)} or the block list do not fit")
+        self._check(self.lib.cima_attention_prefill(qkv.data_ptr(), qkv.shape[1], tile_seq.data_ptr(), tile_row0.data_ptr(),
+                                                    seq_first_row.data_ptr(), out.data_ptr(), out.shape[1], T,
+                                                    tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window,
+                                                    self._stream()), "attention_prefill")
+
+    def attention_decode(self, qkv: torch.Tensor, kv, seq_slot, seq_len, out: torch.Tensor, n_heads: int,
+                         n_kv_heads: int, head_dim: int, scale: float, window: int, max_len: int = 0,
+                         n_splits: Optional[int] = None) -> None:
+        """One query per sequence over the paged cache (bf16, pages of 64, head_dim <= 128), keys split
+        over ``n_splits`` blocks per (sequence, kv head).  ``max_len`` (0 = unknown) only bounds the
+        number of splits chosen here."""
+        self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)
+        self._need(kv.storage, "cache", torch.bfloat16, 5); self._need(kv.block_table, "block_table", torch.int32, 2)
+        B = qkv.shape[0]
+        if tuple(out.shape) != (B, n_heads * head_dim) or seq_slot.numel() < B or seq_len.numel() < B:
+            raise KernelError(f"attention_decode: out {tuple(out.shape)} / sequences do not fit {B} rows")
+        if n_splits is None:
+            mtiles = -(-(n_heads // n_kv_heads) // 16)
+            n_splits = max(1, min(32, -(-444 // (B * n_kv_heads * mtiles))))      # about three blocks per SM
+            if max_len > 0:
+                n_splits = min(n_splits, -(-max_len // 64))
+        part_o = part_ml = None
+        if n_splits > 1:
+            part_o = self._scratch("attn_o", B * n_heads * n_splits * head_dim, qkv.device)
+            part_ml = self._scratch("attn_ml", B * n_heads * n_splits * 2, qkv.device)
+        self._check(self.lib.cima_attention_decode(
+            qkv.data_ptr(), qkv.shape[1], kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
+            kv.ring_pages, kv.page_size, seq_slot.data_ptr(), seq_len.data_ptr(), _ptr(part_o), _ptr(part_ml),
+            out.data_ptr(), out.shape[1], B, n_heads, n_kv_heads, head_dim, scale, window, n_splits, self._stream()),
+            "attention_decode")
+        if n_splits > 1:
+            self.launches += 1
+
+    def _scratch(self, name: str, numel: int, device) -> torch.Tensor:
+        """Float32 scratch that lives as long as this object (grown on demand, outside graph capture:
+        a captured step always follows an eager one of the same sizes)."""
+        t = self._scratch_bufs.get(name)
+        if t is None or t.numel() < numel or t.device != torch.device(device):
+            t = self._scratch_bufs[name] = torch.empty(numel, dtype=torch.float32, device=device)
+        return t
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits: torch.Tensor, tokens: torch.Tensor) -> None:

@@ -170,7 +170,10 @@ def batch_of(seqs, device):
         row_seq += [i] * n
         first.append(first[-1] + n)
     t = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
-    return SimpleNamespace(row_pos=t(row_pos), row_seq=t(row_seq), seq_slot=t([s[0] for s in seqs]),
+    tiles = sorted(((i, r0) for i, s in enumerate(seqs) for r0 in range(0, s[2], 64)), key=lambda x: -x[1])
+    return SimpleNamespace(n_q_tiles=len(tiles) if all(s[1] == 0 for s in seqs) else 0,
+                           q_tile_seq=t([x[0] for x in tiles]), q_tile_row0=t([x[1] for x in tiles]),
+                           row_pos=t(row_pos), row_seq=t(row_seq), seq_slot=t([s[0] for s in seqs]),
                            seq_first_row=t(first), seq_len=t([s[1] + s[2] for s in seqs]),
                            n_rows=len(row_pos), n_seqs=len(seqs), prefill=all(s[1] == 0 for s in seqs),
                            max_len=max(s[1] + s[2] for s in seqs))
@@ -254,15 +257,27 @@ def fill_cache(cpu, gpu, slot, k, v):
     gpu.storage.copy_(cpu.storage)
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("nh,nkv,hd", [(6, 2, 48), (7, 1, 128), (4, 4, 16), (28, 4, 128), (3, 3, 80)])
-def test_attention_decode_over_cache(K, dtype, nh, nkv, hd):
-    """Three sequences of unequal length in scattered pages; a far key stands out in one of them."""
-    page = 16
+def scattered_tables(lens, slots, page, ring=0, seed=0):
+    """Pages for each slot, drawn from a shuffled pool; returns (tables, pool size, table width)."""
+    need = [min(-(-n // page), ring) if ring else -(-n // page) for n in lens]
+    total = sum(need) + 3
+    order = np.random.default_rng(seed).permutation(total).tolist()
+    tables, k = {}, 0
+    for slot, n in zip(slots, need):
+        tables[slot] = order[k:k + n]
+        k += n
+    return tables, total, max(need)
+
+
+@pytest.mark.parametrize("dtype,page", [("float32", 16), ("bfloat16", 16), ("bfloat16", 64)])
+@pytest.mark.parametrize("nh,nkv,hd", [(6, 2, 48), (7, 1, 128), (4, 4, 16), (28, 4, 128), (3, 3, 80), (40, 2, 64), (2, 1, 112)])
+def test_attention_decode_over_cache(K, dtype, page, nh, nkv, hd):
+    """Three sequences of unequal length in scattered pages; a far key stands out in one of them.
+    Pages of 64 in bfloat16 take the split-KV tensor-core kernel, the others the plain one."""
     lens = [300, 1, 77]
-    tables = {1: list(range(39, 20, -1)), 3: [2], 0: [5, 6, 7, 8, 9]}
     slots = [1, 3, 0]
-    cpu, gpu = make_kv(40, nkv, page, hd, 4, 19, 0, 0, DT[dtype], tables)
+    tables, n_pages, width = scattered_tables(lens, slots, page, seed=hd)
+    cpu, gpu = make_kv(n_pages, nkv, page, hd, 4, width, 0, 0, DT[dtype], tables)
     scale = 1.0 / math.sqrt(hd)
     qkv = g(3, (nh + 2 * nkv) * hd, dtype=DT[dtype], seed=3)
     for i, (slot, n) in enumerate(zip(slots, lens)):
@@ -281,16 +296,22 @@ def test_attention_decode_over_cache(K, dtype, nh, nkv, hd):
     plain = torch.empty_like(out)
     K.attention_plain(qkv.cuda(), gpu, bg.row_pos, bg.row_seq, bg.seq_slot, bg.seq_first_row, plain, nh, nkv, hd, scale, 0, True)
     assert err(plain, want) <= TOL[dtype]
+    if dtype == "bfloat16" and page == 64:
+        for n_splits in (1, 2, 3, 32):           # more splits than pages too
+            out.fill_(7.0)
+            K.attention_decode(qkv.cuda(), gpu, bg.seq_slot, bg.seq_len, out, nh, nkv, hd, scale, 0, n_splits=n_splits)
+            assert err(out, want) <= TOL[dtype], n_splits
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("window,n", [(40, 200), (16, 17), (33, 33), (64, 500)])
-def test_attention_decode_window_edge(K, dtype, window, n):
+@pytest.mark.parametrize("dtype,page", [("float32", 16), ("bfloat16", 16), ("bfloat16", 64)])
+@pytest.mark.parametrize("window,n", [(40, 200), (16, 17), (33, 33), (64, 500), (100, 1000), (1, 70)])
+def test_attention_decode_window_edge(K, dtype, page, window, n):
     """A ring of pages; the key just outside the window stands out and must not be seen, the one just
     inside must."""
-    nh, nkv, hd, page = 4, 2, 32, 16
+    nh, nkv, hd = 4, 2, 32
     ring = -(-window // page) + 1
-    cpu, gpu = make_kv(12, nkv, page, hd, 2, ring, ring, window, DT[dtype], {1: list(range(11, 11 - ring, -1))})
+    tables, n_pages, width = scattered_tables([n], [1], page, ring=ring, seed=window)
+    cpu, gpu = make_kv(n_pages, nkv, page, hd, 2, ring, ring, window, DT[dtype], tables)
     scale = 1.0 / math.sqrt(hd)
     qkv = g(1, (nh + 2 * nkv) * hd, dtype=DT[dtype], seed=4)
     k, v = g(n, nkv, hd, dtype=DT[dtype], seed=5), g(n, nkv, hd, dtype=DT[dtype], seed=6)
@@ -300,7 +321,7 @@ def test_attention_decode_window_edge(K, dtype, window, n):
     k[inside, 1] = qkv[0, 2 * hd:3 * hd] * 8.0     # head 2 reads kv head 1: must be seen
     # only what a ring still holds: the newest positions
     fill_cache(cpu, gpu, 1, k, v)
-    bc, bg = batch_of([(1, n - 1, 1)], "cpu"), batch_of([(1, n - 1, 1)], "cuda")
+    bg = batch_of([(1, n - 1, 1)], "cuda")
     # the statement: plain softmax over the visible keys of the full, unwrapped sequence
     want = torch.zeros(1, nh * hd, dtype=torch.float64)
     for h in range(nh):
@@ -312,11 +333,16 @@ def test_attention_decode_window_edge(K, dtype, window, n):
     K.attention(qkv.cuda(), gpu, bg, out, nh, nkv, hd, scale, window, True)
     assert err(out, want) <= TOL[dtype]
     assert err(out[0, 2 * hd:3 * hd], v[inside, 1]) <= 5e-2      # head 2 is (nearly) that one value
+    if dtype == "bfloat16" and page == 64:
+        for n_splits in (1, 2, 7):
+            K.attention_decode(qkv.cuda(), gpu, bg.seq_slot, bg.seq_len, out, nh, nkv, hd, scale, window, n_splits=n_splits)
+            assert err(out, want) <= TOL[dtype], n_splits
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nh,nkv,hd,window", [(6, 2, 48, 0), (7, 1, 128, 0), (4, 2, 64, 50), (2, 2, 256, 0),
-                                              (28, 4, 128, 0), (5, 5, 16, 7)])
+                                              (28, 4, 128, 0), (5, 5, 16, 7), (4, 2, 96, 64), (2, 1, 32, 65),
+                                              (3, 1, 112, 200), (2, 2, 80, 1)])
 def test_attention_prefill_over_the_step(K, dtype, nh, nkv, hd, window):
     """Ragged prompts in one launch; keys and values come from the step's own rows."""
     lens = [130, 1, 67, 300]
@@ -334,6 +360,9 @@ def test_attention_prefill_over_the_step(K, dtype, nh, nkv, hd, window):
     out = torch.empty(T, nh * hd, dtype=DT[dtype], device="cuda")
     K.attention(qkv.cuda(), None, bg, out, nh, nkv, hd, scale, window, False)
     assert err(out, want) <= TOL[dtype]
+    plain = torch.empty_like(out)
+    K.attention_plain(qkv.cuda(), None, bg.row_pos, bg.row_seq, bg.seq_slot, bg.seq_first_row, plain, nh, nkv, hd, scale, window, False)
+    assert err(plain, want) <= TOL[dtype]
 
 
 # ---------------------------------------------------------------------------- sampling
