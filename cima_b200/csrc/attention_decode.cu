@@ -235,22 +235,53 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   }
 }
 
-// out[b, h, :] = sum_s e^(m_s - M) o_s / sum_s e^(m_s - M) l_s, splits in order
-__global__ void k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    __nv_bfloat16* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
+// out[b, h, :] = sum_s e^(m_s - M) o_s / sum_s e^(m_s - M) l_s, splits in order.
+// One block per (head, sequence): the weights e^(m_s - M) are made once (one thread per split) and
+// kept in shared memory; then a thread per dimension sums the splits' accumulators, whose loads
+// are independent of one another.
+constexpr int MAX_SPLITS = 64;
+__global__ void __launch_bounds__(128)
+k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                    __nv_bfloat16* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
+  __shared__ float w[MAX_SPLITS];
+  __shared__ float s_inv;
   const int b = blockIdx.y, h = blockIdx.x;
   const size_t base = ((size_t)b * nh + h) * n_splits;
-  float M = -INFINITY;
-  for (int s = 0; s < n_splits; s++) M = fmaxf(M, part_ml[(base + s) * 2]);
-  const float Ms = M == -INFINITY ? 0.f : M;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    float acc = 0.f, l = 0.f;
-    for (int s = 0; s < n_splits; s++) {
-      const float f = expf(part_ml[(base + s) * 2] - Ms);
-      acc += f * part_o[(base + s) * hd + d];
-      l += f * part_ml[(base + s) * 2 + 1];
+  if (threadIdx.x < 32) {
+    float m[MAX_SPLITS / 32];
+    float M = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MAX_SPLITS / 32; i++) {
+      const int s = threadIdx.x + 32 * i;
+      m[i] = s < n_splits ? part_ml[(base + s) * 2] : -INFINITY;
+      M = fmaxf(M, m[i]);
     }
-    out[(size_t)b * ldo + (size_t)h * hd + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float Ms = M == -INFINITY ? 0.f : M;
+#pragma unroll
+    for (int i = 0; i < MAX_SPLITS / 32; i++) {
+      const int s = threadIdx.x + 32 * i;
+      if (s < n_splits) w[s] = expf(m[i] - Ms);
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) {
+      float L = 0.f;                                   // splits in order, one thread: a fixed sum
+      for (int s = 0; s < n_splits; s++) L += w[s] * part_ml[(base + s) * 2 + 1];
+      s_inv = L > 0.f ? 1.0f / L : 0.f;
+    }
+  }
+  __syncthreads();
+  const float inv = s_inv;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f;
+    int s = 0;
+    for (; s + 4 <= n_splits; s += 4) {
+      const float o0 = part_o[(base + s) * hd + d], o1 = part_o[(base + s + 1) * hd + d];
+      const float o2 = part_o[(base + s + 2) * hd + d], o3 = part_o[(base + s + 3) * hd + d];
+      acc += w[s] * o0; acc += w[s + 1] * o1; acc += w[s + 2] * o2; acc += w[s + 3] * o3;
+    }
+    for (; s < n_splits; s++) acc += w[s] * part_o[(base + s) * hd + d];
+    out[(size_t)b * ldo + (size_t)h * hd + d] = __float2bfloat16_rn(acc * inv);
   }
 }
 
@@ -275,7 +306,7 @@ int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, cons
                                            window, n_splits);
   int rc = cima_launch_result();
   if (rc || n_splits == 1) return rc;
-  k_attention_combine<<<dim3(nh, B), HD >= 64 ? 64 : 32, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, HD, n_splits);
+  k_attention_combine<<<dim3(nh, B), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, HD, n_splits);
   return cima_launch_result();
 }
 
@@ -291,7 +322,7 @@ extern "C" int cima_attention_decode(const void* qkv, int ld, const void* cache,
   if (page_size != PS) return cima_fail(CIMA_E_SIZE, "attention_decode: page size %d; this kernel takes 64", page_size);
   if (hd % 16 || hd < 16 || hd > 128) return cima_fail(CIMA_E_SIZE, "attention_decode: head_dim %d; this kernel takes multiples of 16 up to 128", hd);
   if (nh <= 0 || nkv <= 0 || nh % nkv) return cima_fail(CIMA_E_SIZE, "attention_decode: %d heads are not a multiple of %d kv heads", nh, nkv);
-  if (n_splits < 1 || n_splits > 65535 || B > 65535) return cima_fail(CIMA_E_SIZE, "attention_decode: %d splits / %d sequences exceed one launch", n_splits, B);
+  if (n_splits < 1 || n_splits > MAX_SPLITS || B > 65535) return cima_fail(CIMA_E_SIZE, "attention_decode: %d splits / %d sequences exceed one launch", n_splits, B);
   if (n_splits > 1 && (!part_o || !part_ml)) return cima_fail(CIMA_E_ARG, "attention_decode: more than one split needs the scratch buffers");
   if (ld % 2 || ((uintptr_t)qkv & 3) || ((uintptr_t)cache & 15)) return cima_fail(CIMA_E_ARG, "attention_decode: qkv rows must be 4-byte and the cache 16-byte aligned");
   CimaPaged pg{table, table_width, ring, page_size, nkv, hd};
