@@ -333,3 +333,53 @@ extern "C" int cima_attention_decode(const void* qkv, int ld, const void* cache,
 #undef CASE
   return cima_fail(CIMA_E_SIZE, "attention_decode: head_dim %d is not instantiated", hd);
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same kernel for callers that cannot allocate (see attention_decode_static.h): the splits'
+// partial results go to a fixed array of this library's device image instead of caller scratch.
+// ---------------------------------------------------------------------------------------------
+#include "attention_decode_static.h"
+
+static __device__ __align__(256) float g_decode_static_scratch[CIMA_DECODE_STATIC_FLOATS];
+
+// In host code the array's name is only a handle; kernels need its device address, which differs
+// per device.  Looked up once per device, with that device current.
+static float* decode_static_scratch_address(int* status) {
+  constexpr int MAX_DEVICES = 64;
+  static float* addr[MAX_DEVICES] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { *status = cima_fail((int)e, "attention_decode_static: cudaGetDevice failed: %s", cudaGetErrorString(e)); return nullptr; }
+  if (dev < 0 || dev >= MAX_DEVICES) { *status = cima_fail(CIMA_E_ARG, "attention_decode_static: device ordinal %d is beyond %d", dev, MAX_DEVICES); return nullptr; }
+  if (!addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+    if (e != cudaSuccess || !p) {
+      *status = cima_fail(e != cudaSuccess ? (int)e : CIMA_E_ARG, "attention_decode_static: cannot find the scratch array on device %d: %s", dev, cudaGetErrorString(e));
+      return nullptr;
+    }
+    addr[dev] = static_cast<float*>(p);
+  }
+  *status = 0;
+  return addr[dev];
+}
+
+extern "C" int cima_attention_decode_static(const void* qkv, int ld, const void* cache, const int* table, int table_width,
+                                            int ring, int page_size, const int* seq_slot, const int* seq_len, void* out,
+                                            int ldo, int B, int nh, int nkv, int hd, float scale, int window,
+                                            int n_splits, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (n_splits < 1 || nh <= 0 || hd <= 0) return cima_fail(CIMA_E_SIZE, "attention_decode_static: splits %d, heads %d and head_dim %d must be positive", n_splits, nh, hd);
+  const unsigned long long cells = (unsigned long long)B * nh * n_splits;
+  const unsigned long long need = cells * (unsigned long long)(hd + 2);
+  if (need > (unsigned long long)CIMA_DECODE_STATIC_FLOATS)
+    return cima_fail(CIMA_E_SIZE, "attention_decode_static: %d sequences x %d heads x %d splits x (head_dim %d + 2) = %llu floats of scratch; "
+                     "the fixed array holds %d", B, nh, n_splits, hd, need, CIMA_DECODE_STATIC_FLOATS);
+  int status = 0;
+  float* scratch = decode_static_scratch_address(&status);
+  if (!scratch) return status;
+  float* part_o = scratch;                       // [B, nh, n_splits, hd]
+  float* part_ml = scratch + cells * hd;         // [B, nh, n_splits, 2]
+  return cima_attention_decode(qkv, ld, cache, table, table_width, ring, page_size, seq_slot, seq_len, part_o, part_ml,
+                               out, ldo, B, nh, nkv, hd, scale, window, n_splits, stream);
+}
