@@ -1,0 +1,344 @@
+// Matrix product on the fifth-generation tensor cores (tcgen05) for bfloat16:
+//     D[i, j] = sum_k P[i, k] * Q[j, k]          P [p_rows, K], Q [q_rows, K], both row-major (K contiguous)
+// One block computes a 128 x BN tile of D.  Operand tiles of 64 k (128 bytes per row) are brought by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle) into a ring of shared-memory stages guarded by mbarriers;
+// one elected thread issues tcgen05.mma (128 x BN x 16 per instruction) with the accumulator in tensor
+// memory (TMEM, 128 lanes x BN float32 columns); tcgen05.commit frees a stage and, at the end, tells the
+// epilogue warps that the accumulator is complete; they read it back with tcgen05.ld and apply the
+// epilogue in float32 before the one rounding of the store.
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM allocation + MMA issue,
+// warps 2..5 = epilogue (each owns the 32 TMEM lanes its index modulo 4 may access).
+//
+// Who is P and who is Q decides the use:
+//   * prefill (many rows): P = activations [M, K], Q = weights [N, K]; out[i, j]      (row = token)
+//   * decode with up to 64 rows ("swap A/B"): P = weights, Q = activations; out[j, i]   (transposed store)
+// Epilogues: 0 store bf16 (+ bias)   1 accumulate into the float32 residual (+ bias)
+//            2 silu(gate) * up -> bf16 (Q = [gate rows | up rows]; a tile takes BN/2 rows of each)
+//            3 store float32 (+ bias)
+// Tails in every dimension: TMA fills what lies outside a matrix with zeros, stores are masked.
+// K must be a multiple of 8 (16-byte row pitch for TMA).
+//
+// Every wait on an mbarrier is bounded (2 s); a wait that runs out sets *error_flag, and all roles
+// leave their loops, free the tensor memory and return.
+//
+// The reference has no kernel of this kind: its only tensor-core path is cublasGemmEx
+// (src/cuda.rs:2484-2541), its own k_gemm_f16 is a 16x16 shared-memory tile on CUDA cores
+// (src/kernels.cu:1410-1431).
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128;          // rows of P per tile = TMEM lanes
+constexpr int BK = 64;           // k per stage: 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr unsigned long long WAIT_NS = 2000000000ull;
+
+enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3 };
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when it ran out (the flag is set, the caller leaves its loop).
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, int* error_flag, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer();
+  for (unsigned it = 0;; it++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if (globaltimer() - t0 > WAIT_NS) {
+        *abort_flag = 1;
+        atomicExch(error_flag, 1);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, int x, int y, void* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, groups of 8 rows
+// 1024 bytes apart.  Fields: start address >> 4 [0,14), leading byte offset >> 4 [16,30) (unused for this
+// layout), stride byte offset >> 4 [32,46), descriptor version 1 [46,48), layout type 2 = SWIZZLE_128B [61,64).
+__device__ __forceinline__ unsigned long long umma_smem_desc(unsigned smem_addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)(1u) << 16;
+  d |= (unsigned long long)(1024u >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+// Instruction descriptor, kind::f16: D float32 [4,6) = 1, A and B bfloat16 [7,10) = [10,13) = 1, both K-major,
+// N >> 3 at [17,23), M >> 4 at [24,29).
+__device__ __forceinline__ unsigned umma_idesc(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(void* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+struct GemmArgs {
+  int p_rows, q_rows, K;      // extents of P, Q and of the sum
+  int up_offset;              // EPI_SWIGLU: row of Q where the "up" half starts
+  const float* bias;          // per feature, or null
+  void* out;
+  int ldo;
+  int transposed;             // 0: out[i * ldo + j] (i = P row)   1: out[j * ldo + i]
+  int bias_on_p;              // bias indexed by the P row (swap A/B) instead of the Q row
+  int* error_flag;
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(THREADS, 1)
+k_gemm_tcgen05(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmArgs a) {
+  constexpr int P_BYTES = BM * BK * 2, Q_BYTES = BN * BK * 2;
+  constexpr int QH = EPI == EPI_SWIGLU ? BN / 2 : BN;          // rows of Q per TMA box
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // 1024-byte tiles
+  unsigned char* sp = smem;                                    // [STAGES][BM x 128 B]
+  unsigned char* sq = smem + (size_t)STAGES * P_BYTES;         // [STAGES][BN x 128 B]
+  unsigned long long* full = (unsigned long long*)(sq + (size_t)STAGES * Q_BYTES);
+  unsigned long long* empty = full + STAGES;
+  unsigned long long* acc_done = empty + STAGES;
+  unsigned* tmem_slot = (unsigned*)(acc_done + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int p0 = blockIdx.y * BM;
+  // EPI_SWIGLU: a tile covers QH gate features and the matching QH up features
+  const int q0 = blockIdx.x * QH;
+  const int kblocks = (a.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN < 32 ? 32 : BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      for (int kb = 0; kb < kblocks; kb++) {
+        const int s = kb % STAGES;
+        if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1, a.error_flag, abort_flag)) break;
+        mbar_expect_tx(&full[s], P_BYTES + Q_BYTES);
+        tma_load_2d(sp + (size_t)s * P_BYTES, &map_p, kb * BK, p0, &full[s]);
+        if (EPI == EPI_SWIGLU) {
+          tma_load_2d(sq + (size_t)s * Q_BYTES, &map_q, kb * BK, q0, &full[s]);
+          tma_load_2d(sq + (size_t)s * Q_BYTES + QH * BK * 2, &map_q, kb * BK, a.up_offset + q0, &full[s]);
+        } else {
+          tma_load_2d(sq + (size_t)s * Q_BYTES, &map_q, kb * BK, q0, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issue (one thread)
+    if (lane == 0) {
+      const unsigned idesc = umma_idesc(BM, BN);
+      bool ok = true;
+      for (int kb = 0; kb < kblocks && ok; kb++) {
+        const int s = kb % STAGES;
+        ok = mbar_wait(&full[s], (kb / STAGES) & 1, a.error_flag, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned long long pd = umma_smem_desc(smem_u32(sp + (size_t)s * P_BYTES));
+        const unsigned long long qd = umma_smem_desc(smem_u32(sq + (size_t)s * Q_BYTES));
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; k++)           // 32 bytes further along the swizzled row per step
+          umma_bf16(tmem_base, pd + (unsigned long long)(k * 2), qd + (unsigned long long)(k * 2), idesc, (kb | k) ? 1u : 0u);
+        umma_commit(&empty[s]);                         // the stage is free when these instructions have read it
+      }
+      umma_commit(acc_done);                            // arrives when every instruction above has completed
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue: 4 warps x 32 TMEM lanes
+    const bool ok = mbar_wait(acc_done, 0, a.error_flag, abort_flag);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int quarter = warp & 3;                       // the TMEM lanes this warp may read
+    const int i = p0 + quarter * 32 + lane;             // row of P = row of the accumulator
+    if (ok) {
+      constexpr int COLS = EPI == EPI_SWIGLU ? BN / 2 : BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < COLS; c0 += 32) {
+        float v[32];
+        tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, v);
+        if (EPI == EPI_SWIGLU) {
+          float u[32];
+          tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(BN / 2 + c0), u);
+#pragma unroll
+          for (int e = 0; e < 32; e++) v[e] = v[e] / (1.0f + expf(-v[e])) * u[e];
+        }
+        if (i < a.p_rows) {
+#pragma unroll
+          for (int e = 0; e < 32; e++) {
+            const int j = q0 + c0 + e;                  // row of Q = column of the accumulator
+            if (j >= (EPI == EPI_SWIGLU ? a.up_offset : a.q_rows)) continue;
+            float r = v[e];
+            if (a.bias) r += a.bias[a.bias_on_p ? i : j];
+            const size_t o = a.transposed ? (size_t)j * a.ldo + i : (size_t)i * a.ldo + j;
+            if (EPI == EPI_ACCUM) ((float*)a.out)[o] += r;
+            else if (EPI == EPI_STORE_F32) ((float*)a.out)[o] = r;
+            else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(r);
+          }
+        }
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN < 32 ? 32 : BN) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// A [rows, K] bf16 row-major matrix seen through boxes of 64 k x box_rows rows, 128-byte swizzle, zeros outside.
+int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return cima_fail(CIMA_E_ARG, "gemm_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cima_fail(CIMA_E_ARG, "gemm_tcgen05: cuTensorMapEncodeTiled failed with %d (base %p, rows %d, K %d, box %d)", (int)r, base, rows, K, box_rows);
+  return 0;
+}
+
+template <int BN, int STAGES, int EPI>
+int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, int tiles_q, cudaStream_t stream) {
+  auto kern = k_gemm_tcgen05<BN, STAGES, EPI>;
+  const size_t smem = 1024 + (size_t)STAGES * (BM + BN) * BK * 2 + (2 * STAGES + 1) * 8 + 16;
+  static bool raised = false;
+  if (!raised) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cima_fail((int)e, "gemm_tcgen05: cannot raise shared memory to %zu bytes: %s", smem, cudaGetErrorString(e));
+    raised = true;
+  }
+  dim3 grid(tiles_q, (a.p_rows + BM - 1) / BM);
+  kern<<<grid, THREADS, smem, stream>>>(mp, mq, a);
+  return cima_launch_result();
+}
+
+template <int BN, int STAGES>
+int dispatch_epi(int epi, const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, int tiles_q, cudaStream_t stream) {
+  switch (epi) {
+    case EPI_STORE: return launch<BN, STAGES, EPI_STORE>(mp, mq, a, tiles_q, stream);
+    case EPI_ACCUM: return launch<BN, STAGES, EPI_ACCUM>(mp, mq, a, tiles_q, stream);
+    case EPI_SWIGLU: return launch<BN, STAGES, EPI_SWIGLU>(mp, mq, a, tiles_q, stream);
+    case EPI_STORE_F32: return launch<BN, STAGES, EPI_STORE_F32>(mp, mq, a, tiles_q, stream);
+  }
+  return cima_fail(CIMA_E_ARG, "gemm_tcgen05: epilogue %d is not one of 0..3", epi);
+}
+
+}  // namespace
+
+// out = epilogue(P Q^T).  P [p_rows, K], Q [q_rows, K] bf16 row-major, 16-byte aligned, K % 8 == 0.
+// For epilogue 2, Q is [2 * up_offset, K] (gate rows, then up rows) and q_rows = 2 * up_offset.
+// bn: columns of D per tile (64, 128 or 256; for epilogue 2 a tile holds bn/2 gate and bn/2 up features).
+// error_flag: device int that a wait that ran out sets to 1 (never cleared here).
+extern "C" int cima_gemm_tcgen05(const void* P, const void* Q, const float* bias, void* out, int epi, int p_rows,
+                                 int q_rows, int K, int ldo, int transposed, int bias_on_p, int up_offset, int bn,
+                                 int* error_flag, cudaStream_t stream) {
+  if (p_rows <= 0 || q_rows <= 0) return 0;
+  if (K <= 0 || K % 8) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05: K %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
+  if (((uintptr_t)P | (uintptr_t)Q) & 15) return cima_fail(CIMA_E_ARG, "gemm_tcgen05: P and Q must be 16-byte aligned");
+  if (!error_flag) return cima_fail(CIMA_E_ARG, "gemm_tcgen05: an error flag on the device is needed");
+  if (epi == EPI_SWIGLU && (up_offset <= 0 || q_rows != 2 * up_offset)) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05: the gated epilogue needs Q = [gate | up] with q_rows = 2 * up_offset");
+  if (epi == EPI_SWIGLU && bias) return cima_fail(CIMA_E_ARG, "gemm_tcgen05: the gated epilogue takes no bias");
+  if (bn != 64 && bn != 128 && bn != 256) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05: tile width %d is not 64, 128 or 256", bn);
+  const int qh = epi == EPI_SWIGLU ? bn / 2 : bn;                 // rows of Q per TMA box
+  const int q_feat = epi == EPI_SWIGLU ? up_offset : q_rows;
+  const int tiles_q = (q_feat + qh - 1) / qh;
+  if (tiles_q > 65535 * 32 || (p_rows + BM - 1) / BM > 65535) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05: the grid exceeds one launch");
+  CUtensorMap mp, mq;
+  int rc = make_map(&mp, P, p_rows, K, BM);
+  if (rc) return rc;
+  rc = make_map(&mq, Q, q_rows, K, qh);
+  if (rc) return rc;
+  GemmArgs a{p_rows, q_rows, K, up_offset, bias, out, ldo, transposed, bias_on_p, error_flag};
+  switch (bn) {
+    case 64: return dispatch_epi<64, 8>(epi, mp, mq, a, tiles_q, stream);
+    case 128: return dispatch_epi<128, 6>(epi, mp, mq, a, tiles_q, stream);
+    default: return dispatch_epi<256, 4>(epi, mp, mq, a, tiles_q, stream);
+  }
+}

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
@@ -49,6 +49,7 @@ _SIGNATURES = {
                              _f, _i, _i, _vp],
     "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
     "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "cima_gemm_tcgen05": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
     "cima_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
@@ -83,6 +84,7 @@ class Kernels:
             fn.restype = ctypes.c_int
         self.launches = 0
         self._scratch_bufs = {}
+        self._error_flag = None
 
     # ------------------------------------------------------------------ plumbing
     def _check(self, code: int, what: str) -> None:
@@ -192,6 +194,41 @@ class Kernels:
                 raise KernelError(f"linear_skinny: bias has {bias.numel()} entries, expected {N}")
         self._check(self.lib.cima_linear_skinny(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode,
                                                 M, N, K, K, N, self._stream()), "linear_skinny")
+
+    def gemm_tc(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int,
+                swap: Optional[bool] = None, bn: Optional[int] = None) -> None:
+        """out = epilogue(a @ w.T) on the tcgen05 tensor cores (bf16 operands, float32 accumulation in
+        tensor memory, operands by TMA).  ``mode`` as for ``linear_skinny`` (SK_*); for SK_SWIGLU ``w`` is
+        [2N, K].  ``swap`` makes the weights the 128-row operand (few rows of ``a``, at most 64... 256)."""
+        self._need(a, "a", torch.bfloat16, 2); self._need(w, "w", torch.bfloat16, 2); self._need(out, "out", None, 2)
+        M, K = a.shape
+        N = w.shape[0] // 2 if mode == SK_SWIGLU else w.shape[0]
+        want = torch.float32 if mode in (SK_ACCUM, SK_STORE_F32) else torch.bfloat16
+        if w.shape[1] != K or tuple(out.shape) != (M, N) or out.dtype is not want:
+            raise KernelError(f"gemm_tc(mode {mode}): a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} "
+                              f"{out.dtype} do not agree")
+        if bias is not None:
+            self._need(bias, "bias", torch.float32, 1)
+        if swap is None:
+            swap = M <= 64 and mode != SK_SWIGLU
+        if self._error_flag is None:
+            self._error_flag = torch.zeros(1, dtype=torch.int32, device=a.device)
+        if swap:
+            if mode == SK_SWIGLU:
+                raise KernelError("gemm_tc: the gated epilogue is not offered with swapped operands")
+            bn = bn or (64 if M <= 64 else 128 if M <= 128 else 256)
+            code = self.lib.cima_gemm_tcgen05(w.data_ptr(), a.data_ptr(), _ptr(bias), out.data_ptr(), mode, N, M, K,
+                                              N, 1, 1, 0, bn, self._error_flag.data_ptr(), self._stream())
+        else:
+            bn = bn or (256 if N >= 2048 else 128)
+            code = self.lib.cima_gemm_tcgen05(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, M,
+                                              w.shape[0], K, N, 0, 0, N if mode == SK_SWIGLU else 0, bn,
+                                              self._error_flag.data_ptr(), self._stream())
+        self._check(code, "gemm_tcgen05")
+
+    def device_errors(self) -> int:
+        """The error flag that a bounded wait inside a kernel sets when it runs out (synchronises)."""
+        return 0 if self._error_flag is None else int(self._error_flag.item())
 
     # ------------------------------------------------------------------ attention
     def rope_append(self, qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, row_pos, row_seq, seq_slot,

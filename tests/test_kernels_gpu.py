@@ -376,3 +376,34 @@ def test_argmax_ties_go_to_the_higher_index(K):
     tok = torch.empty(5, dtype=torch.int32, device="cuda")
     K.argmax(x.cuda(), tok)
     assert tok.tolist() == [900, 999, 999, 0, int(torch.nonzero(x[4] == x[4].max()).max())]
+
+
+# ---------------------------------------------------------------------------- tcgen05 matrix product
+@pytest.mark.parametrize("M,N,K_,bn,swap", [(128, 128, 64, 128, False), (200, 328, 200, 128, False),
+                                            (2048, 1000, 448, 256, False), (300, 3584, 192, 256, False),
+                                            (64, 3584, 448, 64, True), (17, 1000, 192, 64, True),
+                                            (1, 200, 8, 64, True), (130, 65, 72, 128, False)])
+def test_gemm_tcgen05_modes(K, M, N, K_, bn, swap):
+    """TMA + tcgen05.mma + TMEM product against float64, every epilogue, tails in every dimension."""
+    from cima_b200.kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
+    a = g(M, K_, dtype=torch.bfloat16, seed=M)
+    w = g(N, K_, dtype=torch.bfloat16, seed=N, scale=1.0 / math.sqrt(K_))
+    b = g(N, seed=7)
+    want = a.double() @ w.double().t()
+    out32 = torch.full((M, N), -777.0, device="cuda")
+    K.gemm_tc(a.cuda(), w.cuda(), b.cuda(), out32, SK_STORE_F32, swap=swap, bn=bn)
+    assert err(out32, want + b.double()) <= 1e-4
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    K.gemm_tc(a.cuda(), w.cuda(), None, out, SK_STORE, swap=swap, bn=bn)
+    assert err(out, want) <= TOL["bfloat16"] * 4
+    x = g(M, N, seed=9)
+    xg = x.cuda()
+    K.gemm_tc(a.cuda(), w.cuda(), None, xg, SK_ACCUM, swap=swap, bn=bn)
+    assert err(xg, x.double() + want) <= 1e-4
+    if N % 2 == 0 and not swap:
+        I = N // 2
+        act = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+        K.gemm_tc(a.cuda(), w.cuda(), None, act, SK_SWIGLU, swap=False, bn=bn)
+        gg, uu = want[:, :I], want[:, I:]
+        assert err(act, gg / (1 + torch.exp(-gg)) * uu) <= TOL["bfloat16"] * 4
+    assert K.device_errors() == 0
