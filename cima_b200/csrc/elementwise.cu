@@ -10,21 +10,32 @@
 // ---------------------------------------------------------------- embedding: x[t,:] = scale * E[ids[t],:]
 template <typename TW>
 __global__ void k_embed(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ x,
-                        int H, int V, float scale) {
+                        int H, int V, float scale, float* __restrict__ ssq) {
+  __shared__ float red[32];
   const int row = blockIdx.x;
   int id = ids[row];
   id = id < 0 ? 0 : (id >= V ? V - 1 : id);    // ids are checked on the host; never read outside the table
   const TW* src = table + (size_t)id * H;
   float* dst = x + (size_t)row * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = cima_to_f32<TW>(src[i]) * scale;
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = cima_to_f32<TW>(src[i]) * scale;
+    dst[i] = v;
+    acc += v * v;
+  }
+  if (ssq) {                                    // the row's sum of squares, for a norm folded into the next product
+    const float total = cima_block_sum(acc, red);
+    if (threadIdx.x == 0) ssq[row] = total;
+  }
 }
 
+// ssq (may be null): [T] sum of squares of each row written.
 extern "C" int cima_embed(const int* ids, const void* table, int table_dtype, float* x, int T, int H, int V,
-                          float scale, cudaStream_t stream) {
+                          float scale, float* ssq, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || V <= 0) return cima_fail(CIMA_E_SIZE, "embed: hidden %d and vocab %d must be positive", H, V);
-  if (table_dtype == CIMA_F32) k_embed<float><<<T, 256, 0, stream>>>(ids, (const float*)table, x, H, V, scale);
-  else if (table_dtype == CIMA_BF16) k_embed<__nv_bfloat16><<<T, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, x, H, V, scale);
+  if (table_dtype == CIMA_F32) k_embed<float><<<T, 256, 0, stream>>>(ids, (const float*)table, x, H, V, scale, ssq);
+  else if (table_dtype == CIMA_BF16) k_embed<__nv_bfloat16><<<T, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, x, H, V, scale, ssq);
   else return cima_fail(CIMA_E_DTYPE, "embed: table dtype code %d is neither float32 nor bfloat16", table_dtype);
   return cima_launch_result();
 }

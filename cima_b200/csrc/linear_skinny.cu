@@ -7,7 +7,10 @@
 // Work split.  One block owns 16 output features (or 16 gate and the 16 matching up features for
 // the gated epilogue).  Its 8 warps split K in interleaved chunks; their partial sums are added in
 // shared memory in warp order 0..7, so a result never depends on scheduling, and a row of X gives
-// the same bits whatever else is in the batch.
+// the same bits whatever else is in the batch.  A matrix with few output features and a long K
+// (the down projection) would leave most of the GPU idle that way, so the blocks of a thread-block
+// cluster (1, 2, 4 or 8, chosen from the matrix's shape alone) split K further; block 0 of the
+// cluster adds the blocks' sums in rank order through distributed shared memory and stores.
 //
 // Operand order.  mma.m16n8k16 wants, per thread, k = {2t, 2t+1, 2t+8, 2t+9} of rows g and g+8.
 // A sum over k does not care in which order k is visited as long as both operands agree, so a
@@ -19,6 +22,8 @@
 //   0 store bf16 (+ bias)      1 accumulate into the float32 residual      2 silu(gate) * up -> bf16
 //   3 store float32 (+ bias), used for logits
 #include "common.cuh"
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
 
 enum { SK_STORE = 0, SK_ACCUM = 1, SK_SWIGLU = 2, SK_STORE_F32 = 3 };
 
@@ -33,6 +38,11 @@ __device__ __forceinline__ uint4 ld_cached16(const void* p) {
   return __ldg(reinterpret_cast<const uint4*>(p));
 }
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -45,17 +55,45 @@ constexpr int SK_WARPS = 8;
 constexpr int SK_ROWS = 16;      // output features per m-tile
 constexpr int SK_PAD = 17;       // row stride of the reduction buffer (bank spread)
 
+// RMSNorm folded into the product.  The rows of X are then the float32 residual stream x; the kernel
+// normalises them on the fly, h = bf16(x * inv * w) with inv = 1 / sqrt(sum(x^2) / K + eps), where
+// sum(x^2) of a row is given as `parts` partial sums that the kernel which wrote x left behind
+// (ssq [M, parts]; summed here in a fixed order).  An accumulating product in turn leaves the partial
+// sums of the rows it has updated (ssq_out [M, tiles], one per 16-feature tile), so that between the
+// two no separate norm kernel has to run.
+struct SkinnyNorm {
+  const float* x32;      // [M, K] float32, row stride ldx; null = X is bf16 activations
+  const float* w;        // [K] norm weight
+  const float* ssq;      // [M, parts]
+  int parts;
+  float eps;
+  float* ssq_out;        // [M, tiles] or null (accumulating epilogue only)
+};
+
 // NT: 8-row tiles of X (M <= 8 * NT).  MT: m-tiles per block (1, or 2 for the gated epilogue).
-// U: 32-wide k steps kept in flight per warp iteration.
-template <int NT, int MT, int U, int MODE>
+// U: 32-wide k steps kept in flight per warp iteration.  NORM: X is the residual stream (see above).
+template <int NT, int MT, int U, int MODE, bool NORM>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                 const float* __restrict__ bias, void* __restrict__ out,
-                int M, int N, int K, int ldx, int ldo, int up_offset) {
-  extern __shared__ float red[];                       // [warps][MT][NT*8][SK_PAD]
+                int M, int N, int K, int ldx, int ldo, int up_offset, SkinnyNorm nm) {
+  extern __shared__ float red[];                       // [warps][MT][NT*8][SK_PAD], then part [MT][NT*8][SK_ROWS]
+  cg::cluster_group cluster = cg::this_cluster();
+  const int S = (int)cluster.num_blocks();              // blocks that share this tile's K
+  const int crank = (int)cluster.block_rank();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * SK_ROWS;
+  const int n0 = (blockIdx.x / S) * SK_ROWS;
+  __shared__ float inv_s[NT * 8];
+  if (NORM) {
+    for (int m = warp; m < M; m += SK_WARPS) {
+      float acc = 0.f;
+      for (int p = lane; p < nm.parts; p += 32) acc += nm.ssq[(size_t)m * nm.parts + p];
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) inv_s[m] = 1.0f / sqrtf(acc / (float)K + nm.eps);
+    }
+    __syncthreads();
+  }
 
   float acc[MT][NT][4];
 #pragma unroll
@@ -81,7 +119,7 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
   // and so the order of summation, is the same for every instantiation.  U only says how many of a
   // chunk's four 32-wide steps are loaded before they are multiplied.
   constexpr int CHUNK = 128;
-  for (int k0 = warp * CHUNK; k0 < K; k0 += SK_WARPS * CHUNK) {
+  for (int k0 = (crank * SK_WARPS + warp) * CHUNK; k0 < K; k0 += S * SK_WARPS * CHUNK) {
 #pragma unroll
     for (int sub = 0; sub < 4; sub += U) {
       uint4 w[MT][2][U];
@@ -97,10 +135,28 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
 #pragma unroll
       for (int s = 0; s < U; s++) {
         const int k = k0 + (sub + s) * 32 + 8 * t;
+        float4 nw0 = make_float4(0.f, 0.f, 0.f, 0.f), nw1 = nw0;
+        if (NORM && k < K) {
+          nw0 = __ldg(reinterpret_cast<const float4*>(nm.w + k));
+          nw1 = __ldg(reinterpret_cast<const float4*>(nm.w + k + 4));
+        }
 #pragma unroll
         for (int j = 0; j < NT; j++) {
           const int m = j * 8 + g;
-          const uint4 x = (m < M && k < K) ? ld_cached16(X + (size_t)m * ldx + k) : make_uint4(0u, 0u, 0u, 0u);
+          uint4 x = make_uint4(0u, 0u, 0u, 0u);
+          if (m < M && k < K) {
+            if (NORM) {
+              const float* xp = nm.x32 + (size_t)m * ldx + k;
+              const float4 a0 = __ldg(reinterpret_cast<const float4*>(xp)), a1 = __ldg(reinterpret_cast<const float4*>(xp + 4));
+              const float inv = inv_s[m];
+              x.x = pack2(a0.x * inv * nw0.x, a0.y * inv * nw0.y);
+              x.y = pack2(a0.z * inv * nw0.z, a0.w * inv * nw0.w);
+              x.z = pack2(a1.x * inv * nw1.x, a1.y * inv * nw1.y);
+              x.w = pack2(a1.z * inv * nw1.z, a1.w * inv * nw1.w);
+            } else {
+              x = ld_cached16(X + (size_t)m * ldx + k);
+            }
+          }
 #pragma unroll
           for (int a = 0; a < MT; a++) {
             mma_16816(acc[a][j], w[a][0][s].x, w[a][1][s].x, w[a][0][s].y, w[a][1][s].y, x.x, x.y);
@@ -126,37 +182,78 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
     }
   __syncthreads();
 
+  // this block's sums over its 8 warps, in warp order
+  float* part = red + (size_t)SK_WARPS * MT * COLS * SK_PAD;          // [MT][COLS][SK_ROWS]
   for (int e = threadIdx.x; e < COLS * SK_ROWS; e += SK_WARPS * 32) {
     const int r = e % SK_ROWS, m = e / SK_ROWS;
-    const int n = n0 + r;
-    if (m >= M || n >= N) continue;
-    float v[MT];
 #pragma unroll
     for (int a = 0; a < MT; a++) {
       float s = 0.f;
 #pragma unroll
       for (int wi = 0; wi < SK_WARPS; wi++) s += red[(((size_t)wi * MT + a) * COLS + m) * SK_PAD + r];
-      v[a] = s;
-    }
-    const size_t o = (size_t)m * ldo + n;
-    if (MODE == SK_STORE) {
-      ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v[0] + (bias ? bias[n] : 0.f));
-    } else if (MODE == SK_ACCUM) {
-      ((float*)out)[o] += v[0] + (bias ? bias[n] : 0.f);
-    } else if (MODE == SK_STORE_F32) {
-      ((float*)out)[o] = v[0] + (bias ? bias[n] : 0.f);
-    } else {
-      const float gate = v[0], up = v[MT - 1];
-      ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+      part[((size_t)a * COLS + m) * SK_ROWS + r] = s;
     }
   }
+  if (S > 1) cluster.sync(); else __syncthreads();
+
+  if (crank == 0) {
+    for (int e = threadIdx.x; e < COLS * SK_ROWS; e += SK_WARPS * 32) {
+      const int r = e % SK_ROWS, m = e / SK_ROWS;
+      const int n = n0 + r;
+      const bool live = m < M && n < N;
+      if (MODE == SK_ACCUM && nm.ssq_out) {
+        // the 16 features of a row sit in 16 consecutive lanes: their squares are summed by shuffles
+        float xn = 0.f;
+        if (live) {
+          float s = part[(size_t)m * SK_ROWS + r];
+          for (int cr = 1; cr < S; cr++) s += cluster.map_shared_rank(part, cr)[(size_t)m * SK_ROWS + r];
+          const size_t o = (size_t)m * ldo + n;
+          xn = ((float*)out)[o] + (s + (bias ? bias[n] : 0.f));
+          ((float*)out)[o] = xn;
+        }
+        float sq = xn * xn;
+        for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (r == 0 && m < M) nm.ssq_out[(size_t)m * gridDim.x / S + blockIdx.x / S] = sq;
+        continue;
+      }
+      if (!live) continue;
+      float v[MT];
+#pragma unroll
+      for (int a = 0; a < MT; a++) {
+        float s = part[((size_t)a * COLS + m) * SK_ROWS + r];
+        for (int cr = 1; cr < S; cr++)                                // the other blocks' sums, in rank order
+          s += cluster.map_shared_rank(part, cr)[((size_t)a * COLS + m) * SK_ROWS + r];
+        v[a] = s;
+      }
+      const size_t o = (size_t)m * ldo + n;
+      if (MODE == SK_STORE) {
+        ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(v[0] + (bias ? bias[n] : 0.f));
+      } else if (MODE == SK_ACCUM) {
+        ((float*)out)[o] += v[0] + (bias ? bias[n] : 0.f);
+      } else if (MODE == SK_STORE_F32) {
+        ((float*)out)[o] = v[0] + (bias ? bias[n] : 0.f);
+      } else {
+        const float gate = v[0], up = v[MT - 1];
+        ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+      }
+    }
+  }
+  if (S > 1) cluster.sync();            // a block's shared memory must outlive block 0's reads of it
 }
 
-template <int NT, int MT, int U, int MODE>
+// Blocks per cluster for a matrix of `tiles` 16-feature tiles and K: enough blocks to fill the GPU,
+// never more virtual warps than K has chunks of 128.  Depends on the matrix only, never on the rows of X.
+static int cluster_size(int tiles, int K) {
+  int s = 1;
+  while (s < 8 && tiles * s < 1184 && (2 * s) * SK_WARPS * 128 <= K) s *= 2;
+  return s;
+}
+
+template <int NT, int MT, int U, int MODE, bool NORM>
 static int launch_skinny(const void* X, const void* W, const float* bias, void* out, int M, int N, int K, int ldx,
-                         int ldo, int up_offset, cudaStream_t stream) {
-  auto kern = k_linear_skinny<NT, MT, U, MODE>;
-  const size_t smem = (size_t)SK_WARPS * MT * NT * 8 * SK_PAD * sizeof(float);
+                         int ldo, int up_offset, const SkinnyNorm& nm, cudaStream_t stream) {
+  auto kern = k_linear_skinny<NT, MT, U, MODE, NORM>;
+  const size_t smem = ((size_t)SK_WARPS * MT * NT * 8 * SK_PAD + (size_t)MT * NT * 8 * SK_ROWS) * sizeof(float);
   if (smem > 48 * 1024) {
     static bool raised = false;     // one attribute per instantiation
     if (!raised) {
@@ -165,37 +262,77 @@ static int launch_skinny(const void* X, const void* W, const float* bias, void* 
       raised = true;
     }
   }
-  kern<<<(N + SK_ROWS - 1) / SK_ROWS, SK_WARPS * 32, smem, stream>>>(
-      (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, out, M, N, K, ldx, ldo, up_offset);
+  const int tiles = (N + SK_ROWS - 1) / SK_ROWS;
+  const int S = cluster_size(tiles, K);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * S);
+  cfg.blockDim = dim3(SK_WARPS * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, out, M, N, K, ldx,
+                                     ldo, up_offset, nm);
+  if (e != cudaSuccess) return cima_fail((int)e, "linear_skinny: launch failed: %s", cudaGetErrorString(e));
   return cima_launch_result();
 }
 
-template <int NT>
+template <int NT, bool NORM>
 static int dispatch_mode(int mode, const void* X, const void* W, const float* bias, void* out, int M, int N, int K,
-                         int ldx, int ldo, cudaStream_t stream) {
+                         int ldx, int ldo, const SkinnyNorm& nm, cudaStream_t stream) {
   constexpr int U = NT <= 2 ? 4 : 2;
   switch (mode) {
-    case SK_STORE: return launch_skinny<NT, 1, U, SK_STORE>(X, W, bias, out, M, N, K, ldx, ldo, 0, stream);
-    case SK_ACCUM: return launch_skinny<NT, 1, U, SK_ACCUM>(X, W, bias, out, M, N, K, ldx, ldo, 0, stream);
-    case SK_STORE_F32: return launch_skinny<NT, 1, U, SK_STORE_F32>(X, W, bias, out, M, N, K, ldx, ldo, 0, stream);
-    case SK_SWIGLU: return launch_skinny<NT, 2, (NT <= 2 ? 2 : 1), SK_SWIGLU>(X, W, bias, out, M, N, K, ldx, ldo, N, stream);
+    case SK_STORE: return launch_skinny<NT, 1, U, SK_STORE, NORM>(X, W, bias, out, M, N, K, ldx, ldo, 0, nm, stream);
+    case SK_ACCUM: return launch_skinny<NT, 1, U, SK_ACCUM, NORM>(X, W, bias, out, M, N, K, ldx, ldo, 0, nm, stream);
+    case SK_STORE_F32: return launch_skinny<NT, 1, U, SK_STORE_F32, NORM>(X, W, bias, out, M, N, K, ldx, ldo, 0, nm, stream);
+    case SK_SWIGLU: return launch_skinny<NT, 2, (NT <= 2 ? 2 : 1), SK_SWIGLU, NORM>(X, W, bias, out, M, N, K, ldx, ldo, N, nm, stream);
     default: return cima_fail(CIMA_E_ARG, "linear_skinny: mode %d is not one of 0..3", mode);
   }
 }
 
-// X [M, K] bf16 (row stride ldx), W [N, K] bf16 (for mode 2: [2N, K], gate rows then up rows),
-// bias float32 [N] or null, out [M, N] (row stride ldo) in the dtype of the mode.
-// Accepts 1 <= M <= 64, any N, K a multiple of 8 (16-byte rows), 16-byte aligned X, W and ldx % 8 == 0.
-extern "C" int cima_linear_skinny(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N,
-                                  int K, int ldx, int ldo, cudaStream_t stream) {
-  if (M <= 0) return 0;
+static int skinny_checks(const void* X, const void* W, const float* bias, int mode, int M, int N, int K, int ldx) {
   if (M > 64) return cima_fail(CIMA_E_SIZE, "linear_skinny: %d rows; this kernel takes at most 64", M);
   if (N <= 0 || K <= 0) return cima_fail(CIMA_E_SIZE, "linear_skinny: N %d and K %d must be positive", N, K);
   if (K % 8 || ldx % 8) return cima_fail(CIMA_E_SIZE, "linear_skinny: K %d and the row stride %d must be multiples of 8 (16-byte loads)", K, ldx);
   if (((uintptr_t)X | (uintptr_t)W) & 15) return cima_fail(CIMA_E_ARG, "linear_skinny: X and W must be 16-byte aligned");
   if (mode == SK_SWIGLU && bias) return cima_fail(CIMA_E_ARG, "linear_skinny: the gated epilogue takes no bias");
-  if (M <= 8) return dispatch_mode<1>(mode, X, W, bias, out, M, N, K, ldx, ldo, stream);
-  if (M <= 16) return dispatch_mode<2>(mode, X, W, bias, out, M, N, K, ldx, ldo, stream);
-  if (M <= 32) return dispatch_mode<4>(mode, X, W, bias, out, M, N, K, ldx, ldo, stream);
-  return dispatch_mode<8>(mode, X, W, bias, out, M, N, K, ldx, ldo, stream);
+  return 0;
+}
+
+// X [M, K] bf16 (row stride ldx), W [N, K] bf16 (for mode 2: [2N, K], gate rows then up rows),
+// bias float32 [N] or null, out [M, N] (row stride ldo) in the dtype of the mode.
+// Accepts 1 <= M <= 64, any N, K a multiple of 8 (16-byte rows), 16-byte aligned X, W and ldx % 8 == 0.
+// ssq_out (mode 1 only, may be null): [M, ceil(N / 16)] partial sums of squares of the updated rows.
+extern "C" int cima_linear_skinny(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N,
+                                  int K, int ldx, int ldo, float* ssq_out, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  int rc = skinny_checks(X, W, bias, mode, M, N, K, ldx);
+  if (rc) return rc;
+  SkinnyNorm nm{nullptr, nullptr, nullptr, 0, 0.f, mode == SK_ACCUM ? ssq_out : nullptr};
+  if (M <= 8) return dispatch_mode<1, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
+  if (M <= 16) return dispatch_mode<2, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
+  if (M <= 32) return dispatch_mode<4, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
+  return dispatch_mode<8, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
+}
+
+// The same with RMSNorm folded in: x32 [M, K] float32 residual rows (row stride ldx), norm weight [K],
+// ssq [M, parts] partial sums of squares of those rows, eps.  At most 16 rows.
+extern "C" int cima_linear_skinny_norm(const float* x32, const float* norm_w, const float* ssq, int parts, float eps,
+                                       const void* W, const float* bias, void* out, int mode, int M, int N, int K,
+                                       int ldx, int ldo, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (M > 16) return cima_fail(CIMA_E_SIZE, "linear_skinny_norm: %d rows; the folded norm takes at most 16", M);
+  if (!x32 || !norm_w || !ssq || parts <= 0) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: the residual rows, the norm weight and the partial sums are needed");
+  if (ldx % 4 || ((uintptr_t)x32 | (uintptr_t)norm_w) & 15) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: x and the norm weight must be 16-byte aligned");
+  if (mode == SK_ACCUM) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: the accumulating epilogue reads activations, not the residual");
+  int rc = skinny_checks(W, W, bias, mode, M, N, K, 8);
+  if (rc) return rc;
+  SkinnyNorm nm{x32, norm_w, ssq, parts, eps, nullptr};
+  if (M <= 8) return dispatch_mode<1, true>(mode, nullptr, W, bias, out, M, N, K, ldx, ldo, nm, stream);
+  return dispatch_mode<2, true>(mode, nullptr, W, bias, out, M, N, K, ldx, ldo, nm, stream);
 }

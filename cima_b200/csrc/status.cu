@@ -16,4 +16,4 @@ int cima_fail(int code, const char* fmt, ...) {
 }
 
 // Version of the entry points' signatures; the Python side refuses a library that answers otherwise.
-extern "C" int cima_abi_version() { return 7; }
+extern "C" int cima_abi_version() { return 8; }

@@ -16,6 +16,7 @@ from ..cache.kv import KVCache, StateRequest
 from ..config.registry import lookup_architecture, read_config_json
 from ..config.specs import ModelSpec
 from ..parts import Linear, Runtime, build_block, build_norm
+from ..parts.linear import FOLDED_NORM_ROWS
 from ..weights.loader import TensorSpec, load_tensors
 from .batch import StepBatch, StepEntry, build_batch
 
@@ -118,19 +119,26 @@ class Model:
     def forward(self, batch: StepBatch) -> torch.Tensor:
         K_, s = self.rt.kernels, self.spec
         x = self.rt.empty(batch.n_rows, s.hidden, dtype=torch.float32)
-        K_.embed(batch.tokens, self.embedding, x, s.embed_scale)
+        # few rows on the bfloat16 path: the kernels hand the rows' sums of squares along, so that every
+        # RMSNorm is folded into the product that follows it
+        ssq = None
+        if batch.n_rows <= FOLDED_NORM_ROWS and not self.rt.full_precision:
+            ssq = self.rt.empty(batch.n_rows, 1, dtype=torch.float32)
+        K_.embed(batch.tokens, self.embedding, x, s.embed_scale, ssq)
         for site, layer in enumerate(s.schedule):
-            self.blocks[layer].forward(x, batch, self.cache, site)
-        return self.project(x, batch)
+            ssq = self.blocks[layer].forward(x, batch, self.cache, site, ssq)
+        return self.project(x, batch, ssq)
 
-    def project(self, x: torch.Tensor, batch: StepBatch) -> torch.Tensor:
+    def project(self, x: torch.Tensor, batch: StepBatch, ssq=None) -> torch.Tensor:
         """Final norm and head at the wanted rows only."""
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=self.rt.device)
         if not batch.want_all_in_order:
             picked = self.rt.empty(batch.n_want, self.spec.hidden, dtype=torch.float32)
             self.rt.kernels.gather_rows(x, batch.want_rows, picked)
-            x = picked
+            x, ssq = picked, None
+        if hasattr(self.final_norm, "lazy"):
+            return self.head.logits(self.final_norm.lazy(x, ssq))
         return self.head.logits(self.final_norm(x))
 
 

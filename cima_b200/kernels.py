@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 7
+ABI_VERSION = 8
 
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
@@ -36,14 +36,15 @@ def dtype_code(dt: torch.dtype) -> int:
 _vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
 
 _SIGNATURES = {
-    "cima_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp],
+    "cima_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp, _vp],
     "cima_rmsnorm": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "cima_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "cima_add_residual": [_vp, _vp, _i, _sz, _vp],
     "cima_gather_rows": [_vp, _vp, _vp, _i, _i, _vp],
     "cima_decode_advance": [_vp, _vp, _vp, _vp, _i, _vp],
     "cima_linear_plain": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "cima_linear_skinny": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_linear_skinny": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "cima_linear_skinny_norm": [_vp, _vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_attention_plain": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                              _f, _i, _i, _vp],
@@ -108,13 +109,19 @@ class Kernels:
             raise KernelError(f"{name} is not contiguous")
 
     # ------------------------------------------------------------------ elementwise
-    def embed(self, ids: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: float = 1.0) -> None:
+    def embed(self, ids: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: float = 1.0,
+              ssq: Optional[torch.Tensor] = None) -> None:
+        """x[t] = scale * table[ids[t]]; ``ssq`` [T, 1] (optional) receives each row's sum of squares."""
         self._need(ids, "ids", torch.int32, 1); self._need(table, "table", None, 2); self._need(x, "x", torch.float32, 2)
         T, (V, H) = ids.numel(), table.shape
         if tuple(x.shape) != (T, H):
             raise KernelError(f"embed: x is {tuple(x.shape)}, expected {(T, H)}")
+        if ssq is not None:
+            self._need(ssq, "ssq", torch.float32, 2)
+            if tuple(ssq.shape) != (T, 1):
+                raise KernelError(f"embed: ssq is {tuple(ssq.shape)}, expected {(T, 1)}")
         self._check(self.lib.cima_embed(ids.data_ptr(), table.data_ptr(), dtype_code(table.dtype), x.data_ptr(),
-                                        T, H, V, scale, self._stream()), "embed")
+                                        T, H, V, scale, _ptr(ssq), self._stream()), "embed")
 
     def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:
         self._need(x, "x", torch.float32, 2); self._need(w, "w", torch.float32, 1); self._need(out, "out", None, 2)
@@ -179,8 +186,9 @@ class Kernels:
                                                    K, N, self._stream()), "linear_plain")
 
     def linear_skinny(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                      mode: int) -> None:
-        """Few rows (<= 64), bf16 operands; ``mode`` is one of SK_*.  For SK_SWIGLU ``w`` is [2N, K]."""
+                      mode: int, ssq_out: Optional[torch.Tensor] = None) -> None:
+        """Few rows (<= 64), bf16 operands; ``mode`` is one of SK_*.  For SK_SWIGLU ``w`` is [2N, K].
+        With SK_ACCUM, ``ssq_out`` [M, ceil(N / 16)] receives partial sums of squares of the updated rows."""
         self._need(a, "a", torch.bfloat16, 2); self._need(w, "w", torch.bfloat16, 2); self._need(out, "out", None, 2)
         M, K = a.shape
         N = w.shape[0] // 2 if mode == SK_SWIGLU else w.shape[0]
@@ -192,8 +200,32 @@ class Kernels:
             self._need(bias, "bias", torch.float32, 1)
             if bias.numel() != N:
                 raise KernelError(f"linear_skinny: bias has {bias.numel()} entries, expected {N}")
+        if ssq_out is not None:
+            self._need(ssq_out, "ssq_out", torch.float32, 2)
+            if mode != SK_ACCUM or tuple(ssq_out.shape) != (M, -(-N // 16)):
+                raise KernelError(f"linear_skinny: ssq_out {tuple(ssq_out.shape)} goes with the accumulating mode and "
+                                  f"must be {(M, -(-N // 16))}")
         self._check(self.lib.cima_linear_skinny(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode,
-                                                M, N, K, K, N, self._stream()), "linear_skinny")
+                                                M, N, K, K, N, _ptr(ssq_out), self._stream()), "linear_skinny")
+
+    def linear_skinny_norm(self, x: torch.Tensor, norm_w: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tensor,
+                           bias: Optional[torch.Tensor], out: torch.Tensor, mode: int) -> None:
+        """``linear_skinny`` of RMSNorm(x): x [M, K] float32 residual rows (M <= 16), ``ssq`` [M, parts] partial
+        sums of squares of those rows (as ``embed`` or an accumulating ``linear_skinny`` left them)."""
+        self._need(x, "x", torch.float32, 2); self._need(norm_w, "norm_w", torch.float32, 1)
+        self._need(ssq, "ssq", torch.float32, 2); self._need(w, "w", torch.bfloat16, 2); self._need(out, "out", None, 2)
+        M, K = x.shape
+        N = w.shape[0] // 2 if mode == SK_SWIGLU else w.shape[0]
+        want = torch.float32 if mode == SK_STORE_F32 else torch.bfloat16
+        if (w.shape[1] != K or norm_w.numel() != K or ssq.shape[0] != M or tuple(out.shape) != (M, N)
+                or out.dtype is not want):
+            raise KernelError(f"linear_skinny_norm(mode {mode}): x {tuple(x.shape)}, w {tuple(w.shape)}, ssq "
+                              f"{tuple(ssq.shape)}, out {tuple(out.shape)} {out.dtype} do not agree")
+        if bias is not None:
+            self._need(bias, "bias", torch.float32, 1)
+        self._check(self.lib.cima_linear_skinny_norm(x.data_ptr(), norm_w.data_ptr(), ssq.data_ptr(), ssq.shape[1], eps,
+                                                     w.data_ptr(), _ptr(bias), out.data_ptr(), mode, M, N, K, K, N,
+                                                     self._stream()), "linear_skinny_norm")
 
     def gemm_tc(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int,
                 swap: Optional[bool] = None, bn: Optional[int] = None) -> None:

@@ -68,7 +68,9 @@ class Attention:
         return [KVRequest(self.spec.n_kv_heads, self.spec.head_dim, self.spec.window)]
 
     # ------------------------------------------------------------------ step
-    def forward(self, h: torch.Tensor, x: torch.Tensor, batch, cache, site: int) -> None:
+    takes_pending_norm = True      # h may be a NormedInput: the q/k/v product folds the norm in when it can
+
+    def forward(self, h, x: torch.Tensor, batch, cache, site: int):
         s, K_ = self.spec, self.rt.kernels
         kv = cache.layer_kv(site)
         writes = s.cache_from is None
@@ -78,7 +80,7 @@ class Attention:
         att = self.rt.empty(h.shape[0], self.qd)
         from_cache = (not batch.prefill) or not writes
         K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, from_cache)
-        self.out.accumulate(att, x)
+        return self.out.accumulate(att, x)
 
 
 register_mixer("attention", Attention)

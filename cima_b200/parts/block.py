@@ -3,7 +3,7 @@
 registries; it does not know which kinds they are, nor which model it is in.
 
 Interface of the parts it holds:
-  norm(x) -> h                      mixer.forward(h, x, batch, cache, site)   (adds into x)
+  norm(x) -> h, norm.lazy(x, ssq)   mixer.forward(h, x, batch, cache, site)   (adds into x)
   feed_forward.forward(h, x, batch) (adds into x)
 """
 from __future__ import annotations
@@ -46,9 +46,19 @@ class PreNormBlock:
     def nbytes(self) -> int:
         return self.mixer_norm.nbytes() + self.mixer.nbytes() + self.ffn_norm.nbytes() + self.feed_forward.nbytes()
 
-    def forward(self, x: torch.Tensor, batch, cache, site: int) -> None:
-        self.mixer.forward(self.mixer_norm(x), x, batch, cache, site)
-        self.feed_forward.forward(self.ffn_norm(x), x, batch)
+    def forward(self, x: torch.Tensor, batch, cache, site: int, ssq=None):
+        """``ssq``: partial sums of squares of x's rows if the kernel that last wrote x left them (else
+        None); the same for the rows as this block leaves them is returned.  A part that declares
+        ``takes_pending_norm`` gets the norm as a ``NormedInput`` and may fold it into its first product;
+        any other part gets the normalised tensor.  A part that returns nothing invalidates the sums."""
+        ssq = self.mixer.forward(self._normed(self.mixer_norm, self.mixer, x, ssq), x, batch, cache, site)
+        return self.feed_forward.forward(self._normed(self.ffn_norm, self.feed_forward, x, ssq), x, batch)
+
+    @staticmethod
+    def _normed(norm, part, x, ssq):
+        if getattr(part, "takes_pending_norm", False) and hasattr(norm, "lazy"):
+            return norm.lazy(x, ssq)
+        return norm(x)
 
 
 register_block("prenorm", PreNormBlock)

@@ -38,12 +38,19 @@ class GatedMLP:
     def nbytes(self) -> int:
         return self.gate_up.nbytes() + self.down.nbytes()
 
-    def forward(self, h: torch.Tensor, x: torch.Tensor, batch) -> None:
+    takes_pending_norm = True
+
+    def forward(self, h, x: torch.Tensor, batch):
         rows = h.shape[0]
         chunk = max(64, _SCRATCH_ELEMS // (2 * self.spec.intermediate))
+        if rows <= chunk:
+            return self.down.accumulate(self.gate_up.activated(h), x)
+        if hasattr(h, "tensor"):
+            h = h.tensor()
         for r0 in range(0, rows, chunk):
             r1 = min(rows, r0 + chunk)
             self.down.accumulate(self.gate_up.activated(h[r0:r1]), x[r0:r1])
+        return None
 
 
 register_feed_forward("gated_mlp", GatedMLP)

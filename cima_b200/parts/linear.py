@@ -15,6 +15,7 @@ import torch
 
 from ..kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
 
+FOLDED_NORM_ROWS = 16    # most rows of the skinny kernel's folded RMSNorm
 SKINNY_ROWS = 8          # measured on B200: above 8 rows the library product streams the weights faster
 
 
@@ -38,14 +39,24 @@ class Linear:
         return n + (self.bias.numel() * 4 if self.bias is not None else 0)
 
     # ------------------------------------------------------------------ products
-    def store(self, a: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """a W^T + bias in the activation dtype."""
+    def _folds(self, a, rows: int) -> bool:
+        """Whether ``a`` is a pending RMSNorm that the skinny kernel can fold in."""
+        return (hasattr(a, "tensor") and a.ssq is not None and self._skinny(rows) and rows <= FOLDED_NORM_ROWS
+                and a.norm.spec.kind == "rmsnorm")
+
+    def store(self, a, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """a W^T + bias in the activation dtype (``a``: activations, or a pending norm)."""
         K_ = self.rt.kernels
         M = a.shape[0]
         if out is None:
             out = self.rt.empty(M, self.N)
         if M == 0:
             return out
+        if self._folds(a, M):
+            K_.linear_skinny_norm(a.x, a.norm.weight, a.ssq, a.norm.spec.eps, self.weight, self.bias, out, SK_STORE)
+            return out
+        if hasattr(a, "tensor"):
+            a = a.tensor()
         if self._plain():
             K_.linear_plain(a, self.weight, self.bias, out)
         elif self._skinny(M):
@@ -59,26 +70,35 @@ class Linear:
                 torch.mm(a, self.weight.t(), out=out)
         return out
 
-    def accumulate(self, a: torch.Tensor, x: torch.Tensor) -> None:
-        """x += a W^T (+ bias), x being the float32 residual stream."""
+    def accumulate(self, a: torch.Tensor, x: torch.Tensor):
+        """x += a W^T (+ bias), x being the float32 residual stream.  Returns the partial sums of squares
+        of the updated rows when the kernel left them (for a norm folded into the next product), else None."""
         K_ = self.rt.kernels
         M = a.shape[0]
         if M == 0:
-            return
+            return None
         if self._plain():
             K_.linear_plain(a, self.weight, self.bias, x, accumulate=True)
         elif self._skinny(M):
-            K_.linear_skinny(a, self.weight, self.bias, x, SK_ACCUM)
+            ssq = self.rt.empty(M, -(-self.N // 16), dtype=torch.float32) if M <= FOLDED_NORM_ROWS else None
+            K_.linear_skinny(a, self.weight, self.bias, x, SK_ACCUM, ssq)
+            return ssq
         else:
             K_.add_residual(x, self.store(a))
+        return None
 
-    def logits(self, a: torch.Tensor) -> torch.Tensor:
+    def logits(self, a) -> torch.Tensor:
         """a W^T + bias in float32 whatever the path (the head)."""
         K_ = self.rt.kernels
         M = a.shape[0]
         out = self.rt.empty(M, self.N, dtype=torch.float32)
         if M == 0:
             return out
+        if self._folds(a, M):
+            K_.linear_skinny_norm(a.x, a.norm.weight, a.ssq, a.norm.spec.eps, self.weight, self.bias, out, SK_STORE_F32)
+            return out
+        if hasattr(a, "tensor"):
+            a = a.tensor()
         if self._plain() or self.K % 8:
             K_.linear_plain(a, self.weight, self.bias, out)
         else:
@@ -104,13 +124,18 @@ class GatedLinearPair:
     def nbytes(self) -> int:
         return self.lin.nbytes()
 
-    def activated(self, a: torch.Tensor) -> torch.Tensor:
+    def activated(self, a) -> torch.Tensor:
         """silu(a Wg^T) * (a Wu^T) in the activation dtype, [M, I]."""
         K_ = self.rt.kernels
         M = a.shape[0]
         out = self.rt.empty(M, self.I)
         if M == 0:
             return out
+        if self.lin._folds(a, M):
+            K_.linear_skinny_norm(a.x, a.norm.weight, a.ssq, a.norm.spec.eps, self.lin.weight, None, out, SK_SWIGLU)
+            return out
+        if hasattr(a, "tensor"):
+            a = a.tensor()
         if self.lin._skinny(M):
             K_.linear_skinny(a, self.lin.weight, None, out, SK_SWIGLU)
         else:

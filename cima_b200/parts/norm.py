@@ -10,6 +10,25 @@ from ..weights.loader import TensorSpec
 from .registry import register_norm
 
 
+class NormedInput:
+    """RMSNorm(x) not yet computed.  A product that can fold the norm in (few rows, bf16) takes ``x``,
+    the norm's weight and ``ssq`` (partial sums of squares of x's rows, left by the kernel that wrote
+    them) directly; everything else calls ``tensor()`` and gets the normalised activations."""
+
+    def __init__(self, norm: "RMSNorm", x: torch.Tensor, ssq):
+        self.norm, self.x, self.ssq = norm, x, ssq
+        self._h = None
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+    def tensor(self) -> torch.Tensor:
+        if self._h is None:
+            self._h = self.norm(self.x)
+        return self._h
+
+
 class RMSNorm:
     def __init__(self, spec, rt):
         self.spec, self.rt = spec, rt
@@ -23,6 +42,9 @@ class RMSNorm:
 
     def nbytes(self) -> int:
         return self.weight.numel() * 4
+
+    def lazy(self, x: torch.Tensor, ssq=None) -> NormedInput:
+        return NormedInput(self, x, ssq)
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         out = self.rt.empty(*x.shape)

@@ -34,8 +34,10 @@ class ReferenceKernels:
         self.launches = 0
 
     # ------------------------------------------------------------------ elementwise
-    def embed(self, ids, table, x, scale=1.0):
+    def embed(self, ids, table, x, scale=1.0, ssq=None):
         x.copy_(table[ids.long()].float() * scale)
+        if ssq is not None:
+            ssq.copy_((x.double() ** 2).sum(dim=1, keepdim=True).float())
 
     def rmsnorm(self, x, w, eps, out):
         xc = x.to(self.compute)
@@ -68,7 +70,12 @@ class ReferenceKernels:
         else:
             out.copy_(y.to(out.dtype))
 
-    def linear_skinny(self, a, w, bias, out, mode):
+    def linear_skinny_norm(self, x, norm_w, ssq, eps, w, bias, out, mode):
+        inv = 1.0 / torch.sqrt(ssq.to(self.compute).sum(dim=1, keepdim=True) / x.shape[1] + eps)
+        h = (x.to(self.compute) * inv * norm_w.to(self.compute)).to(torch.bfloat16)
+        self.linear_skinny(h, w, bias, out, mode)
+
+    def linear_skinny(self, a, w, bias, out, mode, ssq_out=None):
         y = a.to(self.compute) @ w.to(self.compute).t()
         if mode == SK_SWIGLU:
             I = w.shape[0] // 2
@@ -79,6 +86,11 @@ class ReferenceKernels:
             y = y + bias.to(self.compute)
         if mode == SK_ACCUM:
             out.add_(y.to(out.dtype))
+            if ssq_out is not None:
+                N = out.shape[1]
+                sq = torch.zeros(out.shape[0], ssq_out.shape[1] * 16, dtype=torch.float64)
+                sq[:, :N] = out.double() ** 2
+                ssq_out.copy_(sq.view(out.shape[0], -1, 16).sum(dim=2).float())
         else:
             out.copy_(y.to(out.dtype))
 

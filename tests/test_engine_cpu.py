@@ -33,3 +33,17 @@ def test_unequal_batches_reuse_slots():
             assert torch.allclose(g, plain_forward(W, cfg, q).float(), atol=2e-4, rtol=1e-4)
         model.cache.check()
         assert model.cache.slots.held == 0
+
+
+def test_bfloat16_plumbing_with_folded_norms():
+    """The bfloat16 path's host logic (pending norms handed to the products, sums of squares handed on)
+    on the stand-in kernels: one-by-one decoding agrees with whole prompts and with the plain logits."""
+    name = "B"
+    cfg, W = plain_load(model_folder(name))
+    model = cpu_model(name, dtype="bfloat16", max_tokens=512)
+    toks = random_tokens(cfg["vocab_size"], 40, seed=4)
+    want = plain_forward(W, cfg, toks).float()
+    whole = run_whole(model, toks)
+    tail = run_tail_one_by_one(model, toks, 20)
+    assert (whole - want).abs().max().item() <= 2e-2
+    assert (tail - want).abs().max().item() <= 2e-2
