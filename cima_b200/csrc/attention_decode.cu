@@ -59,6 +59,7 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
                    CimaPaged pg, const int* __restrict__ seq_slot, const int* __restrict__ seq_len,
                    float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int ldo,
                    int nh, int nkv, int mtiles, float scale, int window, int n_splits) {
+  cima_pdl_wait();
   constexpr int ROW = HD + 8;                         // padded row of a tile, in elements (16 bytes of padding)
   constexpr int TILE = PS * ROW;                      // elements of one K or V tile
   constexpr int KSTEPS = HD / 16, NTILES = HD / 8;
@@ -196,6 +197,7 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   }
   cp_async_wait<0>();
   __syncthreads();
+  cima_pdl_trigger();
 
   // merge the 4 warps (fixed order) through shared memory, reusing the tiles' space
   float* so = reinterpret_cast<float*>(smem_raw);      // [WARPS][16][HD]
@@ -243,6 +245,7 @@ constexpr int MAX_SPLITS = 64;
 __global__ void __launch_bounds__(128)
 k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                     __nv_bfloat16* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
+  cima_pdl_wait();
   __shared__ float w[MAX_SPLITS];
   __shared__ float s_inv;
   const int b = blockIdx.y, h = blockIdx.x;
@@ -301,12 +304,12 @@ int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, cons
   }
   const int G = nh / nkv, mtiles = (G + 15) / 16;
   dim3 grid(n_splits, nkv * mtiles, B);
-  kern<<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)qkv, ld, (const __nv_bfloat16*)cache, pg, seq_slot,
+  { int rc_ = cima_launch(kern, dim3(grid), dim3(WARPS * 32), (size_t)(smem), stream, 1, (const __nv_bfloat16*)qkv, ld, (const __nv_bfloat16*)cache, pg, seq_slot,
                                            seq_len, part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, nkv, mtiles, scale,
-                                           window, n_splits);
+                                           window, n_splits); if (rc_) return rc_; }
   int rc = cima_launch_result();
   if (rc || n_splits == 1) return rc;
-  k_attention_combine<<<dim3(nh, B), 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, HD, n_splits);
+  { int rc_ = cima_launch(k_attention_combine, dim3(dim3(nh, B)), dim3(128), (size_t)(0), stream, 1, part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, HD, n_splits); if (rc_) return rc_; }
   return cima_launch_result();
 }
 

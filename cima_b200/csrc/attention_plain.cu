@@ -15,6 +15,7 @@ k_attention_plain(const TA* __restrict__ qkv, int ld, const TA* __restrict__ cac
                   const int* __restrict__ row_pos, const int* __restrict__ row_seq,
                   const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
                   TA* __restrict__ out, int ldo, int T, int nh, int nkv, int hd, float scale, int window) {
+  cima_pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = blockIdx.x * (blockDim.x >> 5) + warp;
   const int h = blockIdx.y;
@@ -86,10 +87,10 @@ extern "C" int cima_attention_plain(const void* qkv, int dtype, int ld, const vo
   if (from_cache && (!cache || !table)) return cima_fail(CIMA_E_ARG, "attention_plain: decoding needs the cache and its block table");
   CimaPaged pg{table, table_width, ring, page_size, nkv, hd};
   dim3 grid((T + 3) / 4, nh);
-#define LAUNCH(TA, FC) k_attention_plain<TA, FC><<<grid, 128, 0, stream>>>((const TA*)qkv, ld, (const TA*)cache, pg, \
-    row_pos, row_seq, seq_slot, seq_first_row, (TA*)out, ldo, T, nh, nkv, hd, scale, window)
-  if (dtype == CIMA_F32) { if (from_cache) LAUNCH(float, true); else LAUNCH(float, false); }
-  else if (dtype == CIMA_BF16) { if (from_cache) LAUNCH(__nv_bfloat16, true); else LAUNCH(__nv_bfloat16, false); }
+#define LAUNCH(TA, FC) { int rc_ = cima_launch(k_attention_plain<TA, FC>, dim3(grid), dim3(128), (size_t)(0), stream, 1, (const TA*)qkv, ld, (const TA*)cache, pg, \
+    row_pos, row_seq, seq_slot, seq_first_row, (TA*)out, ldo, T, nh, nkv, hd, scale, window); if (rc_) return rc_; }
+  if (dtype == CIMA_F32) { if (from_cache) LAUNCH(float, true) else LAUNCH(float, false) }
+  else if (dtype == CIMA_BF16) { if (from_cache) LAUNCH(__nv_bfloat16, true) else LAUNCH(__nv_bfloat16, false) }
   else return cima_fail(CIMA_E_DTYPE, "attention_plain: dtype code %d is neither float32 nor bfloat16", dtype);
 #undef LAUNCH
   return cima_launch_result();

@@ -53,6 +53,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ tile_seq,
                     const int* __restrict__ tile_row0, const int* __restrict__ seq_first_row,
                     __nv_bfloat16* __restrict__ out, int ldo, int T, int nh, int nkv, float scale, int window) {
+  cima_pdl_wait();
   constexpr int ROW = HD + 8;
   constexpr int TILE = BN * ROW;
   constexpr int KSTEPS = HD / 16, NTILES = HD / 8, CPR = HD / 8;
@@ -219,8 +220,8 @@ int launch_prefill(const void* qkv, int ld, const int* tile_seq, const int* tile
     if (e != cudaSuccess) return cima_fail((int)e, "attention_prefill: cannot raise shared memory to %zu bytes: %s", smem, cudaGetErrorString(e));
     raised = true;
   }
-  kern<<<dim3(n_tiles, nh), WARPS * 32, smem, stream>>>((const __nv_bfloat16*)qkv, ld, tile_seq, tile_row0, seq_first_row,
-                                                        (__nv_bfloat16*)out, ldo, T, nh, nkv, scale, window);
+  { int rc_ = cima_launch(kern, dim3(dim3(n_tiles, nh)), dim3(WARPS * 32), (size_t)(smem), stream, 1, (const __nv_bfloat16*)qkv, ld, tile_seq, tile_row0, seq_first_row,
+                                                        (__nv_bfloat16*)out, ldo, T, nh, nkv, scale, window); if (rc_) return rc_; }
   return cima_launch_result();
 }
 

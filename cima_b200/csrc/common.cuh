@@ -15,6 +15,17 @@ enum { CIMA_E_ARG = -1, CIMA_E_DTYPE = -2, CIMA_E_SIZE = -3 };
 extern "C" const char* cima_last_error();
 int cima_fail(int code, const char* fmt, ...);
 
+// Programmatic dependent launch.  Every kernel of this library starts with cima_pdl_wait(), which
+// returns once the kernels before it in the stream have completed and their writes are visible.
+// The long kernels call cima_pdl_trigger() when their main loop is over: from then on the next
+// kernel may be scheduled into the space that this one's finishing blocks leave, and sits in its
+// own wait until this one is done, so its launch latency hides behind this one's tail.  (A trigger
+// at the top of a kernel would let a whole chain of waiting kernels crowd out the running one.)
+// Launched without the attribute, both are no-ops.
+__device__ __forceinline__ void cima_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void cima_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+bool cima_pdl_enabled();      // false when the environment has CIMA_NO_PDL=1
+
 static inline int cima_launch_result() {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cima_fail((int)e, "CUDA launch failed: %s", cudaGetErrorString(e));
@@ -70,3 +81,34 @@ struct CimaPaged {
     return ((((size_t)page * 2 + kv) * kv_heads + head) * page_size + (pos % page_size)) * (size_t)head_dim;
   }
 };
+
+// One launch path for all kernels: programmatic stream serialisation (see above) and, for cluster_x > 1,
+// thread-block clusters of that many blocks along x.
+template <typename... KArgs, typename... Args>
+static inline int cima_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              int cluster_x, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cima_pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    n++;
+  }
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    n++;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) return cima_fail((int)e, "CUDA launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}

@@ -11,6 +11,7 @@
 template <typename TW>
 __global__ void k_embed(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ x,
                         int H, int V, float scale, float* __restrict__ ssq) {
+  cima_pdl_wait();
   __shared__ float red[32];
   const int row = blockIdx.x;
   int id = ids[row];
@@ -34,8 +35,8 @@ extern "C" int cima_embed(const int* ids, const void* table, int table_dtype, fl
                           float scale, float* ssq, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || V <= 0) return cima_fail(CIMA_E_SIZE, "embed: hidden %d and vocab %d must be positive", H, V);
-  if (table_dtype == CIMA_F32) k_embed<float><<<T, 256, 0, stream>>>(ids, (const float*)table, x, H, V, scale, ssq);
-  else if (table_dtype == CIMA_BF16) k_embed<__nv_bfloat16><<<T, 256, 0, stream>>>(ids, (const __nv_bfloat16*)table, x, H, V, scale, ssq);
+  if (table_dtype == CIMA_F32) { int rc_ = cima_launch(k_embed<float>, dim3(T), dim3(256), (size_t)(0), stream, 1, ids, (const float*)table, x, H, V, scale, ssq); if (rc_) return rc_; }
+  else if (table_dtype == CIMA_BF16) { int rc_ = cima_launch(k_embed<__nv_bfloat16>, dim3(T), dim3(256), (size_t)(0), stream, 1, ids, (const __nv_bfloat16*)table, x, H, V, scale, ssq); if (rc_) return rc_; }
   else return cima_fail(CIMA_E_DTYPE, "embed: table dtype code %d is neither float32 nor bfloat16", table_dtype);
   return cima_launch_result();
 }
@@ -46,6 +47,7 @@ extern "C" int cima_embed(const int* ids, const void* table, int table_dtype, fl
 template <typename TO>
 __global__ void k_rmsnorm(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ y,
                           int H, float eps) {
+  cima_pdl_wait();
   __shared__ float red[32];
   const float* xi = x + (size_t)blockIdx.x * H;
   TO* yo = y + (size_t)blockIdx.x * H;
@@ -60,8 +62,8 @@ extern "C" int cima_rmsnorm(const float* x, const float* w, void* y, int y_dtype
                             cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0) return cima_fail(CIMA_E_SIZE, "rmsnorm: width %d must be positive", H);
-  if (y_dtype == CIMA_F32) k_rmsnorm<float><<<T, 256, 0, stream>>>(x, w, (float*)y, H, eps);
-  else if (y_dtype == CIMA_BF16) k_rmsnorm<__nv_bfloat16><<<T, 256, 0, stream>>>(x, w, (__nv_bfloat16*)y, H, eps);
+  if (y_dtype == CIMA_F32) { int rc_ = cima_launch(k_rmsnorm<float>, dim3(T), dim3(256), (size_t)(0), stream, 1, x, w, (float*)y, H, eps); if (rc_) return rc_; }
+  else if (y_dtype == CIMA_BF16) { int rc_ = cima_launch(k_rmsnorm<__nv_bfloat16>, dim3(T), dim3(256), (size_t)(0), stream, 1, x, w, (__nv_bfloat16*)y, H, eps); if (rc_) return rc_; }
   else return cima_fail(CIMA_E_DTYPE, "rmsnorm: output dtype code %d is neither float32 nor bfloat16", y_dtype);
   return cima_launch_result();
 }
@@ -70,6 +72,7 @@ extern "C" int cima_rmsnorm(const float* x, const float* w, void* y, int y_dtype
 // gu is [T, 2I] with the gate in columns [0, I) and the up projection in [I, 2I).
 template <typename TA>
 __global__ void k_swiglu(const TA* __restrict__ gu, TA* __restrict__ a, size_t total, int I) {
+  cima_pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / I;
     const int c = (int)(idx - row * I);
@@ -84,8 +87,8 @@ extern "C" int cima_swiglu(const void* gu, void* a, int dtype, int T, int I, cud
   if (I <= 0) return cima_fail(CIMA_E_SIZE, "swiglu: intermediate width %d must be positive", I);
   const size_t total = (size_t)T * I;
   const int grid = (int)((total + 255) / 256 > 148 * 32 ? 148 * 32 : (total + 255) / 256);
-  if (dtype == CIMA_F32) k_swiglu<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)a, total, I);
-  else if (dtype == CIMA_BF16) k_swiglu<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)a, total, I);
+  if (dtype == CIMA_F32) { int rc_ = cima_launch(k_swiglu<float>, dim3(grid), dim3(256), (size_t)(0), stream, 1, (const float*)gu, (float*)a, total, I); if (rc_) return rc_; }
+  else if (dtype == CIMA_BF16) { int rc_ = cima_launch(k_swiglu<__nv_bfloat16>, dim3(grid), dim3(256), (size_t)(0), stream, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)a, total, I); if (rc_) return rc_; }
   else return cima_fail(CIMA_E_DTYPE, "swiglu: dtype code %d is neither float32 nor bfloat16", dtype);
   return cima_launch_result();
 }
@@ -93,6 +96,7 @@ extern "C" int cima_swiglu(const void* gu, void* a, int dtype, int T, int I, cud
 // ---------------------------------------------------------------- residual: x += d  (sum in float32)
 template <typename TA>
 __global__ void k_add_residual(float* __restrict__ x, const TA* __restrict__ d, size_t total) {
+  cima_pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
     x[idx] += cima_to_f32<TA>(d[idx]);
 }
@@ -100,14 +104,15 @@ __global__ void k_add_residual(float* __restrict__ x, const TA* __restrict__ d, 
 extern "C" int cima_add_residual(float* x, const void* d, int d_dtype, size_t total, cudaStream_t stream) {
   if (total == 0) return 0;
   const int grid = (int)((total + 255) / 256 > 148 * 32 ? 148 * 32 : (total + 255) / 256);
-  if (d_dtype == CIMA_F32) k_add_residual<float><<<grid, 256, 0, stream>>>(x, (const float*)d, total);
-  else if (d_dtype == CIMA_BF16) k_add_residual<__nv_bfloat16><<<grid, 256, 0, stream>>>(x, (const __nv_bfloat16*)d, total);
+  if (d_dtype == CIMA_F32) { int rc_ = cima_launch(k_add_residual<float>, dim3(grid), dim3(256), (size_t)(0), stream, 1, x, (const float*)d, total); if (rc_) return rc_; }
+  else if (d_dtype == CIMA_BF16) { int rc_ = cima_launch(k_add_residual<__nv_bfloat16>, dim3(grid), dim3(256), (size_t)(0), stream, 1, x, (const __nv_bfloat16*)d, total); if (rc_) return rc_; }
   else return cima_fail(CIMA_E_DTYPE, "add_residual: dtype code %d is neither float32 nor bfloat16", d_dtype);
   return cima_launch_result();
 }
 
 // ---------------------------------------------------------------- row gather: out[i,:] = x[rows[i],:]
 __global__ void k_gather_rows(const float* __restrict__ x, const int* __restrict__ rows, float* __restrict__ out, int H) {
+  cima_pdl_wait();
   const float* src = x + (size_t)rows[blockIdx.x] * H;
   float* dst = out + (size_t)blockIdx.x * H;
   for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
@@ -115,7 +120,7 @@ __global__ void k_gather_rows(const float* __restrict__ x, const int* __restrict
 
 extern "C" int cima_gather_rows(const float* x, const int* rows, float* out, int n, int H, cudaStream_t stream) {
   if (n <= 0) return 0;
-  k_gather_rows<<<n, 256, 0, stream>>>(x, rows, out, H);
+  { int rc_ = cima_launch(k_gather_rows, dim3(n), dim3(256), (size_t)(0), stream, 1, x, rows, out, H); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
@@ -125,6 +130,7 @@ extern "C" int cima_gather_rows(const float* x, const int* rows, float* out, int
 // captured step the same way: k_argmax_extract and k_pos_bump, src/kernels.cu:309-318).
 __global__ void k_decode_advance(const int* __restrict__ chosen, int* __restrict__ tokens, int* __restrict__ row_pos,
                                  int* __restrict__ seq_len, int B) {
+  cima_pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < B) {
     tokens[i] = chosen[i];
@@ -135,6 +141,6 @@ __global__ void k_decode_advance(const int* __restrict__ chosen, int* __restrict
 
 extern "C" int cima_decode_advance(const int* chosen, int* tokens, int* row_pos, int* seq_len, int B, cudaStream_t stream) {
   if (B <= 0) return 0;
-  k_decode_advance<<<(B + 127) / 128, 128, 0, stream>>>(chosen, tokens, row_pos, seq_len, B);
+  { int rc_ = cima_launch(k_decode_advance, dim3((B + 127) / 128), dim3(128), (size_t)(0), stream, 1, chosen, tokens, row_pos, seq_len, B); if (rc_) return rc_; }
   return cima_launch_result();
 }

@@ -141,6 +141,7 @@ struct GemmArgs {
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 k_gemm_tcgen05(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmArgs a) {
+  cima_pdl_wait();
   constexpr int P_BYTES = BM * BK * 2, Q_BYTES = BN * BK * 2;
   constexpr int QH = EPI == EPI_SWIGLU ? BN / 2 : BN;          // rows of Q per TMA box
   extern __shared__ unsigned char smem_raw[];
@@ -295,7 +296,7 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, int 
     raised = true;
   }
   dim3 grid(tiles_q, (a.p_rows + BM - 1) / BM);
-  kern<<<grid, THREADS, smem, stream>>>(mp, mq, a);
+  { int rc_ = cima_launch(kern, dim3(grid), dim3(THREADS), (size_t)(smem), stream, 1, mp, mq, a); if (rc_) return rc_; }
   return cima_launch_result();
 }
 

@@ -14,6 +14,7 @@ template <typename TA, typename TW, typename TO, int MODE>
 __global__ void __launch_bounds__(256)
 k_linear_plain(const TA* __restrict__ A, const TW* __restrict__ W, const float* __restrict__ bias,
                TO* __restrict__ out, int M, int N, int K, int lda, int ldo) {
+  cima_pdl_wait();
   constexpr int BM = 64, BN = 64, BK = 16;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
@@ -77,9 +78,9 @@ static int launch_plain(const void* A, const void* W, const float* bias, void* o
                         int lda, int ldo, cudaStream_t stream) {
   dim3 grid((N + 63) / 64, (M + 63) / 64);
   if (mode == LIN_STORE)
-    k_linear_plain<TA, TW, TO, LIN_STORE><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, bias, (TO*)out, M, N, K, lda, ldo);
+    { int rc_ = cima_launch(k_linear_plain<TA, TW, TO, LIN_STORE>, dim3(grid), dim3(256), (size_t)(0), stream, 1, (const TA*)A, (const TW*)W, bias, (TO*)out, M, N, K, lda, ldo); if (rc_) return rc_; }
   else
-    k_linear_plain<TA, TW, TO, LIN_ACCUM><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, bias, (TO*)out, M, N, K, lda, ldo);
+    { int rc_ = cima_launch(k_linear_plain<TA, TW, TO, LIN_ACCUM>, dim3(grid), dim3(256), (size_t)(0), stream, 1, (const TA*)A, (const TW*)W, bias, (TO*)out, M, N, K, lda, ldo); if (rc_) return rc_; }
   return cima_launch_result();
 }
 

@@ -84,6 +84,7 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = (blockIdx.x / S) * SK_ROWS;
+  cima_pdl_wait();
   __shared__ float inv_s[NT * 8];
   if (NORM) {
     for (int m = warp; m < M; m += SK_WARPS) {
@@ -167,6 +168,7 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
     }
   }
 
+  cima_pdl_trigger();      // the weights are read: the next kernel may be scheduled while the sums are merged
   // partial sums -> shared memory: red[warp][a][col = j*8 + 2t (+1)][row = g (+8)]
   constexpr int COLS = NT * 8;
   float* mine = red + (size_t)warp * MT * COLS * SK_PAD;
@@ -264,21 +266,9 @@ static int launch_skinny(const void* X, const void* W, const float* bias, void* 
   }
   const int tiles = (N + SK_ROWS - 1) / SK_ROWS;
   const int S = cluster_size(tiles, K);
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(tiles * S);
-  cfg.blockDim = dim3(SK_WARPS * 32);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = S;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, bias, out, M, N, K, ldx,
-                                     ldo, up_offset, nm);
-  if (e != cudaSuccess) return cima_fail((int)e, "linear_skinny: launch failed: %s", cudaGetErrorString(e));
+  int rc = cima_launch(kern, dim3(tiles * S), dim3(SK_WARPS * 32), smem, stream, S, (const __nv_bfloat16*)X,
+                       (const __nv_bfloat16*)W, bias, out, M, N, K, ldx, ldo, up_offset, nm);
+  if (rc) return rc;
   return cima_launch_result();
 }
 

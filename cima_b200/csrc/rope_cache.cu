@@ -16,6 +16,7 @@ __global__ void __launch_bounds__(256)
 k_rope_append(TA* __restrict__ qkv, int ld, const float* __restrict__ inv_freq, int rotary_dim,
               const int* __restrict__ row_pos, const int* __restrict__ row_seq, const int* __restrict__ seq_slot,
               const int* __restrict__ seq_len, TA* __restrict__ cache_in, CimaPaged pg, int nh, int nkv, int hd) {
+  cima_pdl_wait();
   __shared__ float cs[128], sn[128];
   const int row = blockIdx.x;
   const int pos = row_pos[row];
@@ -76,9 +77,9 @@ extern "C" int cima_rope_append(void* qkv, int dtype, int ld, const float* inv_f
   if (cache && (page_size <= 0 || table_width <= 0)) return cima_fail(CIMA_E_SIZE, "rope_append: page size %d and table width %d must be positive", page_size, table_width);
   CimaPaged pg{table, table_width, ring, page_size, nkv, hd};
   if (dtype == CIMA_F32)
-    k_rope_append<float><<<T, 256, 0, stream>>>((float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, hd);
+    { int rc_ = cima_launch(k_rope_append<float>, dim3(T), dim3(256), (size_t)(0), stream, 1, (float*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (float*)cache, pg, nh, nkv, hd); if (rc_) return rc_; }
   else if (dtype == CIMA_BF16)
-    k_rope_append<__nv_bfloat16><<<T, 256, 0, stream>>>((__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, hd);
+    { int rc_ = cima_launch(k_rope_append<__nv_bfloat16>, dim3(T), dim3(256), (size_t)(0), stream, 1, (__nv_bfloat16*)qkv, ld, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, (__nv_bfloat16*)cache, pg, nh, nkv, hd); if (rc_) return rc_; }
   else return cima_fail(CIMA_E_DTYPE, "rope_append: dtype code %d is neither float32 nor bfloat16", dtype);
   return cima_launch_result();
 }

@@ -30,6 +30,7 @@ __device__ __forceinline__ unsigned long long cima_block_max_u64(unsigned long l
 
 __global__ void __launch_bounds__(1024)
 k_argmax(const float* __restrict__ logits, int ld, int V, int* __restrict__ tokens) {
+  cima_pdl_wait();
   __shared__ unsigned long long red[32];
   const float* x = logits + (size_t)blockIdx.x * ld;
   unsigned long long best = 0ULL;
@@ -44,7 +45,7 @@ k_argmax(const float* __restrict__ logits, int ld, int V, int* __restrict__ toke
 extern "C" int cima_argmax(const float* logits, int ld, int n, int V, int* tokens, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (V <= 0 || ld < V) return cima_fail(CIMA_E_SIZE, "argmax: vocabulary %d must be positive and fit the row stride %d", V, ld);
-  k_argmax<<<n, 1024, 0, stream>>>(logits, ld, V, tokens);
+  { int rc_ = cima_launch(k_argmax, dim3(n), dim3(1024), (size_t)(0), stream, 1, logits, ld, V, tokens); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
@@ -100,6 +101,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 k_sample(const float* __restrict__ logits, int ld, int V, const int* __restrict__ row_slot,
          const float* __restrict__ params, unsigned long long* __restrict__ rng, int* __restrict__ ring,
          int* __restrict__ ring_count, float* __restrict__ work, int* __restrict__ tokens) {
+  cima_pdl_wait();
   __shared__ float redf[32];
   __shared__ unsigned long long redk[32];
   __shared__ float s_u;
@@ -212,6 +214,6 @@ extern "C" int cima_sample(const float* logits, int ld, int n, int V, const int*
   if (n <= 0) return 0;
   if (V <= 0 || ld < V) return cima_fail(CIMA_E_SIZE, "sample: vocabulary %d must be positive and fit the row stride %d", V, ld);
   if (V >= (1 << 24)) return cima_fail(CIMA_E_SIZE, "sample: vocabulary %d exceeds 2^24 (counts are summed in float32)", V);
-  k_sample<<<n, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, row_slot, params, rng, ring, ring_count, work, tokens);
+  { int rc_ = cima_launch(k_sample, dim3(n), dim3(SAMPLE_THREADS), (size_t)(0), stream, 1, logits, ld, V, row_slot, params, rng, ring, ring_count, work, tokens); if (rc_) return rc_; }
   return cima_launch_result();
 }

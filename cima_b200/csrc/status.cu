@@ -2,6 +2,8 @@
 #include "common.cuh"
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
 
 static thread_local char g_err[512] = "";
 
@@ -16,4 +18,13 @@ int cima_fail(int code, const char* fmt, ...) {
 }
 
 // Version of the entry points' signatures; the Python side refuses a library that answers otherwise.
-extern "C" int cima_abi_version() { return 8; }
+extern "C" int cima_abi_version() { return 9; }
+
+bool cima_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* v = getenv("CIMA_NO_PDL");
+    on = (v && strcmp(v, "1") == 0) ? 0 : 1;
+  }
+  return on == 1;
+}

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 8
+ABI_VERSION = 9
 
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
