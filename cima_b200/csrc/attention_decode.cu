@@ -160,7 +160,7 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       const float mnew = fmaxf(m_run[r], mx[r]);
       msafe[r] = mnew == -INFINITY ? 0.f : mnew;
-      corr[r] = expf(m_run[r] - msafe[r]);            // exp(-inf) = 0 while nothing was seen
+      corr[r] = __expf(m_run[r] - msafe[r]);            // exp(-inf) = 0 while nothing was seen
       m_run[r] = mnew;
     }
     float psum[2] = {0.f, 0.f};
@@ -168,7 +168,7 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
     for (int j = 0; j < 2; j++)
 #pragma unroll
       for (int e = 0; e < 4; e++) {
-        const float pv = expf(s[j][e] - msafe[e >> 1]);
+        const float pv = __expf(s[j][e] - msafe[e >> 1]);
         s[j][e] = pv;
         psum[e >> 1] += pv;
       }

@@ -5,7 +5,8 @@
 // One block = 64 query rows of one sequence x one head; its 4 warps own 16 rows each.  Key tiles
 // of 64 rows stream through shared memory with cp.async (two in flight).  S = Q K^T and O += P V run
 // on the tensor cores (mma.m16n8k16, bf16 in, f32 out); scores, running maximum, exponentials and
-// sums are float32; P is rounded to bfloat16 only as the operand of P V.  Key tiles wholly above the
+// sums are float32 (exponentials by ex2.approx, whose error is far below the bfloat16 rounding of P);
+// P is rounded to bfloat16 only as the operand of P V.  Key tiles wholly above the
 // diagonal or wholly below the window are skipped.  The list of (sequence, first row) of the blocks
 // comes from the host, heaviest first.
 //
@@ -159,7 +160,7 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       const float mnew = fmaxf(m_run[r], mx[r]);
       msafe[r] = mnew == -INFINITY ? 0.f : mnew;
-      corr[r] = expf(m_run[r] - msafe[r]);
+      corr[r] = __expf(m_run[r] - msafe[r]);
       m_run[r] = mnew;
     }
     float psum[2] = {0.f, 0.f};
@@ -167,7 +168,7 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
     for (int j = 0; j < 8; j++)
 #pragma unroll
       for (int e = 0; e < 4; e++) {
-        const float pv = expf(s[j][e] - msafe[e >> 1]);
+        const float pv = __expf(s[j][e] - msafe[e >> 1]);
         s[j][e] = pv;
         psum[e >> 1] += pv;
       }
