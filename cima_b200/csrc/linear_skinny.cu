@@ -55,10 +55,12 @@ constexpr int SK_WARPS = 8;
 constexpr int SK_ROWS = 16;      // output features per m-tile
 constexpr int SK_PAD = 17;       // row stride of the reduction buffer (bank spread)
 
-// RMSNorm folded into the product.  The rows of X are then the float32 residual stream x; the kernel
-// normalises them on the fly, h = bf16(x * inv * w) with inv = 1 / sqrt(sum(x^2) / K + eps), where
+// RMSNorm folded into the product.  The rows of X are then the float32 residual stream x.  With
+// inv = 1 / sqrt(sum(x^2) / K + eps) a row's result is inv * sum_k bf16(x_k * w_k) W[n, k]: the norm's
+// weight is applied on the fly, the row's factor to the finished sums (so the factor is not needed
+// before the epilogue; against bf16(x * inv * w) as operand this differs by bfloat16 rounding only).
 // sum(x^2) of a row is given as `parts` partial sums that the kernel which wrote x left behind
-// (ssq [M, parts]; summed here in a fixed order).  An accumulating product in turn leaves the partial
+// (ssq [M, parts]; fetched before the K loop, summed after it in a fixed order).  An accumulating product in turn leaves the partial
 // sums of the rows it has updated (ssq_out [M, tiles], one per 16-feature tile), so that between the
 // two no separate norm kernel has to run.
 struct SkinnyNorm {
@@ -85,15 +87,19 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
   const int g = lane >> 2, t = lane & 3;
   const int n0 = (blockIdx.x / S) * SK_ROWS;
   cima_pdl_wait();
+  // Folded norm: the rows' partial sums of squares are fetched now and added up after the K loop, so
+  // that their latency hides behind the weight stream; the factor inv = 1 / sqrt(sum / K + eps) of a
+  // row is applied to its finished dot products (the operand of the tensor core is bf16(x * w)).
   __shared__ float inv_s[NT * 8];
+  constexpr int PARTS_MAX = 256;                         // partial sums per row staged in shared memory
+  __shared__ float ssq_s[NORM ? NT * 8 : 1][NORM ? PARTS_MAX : 1];
   if (NORM) {
-    for (int m = warp; m < M; m += SK_WARPS) {
-      float acc = 0.f;
-      for (int p = lane; p < nm.parts; p += 32) acc += nm.ssq[(size_t)m * nm.parts + p];
-      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (lane == 0) inv_s[m] = 1.0f / sqrtf(acc / (float)K + nm.eps);
-    }
-    __syncthreads();
+    for (int m = warp; m < M; m += SK_WARPS)
+      for (int pidx = lane; pidx < nm.parts && pidx < PARTS_MAX; pidx += 32) {
+        const unsigned dst = (unsigned)__cvta_generic_to_shared(&ssq_s[m][pidx]);
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(nm.ssq + (size_t)m * nm.parts + pidx));
+      }
+    asm volatile("cp.async.commit_group;" ::);
   }
 
   float acc[MT][NT][4];
@@ -149,11 +155,10 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
             if (NORM) {
               const float* xp = nm.x32 + (size_t)m * ldx + k;
               const float4 a0 = __ldg(reinterpret_cast<const float4*>(xp)), a1 = __ldg(reinterpret_cast<const float4*>(xp + 4));
-              const float inv = inv_s[m];
-              x.x = pack2(a0.x * inv * nw0.x, a0.y * inv * nw0.y);
-              x.y = pack2(a0.z * inv * nw0.z, a0.w * inv * nw0.w);
-              x.z = pack2(a1.x * inv * nw1.x, a1.y * inv * nw1.y);
-              x.w = pack2(a1.z * inv * nw1.z, a1.w * inv * nw1.w);
+              x.x = pack2(a0.x * nw0.x, a0.y * nw0.y);
+              x.y = pack2(a0.z * nw0.z, a0.w * nw0.w);
+              x.z = pack2(a1.x * nw1.x, a1.y * nw1.y);
+              x.w = pack2(a1.z * nw1.z, a1.w * nw1.w);
             } else {
               x = ld_cached16(X + (size_t)m * ldx + k);
             }
@@ -169,6 +174,17 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
   }
 
   cima_pdl_trigger();      // the weights are read: the next kernel may be scheduled while the sums are merged
+  if (NORM) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    for (int m = warp; m < M; m += SK_WARPS) {
+      float a = 0.f;
+      for (int pidx = lane; pidx < nm.parts; pidx += 32)
+        a += pidx < PARTS_MAX ? ssq_s[m][pidx] : nm.ssq[(size_t)m * nm.parts + pidx];
+      for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      if (lane == 0) inv_s[m] = 1.0f / sqrtf(a / (float)K + nm.eps);
+    }
+  }
   // partial sums -> shared memory: red[warp][a][col = j*8 + 2t (+1)][row = g (+8)]
   constexpr int COLS = NT * 8;
   float* mine = red + (size_t)warp * MT * COLS * SK_PAD;
@@ -225,7 +241,7 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
         float s = part[((size_t)a * COLS + m) * SK_ROWS + r];
         for (int cr = 1; cr < S; cr++)                                // the other blocks' sums, in rank order
           s += cluster.map_shared_rank(part, cr)[((size_t)a * COLS + m) * SK_ROWS + r];
-        v[a] = s;
+        v[a] = NORM ? s * inv_s[m] : s;
       }
       const size_t o = (size_t)m * ldo + n;
       if (MODE == SK_STORE) {
