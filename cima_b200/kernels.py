@@ -349,7 +349,12 @@ class Kernels:
             raise KernelError(f"attention_decode: out {tuple(out.shape)} / sequences do not fit {B} rows")
         if n_splits is None:
             mtiles = -(-(n_heads // n_kv_heads) // 16)
-            n_splits = max(1, min(32, -(-444 // (B * n_kv_heads * mtiles))))      # about three blocks per SM
+            # one wave of blocks (three of them fit an SM, 444 in all): never a second, nearly empty wave;
+            # beyond 8 splits only while the GPU would otherwise stay mostly idle (measured on B200)
+            base = B * n_kv_heads * mtiles
+            n_splits = max(1, min(32, 444 // base))
+            if n_splits > 8 and base * 8 >= 148:
+                n_splits = 8
             if max_len > 0:
                 n_splits = min(n_splits, -(-max_len // 64))
         part_o = part_ml = None
