@@ -222,14 +222,19 @@ def main(argv=None) -> int:
     if not a.no_e2e:
         prompts = [rng.integers(0, V, size=a.prompt).tolist() for _ in range(a.batch)]
         lm.generate(prompts, GenOptions(temperature=0.0, repeat_penalty=1.0, max_tokens=a.warmup, ignore_eos=True))
+        # bytes that cross per decode step: counted over the decode steps of the timed call (the stepper
+        # counts what it copies; the prefill's share is taken out by a second call that only prefills)
+        st.h2d_bytes = st.d2h_bytes = 0
+        lm.generate(prompts, GenOptions(temperature=0.0, repeat_penalty=1.0, max_tokens=1, ignore_eos=True))
+        pre_h2d, pre_d2h = st.h2d_bytes, st.d2h_bytes
         st.h2d_bytes = st.d2h_bytes = 0
         res = lm.generate(prompts, greedy)
         stats = lm.stats
         assert all(len(r.tokens) == a.steps for r in res)
         # the first token of each sequence comes from the prefill; the decode steps made the rest
         e2e = {"value": a.batch * stats.decode_steps / stats.decode_s, "unit": "tokens/s",
-               "h2d_bytes_per_step": st.h2d_bytes / max(stats.decode_steps, 1),
-               "d2h_bytes_per_step": st.d2h_bytes / max(stats.decode_steps, 1)}
+               "h2d_bytes_per_step": (st.h2d_bytes - pre_h2d) / max(stats.decode_steps, 1),
+               "d2h_bytes_per_step": (st.d2h_bytes - pre_d2h) / max(stats.decode_steps, 1)}
 
     line = {
         "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Qwen2.5-7B bf16)",

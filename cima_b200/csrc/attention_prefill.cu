@@ -50,7 +50,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 3)      // 3 blocks per SM: at most 168 registers
 k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ tile_seq,
                     const int* __restrict__ tile_row0, const int* __restrict__ seq_first_row,
                     __nv_bfloat16* __restrict__ out, int ldo, int T, int nh, int nkv, float scale, int window) {
@@ -129,14 +129,23 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
     for (int j = 0; j < 8; j++)
 #pragma unroll
       for (int e = 0; e < 4; e++) s[j][e] = 0.f;
+    // fragments of the next k-step are fetched while the tensor cores work on the current one
+    uint32_t kb[2][4][4];
+#pragma unroll
+    for (int jp = 0; jp < 4; jp++)
+      ldmatrix_x4(kb[0][jp], Kt + (jp * 16 + (lane & 7) + 8 * (lane >> 4)) * ROW + 8 * ((lane >> 3) & 1));
 #pragma unroll
     for (int kk = 0; kk < KSTEPS; kk++) {
+      const int cur = kk & 1;
+      if (kk + 1 < KSTEPS) {
 #pragma unroll
-      for (int jp = 0; jp < 4; jp++) {                // two n-tiles (16 keys) per ldmatrix
-        uint32_t kb[4];
-        ldmatrix_x4(kb, Kt + (jp * 16 + (lane & 7) + 8 * (lane >> 4)) * ROW + kk * 16 + 8 * ((lane >> 3) & 1));
-        mma_bf16(s[2 * jp], q[kk][0], q[kk][1], q[kk][2], q[kk][3], kb[0], kb[1]);
-        mma_bf16(s[2 * jp + 1], q[kk][0], q[kk][1], q[kk][2], q[kk][3], kb[2], kb[3]);
+        for (int jp = 0; jp < 4; jp++)
+          ldmatrix_x4(kb[cur ^ 1][jp], Kt + (jp * 16 + (lane & 7) + 8 * (lane >> 4)) * ROW + (kk + 1) * 16 + 8 * ((lane >> 3) & 1));
+      }
+#pragma unroll
+      for (int jp = 0; jp < 4; jp++) {
+        mma_bf16(s[2 * jp], q[kk][0], q[kk][1], q[kk][2], q[kk][3], kb[cur][jp][0], kb[cur][jp][1]);
+        mma_bf16(s[2 * jp + 1], q[kk][0], q[kk][1], q[kk][2], q[kk][3], kb[cur][jp][2], kb[cur][jp][3]);
       }
     }
     // scale and mask: key <= query position, and within the window

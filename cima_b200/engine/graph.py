@@ -54,6 +54,14 @@ class DecodeGraph:
         self.params.copy_(torch.from_numpy(params), non_blocking=False)
         self.slots = list(slots)
 
+    def feed(self, tokens: Sequence[int]) -> None:
+        """The next step's input tokens from the host (pinned memory, one small copy).  The captured step
+        has fed its own choices forward already; the host's copy is what a caller that decides the next
+        input itself (forced tokens, another sampler) relies on."""
+        h = self.meta_host.numpy()
+        h[0:self.B] = tokens
+        self.tokens.copy_(self.meta_host[0:self.B], non_blocking=True)
+
     def _step(self) -> None:
         logits = self.model.forward(self.batch)
         self.sampler.sample(logits, self.seq_slot, self.params, self.chosen, self.all_greedy)

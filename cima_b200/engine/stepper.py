@@ -68,6 +68,9 @@ class ModelStepper:
             graph.load(slots, last_tokens, [cache.length(s) for s in slots], params)
             self.h2d_bytes += 4 * (6 * len(slots) + 1) + params.nbytes
             self._armed = (key, tuple(slots))
+        elif last_tokens is not None:
+            graph.feed(last_tokens)
+            self.h2d_bytes += 4 * len(slots)
         return graph
 
     def reserve_ahead(self, slots, steps: int) -> None:

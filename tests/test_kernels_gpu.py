@@ -407,3 +407,49 @@ def test_gemm_tcgen05_modes(K, M, N, K_, bn, swap):
         gg, uu = want[:, :I], want[:, I:]
         assert err(act, gg / (1 + torch.exp(-gg)) * uu) <= TOL["bfloat16"] * 4
     assert K.device_errors() == 0
+
+
+# ---------------------------------------------------------------------------- norm folded into the skinny product
+@pytest.mark.parametrize("M", [1, 5, 8, 16])
+@pytest.mark.parametrize("N,K_", [(200, 328), (4608, 3584), (1000, 192)])
+def test_skinny_accumulate_leaves_sums_of_squares_and_the_next_product_folds_the_norm(K, M, N, K_):
+    """x += a W1^T leaves per-tile sums of squares of the updated rows; the next product takes the rows,
+    the norm's weight and those sums and must equal RMSNorm followed by the product."""
+    from cima_b200.kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
+    H = K_
+    a = g(M, N, dtype=torch.bfloat16, seed=1)
+    w1 = g(H, N, dtype=torch.bfloat16, seed=2, scale=1.0 / math.sqrt(N))
+    x0 = g(M, H, seed=3)
+    x = x0.cuda()
+    ssq = torch.full((M, -(-H // 16)), -1.0, device="cuda")
+    K.linear_skinny(a.cuda(), w1.cuda(), None, x, SK_ACCUM, ssq)
+    want_x = x0.double() + a.double() @ w1.double().t()
+    assert err(x, want_x) <= 1e-4
+    assert err(ssq.sum(dim=1), (x.double() ** 2).sum(dim=1)) <= 1e-3 * max(1.0, float((want_x ** 2).sum(dim=1).max()))
+    nw = 1 + g(H, seed=4, scale=0.1)
+    eps = 1e-5
+    xd = x.double().cpu()
+    h = (xd / torch.sqrt((xd * xd).mean(dim=1, keepdim=True) + eps) * nw.double())
+    w2 = g(2 * 96, H, dtype=torch.bfloat16, seed=5, scale=1.0 / math.sqrt(H))
+    b2 = g(2 * 96, seed=6)
+    want = h @ w2.double().t()
+    out = torch.empty(M, 192, dtype=torch.bfloat16, device="cuda")
+    K.linear_skinny_norm(x, nw.cuda(), ssq, eps, w2.cuda(), b2.cuda(), out, SK_STORE)
+    assert err(out, want + b2.double()) <= TOL["bfloat16"] * 4
+    out32 = torch.empty(M, 192, device="cuda")
+    K.linear_skinny_norm(x, nw.cuda(), ssq, eps, w2.cuda(), None, out32, SK_STORE_F32)
+    # the operand is bf16(x * w): one bfloat16 rounding per term against the float64 statement
+    assert err(out32, want) <= TOL["bfloat16"] * 2
+    act = torch.empty(M, 96, dtype=torch.bfloat16, device="cuda")
+    K.linear_skinny_norm(x, nw.cuda(), ssq, eps, w2.cuda(), None, act, SK_SWIGLU)
+    gg, uu = want[:, :96], want[:, 96:]
+    assert err(act, gg / (1 + torch.exp(-gg)) * uu) <= TOL["bfloat16"] * 4
+
+
+def test_embed_leaves_sums_of_squares(K):
+    table = g(300, 200, dtype=torch.bfloat16)
+    ids = torch.tensor([0, 299, 7], dtype=torch.int32)
+    x = torch.empty(3, 200, device="cuda")
+    ssq = torch.empty(3, 1, device="cuda")
+    K.embed(ids.cuda(), table.cuda(), x, 1.0, ssq)
+    assert err(ssq[:, 0], (table[ids.long()].double() ** 2).sum(dim=1)) <= 1e-3
