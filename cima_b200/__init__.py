@@ -25,10 +25,10 @@ __version__ = "0.1.0"
 class LM:
     """A loaded model with its cache, stepper and generation loop."""
 
-    def __init__(self, model, eos_ids: Sequence[int] = (), max_batch: int = 64):
+    def __init__(self, model, eos_ids: Sequence[int] = (), max_batch: int = 64, pipeline: bool = True):
         from .engine import GenerationLoop, ModelStepper
         self.model = model
-        self.stepper = ModelStepper(model, max_batch=max_batch)
+        self.stepper = ModelStepper(model, max_batch=max_batch, pipeline=pipeline)
         self.loop = GenerationLoop(self.stepper, eos_ids)
 
     @property
@@ -78,10 +78,12 @@ def eos_ids_of(folder: str) -> List[int]:
 
 
 def load(folder: str, dtype: str = "bfloat16", max_tokens: int = 8192, max_seqs: Optional[int] = None,
-         max_batch: int = 64, device: str = "cuda:0", verbose: bool = True) -> LM:
+         max_batch: int = 64, device: str = "cuda:0", verbose: bool = True, pipeline: bool = True) -> LM:
+    """``pipeline``: queue the next decode step before the host has read the current one's tokens
+    (the tokens are fed forward on the device)."""
     from .engine import load_model
     model = load_model(folder, dtype=dtype, max_tokens=max_tokens, max_seqs=max_seqs, device=device, verbose=verbose)
-    return LM(model, eos_ids_of(folder), max_batch=max_batch)
+    return LM(model, eos_ids_of(folder), max_batch=max_batch, pipeline=pipeline)
 
 
 def write_random_model(folder: str, config: Union[dict, Qwen2Config], seed: int = 0) -> None:

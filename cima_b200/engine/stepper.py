@@ -7,14 +7,21 @@ from typing import List, Sequence
 import numpy as np
 import torch
 
+from ..cache.pages import CacheFull
+from ..cache.kv import CapacityError
 from ..sampling.options import GenOptions
 from ..sampling.sampler import DeviceSampler
 from .batch import StepEntry
 
 
 class ModelStepper:
-    def __init__(self, model, max_batch: int = 64, use_graphs: bool = True):
+    def __init__(self, model, max_batch: int = 64, use_graphs: bool = True, pipeline: bool = True):
         self.model = model
+        self.pipeline = pipeline
+        self._flight = None           # the decode step that is queued but not yet read
+        self._inflight = {}           # slot -> steps queued beyond the committed length
+        self._pinned = [None, None]
+        self._pin_next = 0
         self.use_graphs = use_graphs and torch.device(model.rt.device).type == "cuda"
         self._graphs = {}
         self._armed = None            # (graph, slots) whose device-side inputs are those of the next step
@@ -31,10 +38,12 @@ class ModelStepper:
         return self.model.cache.open(count)
 
     def close(self, slots: Sequence[int]) -> None:
+        self._drain()
         self._armed = None
         self.model.cache.close(slots)
 
     def prefill(self, slots, prompts, options) -> List[int]:
+        self._drain()
         self._armed = None
         self.sampler.begin(slots, prompts, options)
         entries = [StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)]
@@ -44,13 +53,97 @@ class ModelStepper:
         if not self.use_graphs:
             entries = [StepEntry(s, [t], [0]) for s, t in zip(slots, last_tokens)]
             return self._choose(self.model.step(entries), slots, options, len(slots))
-        graph = self._arm(slots, last_tokens, options)
-        self.reserve_ahead(slots, 1)
+        if not self.pipeline:
+            graph = self._arm(slots, last_tokens, options)
+            self.reserve_ahead(slots, 1)
+            chosen = graph.run()
+            out = chosen.tolist()                    # the step's result crosses to the host here
+            self._advance_lengths(slots, 1)
+            self.d2h_bytes += 4 * len(slots)
+            return out
+        return self._decode_pipelined(tuple(slots), list(last_tokens), options)
+
+    # ------------------------------------------------------------------ run-ahead
+    # With ``pipeline`` the step after the one being read is already queued on the GPU (its input tokens
+    # were fed forward on the device), so the host's work between two steps (reading tokens, stop checks,
+    # bookkeeping) overlaps the GPU's.  The reference overlaps its 8-byte token fetch with the next step the
+    # same way (src/models/mod.rs:1262-1308, src/cuda.rs:2011-2021).  A step that ran ahead for a sequence
+    # that then stops has only written keys and values beyond that sequence's end.  The caller must feed
+    # back the tokens it was given (the generation loop does); one that feeds other tokens uses
+    # ``pipeline=False``.
+    def _launch(self, graph, slots):
+        """Queue one step of ``graph`` and the copy of its tokens to pinned memory; None if a sequence has
+        no room for the position the step would write."""
+        cache = self.model.cache
+        try:
+            for s in slots:
+                cache.reserve(s, cache.length(s) + self._inflight.get(s, 0) + 1)
+        except (CacheFull, CapacityError):
+            return None
+        cache.flush()
         chosen = graph.run()
-        out = chosen.tolist()                        # the step's result crosses to the host here
-        self._advance_lengths(slots, 1)
+        i = self._pin_next
+        self._pin_next ^= 1
+        if self._pinned[i] is None or self._pinned[i].numel() < len(slots):
+            self._pinned[i] = torch.empty(max(64, len(slots)), dtype=torch.int32).pin_memory()
+        view = self._pinned[i][:len(slots)]
+        view.copy_(chosen, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        for s in slots:
+            self._inflight[s] = self._inflight.get(s, 0) + 1
         self.d2h_bytes += 4 * len(slots)
-        return out
+        return {"slots": slots, "graph": graph, "tokens": view, "event": ev, "fed": None}
+
+    def _read(self, flight, commit_slots) -> List[int]:
+        flight["event"].synchronize()
+        toks = flight["tokens"].tolist()
+        cache = self.model.cache
+        for s in flight["slots"]:
+            self._inflight[s] -= 1
+        for s in commit_slots:
+            cache.commit(s, cache.length(s) + 1)
+        return toks
+
+    def _drain(self) -> None:
+        if self._flight is not None:
+            self._read(self._flight, ())
+            self._flight = None
+        self._inflight.clear()
+
+    def _decode_pipelined(self, slots, last_tokens, options) -> List[int]:
+        fl = self._flight
+        if fl is not None and fl["fed"] is not None and set(slots) <= set(fl["slots"]) and \
+                all(fl["fed"][s] == t for s, t in zip(slots, last_tokens)):
+            if fl["slots"] == slots:
+                nxt = self._launch(fl["graph"], slots)           # the step after, before this one is read
+                toks = self._read(fl, slots)
+                if nxt is not None:
+                    nxt["fed"] = dict(zip(slots, toks))
+                self._flight = nxt
+                return toks
+            # some sequences of the step in flight have ended: its tokens for the others are still theirs
+            all_toks = dict(zip(fl["slots"], self._read(fl, slots)))
+            self._flight = None
+            self._inflight.clear()
+            toks = [all_toks[s] for s in slots]
+            graph = self._arm(slots, toks, options)
+            nxt = self._launch(graph, slots)
+            if nxt is not None:
+                nxt["fed"] = dict(zip(slots, toks))
+            self._flight = nxt
+            return toks
+        self._drain()
+        graph = self._arm(slots, last_tokens, options)
+        first = self._launch(graph, slots)
+        if first is None:
+            raise CacheFull("no room for the next position of a sequence")
+        nxt = self._launch(graph, slots)
+        toks = self._read(first, slots)
+        if nxt is not None:
+            nxt["fed"] = dict(zip(slots, toks))
+        self._flight = nxt
+        return toks
 
     # ------------------------------------------------------------------ graph plumbing
     def _arm(self, slots, last_tokens, options):
@@ -87,6 +180,7 @@ class ModelStepper:
     def decode_on_device(self, slots, last_tokens, options, steps: int) -> torch.Tensor:
         """``steps`` decode steps without a host round trip between them (tokens are fed forward on
         the device); returns the last step's chosen tokens (device).  Used to time the device alone."""
+        self._drain()
         graph = self._arm(slots, last_tokens, options)
         self.reserve_ahead(slots, steps)
         for _ in range(steps):

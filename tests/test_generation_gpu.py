@@ -162,3 +162,21 @@ def test_trace_run_three_ways(tmp_path, dtype, tol):
                 assert (got[r] - want[k][start + w]).abs().max().item() <= tol, (s["step"], e["id"], start + w)
                 r += 1
             fed[e["id"]] = start + len(e["tokens"])
+
+
+def test_pipelined_and_plain_decoding_give_the_same_tokens():
+    """Run-ahead decoding (the default) against the step-by-step loop: greedy and sampled, early stops."""
+    name = "B"
+    prompts = [random_tokens(1000, n, seed=70 + n) for n in (3, 17, 40, 9, 1)]
+    outs = []
+    for pipeline in (True, False):
+        lm = cima_b200.load(model_folder(name), dtype="bfloat16", max_tokens=2048, verbose=False, pipeline=pipeline)
+        free = lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=40)
+        stops = (free[1].tokens[5], free[3].tokens[20])
+        a = lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=40, stop=stops)
+        b = lm.generate(prompts, temperature=0.9, top_k=20, top_p=0.95, repeat_penalty=1.1, seed=5, max_tokens=30)
+        c = lm.generate(prompts[:2], temperature=0, repeat_penalty=1.0, max_tokens=230)      # up to the last position
+        outs.append([[r.tokens for r in x] + [[r.finish_reason for r in x]] for x in (free, a, b, c)])
+        lm.model.cache.check()
+        assert lm.model.cache.slots.held == 0
+    assert outs[0] == outs[1]
