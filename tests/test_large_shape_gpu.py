@@ -1,0 +1,84 @@
+"""The Qwen2.5-7B layer shape (hidden 3584, 28/4 heads of 128, intermediate 18944) with two layers and a
+smaller vocabulary: the kernels at the sizes the benchmark runs them, against the plain implementation
+(float64, CPU) and against each other in every cutting."""
+import tempfile
+
+import pytest
+import torch
+
+import cima_b200
+from cima_b200.engine import load_model
+from helpers import random_tokens, run_batched, run_tail_one_by_one, run_whole
+from qwen2_plain import plain_forward, plain_load
+
+pytestmark = pytest.mark.gpu
+
+# The tiny models' bfloat16 tolerance (2e-2 on logits whose standard deviation is 0.28) as a fraction of
+# the logits' standard deviation; at this width the logits are about four times larger.
+REL_BF16 = 2e-2 / 0.28
+
+SHAPE = dict(model_type="qwen2", architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, hidden_size=3584,
+             num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944,
+             vocab_size=20008, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+             use_sliding_window=False, max_position_embeddings=4096)
+
+
+@pytest.fixture(scope="module")
+def folder():
+    d = tempfile.mkdtemp(prefix="cima_7bshape_")
+    cima_b200.write_random_model(d, SHAPE, seed=11)
+    return d
+
+
+def test_7b_layer_shape_in_every_cutting(folder):
+    cfg, W = plain_load(folder)
+    toks = random_tokens(SHAPE["vocab_size"], 100, seed=1)
+    want = plain_forward(W, cfg, toks).float()
+    m32 = load_model(folder, dtype="float32", max_tokens=4096, verbose=False)
+    whole32 = run_whole(m32, toks)
+    # sums over 3584 to 18944 float32 terms, two layers, logits of magnitude about 1
+    assert (whole32 - want).abs().max().item() <= 1e-4
+    assert torch.equal(run_tail_one_by_one(m32, toks, 32), whole32)
+    del m32
+    torch.cuda.empty_cache()
+    m16 = load_model(folder, dtype="bfloat16", max_tokens=4096, verbose=False)
+    tol = REL_BF16 * want.std().item()
+    whole16 = run_whole(m16, toks)
+    assert (whole16 - want).abs().max().item() <= tol
+    assert (run_tail_one_by_one(m16, toks, 32) - want).abs().max().item() <= tol
+    seqs = [random_tokens(SHAPE["vocab_size"], n, seed=20 + n) for n in (70, 9, 130, 31)] + [toks]
+    got = run_batched(m16, seqs, [60, 1, 100, 20, 68])
+    assert (got[4] - want).abs().max().item() <= tol
+    for q, g in zip(seqs[:2], got[:2]):
+        assert (g - plain_forward(W, cfg, q).float()).abs().max().item() <= tol
+    m16.cache.check()
+
+
+def test_long_context_decode_against_whole_prompt(folder):
+    """3,000 positions: the last 8 tokens one by one (split-KV decode attention over 47 pages) against the
+    same positions of the whole prompt (flash prefill), bfloat16; both against float32 at the end."""
+    toks = random_tokens(SHAPE["vocab_size"], 3000, seed=3)
+    m16 = load_model(folder, dtype="bfloat16", max_tokens=4096, verbose=False)
+    (slot,) = m16.cache.open(1)
+    from cima_b200.engine import StepEntry
+    try:
+        whole = m16.step([StepEntry(slot, toks, list(range(2992, 3000)))]).float().cpu()
+    finally:
+        m16.cache.close([slot])
+    (slot,) = m16.cache.open(1)
+    try:
+        m16.step([StepEntry(slot, toks[:2992], [])])
+        tail = torch.cat([m16.step([StepEntry(slot, [t], [0])]).float().cpu() for t in toks[2992:]])
+    finally:
+        m16.cache.close([slot])
+    tol = REL_BF16 * whole.std().item()
+    assert (tail - whole).abs().max().item() <= tol
+    del m16
+    torch.cuda.empty_cache()
+    m32 = load_model(folder, dtype="float32", max_tokens=4096, verbose=False)
+    (slot,) = m32.cache.open(1)
+    try:
+        ref = m32.step([StepEntry(slot, toks, list(range(2992, 3000)))]).float().cpu()
+    finally:
+        m32.cache.close([slot])
+    assert (whole - ref).abs().max().item() <= tol and (tail - ref).abs().max().item() <= tol
