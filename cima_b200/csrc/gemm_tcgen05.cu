@@ -138,37 +138,46 @@ struct GemmArgs {
   int* error_flag;
 };
 
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent: the grid has at most one block per SM; a block takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...
+// Tile t -> (t % p_tiles, t / p_tiles): the blocks that run together cover all tiles of P (few) times a few
+// tiles of Q, so a tile of Q (weights) is fetched from HBM once and shared through L2.
+// Two accumulators in tensor memory (2 x BN columns): the epilogue warps drain one while the tensor cores
+// fill the other; the ring of shared-memory stages runs on across tiles.
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
-k_gemm_tcgen05(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmArgs a) {
+k_gemm_tcgen05(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, GemmArgs a,
+               int p_tiles, int n_tiles) {
   cima_pdl_wait();
   constexpr int P_BYTES = BM * BK * 2, Q_BYTES = BN * BK * 2;
   constexpr int QH = EPI == EPI_SWIGLU ? BN / 2 : BN;          // rows of Q per TMA box
+  constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // 1024-byte tiles
   unsigned char* sp = smem;                                    // [STAGES][BM x 128 B]
   unsigned char* sq = smem + (size_t)STAGES * P_BYTES;         // [STAGES][BN x 128 B]
   unsigned long long* full = (unsigned long long*)(sq + (size_t)STAGES * Q_BYTES);
   unsigned long long* empty = full + STAGES;
-  unsigned long long* acc_done = empty + STAGES;
-  unsigned* tmem_slot = (unsigned*)(acc_done + 1);
+  unsigned long long* acc_full = empty + STAGES;               // [2] accumulator complete
+  unsigned long long* acc_free = acc_full + 2;                 // [2] accumulator drained
+  unsigned* tmem_slot = (unsigned*)(acc_free + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int p0 = blockIdx.y * BM;
-  // EPI_SWIGLU: a tile covers QH gate features and the matching QH up features
-  const int q0 = blockIdx.x * QH;
   const int kblocks = (a.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    mbar_init(acc_done, 1);
+    for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_free[b], 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN < 32 ? 32 : BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -179,16 +188,21 @@ k_gemm_tcgen05(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      for (int kb = 0; kb < kblocks; kb++) {
-        const int s = kb % STAGES;
-        if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1, a.error_flag, abort_flag)) break;
-        mbar_expect_tx(&full[s], P_BYTES + Q_BYTES);
-        tma_load_2d(sp + (size_t)s * P_BYTES, &map_p, kb * BK, p0, &full[s]);
-        if (EPI == EPI_SWIGLU) {
-          tma_load_2d(sq + (size_t)s * Q_BYTES, &map_q, kb * BK, q0, &full[s]);
-          tma_load_2d(sq + (size_t)s * Q_BYTES + QH * BK * 2, &map_q, kb * BK, a.up_offset + q0, &full[s]);
-        } else {
-          tma_load_2d(sq + (size_t)s * Q_BYTES, &map_q, kb * BK, q0, &full[s]);
+      int g = 0;                                        // k-blocks issued so far, over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int p0 = (tile % p_tiles) * BM, q0 = (tile / p_tiles) * QH;
+        for (int kb = 0; kb < kblocks; kb++, g++) {
+          const int s = g % STAGES;
+          if (g >= STAGES && !mbar_wait(&empty[s], ((g / STAGES) - 1) & 1, a.error_flag, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&full[s], P_BYTES + Q_BYTES);
+          tma_load_2d(sp + (size_t)s * P_BYTES, &map_p, kb * BK, p0, &full[s]);
+          if (EPI == EPI_SWIGLU) {
+            tma_load_2d(sq + (size_t)s * Q_BYTES, &map_q, kb * BK, q0, &full[s]);
+            tma_load_2d(sq + (size_t)s * Q_BYTES + QH * BK * 2, &map_q, kb * BK, a.up_offset + q0, &full[s]);
+          } else {
+            tma_load_2d(sq + (size_t)s * Q_BYTES, &map_q, kb * BK, q0, &full[s]);
+          }
         }
       }
     }
@@ -196,60 +210,111 @@ k_gemm_tcgen05(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     // ---------------------------------------------------------------- MMA issue (one thread)
     if (lane == 0) {
       const unsigned idesc = umma_idesc(BM, BN);
+      int g = 0, it = 0;
       bool ok = true;
-      for (int kb = 0; kb < kblocks && ok; kb++) {
-        const int s = kb % STAGES;
-        ok = mbar_wait(&full[s], (kb / STAGES) & 1, a.error_flag, abort_flag);
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, it++) {
+        const int ab = it & 1;
+        if (it >= 2) ok = mbar_wait(&acc_free[ab], ((it >> 1) - 1) & 1, a.error_flag, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const unsigned long long pd = umma_smem_desc(smem_u32(sp + (size_t)s * P_BYTES));
-        const unsigned long long qd = umma_smem_desc(smem_u32(sq + (size_t)s * Q_BYTES));
+        const unsigned acc = tmem_base + (unsigned)(ab * BN);
+        for (int kb = 0; kb < kblocks; kb++, g++) {
+          const int s = g % STAGES;
+          ok = mbar_wait(&full[s], (g / STAGES) & 1, a.error_flag, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const unsigned long long pd = umma_smem_desc(smem_u32(sp + (size_t)s * P_BYTES));
+          const unsigned long long qd = umma_smem_desc(smem_u32(sq + (size_t)s * Q_BYTES));
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; k++)           // 32 bytes further along the swizzled row per step
-          umma_bf16(tmem_base, pd + (unsigned long long)(k * 2), qd + (unsigned long long)(k * 2), idesc, (kb | k) ? 1u : 0u);
-        umma_commit(&empty[s]);                         // the stage is free when these instructions have read it
+          for (int k = 0; k < BK / UMMA_K; k++)         // 32 bytes further along the swizzled row per step
+            umma_bf16(acc, pd + (unsigned long long)(k * 2), qd + (unsigned long long)(k * 2), idesc, (kb | k) ? 1u : 0u);
+          umma_commit(&empty[s]);                       // the stage is free when these instructions have read it
+        }
+        if (ok) umma_commit(&acc_full[ab]);             // arrives when every instruction of the tile has completed
       }
-      umma_commit(acc_done);                            // arrives when every instruction above has completed
     }
   } else {
     // ---------------------------------------------------------------- epilogue: 4 warps x 32 TMEM lanes
-    const bool ok = mbar_wait(acc_done, 0, a.error_flag, abort_flag);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int quarter = warp & 3;                       // the TMEM lanes this warp may read
-    const int i = p0 + quarter * 32 + lane;             // row of P = row of the accumulator
-    if (ok) {
+    int it = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, it++) {
+      const int ab = it & 1;
+      const int p0 = (tile % p_tiles) * BM, q0 = (tile / p_tiles) * QH;
+      if (!mbar_wait(&acc_full[ab], (it >> 1) & 1, a.error_flag, abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int i = p0 + quarter * 32 + lane;           // row of P = row of the accumulator
+      const unsigned acc = tmem_base + (unsigned)(ab * BN) + ((unsigned)(quarter * 32) << 16);
       constexpr int COLS = EPI == EPI_SWIGLU ? BN / 2 : BN;
 #pragma unroll 1
       for (int c0 = 0; c0 < COLS; c0 += 32) {
         float v[32];
-        tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c0, v);
+        tmem_ld32(acc + (unsigned)c0, v);
         if (EPI == EPI_SWIGLU) {
           float u[32];
-          tmem_ld32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(BN / 2 + c0), u);
+          tmem_ld32(acc + (unsigned)(BN / 2 + c0), u);
 #pragma unroll
           for (int e = 0; e < 32; e++) v[e] = v[e] / (1.0f + expf(-v[e])) * u[e];
         }
         if (i < a.p_rows) {
+          const int jmax = EPI == EPI_SWIGLU ? a.up_offset : a.q_rows;
+          const int j0 = q0 + c0;
+          // a thread holds 32 consecutive columns of its row: whole 16-byte pieces when the row allows it
+          const bool wide = !a.transposed && j0 + 32 <= jmax && (a.ldo & 7) == 0 && ((uintptr_t)a.out & 15) == 0;
+          if (wide) {
+            if (a.bias && !a.bias_on_p) {
 #pragma unroll
-          for (int e = 0; e < 32; e++) {
-            const int j = q0 + c0 + e;                  // row of Q = column of the accumulator
-            if (j >= (EPI == EPI_SWIGLU ? a.up_offset : a.q_rows)) continue;
-            float r = v[e];
-            if (a.bias) r += a.bias[a.bias_on_p ? i : j];
-            const size_t o = a.transposed ? (size_t)j * a.ldo + i : (size_t)i * a.ldo + j;
-            if (EPI == EPI_ACCUM) ((float*)a.out)[o] += r;
-            else if (EPI == EPI_STORE_F32) ((float*)a.out)[o] = r;
-            else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(r);
+              for (int e = 0; e < 32; e++) v[e] += a.bias[j0 + e];
+            } else if (a.bias) {
+              const float b = a.bias[i];
+#pragma unroll
+              for (int e = 0; e < 32; e++) v[e] += b;
+            }
+            const size_t o = (size_t)i * a.ldo + j0;
+            if (EPI == EPI_ACCUM || EPI == EPI_STORE_F32) {
+              float4* dst = reinterpret_cast<float4*>((float*)a.out + o);
+#pragma unroll
+              for (int e = 0; e < 8; e++) {
+                float4 t = make_float4(v[4 * e], v[4 * e + 1], v[4 * e + 2], v[4 * e + 3]);
+                if (EPI == EPI_ACCUM) { const float4 old = dst[e]; t.x += old.x; t.y += old.y; t.z += old.z; t.w += old.w; }
+                dst[e] = t;
+              }
+            } else {
+              uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)a.out + o);
+#pragma unroll
+              for (int e = 0; e < 4; e++) {
+                uint4 t;
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+                for (int k = 0; k < 4; k++) h2[k] = __floats2bfloat162_rn(v[8 * e + 2 * k], v[8 * e + 2 * k + 1]);
+                dst[e] = t;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 32; e++) {
+              const int j = j0 + e;                     // row of Q = column of the accumulator
+              if (j >= jmax) continue;
+              float r = v[e];
+              if (a.bias) r += a.bias[a.bias_on_p ? i : j];
+              const size_t o = a.transposed ? (size_t)j * a.ldo + i : (size_t)i * a.ldo + j;
+              if (EPI == EPI_ACCUM) ((float*)a.out)[o] += r;
+              else if (EPI == EPI_STORE_F32) ((float*)a.out)[o] = r;
+              else ((__nv_bfloat16*)a.out)[o] = __float2bfloat16_rn(r);
+            }
           }
         }
       }
+      // the accumulator may be overwritten: one arrival per epilogue warp
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_free[ab]);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN < 32 ? 32 : BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -285,18 +350,29 @@ int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) 
   return 0;
 }
 
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
 template <int BN, int STAGES, int EPI>
 int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmArgs& a, int tiles_q, cudaStream_t stream) {
   auto kern = k_gemm_tcgen05<BN, STAGES, EPI>;
-  const size_t smem = 1024 + (size_t)STAGES * (BM + BN) * BK * 2 + (2 * STAGES + 1) * 8 + 16;
+  const size_t smem = 1024 + (size_t)STAGES * (BM + BN) * BK * 2 + (2 * STAGES + 4) * 8 + 16;
   static bool raised = false;
   if (!raised) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cima_fail((int)e, "gemm_tcgen05: cannot raise shared memory to %zu bytes: %s", smem, cudaGetErrorString(e));
     raised = true;
   }
-  dim3 grid(tiles_q, (a.p_rows + BM - 1) / BM);
-  { int rc_ = cima_launch(kern, dim3(grid), dim3(THREADS), (size_t)(smem), stream, 1, mp, mq, a); if (rc_) return rc_; }
+  const int p_tiles = (a.p_rows + BM - 1) / BM, n_tiles = p_tiles * tiles_q;
+  const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
+  { int rc_ = cima_launch(kern, dim3(grid), dim3(THREADS), (size_t)(smem), stream, 1, mp, mq, a, p_tiles, n_tiles); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
@@ -330,7 +406,6 @@ extern "C" int cima_gemm_tcgen05(const void* P, const void* Q, const float* bias
   const int qh = epi == EPI_SWIGLU ? bn / 2 : bn;                 // rows of Q per TMA box
   const int q_feat = epi == EPI_SWIGLU ? up_offset : q_rows;
   const int tiles_q = (q_feat + qh - 1) / qh;
-  if (tiles_q > 65535 * 32 || (p_rows + BM - 1) / BM > 65535) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05: the grid exceeds one launch");
   CUtensorMap mp, mq;
   int rc = make_map(&mp, P, p_rows, K, BM);
   if (rc) return rc;

@@ -116,6 +116,12 @@ class Model:
             cache.commit(e.slot, s + len(e.tokens))
         return logits
 
+    def check_device(self) -> None:
+        """Raise if a bounded wait inside a kernel ran out since the last check (synchronises)."""
+        k = self.rt.kernels
+        if hasattr(k, "device_errors") and k.device_errors():
+            raise RuntimeError("a kernel's bounded wait ran out (TMA or tensor-core pipeline): results are invalid")
+
     def forward(self, batch: StepBatch) -> torch.Tensor:
         K_, s = self.rt.kernels, self.spec
         x = self.rt.empty(batch.n_rows, s.hidden, dtype=torch.float32)

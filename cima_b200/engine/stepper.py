@@ -200,4 +200,6 @@ class ModelStepper:
             self.sampler.sample(logits, row_slot, DeviceSampler.params(options, dev), tokens, False)
         self.h2d_bytes += 4 * (3 * tokens_in + 3 * n + 1 + n)
         self.d2h_bytes += 4 * n
-        return tokens.tolist()
+        out = tokens.tolist()
+        self.model.check_device()
+        return out

@@ -48,6 +48,7 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines, out
                 tmp = os.path.join(out_dir, f".{step}.f32.tmp")
                 arr.tofile(tmp)
                 os.replace(tmp, os.path.join(out_dir, f"{step}.f32"))
+                model.check_device()
             elif device != "cpu":
                 import torch
                 torch.cuda.synchronize()

@@ -17,6 +17,7 @@ from ..kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
 
 FOLDED_NORM_ROWS = 16    # most rows of the skinny kernel's folded RMSNorm
 FOLDED_NORM_FEATURES = 65536
+TCGEN05_ROWS = 256       # from this many rows on, the gated product runs on the tcgen05 kernel
 SKINNY_ROWS = 8          # measured on B200: above 8 rows the library product streams the weights faster
 
 
@@ -141,6 +142,10 @@ class GatedLinearPair:
             a = a.tensor()
         if self.lin._skinny(M):
             K_.linear_skinny(a, self.lin.weight, None, out, SK_SWIGLU)
+        elif (not self.lin._plain()) and M >= TCGEN05_ROWS and self.lin.K % 8 == 0 and hasattr(K_, "gemm_tc"):
+            # many rows: the tcgen05 product with the activation in its epilogue (measured equal in time to the
+            # library product followed by the activation kernel, without the [rows, 2I] intermediate)
+            K_.gemm_tc(a, self.lin.weight, None, out, SK_SWIGLU, swap=False, bn=256)
         else:
             K_.swiglu(self.lin.store(a), out)
         return out
