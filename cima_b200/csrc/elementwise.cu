@@ -137,6 +137,38 @@ extern "C" int cima_add_residual(float* x, const void* d, int d_dtype, size_t to
   return cima_launch_result();
 }
 
+// ---------------------------------------------------------------- residual + norm: x += d; h = RMSNorm(x)
+// One block per row, the same order of summation as k_rmsnorm: bit for bit what add_residual followed by
+// rmsnorm gives, in one pass over the row less.
+template <typename TA>
+__global__ void k_add_rmsnorm(float* __restrict__ x, const TA* __restrict__ d, const float* __restrict__ w,
+                              TA* __restrict__ h, int H, float eps) {
+  cima_pdl_wait();
+  __shared__ float red[32];
+  float* xi = x + (size_t)blockIdx.x * H;
+  const TA* di = d + (size_t)blockIdx.x * H;
+  TA* ho = h + (size_t)blockIdx.x * H;
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = xi[i] + cima_to_f32<TA>(di[i]);
+    xi[i] = v;
+    acc += v * v;
+  }
+  const float total = cima_block_sum(acc, red);
+  const float inv = 1.0f / sqrtf(total / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) ho[i] = cima_from_f32<TA>(xi[i] * inv * w[i]);
+}
+
+extern "C" int cima_add_rmsnorm(float* x, const void* d, const float* w, void* h, int dtype, int T, int H, float eps,
+                                cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0) return cima_fail(CIMA_E_SIZE, "add_rmsnorm: width %d must be positive", H);
+  if (dtype == CIMA_F32) { int rc_ = cima_launch(k_add_rmsnorm<float>, dim3(T), dim3(256), (size_t)0, stream, 1, x, (const float*)d, w, (float*)h, H, eps); if (rc_) return rc_; }
+  else if (dtype == CIMA_BF16) { int rc_ = cima_launch(k_add_rmsnorm<__nv_bfloat16>, dim3(T), dim3(256), (size_t)0, stream, 1, x, (const __nv_bfloat16*)d, w, (__nv_bfloat16*)h, H, eps); if (rc_) return rc_; }
+  else return cima_fail(CIMA_E_DTYPE, "add_rmsnorm: dtype code %d is neither float32 nor bfloat16", dtype);
+  return cima_launch_result();
+}
+
 // ---------------------------------------------------------------- row gather: out[i,:] = x[rows[i],:]
 __global__ void k_gather_rows(const float* __restrict__ x, const int* __restrict__ rows, float* __restrict__ out, int H) {
   cima_pdl_wait();

@@ -17,6 +17,7 @@ from ..config.registry import lookup_architecture, read_config_json
 from ..config.specs import ModelSpec
 from ..parts import Linear, Runtime, build_block, build_norm
 from ..parts.linear import FOLDED_NORM_ROWS
+from ..parts.norm import RowsInfo
 from ..weights.loader import TensorSpec, load_tensors
 from .batch import StepBatch, StepEntry, build_batch
 
@@ -125,26 +126,36 @@ class Model:
     def forward(self, batch: StepBatch) -> torch.Tensor:
         K_, s = self.rt.kernels, self.spec
         x = self.rt.empty(batch.n_rows, s.hidden, dtype=torch.float32)
-        # few rows on the bfloat16 path: the kernels hand the rows' sums of squares along, so that every
-        # RMSNorm is folded into the product that follows it
-        ssq = None
+        # What a kernel leaves behind about the rows it wrote travels along as a RowsInfo, so that norms are
+        # folded into the products around them (few rows) or run together with the residual add (many rows).
+        info = None
         if batch.n_rows <= FOLDED_NORM_ROWS and not self.rt.full_precision:
             ssq = self.rt.empty(batch.n_rows, 1, dtype=torch.float32)
-        K_.embed(batch.tokens, self.embedding, x, s.embed_scale, ssq)
-        for site, layer in enumerate(s.schedule):
-            ssq = self.blocks[layer].forward(x, batch, self.cache, site, ssq)
-        return self.project(x, batch, ssq)
+            K_.embed(batch.tokens, self.embedding, x, s.embed_scale, ssq)
+            info = RowsInfo(ssq=ssq)
+        else:
+            K_.embed(batch.tokens, self.embedding, x, s.embed_scale)
+        order = [self.blocks[layer] for layer in s.schedule]
+        for site, block in enumerate(order):
+            if site + 1 < len(order):
+                nxt = getattr(order[site + 1], "mixer_norm", None)
+            else:
+                nxt = self.final_norm if batch.want_all_in_order else None
+            info = block.forward(x, batch, self.cache, site, info, nxt)
+        return self.project(x, batch, info)
 
-    def project(self, x: torch.Tensor, batch: StepBatch, ssq=None) -> torch.Tensor:
+    def project(self, x: torch.Tensor, batch: StepBatch, info=None) -> torch.Tensor:
         """Final norm and head at the wanted rows only."""
         if batch.n_want == 0:
             return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=self.rt.device)
         if not batch.want_all_in_order:
             picked = self.rt.empty(batch.n_want, self.spec.hidden, dtype=torch.float32)
             self.rt.kernels.gather_rows(x, batch.want_rows, picked)
-            x, ssq = picked, None
+            x, info = picked, None
+        if info is not None and getattr(info, "norm", None) is self.final_norm and info.h is not None:
+            return self.head.logits(info.h)
         if hasattr(self.final_norm, "lazy"):
-            return self.head.logits(self.final_norm.lazy(x, ssq))
+            return self.head.logits(self.final_norm.lazy(x, getattr(info, "ssq", None) if info is not None else None))
         return self.head.logits(self.final_norm(x))
 
 

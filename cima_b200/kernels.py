@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 9
+ABI_VERSION = 10
 
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
@@ -41,6 +41,7 @@ _SIGNATURES = {
     "cima_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "cima_add_residual": [_vp, _vp, _i, _sz, _vp],
     "cima_gather_rows": [_vp, _vp, _vp, _i, _i, _vp],
+    "cima_add_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "cima_decode_advance": [_vp, _vp, _vp, _vp, _i, _vp],
     "cima_linear_plain": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_linear_skinny": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
@@ -145,6 +146,17 @@ class Kernels:
             raise KernelError(f"add_residual: x {tuple(x.shape)} and delta {tuple(delta.shape)} differ")
         self._check(self.lib.cima_add_residual(x.data_ptr(), delta.data_ptr(), dtype_code(delta.dtype),
                                                x.numel(), self._stream()), "add_residual")
+
+    def add_rmsnorm(self, x: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+        """x += delta (float32 sum), then out = RMSNorm(x; w, eps): the two kernels' results in one pass."""
+        self._need(x, "x", torch.float32, 2); self._need(delta, "delta", None, 2); self._need(w, "w", torch.float32, 1)
+        self._need(out, "out", delta.dtype, 2)
+        T, H = x.shape
+        if delta.shape != x.shape or out.shape != x.shape or w.numel() != H:
+            raise KernelError(f"add_rmsnorm: x {tuple(x.shape)}, delta {tuple(delta.shape)}, out {tuple(out.shape)}, "
+                              f"w {tuple(w.shape)} do not agree")
+        self._check(self.lib.cima_add_rmsnorm(x.data_ptr(), delta.data_ptr(), w.data_ptr(), out.data_ptr(),
+                                              dtype_code(delta.dtype), T, H, eps, self._stream()), "add_rmsnorm")
 
     def gather_rows(self, x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
         self._need(x, "x", torch.float32, 2); self._need(rows, "rows", torch.int32, 1); self._need(out, "out", torch.float32, 2)

@@ -69,8 +69,9 @@ class Attention:
 
     # ------------------------------------------------------------------ step
     takes_pending_norm = True      # h may be a NormedInput: the q/k/v product folds the norm in when it can
+    takes_next_norm = True         # forward(..., next_norm=): the norm that will read x next, for its last product
 
-    def forward(self, h, x: torch.Tensor, batch, cache, site: int):
+    def forward(self, h, x: torch.Tensor, batch, cache, site: int, next_norm=None):
         s, K_ = self.spec, self.rt.kernels
         kv = cache.layer_kv(site)
         writes = s.cache_from is None
@@ -80,7 +81,7 @@ class Attention:
         att = self.rt.empty(h.shape[0], self.qd)
         from_cache = (not batch.prefill) or not writes
         K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, from_cache)
-        return self.out.accumulate(att, x)
+        return self.out.accumulate(att, x, next_norm)
 
 
 register_mixer("attention", Attention)

@@ -3,7 +3,7 @@
 registries; it does not know which kinds they are, nor which model it is in.
 
 Interface of the parts it holds:
-  norm(x) -> h, norm.lazy(x, ssq)   mixer.forward(h, x, batch, cache, site)   (adds into x)
+  norm(x) -> h, norm.lazy(x, ssq)   mixer.forward(h, x, batch, cache, site[, next_norm=])   (adds into x)
   feed_forward.forward(h, x, batch) (adds into x)
 """
 from __future__ import annotations
@@ -46,19 +46,28 @@ class PreNormBlock:
     def nbytes(self) -> int:
         return self.mixer_norm.nbytes() + self.mixer.nbytes() + self.ffn_norm.nbytes() + self.feed_forward.nbytes()
 
-    def forward(self, x: torch.Tensor, batch, cache, site: int, ssq=None):
-        """``ssq``: partial sums of squares of x's rows if the kernel that last wrote x left them (else
-        None); the same for the rows as this block leaves them is returned.  A part that declares
-        ``takes_pending_norm`` gets the norm as a ``NormedInput`` and may fold it into its first product;
-        any other part gets the normalised tensor.  A part that returns nothing invalidates the sums."""
-        ssq = self.mixer.forward(self._normed(self.mixer_norm, self.mixer, x, ssq), x, batch, cache, site)
-        return self.feed_forward.forward(self._normed(self.ffn_norm, self.feed_forward, x, ssq), x, batch)
+    def forward(self, x: torch.Tensor, batch, cache, site: int, info=None, next_norm=None):
+        """``info`` (a ``RowsInfo`` or None): what the kernel that last wrote x left behind; the same for the
+        rows as this block leaves them is returned.  ``next_norm``: the norm that reads x after this block.
+        A part that declares ``takes_pending_norm`` gets its norm as a ``NormedInput`` and may fold it into
+        its first product; one that declares ``takes_next_norm`` is told which norm follows it and may produce
+        it with its last product.  Any other part gets the normalised tensor, and what it returns is
+        ignored."""
+        info = self._run(self.mixer, self.mixer_norm, info, self.ffn_norm, x, (batch, cache, site))
+        return self._run(self.feed_forward, self.ffn_norm, info, next_norm, x, (batch,))
 
     @staticmethod
-    def _normed(norm, part, x, ssq):
-        if getattr(part, "takes_pending_norm", False) and hasattr(norm, "lazy"):
-            return norm.lazy(x, ssq)
-        return norm(x)
+    def _run(part, norm, info, next_norm, x, args):
+        if info is not None and getattr(info, "norm", None) is norm and info.h is not None:
+            h = info.h                                             # the rows came normalised already
+        elif getattr(part, "takes_pending_norm", False) and hasattr(norm, "lazy"):
+            h = norm.lazy(x, getattr(info, "ssq", None) if info is not None else None)
+        else:
+            h = norm(x)
+        if getattr(part, "takes_next_norm", False):
+            return part.forward(h, x, *args, next_norm=next_norm)
+        part.forward(h, x, *args)
+        return None
 
 
 register_block("prenorm", PreNormBlock)

@@ -39,12 +39,13 @@ class GatedMLP:
         return self.gate_up.nbytes() + self.down.nbytes()
 
     takes_pending_norm = True
+    takes_next_norm = True
 
-    def forward(self, h, x: torch.Tensor, batch):
+    def forward(self, h, x: torch.Tensor, batch, next_norm=None):
         rows = h.shape[0]
         chunk = max(64, _SCRATCH_ELEMS // (2 * self.spec.intermediate))
         if rows <= chunk:
-            return self.down.accumulate(self.gate_up.activated(h), x)
+            return self.down.accumulate(self.gate_up.activated(h), x, next_norm)
         if hasattr(h, "tensor"):
             h = h.tensor()
         for r0 in range(0, rows, chunk):

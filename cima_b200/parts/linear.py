@@ -74,9 +74,12 @@ class Linear:
                 torch.mm(a, self.weight.t(), out=out)
         return out
 
-    def accumulate(self, a: torch.Tensor, x: torch.Tensor):
-        """x += a W^T (+ bias), x being the float32 residual stream.  Returns the partial sums of squares
-        of the updated rows when the kernel left them (for a norm folded into the next product), else None."""
+    def accumulate(self, a: torch.Tensor, x: torch.Tensor, next_norm=None):
+        """x += a W^T (+ bias), x being the float32 residual stream.  Returns a ``RowsInfo`` about the updated
+        rows when the kernels left something behind that saves the next norm a pass: partial sums of squares
+        (skinny product), or the rows already normalised with ``next_norm`` (library product: the residual add
+        and the norm run as one kernel)."""
+        from .norm import RowsInfo
         K_ = self.rt.kernels
         M = a.shape[0]
         if M == 0:
@@ -86,7 +89,12 @@ class Linear:
         elif self._skinny(M):
             ssq = self.rt.empty(M, -(-self.N // 16), dtype=torch.float32) if M <= FOLDED_NORM_ROWS else None
             K_.linear_skinny(a, self.weight, self.bias, x, SK_ACCUM, ssq)
-            return ssq
+            return RowsInfo(ssq=ssq) if ssq is not None else None
+        elif (next_norm is not None and getattr(next_norm, "weight", None) is not None
+              and next_norm.spec.kind == "rmsnorm" and next_norm.spec.size == self.N and hasattr(K_, "add_rmsnorm")):
+            h = self.rt.empty(M, self.N)
+            K_.add_rmsnorm(x, self.store(a), next_norm.weight, next_norm.spec.eps, h)
+            return RowsInfo(norm=next_norm, h=h)
         else:
             K_.add_residual(x, self.store(a))
         return None

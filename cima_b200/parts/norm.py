@@ -10,6 +10,15 @@ from ..weights.loader import TensorSpec
 from .registry import register_norm
 
 
+class RowsInfo:
+    """What the kernel that last wrote the residual rows left behind, handed from part to part:
+    ``ssq`` - partial sums of squares of the rows [rows, parts] (a skinny product can fold the next norm in);
+    ``norm`` / ``h`` - the rows already normalised with that norm (the residual add and the norm ran as one)."""
+
+    def __init__(self, ssq=None, norm=None, h=None):
+        self.ssq, self.norm, self.h = ssq, norm, h
+
+
 class NormedInput:
     """RMSNorm(x) not yet computed.  A product that can fold the norm in (few rows, bf16) takes ``x``,
     the norm's weight and ``ssq`` (partial sums of squares of x's rows, left by the kernel that wrote

@@ -52,6 +52,10 @@ class ReferenceKernels:
     def add_residual(self, x, delta):
         x.add_(delta.float())
 
+    def add_rmsnorm(self, x, delta, w, eps, out):
+        self.add_residual(x, delta)
+        self.rmsnorm(x, w, eps, out)
+
     def gather_rows(self, x, rows, out):
         out.copy_(x[rows.long()])
 

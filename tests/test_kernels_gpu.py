@@ -453,3 +453,19 @@ def test_embed_leaves_sums_of_squares(K):
     ssq = torch.empty(3, 1, device="cuda")
     K.embed(ids.cuda(), table.cuda(), x, 1.0, ssq)
     assert err(ssq[:, 0], (table[ids.long()].double() ** 2).sum(dim=1)) <= 1e-3
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("T,H", [(5, 200), (64, 3584), (300, 1000)])
+def test_add_rmsnorm_equals_the_two_kernels(K, dtype, T, H):
+    x0, d, w = g(T, H, seed=1, scale=2.0), g(T, H, dtype=DT[dtype], seed=2), 1 + g(H, seed=3, scale=0.1)
+    xa, xb = x0.cuda(), x0.cuda()
+    ha = torch.empty(T, H, dtype=DT[dtype], device="cuda")
+    hb = torch.empty_like(ha)
+    K.add_rmsnorm(xa, d.cuda(), w.cuda(), 1e-5, ha)
+    K.add_residual(xb, d.cuda())
+    K.rmsnorm(xb, w.cuda(), 1e-5, hb)
+    assert torch.equal(xa, xb) and torch.equal(ha, hb)
+    want = torch.empty(T, H, dtype=torch.float64)
+    REF.rmsnorm(x0 + d.float(), w, 1e-5, want)
+    assert err(ha, want) <= TOL[dtype] * 4
