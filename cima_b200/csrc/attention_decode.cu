@@ -48,6 +48,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float ex2(float x) {          // 2^x, float32, about 2 ulp; 2^(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -76,6 +81,7 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   const int g = lane >> 2, t = lane & 3;
 
   const int len = seq_len[b];
+  const float sc2 = scale * 1.4426950408889634f;        // scores, running maxima and partial m are in the base-2 domain
   const int slot = seq_slot[b];
   const int lo = (window > 0 && len > window) ? len - window : 0;
   const int pf = lo / PS, pl = (len - 1) / PS;
@@ -149,7 +155,7 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
 #pragma unroll
       for (int e = 0; e < 4; e++) {
         const int key = key0 + j * 8 + 2 * t + (e & 1);
-        const float v = (key >= lo && key < len) ? s[j][e] * scale : -INFINITY;
+        const float v = (key >= lo && key < len) ? s[j][e] * sc2 : -INFINITY;
         s[j][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
       }
@@ -160,7 +166,7 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       const float mnew = fmaxf(m_run[r], mx[r]);
       msafe[r] = mnew == -INFINITY ? 0.f : mnew;
-      corr[r] = __expf(m_run[r] - msafe[r]);            // exp(-inf) = 0 while nothing was seen
+      corr[r] = ex2(m_run[r] - msafe[r]);               // 2^(-inf) = 0 while nothing was seen
       m_run[r] = mnew;
     }
     float psum[2] = {0.f, 0.f};
@@ -168,7 +174,7 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
     for (int j = 0; j < 2; j++)
 #pragma unroll
       for (int e = 0; e < 4; e++) {
-        const float pv = __expf(s[j][e] - msafe[e >> 1]);
+        const float pv = ex2(s[j][e] - msafe[e >> 1]);
         s[j][e] = pv;
         psum[e >> 1] += pv;
       }
@@ -222,7 +228,7 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
     float acc = 0.f, l = 0.f;
 #pragma unroll
     for (int w = 0; w < WARPS; w++) {
-      const float f = expf(sml[(w * 16 + r) * 2] - Ms);
+      const float f = ex2(sml[(w * 16 + r) * 2] - Ms);
       acc += f * so[((size_t)w * 16 + r) * HD + d];
       l += f * sml[(w * 16 + r) * 2 + 1];
     }
@@ -264,7 +270,7 @@ k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ 
 #pragma unroll
     for (int i = 0; i < MAX_SPLITS / 32; i++) {
       const int s = threadIdx.x + 32 * i;
-      if (s < n_splits) w[s] = expf(m[i] - Ms);
+      if (s < n_splits) w[s] = ex2(m[i] - Ms);
     }
     __syncwarp();
     if (threadIdx.x == 0) {

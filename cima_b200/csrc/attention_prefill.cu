@@ -5,7 +5,8 @@
 // One block = 64 query rows of one sequence x one head; its 4 warps own 16 rows each.  Key tiles
 // of 64 rows stream through shared memory with cp.async (two in flight).  S = Q K^T and O += P V run
 // on the tensor cores (mma.m16n8k16, bf16 in, f32 out); scores, running maximum, exponentials and
-// sums are float32 (exponentials by ex2.approx, whose error is far below the bfloat16 rounding of P);
+// sums are float32 (exponentials as 2^(s * scale * log2 e - m) by ex2.approx, whose error is far below
+// the bfloat16 rounding of P);
 // P is rounded to bfloat16 only as the operand of P V.  Key tiles wholly above the
 // diagonal or wholly below the window are skipped.  The list of (sequence, first row) of the blocks
 // comes from the host, heaviest first.
@@ -44,6 +45,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float ex2(float x) {          // 2^x, float32, about 2 ulp; 2^(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -69,6 +75,7 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int kcol = (nh + kvh) * HD, vcol = (nh + nkv + kvh) * HD;
+  const float sc2 = scale * 1.4426950408889634f;       // scores are kept in the base-2 domain
 
   // this thread's two query rows (positions within the sequence)
   const int r0 = q0 + warp * 16 + g, r1 = r0 + 8;
@@ -148,20 +155,34 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
         mma_bf16(s[2 * jp + 1], q[kk][0], q[kk][1], q[kk][2], q[kk][3], kb[cur][jp][2], kb[cur][jp][3]);
       }
     }
-    // scale and mask: key <= query position, and within the window
+    // Scores in the base-2 domain: t = s * scale * log2(e), p = 2^(t - m).  Only tiles that touch the
+    // diagonal or the window's lower edge need the mask (a warp-uniform choice).
     const int key_base = kt * BN;
+    const int wr0 = q0 + warp * 16;                    // this warp's first query position
+    const bool masked = key_base + BN - 1 > wr0 || (window > 0 && wr0 + 15 - key_base >= window);
     float mx[2] = {-INFINITY, -INFINITY};
+    if (masked) {
 #pragma unroll
-    for (int j = 0; j < 8; j++)
+      for (int j = 0; j < 8; j++)
 #pragma unroll
-      for (int e = 0; e < 4; e++) {
-        const int key = key_base + j * 8 + 2 * t + (e & 1);
-        const int qp = (e >> 1) ? r1 : r0;
-        const bool seen = key <= qp && (window <= 0 || qp - key < window);
-        const float v = seen ? s[j][e] * scale : -INFINITY;
-        s[j][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
-      }
+        for (int e = 0; e < 4; e++) {
+          const int key = key_base + j * 8 + 2 * t + (e & 1);
+          const int qp = (e >> 1) ? r1 : r0;
+          const bool seen = key <= qp && (window <= 0 || qp - key < window);
+          const float v = seen ? s[j][e] * sc2 : -INFINITY;
+          s[j][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          const float v = s[j][e] * sc2;
+          s[j][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
+        }
+    }
     float corr[2], msafe[2];
 #pragma unroll
     for (int r = 0; r < 2; r++) {
@@ -169,7 +190,7 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
       const float mnew = fmaxf(m_run[r], mx[r]);
       msafe[r] = mnew == -INFINITY ? 0.f : mnew;
-      corr[r] = __expf(m_run[r] - msafe[r]);
+      corr[r] = ex2(m_run[r] - msafe[r]);
       m_run[r] = mnew;
     }
     float psum[2] = {0.f, 0.f};
@@ -177,7 +198,7 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
     for (int j = 0; j < 8; j++)
 #pragma unroll
       for (int e = 0; e < 4; e++) {
-        const float pv = __expf(s[j][e] - msafe[e >> 1]);
+        const float pv = ex2(s[j][e] - msafe[e >> 1]);
         s[j][e] = pv;
         psum[e >> 1] += pv;
       }
@@ -187,10 +208,13 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
       psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
       l_run[r] = l_run[r] * corr[r] + psum[r];
     }
+    // the accumulator is rescaled only when some row's maximum moved (after the first tiles it rarely does)
+    if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
 #pragma unroll
-    for (int j = 0; j < NTILES; j++) {
-      o[j][0] *= corr[0]; o[j][1] *= corr[0];
-      o[j][2] *= corr[1]; o[j][3] *= corr[1];
+      for (int j = 0; j < NTILES; j++) {
+        o[j][0] *= corr[0]; o[j][1] *= corr[0];
+        o[j][2] *= corr[1]; o[j][3] *= corr[1];
+      }
     }
 #pragma unroll
     for (int ks = 0; ks < 4; ks++) {                  // 16 keys per k-step
