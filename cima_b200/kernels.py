@@ -52,6 +52,7 @@ _SIGNATURES = {
     "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
     "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "cima_gemm_tcgen05": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
     "cima_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
@@ -269,6 +270,25 @@ class Kernels:
                                               w.shape[0], K, N, 0, 0, N if mode == SK_SWIGLU else 0, bn,
                                               self._error_flag.data_ptr(), self._stream())
         self._check(code, "gemm_tcgen05")
+
+    def gemm_tc_pair(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                     mode: int) -> None:
+        """``gemm_tc`` for many rows on pairs of SMs (tcgen05 cta_group::2, tiles of 256 x 256): each SM of a
+        pair stages only half of the weight tile.  Same modes and layouts as ``gemm_tc`` without ``swap``."""
+        self._need(a, "a", torch.bfloat16, 2); self._need(w, "w", torch.bfloat16, 2); self._need(out, "out", None, 2)
+        M, K = a.shape
+        N = w.shape[0] // 2 if mode == SK_SWIGLU else w.shape[0]
+        want = torch.float32 if mode in (SK_ACCUM, SK_STORE_F32) else torch.bfloat16
+        if w.shape[1] != K or tuple(out.shape) != (M, N) or out.dtype is not want:
+            raise KernelError(f"gemm_tc_pair(mode {mode}): a {tuple(a.shape)}, w {tuple(w.shape)}, out "
+                              f"{tuple(out.shape)} {out.dtype} do not agree")
+        if bias is not None:
+            self._need(bias, "bias", torch.float32, 1)
+        if self._error_flag is None:
+            self._error_flag = torch.zeros(1, dtype=torch.int32, device=a.device)
+        self._check(self.lib.cima_gemm_tcgen05_pair(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, M,
+                                                    w.shape[0], K, N, N if mode == SK_SWIGLU else 0,
+                                                    self._error_flag.data_ptr(), self._stream()), "gemm_tcgen05_pair")
 
     def device_errors(self) -> int:
         """The error flag that a bounded wait inside a kernel sets when it runs out (synchronises)."""

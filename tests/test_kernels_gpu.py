@@ -469,3 +469,31 @@ def test_add_rmsnorm_equals_the_two_kernels(K, dtype, T, H):
     want = torch.empty(T, H, dtype=torch.float64)
     REF.rmsnorm(x0 + d.float(), w, 1e-5, want)
     assert err(ha, want) <= TOL[dtype] * 4
+
+
+@pytest.mark.parametrize("M,N,K_", [(256, 256, 64), (300, 328, 200), (2048, 1000, 448), (513, 3584, 192), (130, 66, 72),
+                                    (1, 8, 8)])
+def test_gemm_tcgen05_pair_modes(K, M, N, K_):
+    """The product on pairs of SMs (cta_group::2) against float64, every epilogue, tails in every dimension."""
+    from cima_b200.kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
+    a = g(M, K_, dtype=torch.bfloat16, seed=M)
+    w = g(N, K_, dtype=torch.bfloat16, seed=N, scale=1.0 / math.sqrt(K_))
+    b = g(N, seed=7)
+    want = a.double() @ w.double().t()
+    out32 = torch.full((M, N), -777.0, device="cuda")
+    K.gemm_tc_pair(a.cuda(), w.cuda(), b.cuda(), out32, SK_STORE_F32)
+    assert err(out32, want + b.double()) <= 1e-4
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    K.gemm_tc_pair(a.cuda(), w.cuda(), None, out, SK_STORE)
+    assert err(out, want) <= TOL["bfloat16"] * 4
+    x = g(M, N, seed=9)
+    xg = x.cuda()
+    K.gemm_tc_pair(a.cuda(), w.cuda(), None, xg, SK_ACCUM)
+    assert err(xg, x.double() + want) <= 1e-4
+    if N % 2 == 0:
+        I = N // 2
+        act = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+        K.gemm_tc_pair(a.cuda(), w.cuda(), None, act, SK_SWIGLU)
+        gg, uu = want[:, :I], want[:, I:]
+        assert err(act, gg / (1 + torch.exp(-gg)) * uu) <= TOL["bfloat16"] * 4
+    assert K.device_errors() == 0
