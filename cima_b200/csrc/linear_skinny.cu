@@ -25,7 +25,7 @@
 #include <cooperative_groups.h>
 namespace cg = cooperative_groups;
 
-enum { SK_STORE = 0, SK_ACCUM = 1, SK_SWIGLU = 2, SK_STORE_F32 = 3 };
+enum { SK_STORE = 0, SK_ACCUM = 1, SK_SWIGLU = 2, SK_STORE_F32 = 3, SK_QKV_ROPE = 4 };
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   uint4 v;
@@ -72,13 +72,30 @@ struct SkinnyNorm {
   float* ssq_out;        // [M, tiles] or null (accumulating epilogue only)
 };
 
+// Mode 4: the q/k/v projection of a decode step with the rotary encoding and the append to the cache in its
+// epilogue.  W is [q heads | k heads | v heads] x head_dim rows.  A block's 16 rows are then not 16
+// consecutive features: for a head that rotates they are features 8s..8s+7 and their rotation partners
+// head_dim/2 + 8s.., so that both halves of every pair (i, i + head_dim/2) meet in one block.  The rotated q
+// goes to the qkv buffer (decode attention reads it there), the rotated k and the v straight to their place
+// in the layer's pages.  Angles, sine and cosine are float32 as in rope_cache.cu; the projection is rotated
+// before its one rounding to bfloat16.
+struct SkinnyRope {
+  const float* inv_freq;      // [head_dim / 2]
+  const int* row_pos;         // [M] position of each row
+  const int* row_seq;         // [M] sequence of each row
+  const int* seq_slot;        // [sequences]
+  __nv_bfloat16* cache;       // this layer's pages
+  CimaPaged pg;
+  int nh, nkv, hd;
+};
+
 // NT: 8-row tiles of X (M <= 8 * NT).  MT: m-tiles per block (1, or 2 for the gated epilogue).
 // U: 32-wide k steps kept in flight per warp iteration.  NORM: X is the residual stream (see above).
 template <int NT, int MT, int U, int MODE, bool NORM>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
                 const float* __restrict__ bias, void* __restrict__ out,
-                int M, int N, int K, int ldx, int ldo, int up_offset, SkinnyNorm nm) {
+                int M, int N, int K, int ldx, int ldo, int up_offset, SkinnyNorm nm, SkinnyRope rp) {
   extern __shared__ float red[];                       // [warps][MT][NT*8][SK_PAD], then part [MT][NT*8][SK_ROWS]
   cg::cluster_group cluster = cg::this_cluster();
   const int S = (int)cluster.num_blocks();              // blocks that share this tile's K
@@ -86,6 +103,21 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = (blockIdx.x / S) * SK_ROWS;
+  // mode 4: which head this block works on, which 8 pairs of it, and whether the head rotates
+  int rp_head = 0, rp_sub = 0;
+  bool rp_rot = false;
+  if (MODE == SK_QKV_ROPE) {
+    const int tph = rp.hd / 16;
+    rp_head = (blockIdx.x / S) / tph;
+    rp_sub = (blockIdx.x / S) % tph;
+    rp_rot = rp_head < rp.nh + rp.nkv;
+  }
+  // feature (row of W, column of the output) of row r in 0..15 of this block
+  auto feature = [&](int r) -> int {
+    if (MODE != SK_QKV_ROPE) return n0 + r;
+    if (rp_rot) return rp_head * rp.hd + (r < 8 ? rp_sub * 8 + r : rp.hd / 2 + rp_sub * 8 + (r - 8));
+    return rp_head * rp.hd + rp_sub * 16 + r;
+  };
   cima_pdl_wait();
   // Folded norm: the rows' partial sums of squares are fetched now and added up after the K loop, so
   // that their latency hides behind the weight stream; the factor inv = 1 / sqrt(sum / K + eps) of a
@@ -117,7 +149,7 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
   for (int a = 0; a < MT; a++)
 #pragma unroll
     for (int h = 0; h < 2; h++) {
-      const int r = n0 + g + 8 * h;
+      const int r = feature(g + 8 * h);
       wok[a][h] = r < N;
       wrow[a][h] = W + (size_t)((wok[a][h] ? r : 0) + a * up_offset) * K;
     }
@@ -217,8 +249,32 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
   if (crank == 0) {
     for (int e = threadIdx.x; e < COLS * SK_ROWS; e += SK_WARPS * 32) {
       const int r = e % SK_ROWS, m = e / SK_ROWS;
-      const int n = n0 + r;
+      const int n = feature(r);
       const bool live = m < M && n < N;
+      if (MODE == SK_QKV_ROPE) {
+        float s = part[(size_t)m * SK_ROWS + r];
+        for (int cr = 1; cr < S; cr++) s += cluster.map_shared_rank(part, cr)[(size_t)m * SK_ROWS + r];
+        float v = (NORM ? s * inv_s[m < M ? m : 0] : s) + (bias ? bias[n] : 0.f);
+        const int pos = live ? rp.row_pos[m] : 0;
+        if (rp_rot) {
+          const float other = __shfl_xor_sync(0xffffffffu, v, 8);     // the pair's other half, 8 lanes away
+          float sn, cs;
+          sincosf((float)pos * rp.inv_freq[rp_sub * 8 + (r & 7)], &sn, &cs);
+          v = r < 8 ? v * cs - other * sn : other * sn + v * cs;
+        }
+        if (live) {
+          const __nv_bfloat16 o16 = __float2bfloat16_rn(v);
+          if (rp_head < rp.nh) {
+            ((__nv_bfloat16*)out)[(size_t)m * ldo + n] = o16;
+          } else {
+            const int slot = rp.seq_slot[rp.row_seq[m]];
+            const bool is_v = rp_head >= rp.nh + rp.nkv;
+            const int kvh = rp_head - rp.nh - (is_v ? rp.nkv : 0);
+            rp.cache[rp.pg.offset(slot, pos, is_v ? 1 : 0, kvh) + (n - rp_head * rp.hd)] = o16;
+          }
+        }
+        continue;
+      }
       if (MODE == SK_ACCUM && nm.ssq_out) {
         // the 16 features of a row sit in 16 consecutive lanes: their squares are summed by shuffles
         float xn = 0.f;
@@ -269,7 +325,8 @@ static int cluster_size(int tiles, int K) {
 
 template <int NT, int MT, int U, int MODE, bool NORM>
 static int launch_skinny(const void* X, const void* W, const float* bias, void* out, int M, int N, int K, int ldx,
-                         int ldo, int up_offset, const SkinnyNorm& nm, cudaStream_t stream) {
+                         int ldo, int up_offset, const SkinnyNorm& nm, cudaStream_t stream,
+                         const SkinnyRope& rp = SkinnyRope{}) {
   auto kern = k_linear_skinny<NT, MT, U, MODE, NORM>;
   const size_t smem = ((size_t)SK_WARPS * MT * NT * 8 * SK_PAD + (size_t)MT * NT * 8 * SK_ROWS) * sizeof(float);
   if (smem > 48 * 1024) {
@@ -283,7 +340,7 @@ static int launch_skinny(const void* X, const void* W, const float* bias, void* 
   const int tiles = (N + SK_ROWS - 1) / SK_ROWS;
   const int S = cluster_size(tiles, K);
   int rc = cima_launch(kern, dim3(tiles * S), dim3(SK_WARPS * 32), smem, stream, S, (const __nv_bfloat16*)X,
-                       (const __nv_bfloat16*)W, bias, out, M, N, K, ldx, ldo, up_offset, nm);
+                       (const __nv_bfloat16*)W, bias, out, M, N, K, ldx, ldo, up_offset, nm, rp);
   if (rc) return rc;
   return cima_launch_result();
 }
@@ -341,4 +398,33 @@ extern "C" int cima_linear_skinny_norm(const float* x32, const float* norm_w, co
   SkinnyNorm nm{x32, norm_w, ssq, parts, eps, nullptr};
   if (M <= 8) return dispatch_mode<1, true>(mode, nullptr, W, bias, out, M, N, K, ldx, ldo, nm, stream);
   return dispatch_mode<2, true>(mode, nullptr, W, bias, out, M, N, K, ldx, ldo, nm, stream);
+}
+
+// Mode 4 (see SkinnyRope): qkv [M, (nh + 2 nkv) * hd] receives the rotated q; k and v go to the cache.
+// Activations either as bf16 rows X (x32 == null) or as float32 residual rows with the norm folded in.
+// At most 16 rows; head_dim a multiple of 16; every dimension of a head rotates (rotary_dim == head_dim).
+extern "C" int cima_qkv_rope_skinny(const void* X, const float* x32, const float* norm_w, const float* ssq, int parts,
+                                    float eps, const void* W, const float* bias, void* qkv, int M, int K, int ldx,
+                                    int ldo, const float* inv_freq, const int* row_pos, const int* row_seq,
+                                    const int* seq_slot, void* cache, const int* table, int table_width, int ring,
+                                    int page_size, int nh, int nkv, int hd, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (M > 16) return cima_fail(CIMA_E_SIZE, "qkv_rope_skinny: %d rows; at most 16", M);
+  if (hd <= 0 || hd % 16 || nh <= 0 || nkv <= 0) return cima_fail(CIMA_E_SIZE, "qkv_rope_skinny: head_dim %d must be a multiple of 16 and the head counts positive", hd);
+  if (!cache || !table || !inv_freq || !row_pos || !row_seq || !seq_slot) return cima_fail(CIMA_E_ARG, "qkv_rope_skinny: positions, frequencies and the cache are needed");
+  const int N = (nh + 2 * nkv) * hd;
+  const bool norm = x32 != nullptr;
+  if (norm && (!norm_w || !ssq || parts <= 0 || ldx % 4 || (((uintptr_t)x32 | (uintptr_t)norm_w) & 15)))
+    return cima_fail(CIMA_E_ARG, "qkv_rope_skinny: the folded norm needs aligned rows, its weight and the partial sums");
+  int rc = skinny_checks(norm ? W : X, W, bias, SK_STORE, M, N, K, norm ? 8 : ldx);
+  if (rc) return rc;
+  SkinnyNorm nm{x32, norm_w, ssq, parts, eps, nullptr};
+  SkinnyRope rp{inv_freq, row_pos, row_seq, seq_slot, (__nv_bfloat16*)cache,
+                CimaPaged{table, table_width, ring, page_size, nkv, hd}, nh, nkv, hd};
+  if (norm) {
+    if (M <= 8) return launch_skinny<1, 1, 4, SK_QKV_ROPE, true>(nullptr, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
+    return launch_skinny<2, 1, 4, SK_QKV_ROPE, true>(nullptr, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
+  }
+  if (M <= 8) return launch_skinny<1, 1, 4, SK_QKV_ROPE, false>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
+  return launch_skinny<2, 1, 4, SK_QKV_ROPE, false>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
 }

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 10
+ABI_VERSION = 11
 
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
@@ -46,6 +46,8 @@ _SIGNATURES = {
     "cima_linear_plain": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_linear_skinny": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_linear_skinny_norm": [_vp, _vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_qkv_rope_skinny": [_vp, _vp, _vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
+                             _i, _i, _i, _i, _vp],
     "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_attention_plain": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                              _f, _i, _i, _vp],
@@ -239,6 +241,37 @@ class Kernels:
         self._check(self.lib.cima_linear_skinny_norm(x.data_ptr(), norm_w.data_ptr(), ssq.data_ptr(), ssq.shape[1], eps,
                                                      w.data_ptr(), _ptr(bias), out.data_ptr(), mode, M, N, K, K, N,
                                                      self._stream()), "linear_skinny_norm")
+
+    def qkv_rope(self, a, w: torch.Tensor, bias: Optional[torch.Tensor], qkv: torch.Tensor, inv_freq: torch.Tensor,
+                 row_pos, row_seq, seq_slot, kv, n_heads: int, n_kv_heads: int, head_dim: int, norm=None) -> None:
+        """The q/k/v projection of a decode step (at most 16 rows) with rotation and cache append in its
+        epilogue: the rotated q lands in ``qkv`` [rows, (heads + 2 kv_heads) * head_dim], k and v in the layer's
+        pages.  ``a``: bf16 activations, or with ``norm = (norm_weight, ssq, eps)`` the float32 residual rows
+        whose RMSNorm is folded in."""
+        self._need(w, "w", torch.bfloat16, 2); self._need(qkv, "qkv", torch.bfloat16, 2)
+        self._need(inv_freq, "inv_freq", torch.float32, 1)
+        M, K = a.shape
+        N = (n_heads + 2 * n_kv_heads) * head_dim
+        if tuple(w.shape) != (N, K) or tuple(qkv.shape) != (M, N) or inv_freq.numel() != head_dim // 2:
+            raise KernelError(f"qkv_rope: a {tuple(a.shape)}, w {tuple(w.shape)}, qkv {tuple(qkv.shape)}, inv_freq "
+                              f"{tuple(inv_freq.shape)} do not agree with {n_heads}+2x{n_kv_heads} heads of {head_dim}")
+        self._need(kv.storage, "cache", torch.bfloat16, 5); self._need(kv.block_table, "block_table", torch.int32, 2)
+        if tuple(kv.storage.shape[1:]) != (2, n_kv_heads, kv.page_size, head_dim):
+            raise KernelError(f"qkv_rope: cache pages are {tuple(kv.storage.shape)}")
+        if bias is not None:
+            self._need(bias, "bias", torch.float32, 1)
+        if norm is None:
+            self._need(a, "a", torch.bfloat16, 2)
+            head = (a.data_ptr(), None, None, None, 0, 0.0)
+        else:
+            nw, ssq, eps = norm
+            self._need(a, "x", torch.float32, 2); self._need(nw, "norm_w", torch.float32, 1); self._need(ssq, "ssq", torch.float32, 2)
+            head = (None, a.data_ptr(), nw.data_ptr(), ssq.data_ptr(), ssq.shape[1], eps)
+        self._check(self.lib.cima_qkv_rope_skinny(*head, w.data_ptr(), _ptr(bias), qkv.data_ptr(), M, K, K, N,
+                                                  inv_freq.data_ptr(), row_pos.data_ptr(), row_seq.data_ptr(),
+                                                  seq_slot.data_ptr(), kv.storage.data_ptr(), kv.block_table.data_ptr(),
+                                                  kv.block_table.shape[1], kv.ring_pages, kv.page_size, n_heads,
+                                                  n_kv_heads, head_dim, self._stream()), "qkv_rope_skinny")
 
     def gemm_tc(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int,
                 swap: Optional[bool] = None, bn: Optional[int] = None) -> None:

@@ -75,9 +75,23 @@ class Attention:
         s, K_ = self.spec, self.rt.kernels
         kv = cache.layer_kv(site)
         writes = s.cache_from is None
-        qkv = self.qkv.store(h)
-        K_.rope_append(qkv, self.position.inv_freq, self.position.rotary_dim, batch.row_pos, batch.row_seq,
-                       batch.seq_slot, batch.seq_len, kv if writes else None, s.n_heads, s.n_kv_heads, s.head_dim)
+        rows = h.shape[0]
+        if (not batch.prefill and writes and rows <= 16 and self.qkv._skinny(rows) and kv.storage.dtype is torch.bfloat16
+                and self.position.rotary_dim == s.head_dim and hasattr(K_, "qkv_rope")):
+            # decoding: projection, rotation and the append to the cache as one kernel
+            qkv = self.rt.empty(rows, self.qd + 2 * self.kvd)
+            if self.qkv._folds(h, rows):
+                K_.qkv_rope(h.x, self.qkv.weight, self.qkv.bias, qkv, self.position.inv_freq, batch.row_pos,
+                            batch.row_seq, batch.seq_slot, kv, s.n_heads, s.n_kv_heads, s.head_dim,
+                            norm=(h.norm.weight, h.ssq, h.norm.spec.eps))
+            else:
+                K_.qkv_rope(h.tensor() if hasattr(h, "tensor") else h, self.qkv.weight, self.qkv.bias, qkv,
+                            self.position.inv_freq, batch.row_pos, batch.row_seq, batch.seq_slot, kv, s.n_heads,
+                            s.n_kv_heads, s.head_dim)
+        else:
+            qkv = self.qkv.store(h)
+            K_.rope_append(qkv, self.position.inv_freq, self.position.rotary_dim, batch.row_pos, batch.row_seq,
+                           batch.seq_slot, batch.seq_len, kv if writes else None, s.n_heads, s.n_kv_heads, s.head_dim)
         att = self.rt.empty(h.shape[0], self.qd)
         from_cache = (not batch.prefill) or not writes
         K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, from_cache)

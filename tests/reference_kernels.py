@@ -99,6 +99,18 @@ class ReferenceKernels:
             out.copy_(y.to(out.dtype))
 
     # ------------------------------------------------------------------ attention
+    def qkv_rope(self, a, w, bias, qkv, inv_freq, row_pos, row_seq, seq_slot, kv, n_heads, n_kv_heads, head_dim, norm=None):
+        if norm is not None:
+            nw, ssq, eps = norm
+            inv = 1.0 / torch.sqrt(ssq.to(self.compute).sum(dim=1, keepdim=True) / a.shape[1] + eps)
+            a = (a.to(self.compute) * inv * nw.to(self.compute)).to(torch.bfloat16)
+        y = a.to(self.compute) @ w.to(self.compute).t()
+        if bias is not None:
+            y = y + bias.to(self.compute)
+        seq_len = torch.zeros(int(row_seq.max()) + 1, dtype=torch.int32)
+        self.rope_append(y, inv_freq, head_dim, row_pos, row_seq, seq_slot, seq_len, kv, n_heads, n_kv_heads, head_dim)
+        qkv.copy_(y.to(qkv.dtype))
+
     def rope_append(self, qkv, inv_freq, rotary_dim, row_pos, row_seq, seq_slot, seq_len, kv, n_heads, n_kv_heads, head_dim):
         T = qkv.shape[0]
         half = rotary_dim // 2

@@ -497,3 +497,45 @@ def test_gemm_tcgen05_pair_modes(K, M, N, K_):
         gg, uu = want[:, :I], want[:, I:]
         assert err(act, gg / (1 + torch.exp(-gg)) * uu) <= TOL["bfloat16"] * 4
     assert K.device_errors() == 0
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 16])
+@pytest.mark.parametrize("nh,nkv,hd,H", [(6, 2, 48, 200), (28, 4, 128, 3584), (3, 1, 64, 192), (4, 4, 16, 64)])
+def test_qkv_rope_skinny_equals_projection_then_rope_append(K, M, nh, nkv, hd, H):
+    """The decode projection with rotation and cache append in its epilogue against the two separate steps
+    (float64 statement): rotated q in the buffer, rotated k and v in the right pages, other pages untouched."""
+    from cima_b200.kernels import SK_ACCUM
+    page = 64
+    N = (nh + 2 * nkv) * hd
+    lens = [int(x) for x in np.random.default_rng(M).integers(1, 200, size=M)]
+    slots = list(np.random.default_rng(M + 1).permutation(M + 3)[:M])
+    tables, n_pages, width = scattered_tables(lens, slots, page, seed=hd + M)
+    cpu, gpu = make_kv(n_pages, nkv, page, hd, M + 3, width, 0, 0, torch.bfloat16, tables)
+    seqs = [(int(slots[i]), lens[i] - 1, 1) for i in range(M)]
+    bc, bg = batch_of(seqs, "cpu"), batch_of(seqs, "cuda")
+    a = g(M, H, dtype=torch.bfloat16, seed=1)
+    w = g(N, H, dtype=torch.bfloat16, seed=2, scale=1.0 / math.sqrt(H))
+    b = g(N, seed=3, scale=0.5)
+    inv = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd).float()
+    # statement: projection in float64, rotation and append by the reference (rounded once at the end)
+    want = (a.double() @ w.double().t() + b.double())
+    REF.rope_append(want, inv, hd, bc.row_pos, bc.row_seq, bc.seq_slot, bc.seq_len, cpu, nh, nkv, hd)
+    qkv = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.qkv_rope(a.cuda(), w.cuda(), b.cuda(), qkv, inv.cuda(), bg.row_pos, bg.row_seq, bg.seq_slot, gpu, nh, nkv, hd)
+    assert err(qkv[:, :nh * hd], want[:, :nh * hd]) <= TOL["bfloat16"] * 4
+    assert err(gpu.storage, cpu.storage) <= TOL["bfloat16"] * 4
+    # with the norm folded in: x float32 rows, partial sums of squares as an accumulating product leaves them
+    x = g(M, H, seed=4, scale=1.5).cuda()
+    ssq = torch.empty(M, -(-H // 16), device="cuda")
+    zero_w = torch.zeros(H, 8, dtype=torch.bfloat16, device="cuda")
+    K.linear_skinny(torch.zeros(M, 8, dtype=torch.bfloat16, device="cuda"), zero_w, None, x, SK_ACCUM, ssq)
+    nw = (1 + g(H, seed=5, scale=0.1))
+    xd = x.double().cpu()
+    hh = xd / torch.sqrt((xd * xd).mean(dim=1, keepdim=True) + 1e-6) * nw.double()
+    want2 = hh @ w.double().t() + b.double()
+    cpu2, gpu2 = make_kv(n_pages, nkv, page, hd, M + 3, width, 0, 0, torch.bfloat16, tables)
+    REF.rope_append(want2, inv, hd, bc.row_pos, bc.row_seq, bc.seq_slot, bc.seq_len, cpu2, nh, nkv, hd)
+    K.qkv_rope(x, w.cuda(), b.cuda(), qkv, inv.cuda(), bg.row_pos, bg.row_seq, bg.seq_slot, gpu2, nh, nkv, hd,
+               norm=(nw.cuda(), ssq, 1e-6))
+    assert err(qkv[:, :nh * hd], want2[:, :nh * hd]) <= TOL["bfloat16"] * 4
+    assert err(gpu2.storage, cpu2.storage) <= TOL["bfloat16"] * 4
