@@ -10,7 +10,8 @@
 // ---------------------------------------------------------------- embedding: x[t,:] = scale * E[ids[t],:]
 template <typename TW>
 __global__ void k_embed(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ x,
-                        int H, int V, float scale, float* __restrict__ ssq) {
+                        int H, int V, float scale, float* __restrict__ ssq, const float* __restrict__ w_next,
+                        __nv_bfloat16* __restrict__ xw) {
   cima_pdl_wait();
   __shared__ float red[32];
   const int row = blockIdx.x;
@@ -22,6 +23,7 @@ __global__ void k_embed(const int* __restrict__ ids, const TW* __restrict__ tabl
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
     const float v = cima_to_f32<TW>(src[i]) * scale;
     dst[i] = v;
+    if (xw) xw[(size_t)row * H + i] = __float2bfloat16_rn(v * w_next[i]);      // for a norm folded into the next product
     acc += v * v;
   }
   if (ssq) {                                    // the row's sum of squares, for a norm folded into the next product
@@ -30,13 +32,14 @@ __global__ void k_embed(const int* __restrict__ ids, const TW* __restrict__ tabl
   }
 }
 
-// ssq (may be null): [T] sum of squares of each row written.
+// ssq (may be null): [T] sum of squares of each row written.  w_next / xw (may be null): weight [H] of the norm
+// that follows and where to put bf16(row * weight), [T, H].
 extern "C" int cima_embed(const int* ids, const void* table, int table_dtype, float* x, int T, int H, int V,
-                          float scale, float* ssq, cudaStream_t stream) {
+                          float scale, float* ssq, const float* w_next, void* xw, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || V <= 0) return cima_fail(CIMA_E_SIZE, "embed: hidden %d and vocab %d must be positive", H, V);
-  if (table_dtype == CIMA_F32) { int rc_ = cima_launch(k_embed<float>, dim3(T), dim3(256), (size_t)(0), stream, 1, ids, (const float*)table, x, H, V, scale, ssq); if (rc_) return rc_; }
-  else if (table_dtype == CIMA_BF16) { int rc_ = cima_launch(k_embed<__nv_bfloat16>, dim3(T), dim3(256), (size_t)(0), stream, 1, ids, (const __nv_bfloat16*)table, x, H, V, scale, ssq); if (rc_) return rc_; }
+  if (table_dtype == CIMA_F32) { int rc_ = cima_launch(k_embed<float>, dim3(T), dim3(256), (size_t)(0), stream, 1, ids, (const float*)table, x, H, V, scale, ssq, w_next, (__nv_bfloat16*)xw); if (rc_) return rc_; }
+  else if (table_dtype == CIMA_BF16) { int rc_ = cima_launch(k_embed<__nv_bfloat16>, dim3(T), dim3(256), (size_t)(0), stream, 1, ids, (const __nv_bfloat16*)table, x, H, V, scale, ssq, w_next, (__nv_bfloat16*)xw); if (rc_) return rc_; }
   else return cima_fail(CIMA_E_DTYPE, "embed: table dtype code %d is neither float32 nor bfloat16", table_dtype);
   return cima_launch_result();
 }

@@ -55,21 +55,21 @@ constexpr int SK_WARPS = 8;
 constexpr int SK_ROWS = 16;      // output features per m-tile
 constexpr int SK_PAD = 17;       // row stride of the reduction buffer (bank spread)
 
-// RMSNorm folded into the product.  The rows of X are then the float32 residual stream x.  With
-// inv = 1 / sqrt(sum(x^2) / K + eps) a row's result is inv * sum_k bf16(x_k * w_k) W[n, k]: the norm's
-// weight is applied on the fly, the row's factor to the finished sums (so the factor is not needed
-// before the epilogue; against bf16(x * inv * w) as operand this differs by bfloat16 rounding only).
-// sum(x^2) of a row is given as `parts` partial sums that the kernel which wrote x left behind
-// (ssq [M, parts]; fetched before the K loop, summed after it in a fixed order).  An accumulating product in turn leaves the partial
-// sums of the rows it has updated (ssq_out [M, tiles], one per 16-feature tile), so that between the
-// two no separate norm kernel has to run.
+// RMSNorm folded into the product.  With inv = 1 / sqrt(sum(x^2) / K + eps) a normed row is inv * (x * w), so
+// the product of the normed row is inv * sum_k bf16(x_k * w_k) W[n, k]: the kernel that wrote the residual row x
+// also leaves xw = bf16(x * w) (w = the weight of the norm that follows) and partial sums of x^2; the product
+// after the norm (NORM = true) reads xw as plain bf16 activations and applies the row's factor to its finished
+// sums.  Against bf16(x * inv * w) as operand this differs by bfloat16 rounding only, and no separate norm
+// kernel runs between the two.  The partial sums (ssq [M, parts]) are fetched before the K loop and summed
+// after it in a fixed order.  An accumulating product leaves, for the rows it has updated, one partial sum
+// per 16-feature tile (ssq_out [M, tiles]) and xw_out [M, N] = bf16(x_new * w_next).
 struct SkinnyNorm {
-  const float* x32;      // [M, K] float32, row stride ldx; null = X is bf16 activations
-  const float* w;        // [K] norm weight
-  const float* ssq;      // [M, parts]
+  const float* ssq;      // [M, parts] (NORM kernels)
   int parts;
   float eps;
   float* ssq_out;        // [M, tiles] or null (accumulating epilogue only)
+  const float* w_next;   // [N] weight of the norm that follows, with xw_out; both null = not wanted
+  __nv_bfloat16* xw_out;
 };
 
 // Mode 4: the q/k/v projection of a decode step with the rotary encoding and the append to the cache in its
@@ -90,7 +90,7 @@ struct SkinnyRope {
 };
 
 // NT: 8-row tiles of X (M <= 8 * NT).  MT: m-tiles per block (1, or 2 for the gated epilogue).
-// U: 32-wide k steps kept in flight per warp iteration.  NORM: X is the residual stream (see above).
+// U: 32-wide k steps kept in flight per warp iteration.  NORM: X is bf16(x * w), see above.
 template <int NT, int MT, int U, int MODE, bool NORM>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W,
@@ -174,27 +174,10 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
 #pragma unroll
       for (int s = 0; s < U; s++) {
         const int k = k0 + (sub + s) * 32 + 8 * t;
-        float4 nw0 = make_float4(0.f, 0.f, 0.f, 0.f), nw1 = nw0;
-        if (NORM && k < K) {
-          nw0 = __ldg(reinterpret_cast<const float4*>(nm.w + k));
-          nw1 = __ldg(reinterpret_cast<const float4*>(nm.w + k + 4));
-        }
 #pragma unroll
         for (int j = 0; j < NT; j++) {
           const int m = j * 8 + g;
-          uint4 x = make_uint4(0u, 0u, 0u, 0u);
-          if (m < M && k < K) {
-            if (NORM) {
-              const float* xp = nm.x32 + (size_t)m * ldx + k;
-              const float4 a0 = __ldg(reinterpret_cast<const float4*>(xp)), a1 = __ldg(reinterpret_cast<const float4*>(xp + 4));
-              x.x = pack2(a0.x * nw0.x, a0.y * nw0.y);
-              x.y = pack2(a0.z * nw0.z, a0.w * nw0.w);
-              x.z = pack2(a1.x * nw1.x, a1.y * nw1.y);
-              x.w = pack2(a1.z * nw1.z, a1.w * nw1.w);
-            } else {
-              x = ld_cached16(X + (size_t)m * ldx + k);
-            }
-          }
+          const uint4 x = (m < M && k < K) ? ld_cached16(X + (size_t)m * ldx + k) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
           for (int a = 0; a < MT; a++) {
             mma_16816(acc[a][j], w[a][0][s].x, w[a][1][s].x, w[a][0][s].y, w[a][1][s].y, x.x, x.y);
@@ -284,6 +267,7 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
           const size_t o = (size_t)m * ldo + n;
           xn = ((float*)out)[o] + (s + (bias ? bias[n] : 0.f));
           ((float*)out)[o] = xn;
+          if (nm.xw_out) nm.xw_out[o] = __float2bfloat16_rn(xn * nm.w_next[n]);
         }
         float sq = xn * xn;
         for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
@@ -371,59 +355,62 @@ static int skinny_checks(const void* X, const void* W, const float* bias, int mo
 // bias float32 [N] or null, out [M, N] (row stride ldo) in the dtype of the mode.
 // Accepts 1 <= M <= 64, any N, K a multiple of 8 (16-byte rows), 16-byte aligned X, W and ldx % 8 == 0.
 // ssq_out (mode 1 only, may be null): [M, ceil(N / 16)] partial sums of squares of the updated rows.
+// w_next / xw_out (mode 1 with ssq_out, may be null): weight [N] of the norm that follows, and where to put
+// bf16(updated row * that weight), [M, N] with row stride ldo.
 extern "C" int cima_linear_skinny(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N,
-                                  int K, int ldx, int ldo, float* ssq_out, cudaStream_t stream) {
+                                  int K, int ldx, int ldo, float* ssq_out, const float* w_next, void* xw_out,
+                                  cudaStream_t stream) {
   if (M <= 0) return 0;
   int rc = skinny_checks(X, W, bias, mode, M, N, K, ldx);
   if (rc) return rc;
-  SkinnyNorm nm{nullptr, nullptr, nullptr, 0, 0.f, mode == SK_ACCUM ? ssq_out : nullptr};
+  if (xw_out && (mode != SK_ACCUM || !ssq_out || !w_next)) return cima_fail(CIMA_E_ARG, "linear_skinny: the scaled rows go with mode 1, the partial sums and the next norm's weight");
+  SkinnyNorm nm{nullptr, 0, 0.f, mode == SK_ACCUM ? ssq_out : nullptr,
+                mode == SK_ACCUM ? w_next : nullptr, mode == SK_ACCUM ? (__nv_bfloat16*)xw_out : nullptr};
   if (M <= 8) return dispatch_mode<1, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
   if (M <= 16) return dispatch_mode<2, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
   if (M <= 32) return dispatch_mode<4, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
   return dispatch_mode<8, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
 }
 
-// The same with RMSNorm folded in: x32 [M, K] float32 residual rows (row stride ldx), norm weight [K],
-// ssq [M, parts] partial sums of squares of those rows, eps.  At most 16 rows.
-extern "C" int cima_linear_skinny_norm(const float* x32, const float* norm_w, const float* ssq, int parts, float eps,
-                                       const void* W, const float* bias, void* out, int mode, int M, int N, int K,
-                                       int ldx, int ldo, cudaStream_t stream) {
+// The same with RMSNorm folded in: xw [M, K] bf16 = bf16(x * w) as cima_embed or an accumulating product left
+// it (row stride ldx), ssq [M, parts] the partial sums of squares of the rows x, and eps.  At most 16 rows.
+extern "C" int cima_linear_skinny_norm(const void* xw, const float* ssq, int parts, float eps, const void* W,
+                                       const float* bias, void* out, int mode, int M, int N, int K, int ldx, int ldo,
+                                       cudaStream_t stream) {
   if (M <= 0) return 0;
   if (M > 16) return cima_fail(CIMA_E_SIZE, "linear_skinny_norm: %d rows; the folded norm takes at most 16", M);
-  if (!x32 || !norm_w || !ssq || parts <= 0) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: the residual rows, the norm weight and the partial sums are needed");
-  if (ldx % 4 || ((uintptr_t)x32 | (uintptr_t)norm_w) & 15) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: x and the norm weight must be 16-byte aligned");
+  if (!ssq || parts <= 0) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: the partial sums of squares are needed");
   if (mode == SK_ACCUM) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: the accumulating epilogue reads activations, not the residual");
-  int rc = skinny_checks(W, W, bias, mode, M, N, K, 8);
+  int rc = skinny_checks(xw, W, bias, mode, M, N, K, ldx);
   if (rc) return rc;
-  SkinnyNorm nm{x32, norm_w, ssq, parts, eps, nullptr};
-  if (M <= 8) return dispatch_mode<1, true>(mode, nullptr, W, bias, out, M, N, K, ldx, ldo, nm, stream);
-  return dispatch_mode<2, true>(mode, nullptr, W, bias, out, M, N, K, ldx, ldo, nm, stream);
+  SkinnyNorm nm{ssq, parts, eps, nullptr, nullptr, nullptr};
+  if (M <= 8) return dispatch_mode<1, true>(mode, xw, W, bias, out, M, N, K, ldx, ldo, nm, stream);
+  return dispatch_mode<2, true>(mode, xw, W, bias, out, M, N, K, ldx, ldo, nm, stream);
 }
 
 // Mode 4 (see SkinnyRope): qkv [M, (nh + 2 nkv) * hd] receives the rotated q; k and v go to the cache.
-// Activations either as bf16 rows X (x32 == null) or as float32 residual rows with the norm folded in.
+// X: bf16 activations, or (ssq != null) bf16(x * w) with the partial sums of the rows: the norm folded in.
 // At most 16 rows; head_dim a multiple of 16; every dimension of a head rotates (rotary_dim == head_dim).
-extern "C" int cima_qkv_rope_skinny(const void* X, const float* x32, const float* norm_w, const float* ssq, int parts,
-                                    float eps, const void* W, const float* bias, void* qkv, int M, int K, int ldx,
-                                    int ldo, const float* inv_freq, const int* row_pos, const int* row_seq,
+extern "C" int cima_qkv_rope_skinny(const void* X, const float* ssq, int parts, float eps, const void* W,
+                                    const float* bias, void* qkv, int M, int K, int ldx, int ldo,
+                                    const float* inv_freq, const int* row_pos, const int* row_seq,
                                     const int* seq_slot, void* cache, const int* table, int table_width, int ring,
                                     int page_size, int nh, int nkv, int hd, cudaStream_t stream) {
   if (M <= 0) return 0;
-  if (M > 16) return cima_fail(CIMA_E_SIZE, "qkv_rope_skinny: %d rows; at most 16", M);
+  if (M > 16) return cima_fail(CIMA_E_SIZE, "qkv_rope_skinny: %d rows; this kernel takes at most 16", M);
   if (hd <= 0 || hd % 16 || nh <= 0 || nkv <= 0) return cima_fail(CIMA_E_SIZE, "qkv_rope_skinny: head_dim %d must be a multiple of 16 and the head counts positive", hd);
   if (!cache || !table || !inv_freq || !row_pos || !row_seq || !seq_slot) return cima_fail(CIMA_E_ARG, "qkv_rope_skinny: positions, frequencies and the cache are needed");
   const int N = (nh + 2 * nkv) * hd;
-  const bool norm = x32 != nullptr;
-  if (norm && (!norm_w || !ssq || parts <= 0 || ldx % 4 || (((uintptr_t)x32 | (uintptr_t)norm_w) & 15)))
-    return cima_fail(CIMA_E_ARG, "qkv_rope_skinny: the folded norm needs aligned rows, its weight and the partial sums");
-  int rc = skinny_checks(norm ? W : X, W, bias, SK_STORE, M, N, K, norm ? 8 : ldx);
+  const bool norm = ssq != nullptr;
+  if (norm && parts <= 0) return cima_fail(CIMA_E_ARG, "qkv_rope_skinny: the folded norm needs the number of partial sums");
+  int rc = skinny_checks(X, W, bias, SK_STORE, M, N, K, ldx);
   if (rc) return rc;
-  SkinnyNorm nm{x32, norm_w, ssq, parts, eps, nullptr};
+  SkinnyNorm nm{ssq, parts, eps, nullptr, nullptr, nullptr};
   SkinnyRope rp{inv_freq, row_pos, row_seq, seq_slot, (__nv_bfloat16*)cache,
                 CimaPaged{table, table_width, ring, page_size, nkv, hd}, nh, nkv, hd};
   if (norm) {
-    if (M <= 8) return launch_skinny<1, 1, 4, SK_QKV_ROPE, true>(nullptr, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
-    return launch_skinny<2, 1, 4, SK_QKV_ROPE, true>(nullptr, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
+    if (M <= 8) return launch_skinny<1, 1, 4, SK_QKV_ROPE, true>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
+    return launch_skinny<2, 1, 4, SK_QKV_ROPE, true>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
   }
   if (M <= 8) return launch_skinny<1, 1, 4, SK_QKV_ROPE, false>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
   return launch_skinny<2, 1, 4, SK_QKV_ROPE, false>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);

@@ -129,13 +129,20 @@ class Model:
         # What a kernel leaves behind about the rows it wrote travels along as a RowsInfo, so that norms are
         # folded into the products around them (few rows) or run together with the residual add (many rows).
         info = None
+        order = [self.blocks[layer] for layer in s.schedule]
         if batch.n_rows <= FOLDED_NORM_ROWS and not self.rt.full_precision:
             ssq = self.rt.empty(batch.n_rows, 1, dtype=torch.float32)
-            K_.embed(batch.tokens, self.embedding, x, s.embed_scale, ssq)
-            info = RowsInfo(ssq=ssq)
+            first = getattr(order[0], "mixer_norm", None) if order else self.final_norm
+            if (getattr(first, "weight", None) is not None and first.spec.kind == "rmsnorm"
+                    and first.spec.size == s.hidden):
+                xw = self.rt.empty(batch.n_rows, s.hidden)
+                K_.embed(batch.tokens, self.embedding, x, s.embed_scale, ssq, first.weight, xw)
+                info = RowsInfo(ssq=ssq, xw=xw, xw_norm=first)
+            else:
+                K_.embed(batch.tokens, self.embedding, x, s.embed_scale, ssq)
+                info = RowsInfo(ssq=ssq)
         else:
             K_.embed(batch.tokens, self.embedding, x, s.embed_scale)
-        order = [self.blocks[layer] for layer in s.schedule]
         for site, block in enumerate(order):
             if site + 1 < len(order):
                 nxt = getattr(order[site + 1], "mixer_norm", None)
@@ -155,7 +162,9 @@ class Model:
         if info is not None and getattr(info, "norm", None) is self.final_norm and info.h is not None:
             return self.head.logits(info.h)
         if hasattr(self.final_norm, "lazy"):
-            return self.head.logits(self.final_norm.lazy(x, getattr(info, "ssq", None) if info is not None else None))
+            ssq = getattr(info, "ssq", None) if info is not None else None
+            xw = info.xw if (info is not None and getattr(info, "xw_norm", None) is self.final_norm) else None
+            return self.head.logits(self.final_norm.lazy(x, ssq, xw))
         return self.head.logits(self.final_norm(x))
 
 

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 11
+ABI_VERSION = 12
 
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
@@ -36,7 +36,7 @@ def dtype_code(dt: torch.dtype) -> int:
 _vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
 
 _SIGNATURES = {
-    "cima_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp, _vp],
+    "cima_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp, _vp, _vp, _vp],
     "cima_rmsnorm": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "cima_swiglu": [_vp, _vp, _i, _i, _i, _vp],
     "cima_add_residual": [_vp, _vp, _i, _sz, _vp],
@@ -44,9 +44,9 @@ _SIGNATURES = {
     "cima_add_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "cima_decode_advance": [_vp, _vp, _vp, _vp, _i, _vp],
     "cima_linear_plain": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "cima_linear_skinny": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
-    "cima_linear_skinny_norm": [_vp, _vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
-    "cima_qkv_rope_skinny": [_vp, _vp, _vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
+    "cima_linear_skinny": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
+    "cima_linear_skinny_norm": [_vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_qkv_rope_skinny": [_vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
                              _i, _i, _i, _i, _vp],
     "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_attention_plain": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
@@ -114,8 +114,10 @@ class Kernels:
 
     # ------------------------------------------------------------------ elementwise
     def embed(self, ids: torch.Tensor, table: torch.Tensor, x: torch.Tensor, scale: float = 1.0,
-              ssq: Optional[torch.Tensor] = None) -> None:
-        """x[t] = scale * table[ids[t]]; ``ssq`` [T, 1] (optional) receives each row's sum of squares."""
+              ssq: Optional[torch.Tensor] = None, w_next: Optional[torch.Tensor] = None,
+              xw: Optional[torch.Tensor] = None) -> None:
+        """x[t] = scale * table[ids[t]]; ``ssq`` [T, 1] (optional) receives each row's sum of squares, ``xw``
+        [T, H] bf16 (optional) the rows times ``w_next`` (the weight of the norm that follows)."""
         self._need(ids, "ids", torch.int32, 1); self._need(table, "table", None, 2); self._need(x, "x", torch.float32, 2)
         T, (V, H) = ids.numel(), table.shape
         if tuple(x.shape) != (T, H):
@@ -124,8 +126,13 @@ class Kernels:
             self._need(ssq, "ssq", torch.float32, 2)
             if tuple(ssq.shape) != (T, 1):
                 raise KernelError(f"embed: ssq is {tuple(ssq.shape)}, expected {(T, 1)}")
+        if xw is not None:
+            self._need(xw, "xw", torch.bfloat16, 2); self._need(w_next, "w_next", torch.float32, 1)
+            if tuple(xw.shape) != (T, H) or w_next.numel() != H:
+                raise KernelError(f"embed: xw {tuple(xw.shape)} / w_next {tuple(w_next.shape)} do not fit {(T, H)}")
         self._check(self.lib.cima_embed(ids.data_ptr(), table.data_ptr(), dtype_code(table.dtype), x.data_ptr(),
-                                        T, H, V, scale, _ptr(ssq), self._stream()), "embed")
+                                        T, H, V, scale, _ptr(ssq), _ptr(w_next) if xw is not None else None, _ptr(xw),
+                                        self._stream()), "embed")
 
     def rmsnorm(self, x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor) -> None:
         self._need(x, "x", torch.float32, 2); self._need(w, "w", torch.float32, 1); self._need(out, "out", None, 2)
@@ -201,9 +208,11 @@ class Kernels:
                                                    K, N, self._stream()), "linear_plain")
 
     def linear_skinny(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                      mode: int, ssq_out: Optional[torch.Tensor] = None) -> None:
+                      mode: int, ssq_out: Optional[torch.Tensor] = None, w_next: Optional[torch.Tensor] = None,
+                      xw_out: Optional[torch.Tensor] = None) -> None:
         """Few rows (<= 64), bf16 operands; ``mode`` is one of SK_*.  For SK_SWIGLU ``w`` is [2N, K].
-        With SK_ACCUM, ``ssq_out`` [M, ceil(N / 16)] receives partial sums of squares of the updated rows."""
+        With SK_ACCUM, ``ssq_out`` [M, ceil(N / 16)] receives partial sums of squares of the updated rows and
+        ``xw_out`` [M, N] bf16 the updated rows times ``w_next`` (the weight of the norm that follows)."""
         self._need(a, "a", torch.bfloat16, 2); self._need(w, "w", torch.bfloat16, 2); self._need(out, "out", None, 2)
         M, K = a.shape
         N = w.shape[0] // 2 if mode == SK_SWIGLU else w.shape[0]
@@ -220,34 +229,39 @@ class Kernels:
             if mode != SK_ACCUM or tuple(ssq_out.shape) != (M, -(-N // 16)):
                 raise KernelError(f"linear_skinny: ssq_out {tuple(ssq_out.shape)} goes with the accumulating mode and "
                                   f"must be {(M, -(-N // 16))}")
+        if xw_out is not None:
+            self._need(xw_out, "xw_out", torch.bfloat16, 2); self._need(w_next, "w_next", torch.float32, 1)
+            if ssq_out is None or tuple(xw_out.shape) != (M, N) or w_next.numel() != N:
+                raise KernelError("linear_skinny: xw_out goes with ssq_out and must be [rows, N], w_next [N]")
         self._check(self.lib.cima_linear_skinny(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode,
-                                                M, N, K, K, N, _ptr(ssq_out), self._stream()), "linear_skinny")
+                                                M, N, K, K, N, _ptr(ssq_out), _ptr(w_next) if xw_out is not None else None,
+                                                _ptr(xw_out), self._stream()), "linear_skinny")
 
-    def linear_skinny_norm(self, x: torch.Tensor, norm_w: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tensor,
+    def linear_skinny_norm(self, xw: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tensor,
                            bias: Optional[torch.Tensor], out: torch.Tensor, mode: int) -> None:
-        """``linear_skinny`` of RMSNorm(x): x [M, K] float32 residual rows (M <= 16), ``ssq`` [M, parts] partial
-        sums of squares of those rows (as ``embed`` or an accumulating ``linear_skinny`` left them)."""
-        self._need(x, "x", torch.float32, 2); self._need(norm_w, "norm_w", torch.float32, 1)
-        self._need(ssq, "ssq", torch.float32, 2); self._need(w, "w", torch.bfloat16, 2); self._need(out, "out", None, 2)
-        M, K = x.shape
+        """``linear_skinny`` of RMSNorm(x) for at most 16 rows: ``xw`` [M, K] bf16 = bf16(x * norm weight) and
+        ``ssq`` [M, parts], the partial sums of squares of the rows x, as ``embed`` or an accumulating
+        ``linear_skinny`` left them."""
+        self._need(xw, "xw", torch.bfloat16, 2); self._need(ssq, "ssq", torch.float32, 2)
+        self._need(w, "w", torch.bfloat16, 2); self._need(out, "out", None, 2)
+        M, K = xw.shape
         N = w.shape[0] // 2 if mode == SK_SWIGLU else w.shape[0]
         want = torch.float32 if mode == SK_STORE_F32 else torch.bfloat16
-        if (w.shape[1] != K or norm_w.numel() != K or ssq.shape[0] != M or tuple(out.shape) != (M, N)
-                or out.dtype is not want):
-            raise KernelError(f"linear_skinny_norm(mode {mode}): x {tuple(x.shape)}, w {tuple(w.shape)}, ssq "
+        if w.shape[1] != K or ssq.shape[0] != M or tuple(out.shape) != (M, N) or out.dtype is not want:
+            raise KernelError(f"linear_skinny_norm(mode {mode}): xw {tuple(xw.shape)}, w {tuple(w.shape)}, ssq "
                               f"{tuple(ssq.shape)}, out {tuple(out.shape)} {out.dtype} do not agree")
         if bias is not None:
             self._need(bias, "bias", torch.float32, 1)
-        self._check(self.lib.cima_linear_skinny_norm(x.data_ptr(), norm_w.data_ptr(), ssq.data_ptr(), ssq.shape[1], eps,
-                                                     w.data_ptr(), _ptr(bias), out.data_ptr(), mode, M, N, K, K, N,
-                                                     self._stream()), "linear_skinny_norm")
+        self._check(self.lib.cima_linear_skinny_norm(xw.data_ptr(), ssq.data_ptr(), ssq.shape[1], eps, w.data_ptr(),
+                                                     _ptr(bias), out.data_ptr(), mode, M, N, K, K, N, self._stream()),
+                    "linear_skinny_norm")
 
     def qkv_rope(self, a, w: torch.Tensor, bias: Optional[torch.Tensor], qkv: torch.Tensor, inv_freq: torch.Tensor,
                  row_pos, row_seq, seq_slot, kv, n_heads: int, n_kv_heads: int, head_dim: int, norm=None) -> None:
         """The q/k/v projection of a decode step (at most 16 rows) with rotation and cache append in its
         epilogue: the rotated q lands in ``qkv`` [rows, (heads + 2 kv_heads) * head_dim], k and v in the layer's
-        pages.  ``a``: bf16 activations, or with ``norm = (norm_weight, ssq, eps)`` the float32 residual rows
-        whose RMSNorm is folded in."""
+        pages.  ``a``: bf16 activations, or with ``norm = (ssq, eps)`` the rows bf16(x * norm weight) and
+        the partial sums of squares of x: the RMSNorm is folded in."""
         self._need(w, "w", torch.bfloat16, 2); self._need(qkv, "qkv", torch.bfloat16, 2)
         self._need(inv_freq, "inv_freq", torch.float32, 1)
         M, K = a.shape
@@ -260,13 +274,15 @@ class Kernels:
             raise KernelError(f"qkv_rope: cache pages are {tuple(kv.storage.shape)}")
         if bias is not None:
             self._need(bias, "bias", torch.float32, 1)
+        self._need(a, "a", torch.bfloat16, 2)
         if norm is None:
-            self._need(a, "a", torch.bfloat16, 2)
-            head = (a.data_ptr(), None, None, None, 0, 0.0)
+            head = (a.data_ptr(), None, 0, 0.0)
         else:
-            nw, ssq, eps = norm
-            self._need(a, "x", torch.float32, 2); self._need(nw, "norm_w", torch.float32, 1); self._need(ssq, "ssq", torch.float32, 2)
-            head = (None, a.data_ptr(), nw.data_ptr(), ssq.data_ptr(), ssq.shape[1], eps)
+            ssq, eps = norm
+            self._need(ssq, "ssq", torch.float32, 2)
+            if ssq.shape[0] != M:
+                raise KernelError(f"qkv_rope: ssq {tuple(ssq.shape)} does not fit {M} rows")
+            head = (a.data_ptr(), ssq.data_ptr(), ssq.shape[1], eps)
         self._check(self.lib.cima_qkv_rope_skinny(*head, w.data_ptr(), _ptr(bias), qkv.data_ptr(), M, K, K, N,
                                                   inv_freq.data_ptr(), row_pos.data_ptr(), row_seq.data_ptr(),
                                                   seq_slot.data_ptr(), kv.storage.data_ptr(), kv.block_table.data_ptr(),

@@ -81,9 +81,9 @@ class Attention:
             # decoding: projection, rotation and the append to the cache as one kernel
             qkv = self.rt.empty(rows, self.qd + 2 * self.kvd)
             if self.qkv._folds(h, rows):
-                K_.qkv_rope(h.x, self.qkv.weight, self.qkv.bias, qkv, self.position.inv_freq, batch.row_pos,
+                K_.qkv_rope(h.xw, self.qkv.weight, self.qkv.bias, qkv, self.position.inv_freq, batch.row_pos,
                             batch.row_seq, batch.seq_slot, kv, s.n_heads, s.n_kv_heads, s.head_dim,
-                            norm=(h.norm.weight, h.ssq, h.norm.spec.eps))
+                            norm=(h.ssq, h.norm.spec.eps))
             else:
                 K_.qkv_rope(h.tensor() if hasattr(h, "tensor") else h, self.qkv.weight, self.qkv.bias, qkv,
                             self.position.inv_freq, batch.row_pos, batch.row_seq, batch.seq_slot, kv, s.n_heads,

@@ -61,7 +61,9 @@ class PreNormBlock:
         if info is not None and getattr(info, "norm", None) is norm and info.h is not None:
             h = info.h                                             # the rows came normalised already
         elif getattr(part, "takes_pending_norm", False) and hasattr(norm, "lazy"):
-            h = norm.lazy(x, getattr(info, "ssq", None) if info is not None else None)
+            ssq = getattr(info, "ssq", None) if info is not None else None
+            xw = info.xw if (info is not None and getattr(info, "xw_norm", None) is norm) else None
+            h = norm.lazy(x, ssq, xw)
         else:
             h = norm(x)
         if getattr(part, "takes_next_norm", False):

@@ -43,10 +43,10 @@ class Linear:
     # ------------------------------------------------------------------ products
     def _folds(self, a, rows: int) -> bool:
         """Whether ``a`` is a pending RMSNorm that the skinny kernel can fold in."""
-        # every 16-feature tile of the product re-reads the float32 rows and the norm's weight: worth it for
-        # a layer's projections, not for a head of a hundred thousand features (measured on B200)
-        return (hasattr(a, "tensor") and a.ssq is not None and self._skinny(rows) and rows <= FOLDED_NORM_ROWS
-                and a.norm.spec.kind == "rmsnorm" and self.N <= FOLDED_NORM_FEATURES)
+        # every 16-feature tile of the product re-reads the rows' partial sums: worth it for a layer's
+        # projections, not for a head of a hundred thousand features (measured on B200)
+        return (hasattr(a, "tensor") and a.ssq is not None and a.xw is not None and self._skinny(rows)
+                and rows <= FOLDED_NORM_ROWS and a.norm.spec.kind == "rmsnorm" and self.N <= FOLDED_NORM_FEATURES)
 
     def store(self, a, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """a W^T + bias in the activation dtype (``a``: activations, or a pending norm)."""
@@ -57,7 +57,7 @@ class Linear:
         if M == 0:
             return out
         if self._folds(a, M):
-            K_.linear_skinny_norm(a.x, a.norm.weight, a.ssq, a.norm.spec.eps, self.weight, self.bias, out, SK_STORE)
+            K_.linear_skinny_norm(a.xw, a.ssq, a.norm.spec.eps, self.weight, self.bias, out, SK_STORE)
             return out
         if hasattr(a, "tensor"):
             a = a.tensor()
@@ -87,9 +87,19 @@ class Linear:
         if self._plain():
             K_.linear_plain(a, self.weight, self.bias, x, accumulate=True)
         elif self._skinny(M):
-            ssq = self.rt.empty(M, -(-self.N // 16), dtype=torch.float32) if M <= FOLDED_NORM_ROWS else None
+            if M > FOLDED_NORM_ROWS:
+                K_.linear_skinny(a, self.weight, self.bias, x, SK_ACCUM)
+                return None
+            ssq = self.rt.empty(M, -(-self.N // 16), dtype=torch.float32)
+            if (next_norm is not None and getattr(next_norm, "weight", None) is not None
+                    and next_norm.spec.kind == "rmsnorm" and next_norm.spec.size == self.N):
+                # the rows also leave multiplied by the next norm's weight: the product after that norm then
+                # reads plain bf16 activations and applies the rows' factors at its end
+                xw = self.rt.empty(M, self.N)
+                K_.linear_skinny(a, self.weight, self.bias, x, SK_ACCUM, ssq, next_norm.weight, xw)
+                return RowsInfo(ssq=ssq, xw=xw, xw_norm=next_norm)
             K_.linear_skinny(a, self.weight, self.bias, x, SK_ACCUM, ssq)
-            return RowsInfo(ssq=ssq) if ssq is not None else None
+            return RowsInfo(ssq=ssq)
         elif (next_norm is not None and getattr(next_norm, "weight", None) is not None
               and next_norm.spec.kind == "rmsnorm" and next_norm.spec.size == self.N and hasattr(K_, "add_rmsnorm")):
             h = self.rt.empty(M, self.N)
@@ -107,7 +117,7 @@ class Linear:
         if M == 0:
             return out
         if self._folds(a, M):
-            K_.linear_skinny_norm(a.x, a.norm.weight, a.ssq, a.norm.spec.eps, self.weight, self.bias, out, SK_STORE_F32)
+            K_.linear_skinny_norm(a.xw, a.ssq, a.norm.spec.eps, self.weight, self.bias, out, SK_STORE_F32)
             return out
         if hasattr(a, "tensor"):
             a = a.tensor()
@@ -144,7 +154,7 @@ class GatedLinearPair:
         if M == 0:
             return out
         if self.lin._folds(a, M):
-            K_.linear_skinny_norm(a.x, a.norm.weight, a.ssq, a.norm.spec.eps, self.lin.weight, None, out, SK_SWIGLU)
+            K_.linear_skinny_norm(a.xw, a.ssq, a.norm.spec.eps, self.lin.weight, None, out, SK_SWIGLU)
             return out
         if hasattr(a, "tensor"):
             a = a.tensor()

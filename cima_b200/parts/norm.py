@@ -12,20 +12,22 @@ from .registry import register_norm
 
 class RowsInfo:
     """What the kernel that last wrote the residual rows left behind, handed from part to part:
-    ``ssq`` - partial sums of squares of the rows [rows, parts] (a skinny product can fold the next norm in);
+    ``ssq`` - partial sums of squares of the rows [rows, parts] (a skinny product can fold the next norm in),
+    with ``xw`` = bf16(rows * weight of ``xw_norm``) when the writer knew which norm follows;
     ``norm`` / ``h`` - the rows already normalised with that norm (the residual add and the norm ran as one)."""
 
-    def __init__(self, ssq=None, norm=None, h=None):
+    def __init__(self, ssq=None, norm=None, h=None, xw=None, xw_norm=None):
         self.ssq, self.norm, self.h = ssq, norm, h
+        self.xw, self.xw_norm = xw, xw_norm       # rows times the weight of ``xw_norm``, bf16 (goes with ssq)
 
 
 class NormedInput:
-    """RMSNorm(x) not yet computed.  A product that can fold the norm in (few rows, bf16) takes ``x``,
-    the norm's weight and ``ssq`` (partial sums of squares of x's rows, left by the kernel that wrote
-    them) directly; everything else calls ``tensor()`` and gets the normalised activations."""
+    """RMSNorm(x) not yet computed.  A product that can fold the norm in (few rows, bf16) takes ``xw``
+    (bf16(x * weight)) and ``ssq`` (partial sums of squares of x's rows), both left by the kernel that
+    wrote the rows; everything else calls ``tensor()`` and gets the normalised activations."""
 
-    def __init__(self, norm: "RMSNorm", x: torch.Tensor, ssq):
-        self.norm, self.x, self.ssq = norm, x, ssq
+    def __init__(self, norm: "RMSNorm", x: torch.Tensor, ssq, xw=None):
+        self.norm, self.x, self.ssq, self.xw = norm, x, ssq, xw
         self._h = None
 
     @property
@@ -52,8 +54,8 @@ class RMSNorm:
     def nbytes(self) -> int:
         return self.weight.numel() * 4
 
-    def lazy(self, x: torch.Tensor, ssq=None) -> NormedInput:
-        return NormedInput(self, x, ssq)
+    def lazy(self, x: torch.Tensor, ssq=None, xw=None) -> NormedInput:
+        return NormedInput(self, x, ssq, xw)
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         out = self.rt.empty(*x.shape)

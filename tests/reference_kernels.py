@@ -34,10 +34,12 @@ class ReferenceKernels:
         self.launches = 0
 
     # ------------------------------------------------------------------ elementwise
-    def embed(self, ids, table, x, scale=1.0, ssq=None):
+    def embed(self, ids, table, x, scale=1.0, ssq=None, w_next=None, xw=None):
         x.copy_(table[ids.long()].float() * scale)
         if ssq is not None:
             ssq.copy_((x.double() ** 2).sum(dim=1, keepdim=True).float())
+        if xw is not None:
+            xw.copy_((x * w_next).to(xw.dtype))
 
     def rmsnorm(self, x, w, eps, out):
         xc = x.to(self.compute)
@@ -74,12 +76,12 @@ class ReferenceKernels:
         else:
             out.copy_(y.to(out.dtype))
 
-    def linear_skinny_norm(self, x, norm_w, ssq, eps, w, bias, out, mode):
-        inv = 1.0 / torch.sqrt(ssq.to(self.compute).sum(dim=1, keepdim=True) / x.shape[1] + eps)
-        h = (x.to(self.compute) * inv * norm_w.to(self.compute)).to(torch.bfloat16)
+    def linear_skinny_norm(self, xw, ssq, eps, w, bias, out, mode):
+        inv = 1.0 / torch.sqrt(ssq.to(self.compute).sum(dim=1, keepdim=True) / xw.shape[1] + eps)
+        h = (xw.to(self.compute) * inv).to(torch.bfloat16)
         self.linear_skinny(h, w, bias, out, mode)
 
-    def linear_skinny(self, a, w, bias, out, mode, ssq_out=None):
+    def linear_skinny(self, a, w, bias, out, mode, ssq_out=None, w_next=None, xw_out=None):
         y = a.to(self.compute) @ w.to(self.compute).t()
         if mode == SK_SWIGLU:
             I = w.shape[0] // 2
@@ -95,15 +97,17 @@ class ReferenceKernels:
                 sq = torch.zeros(out.shape[0], ssq_out.shape[1] * 16, dtype=torch.float64)
                 sq[:, :N] = out.double() ** 2
                 ssq_out.copy_(sq.view(out.shape[0], -1, 16).sum(dim=2).float())
+            if xw_out is not None:
+                xw_out.copy_((out * w_next).to(xw_out.dtype))
         else:
             out.copy_(y.to(out.dtype))
 
     # ------------------------------------------------------------------ attention
     def qkv_rope(self, a, w, bias, qkv, inv_freq, row_pos, row_seq, seq_slot, kv, n_heads, n_kv_heads, head_dim, norm=None):
         if norm is not None:
-            nw, ssq, eps = norm
+            ssq, eps = norm
             inv = 1.0 / torch.sqrt(ssq.to(self.compute).sum(dim=1, keepdim=True) / a.shape[1] + eps)
-            a = (a.to(self.compute) * inv * nw.to(self.compute)).to(torch.bfloat16)
+            a = (a.to(self.compute) * inv).to(torch.bfloat16)
         y = a.to(self.compute) @ w.to(self.compute).t()
         if bias is not None:
             y = y + bias.to(self.compute)

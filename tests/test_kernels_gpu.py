@@ -426,7 +426,14 @@ def test_skinny_accumulate_leaves_sums_of_squares_and_the_next_product_folds_the
     want_x = x0.double() + a.double() @ w1.double().t()
     assert err(x, want_x) <= 1e-4
     assert err(ssq.sum(dim=1), (x.double() ** 2).sum(dim=1)) <= 1e-3 * max(1.0, float((want_x ** 2).sum(dim=1).max()))
+    # the writer also leaves the rows times the next norm's weight; the product after the norm reads those
     nw = 1 + g(H, seed=4, scale=0.1)
+    xb = x0.cuda()
+    ssq_b = torch.full_like(ssq, -1.0)
+    xw = torch.full((M, H), 9.0, dtype=torch.bfloat16, device="cuda")
+    K.linear_skinny(a.cuda(), w1.cuda(), None, xb, SK_ACCUM, ssq_b, nw.cuda(), xw)
+    assert torch.equal(xb, x) and torch.equal(ssq_b, ssq)
+    assert torch.equal(xw, (x * nw.cuda()).to(torch.bfloat16))
     eps = 1e-5
     xd = x.double().cpu()
     h = (xd / torch.sqrt((xd * xd).mean(dim=1, keepdim=True) + eps) * nw.double())
@@ -434,14 +441,14 @@ def test_skinny_accumulate_leaves_sums_of_squares_and_the_next_product_folds_the
     b2 = g(2 * 96, seed=6)
     want = h @ w2.double().t()
     out = torch.empty(M, 192, dtype=torch.bfloat16, device="cuda")
-    K.linear_skinny_norm(x, nw.cuda(), ssq, eps, w2.cuda(), b2.cuda(), out, SK_STORE)
+    K.linear_skinny_norm(xw, ssq, eps, w2.cuda(), b2.cuda(), out, SK_STORE)
     assert err(out, want + b2.double()) <= TOL["bfloat16"] * 4
     out32 = torch.empty(M, 192, device="cuda")
-    K.linear_skinny_norm(x, nw.cuda(), ssq, eps, w2.cuda(), None, out32, SK_STORE_F32)
+    K.linear_skinny_norm(xw, ssq, eps, w2.cuda(), None, out32, SK_STORE_F32)
     # the operand is bf16(x * w): one bfloat16 rounding per term against the float64 statement
     assert err(out32, want) <= TOL["bfloat16"] * 2
     act = torch.empty(M, 96, dtype=torch.bfloat16, device="cuda")
-    K.linear_skinny_norm(x, nw.cuda(), ssq, eps, w2.cuda(), None, act, SK_SWIGLU)
+    K.linear_skinny_norm(xw, ssq, eps, w2.cuda(), None, act, SK_SWIGLU)
     gg, uu = want[:, :96], want[:, 96:]
     assert err(act, gg / (1 + torch.exp(-gg)) * uu) <= TOL["bfloat16"] * 4
 
@@ -453,6 +460,12 @@ def test_embed_leaves_sums_of_squares(K):
     ssq = torch.empty(3, 1, device="cuda")
     K.embed(ids.cuda(), table.cuda(), x, 1.0, ssq)
     assert err(ssq[:, 0], (table[ids.long()].double() ** 2).sum(dim=1)) <= 1e-3
+    nw = (1 + g(200, seed=4, scale=0.1)).cuda()
+    x2, ssq2 = torch.empty_like(x), torch.empty_like(ssq)
+    xw = torch.empty(3, 200, dtype=torch.bfloat16, device="cuda")
+    K.embed(ids.cuda(), table.cuda(), x2, 1.0, ssq2, nw, xw)
+    assert torch.equal(x2, x) and torch.equal(ssq2, ssq)
+    assert torch.equal(xw, (x * nw).to(torch.bfloat16))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -524,18 +537,20 @@ def test_qkv_rope_skinny_equals_projection_then_rope_append(K, M, nh, nkv, hd, H
     K.qkv_rope(a.cuda(), w.cuda(), b.cuda(), qkv, inv.cuda(), bg.row_pos, bg.row_seq, bg.seq_slot, gpu, nh, nkv, hd)
     assert err(qkv[:, :nh * hd], want[:, :nh * hd]) <= TOL["bfloat16"] * 4
     assert err(gpu.storage, cpu.storage) <= TOL["bfloat16"] * 4
-    # with the norm folded in: x float32 rows, partial sums of squares as an accumulating product leaves them
+    # with the norm folded in: rows times the norm's weight and partial sums of squares, as an accumulating
+    # product leaves them
     x = g(M, H, seed=4, scale=1.5).cuda()
-    ssq = torch.empty(M, -(-H // 16), device="cuda")
-    zero_w = torch.zeros(H, 8, dtype=torch.bfloat16, device="cuda")
-    K.linear_skinny(torch.zeros(M, 8, dtype=torch.bfloat16, device="cuda"), zero_w, None, x, SK_ACCUM, ssq)
     nw = (1 + g(H, seed=5, scale=0.1))
+    ssq = torch.empty(M, -(-H // 16), device="cuda")
+    xw = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+    zero_w = torch.zeros(H, 8, dtype=torch.bfloat16, device="cuda")
+    K.linear_skinny(torch.zeros(M, 8, dtype=torch.bfloat16, device="cuda"), zero_w, None, x, SK_ACCUM, ssq, nw.cuda(), xw)
     xd = x.double().cpu()
     hh = xd / torch.sqrt((xd * xd).mean(dim=1, keepdim=True) + 1e-6) * nw.double()
     want2 = hh @ w.double().t() + b.double()
     cpu2, gpu2 = make_kv(n_pages, nkv, page, hd, M + 3, width, 0, 0, torch.bfloat16, tables)
     REF.rope_append(want2, inv, hd, bc.row_pos, bc.row_seq, bc.seq_slot, bc.seq_len, cpu2, nh, nkv, hd)
-    K.qkv_rope(x, w.cuda(), b.cuda(), qkv, inv.cuda(), bg.row_pos, bg.row_seq, bg.seq_slot, gpu2, nh, nkv, hd,
-               norm=(nw.cuda(), ssq, 1e-6))
+    K.qkv_rope(xw, w.cuda(), b.cuda(), qkv, inv.cuda(), bg.row_pos, bg.row_seq, bg.seq_slot, gpu2, nh, nkv, hd,
+               norm=(ssq, 1e-6))
     assert err(qkv[:, :nh * hd], want2[:, :nh * hd]) <= TOL["bfloat16"] * 4
     assert err(gpu2.storage, cpu2.storage) <= TOL["bfloat16"] * 4
