@@ -9,7 +9,7 @@
 // shared memory in warp order 0..7, so a result never depends on scheduling, and a row of X gives
 // the same bits whatever else is in the batch.  A matrix with few output features and a long K
 // (the down projection) would leave most of the GPU idle that way, so the blocks of a thread-block
-// cluster (1, 2, 4 or 8, chosen from the matrix's shape alone) split K further; block 0 of the
+// cluster (1 to 8, chosen from the matrix's shape alone) split K further; block 0 of the
 // cluster adds the blocks' sums in rank order through distributed shared memory and stores.
 //
 // Operand order.  mma.m16n8k16 wants, per thread, k = {2t, 2t+1, 2t+8, 2t+9} of rows g and g+8.
@@ -118,22 +118,6 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
     if (rp_rot) return rp_head * rp.hd + (r < 8 ? rp_sub * 8 + r : rp.hd / 2 + rp_sub * 8 + (r - 8));
     return rp_head * rp.hd + rp_sub * 16 + r;
   };
-  cima_pdl_wait();
-  // Folded norm: the rows' partial sums of squares are fetched now and added up after the K loop, so
-  // that their latency hides behind the weight stream; the factor inv = 1 / sqrt(sum / K + eps) of a
-  // row is applied to its finished dot products (the operand of the tensor core is bf16(x * w)).
-  __shared__ float inv_s[NT * 8];
-  constexpr int PARTS_MAX = 256;                         // partial sums per row staged in shared memory
-  __shared__ float ssq_s[NORM ? NT * 8 : 1][NORM ? PARTS_MAX : 1];
-  if (NORM) {
-    for (int m = warp; m < M; m += SK_WARPS)
-      for (int pidx = lane; pidx < nm.parts && pidx < PARTS_MAX; pidx += 32) {
-        const unsigned dst = (unsigned)__cvta_generic_to_shared(&ssq_s[m][pidx]);
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(nm.ssq + (size_t)m * nm.parts + pidx));
-      }
-    asm volatile("cp.async.commit_group;" ::);
-  }
-
   float acc[MT][NT][4];
 #pragma unroll
   for (int a = 0; a < MT; a++)
@@ -158,32 +142,65 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
   // and so the order of summation, is the same for every instantiation.  U only says how many of a
   // chunk's four 32-wide steps are loaded before they are multiplied.
   constexpr int CHUNK = 128;
-  for (int k0 = (crank * SK_WARPS + warp) * CHUNK; k0 < K; k0 += S * SK_WARPS * CHUNK) {
+  uint4 w[MT][2][U];
+  auto load_w = [&](int k0, int sub) {
 #pragma unroll
-    for (int sub = 0; sub < 4; sub += U) {
-      uint4 w[MT][2][U];
+    for (int s = 0; s < U; s++) {
+      const int k = k0 + (sub + s) * 32 + 8 * t;
 #pragma unroll
-      for (int s = 0; s < U; s++) {
-        const int k = k0 + (sub + s) * 32 + 8 * t;
+      for (int a = 0; a < MT; a++)
 #pragma unroll
-        for (int a = 0; a < MT; a++)
+        for (int h = 0; h < 2; h++)
+          w[a][h][s] = (wok[a][h] && k < K) ? ld_stream16(wrow[a][h] + k) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  };
+  auto multiply = [&](int k0, int sub) {
 #pragma unroll
-          for (int h = 0; h < 2; h++)
-            w[a][h][s] = (wok[a][h] && k < K) ? ld_stream16(wrow[a][h] + k) : make_uint4(0u, 0u, 0u, 0u);
-      }
+    for (int s = 0; s < U; s++) {
+      const int k = k0 + (sub + s) * 32 + 8 * t;
 #pragma unroll
-      for (int s = 0; s < U; s++) {
-        const int k = k0 + (sub + s) * 32 + 8 * t;
+      for (int j = 0; j < NT; j++) {
+        const int m = j * 8 + g;
+        const uint4 x = (m < M && k < K) ? ld_cached16(X + (size_t)m * ldx + k) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-        for (int j = 0; j < NT; j++) {
-          const int m = j * 8 + g;
-          const uint4 x = (m < M && k < K) ? ld_cached16(X + (size_t)m * ldx + k) : make_uint4(0u, 0u, 0u, 0u);
-#pragma unroll
-          for (int a = 0; a < MT; a++) {
-            mma_16816(acc[a][j], w[a][0][s].x, w[a][1][s].x, w[a][0][s].y, w[a][1][s].y, x.x, x.y);
-            mma_16816(acc[a][j], w[a][0][s].z, w[a][1][s].z, w[a][0][s].w, w[a][1][s].w, x.z, x.w);
-          }
+        for (int a = 0; a < MT; a++) {
+          mma_16816(acc[a][j], w[a][0][s].x, w[a][1][s].x, w[a][0][s].y, w[a][1][s].y, x.x, x.y);
+          mma_16816(acc[a][j], w[a][0][s].z, w[a][1][s].z, w[a][0][s].w, w[a][1][s].w, x.z, x.w);
         }
+      }
+    }
+  };
+  // The weights do not depend on the kernel before this one: the first loads of every warp are issued before
+  // the wait for it, so that the weight stream starts while that kernel's last blocks are still finishing.
+  const int k_first = (crank * SK_WARPS + warp) * CHUNK;
+  if (k_first < K) load_w(k_first, 0);
+  cima_pdl_wait();
+  // Folded norm: the rows' partial sums of squares are fetched now and added up after the K loop, so
+  // that their latency hides behind the weight stream; the factor inv = 1 / sqrt(sum / K + eps) of a
+  // row is applied to its finished dot products (the operand of the tensor core is bf16(x * w)).
+  __shared__ float inv_s[NT * 8];
+  constexpr int PARTS_MAX = 256;                         // partial sums per row staged in shared memory
+  __shared__ float ssq_s[NORM ? NT * 8 : 1][NORM ? PARTS_MAX : 1];
+  if (NORM) {
+    for (int m = warp; m < M; m += SK_WARPS)
+      for (int pidx = lane; pidx < nm.parts && pidx < PARTS_MAX; pidx += 32) {
+        const unsigned dst = (unsigned)__cvta_generic_to_shared(&ssq_s[m][pidx]);
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(nm.ssq + (size_t)m * nm.parts + pidx));
+      }
+    asm volatile("cp.async.commit_group;" ::);
+  }
+  if (k_first < K) {
+    multiply(k_first, 0);
+#pragma unroll
+    for (int sub = U; sub < 4; sub += U) {
+      load_w(k_first, sub);
+      multiply(k_first, sub);
+    }
+    for (int k0 = k_first + S * SK_WARPS * CHUNK; k0 < K; k0 += S * SK_WARPS * CHUNK) {
+#pragma unroll
+      for (int sub = 0; sub < 4; sub += U) {
+        load_w(k0, sub);
+        multiply(k0, sub);
       }
     }
   }
@@ -299,11 +316,23 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
   if (S > 1) cluster.sync();            // a block's shared memory must outlive block 0's reads of it
 }
 
-// Blocks per cluster for a matrix of `tiles` 16-feature tiles and K: enough blocks to fill the GPU,
-// never more virtual warps than K has chunks of 128.  Depends on the matrix only, never on the rows of X.
+// Blocks per cluster for a matrix of `tiles` 16-feature tiles and K: the largest power of two that keeps all
+// blocks resident at once (four blocks of 256 threads per SM) and leaves every warp at least two chunks of 128.
+// Measured inside the decode step of a 3584-wide model on B200 (tokens per second at batch 8, K 18944, 224
+// tiles): 2 blocks 2496, 4 blocks 2414, 1, 3, 5, 6 or 8 blocks 2230 to 2290: a second, partly filled wave
+// costs more than its parallelism brings, and clusters of odd size were slower than their neighbours.
+// Depends on the matrix and the device only, never on the rows of X, so that a row's sum has the same order
+// whatever the batch.
 static int cluster_size(int tiles, int K) {
+  static int resident = 0;
+  if (!resident) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    resident = sms * 4;
+  }
   int s = 1;
-  while (s < 8 && tiles * s < 1184 && (2 * s) * SK_WARPS * 128 <= K) s *= 2;
+  while (s < 8 && tiles * (2 * s) <= resident && (2 * s) * 2 * SK_WARPS * 128 <= K) s *= 2;
   return s;
 }
 
