@@ -58,18 +58,24 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+constexpr int MAX_SPLITS = 64;
+constexpr int STAGES = 3;         // pages in flight per block (two blocks of 3 x 34 KB fit an SM at head_dim 128)
+
+// early: the sequence's lengths, slots and block table, and every page before the one that holds the newest
+// position, are not written by the kernel launched just before this one (the q/k/v projection with its cache
+// append writes the newest position only); the first pages are then fetched before the wait on that kernel.
 template <int HD>
 __global__ void __launch_bounds__(WARPS * 32)
 k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfloat16* __restrict__ cache,
                    CimaPaged pg, const int* __restrict__ seq_slot, const int* __restrict__ seq_len,
                    float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int ldo,
-                   int nh, int nkv, int mtiles, float scale, int window, int n_splits) {
-  cima_pdl_wait();
+                   int nh, int nkv, int mtiles, float scale, int window, int n_splits, int early) {
+  if (!early) cima_pdl_wait();
   constexpr int ROW = HD + 8;                         // padded row of a tile, in elements (16 bytes of padding)
   constexpr int TILE = PS * ROW;                      // elements of one K or V tile
   constexpr int KSTEPS = HD / 16, NTILES = HD / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [2 stages][K|V][PS][ROW]
+  __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [STAGES][K|V][PS][ROW]
 
   const int split = blockIdx.x;
   const int kvh = blockIdx.y / mtiles, mt = blockIdx.y % mtiles;
@@ -85,9 +91,46 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   const int slot = seq_slot[b];
   const int lo = (window > 0 && len > window) ? len - window : 0;
   const int pf = lo / PS, pl = (len - 1) / PS;
-  const int per = (pl - pf + 1 + n_splits - 1) / n_splits;
-  const int p0 = pf + split * per;
-  const int p1 = min(p0 + per, pl + 1);
+  const int npages = pl - pf + 1;                      // shared evenly: split s takes pages [s n / S, (s + 1) n / S)
+  const int p0 = pf + (int)((long long)split * npages / n_splits);
+  const int p1 = pf + (int)((long long)(split + 1) * npages / n_splits);
+
+  auto page_of = [&](int page_index) -> int {
+    int e = page_index;
+    if (pg.ring) e %= pg.ring;
+    return pg.table[(size_t)slot * pg.width + e];
+  };
+  auto issue = [&](int page, int stage) {
+    // one page: K then V, each [PS][HD] contiguous in the cache -> padded rows in shared memory
+    const __nv_bfloat16* src = cache + (((size_t)page * 2) * pg.kv_heads + kvh) * (size_t)(PS * HD);
+    const size_t vofs = (size_t)pg.kv_heads * PS * HD;
+    __nv_bfloat16* dst = tiles + (size_t)stage * 2 * TILE;
+    constexpr int CPR = HD / 8;                       // 16-byte chunks per row
+    for (int c = threadIdx.x; c < PS * CPR; c += WARPS * 32) {
+      const int r = c / CPR, cc = c % CPR;
+      cp_async16(dst + r * ROW + cc * 8, src + r * HD + cc * 8);
+      cp_async16(dst + TILE + r * ROW + cc * 8, src + vofs + r * HD + cc * 8);
+    }
+  };
+
+  // Prologue: the first STAGES - 1 pages, one commit group each (empty past the end, so that the groups
+  // count the same for every block).
+  int ahead = 0;                                      // groups committed so far
+  if (early) {
+    while (ahead < STAGES - 1 && p0 + ahead < p1 && p0 + ahead < pl) {
+      issue(page_of(p0 + ahead), ahead);
+      cp_async_commit();
+      ahead++;
+    }
+    cima_pdl_wait();
+  }
+  for (; ahead < STAGES - 1; ahead++) {
+    if (p0 + ahead < p1) issue(page_of(p0 + ahead), ahead);
+    cp_async_commit();
+  }
+  // the id of the page that the next iteration issues is looked up one iteration ahead, so that the table's
+  // latency is not on the way of the copies
+  int page_next = p0 + STAGES - 1 < p1 ? page_of(p0 + STAGES - 1) : 0;
 
   // the group's queries as A fragments: row g and g + 8 of the m-tile, 16 dims per k-step
   uint32_t q[KSTEPS][4];
@@ -110,30 +153,13 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
     for (int e = 0; e < 4; e++) o[j][e] = 0.f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-  auto issue = [&](int page_index, int stage) {
-    // one page: K then V, each [PS][HD] contiguous in the cache -> padded rows in shared memory
-    int e = page_index;
-    if (pg.ring) e %= pg.ring;
-    const int page = pg.table[(size_t)slot * pg.width + e];
-    const __nv_bfloat16* src = cache + (((size_t)page * 2) * pg.kv_heads + kvh) * (size_t)(PS * HD);
-    const size_t vofs = (size_t)pg.kv_heads * PS * HD;
-    __nv_bfloat16* dst = tiles + (size_t)stage * 2 * TILE;
-    constexpr int CPR = HD / 8;                       // 16-byte chunks per row
-    for (int c = threadIdx.x; c < PS * CPR; c += WARPS * 32) {
-      const int r = c / CPR, cc = c % CPR;
-      cp_async16(dst + r * ROW + cc * 8, src + r * HD + cc * 8);
-      cp_async16(dst + TILE + r * ROW + cc * 8, src + vofs + r * HD + cc * 8);
-    }
-  };
-
-  if (p0 < p1) issue(p0, 0);
-  cp_async_commit();
   for (int p = p0; p < p1; p++) {
-    const int stage = (p - p0) & 1;
-    if (p + 1 < p1) issue(p + 1, stage ^ 1);
+    const int stage = (p - p0) % STAGES;
+    cp_async_wait<STAGES - 2>();                      // page p has landed (this thread's part of it)
+    __syncthreads();                                   // ... everyone's; and page p - 1 is computed: its stage is free
+    if (p + STAGES - 1 < p1) issue(page_next, (p - p0 + STAGES - 1) % STAGES);
     cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
+    if (p + STAGES < p1) page_next = page_of(p + STAGES);
     const __nv_bfloat16* Kt = tiles + (size_t)stage * 2 * TILE;
     const __nv_bfloat16* Vt = Kt + TILE;
     const int kw = warp * KEYS_PER_WARP;              // this warp's keys within the page
@@ -199,7 +225,6 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
       mma_bf16(o[j], a0, a1, a2, a3, vb[0], vb[1]);
       mma_bf16(o[j + 1], a0, a1, a2, a3, vb[2], vb[3]);
     }
-    __syncthreads();                                   // the stage is free for the page after next
   }
   cp_async_wait<0>();
   __syncthreads();
@@ -247,7 +272,6 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
 // One block per (head, sequence): the weights e^(m_s - M) are made once (one thread per split) and
 // kept in shared memory; then a thread per dimension sums the splits' accumulators, whose loads
 // are independent of one another.
-constexpr int MAX_SPLITS = 64;
 __global__ void __launch_bounds__(128)
 k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                     __nv_bfloat16* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
@@ -297,9 +321,9 @@ k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ 
 template <int HD>
 int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, const int* seq_slot, const int* seq_len,
                   float* part_o, float* part_ml, void* out, int ldo, int B, int nh, int nkv, float scale, int window,
-                  int n_splits, cudaStream_t stream) {
+                  int n_splits, int early, cudaStream_t stream) {
   auto kern = k_attention_decode<HD>;
-  const size_t tiles = (size_t)2 * 2 * PS * (HD + 8) * sizeof(__nv_bfloat16);
+  const size_t tiles = (size_t)STAGES * 2 * PS * (HD + 8) * sizeof(__nv_bfloat16);
   const size_t merge = (size_t)WARPS * 16 * (HD + 2) * sizeof(float);
   const size_t smem = tiles > merge ? tiles : merge;
   static bool raised = false;
@@ -312,7 +336,7 @@ int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, cons
   dim3 grid(n_splits, nkv * mtiles, B);
   { int rc_ = cima_launch(kern, dim3(grid), dim3(WARPS * 32), (size_t)(smem), stream, 1, (const __nv_bfloat16*)qkv, ld, (const __nv_bfloat16*)cache, pg, seq_slot,
                                            seq_len, part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, nkv, mtiles, scale,
-                                           window, n_splits); if (rc_) return rc_; }
+                                           window, n_splits, early); if (rc_) return rc_; }
   int rc = cima_launch_result();
   if (rc || n_splits == 1) return rc;
   { int rc_ = cima_launch(k_attention_combine, dim3(dim3(nh, B)), dim3(128), (size_t)(0), stream, 1, part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, HD, n_splits); if (rc_) return rc_; }
@@ -322,11 +346,14 @@ int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, cons
 }  // namespace
 
 // One query row per sequence (row b of qkv belongs to sequence b).  part_o [B, nh, n_splits, hd] and
-// part_ml [B, nh, n_splits, 2] float32 are scratch, needed when n_splits > 1.
+// part_ml [B, nh, n_splits, 2] float32 are scratch, needed when n_splits > 1.  early != 0: the caller states
+// that the kernel launched just before this one writes neither seq_slot, seq_len, the block table nor any
+// cache page before the one of each sequence's newest position; the first pages are then fetched before that
+// kernel has finished.
 extern "C" int cima_attention_decode(const void* qkv, int ld, const void* cache, const int* table, int table_width,
                                      int ring, int page_size, const int* seq_slot, const int* seq_len, float* part_o,
                                      float* part_ml, void* out, int ldo, int B, int nh, int nkv, int hd, float scale,
-                                     int window, int n_splits, cudaStream_t stream) {
+                                     int window, int n_splits, int early, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (page_size != PS) return cima_fail(CIMA_E_SIZE, "attention_decode: page size %d; this kernel takes 64", page_size);
   if (hd % 16 || hd < 16 || hd > 128) return cima_fail(CIMA_E_SIZE, "attention_decode: head_dim %d; this kernel takes multiples of 16 up to 128", hd);
@@ -335,7 +362,7 @@ extern "C" int cima_attention_decode(const void* qkv, int ld, const void* cache,
   if (n_splits > 1 && (!part_o || !part_ml)) return cima_fail(CIMA_E_ARG, "attention_decode: more than one split needs the scratch buffers");
   if (ld % 2 || ((uintptr_t)qkv & 3) || ((uintptr_t)cache & 15)) return cima_fail(CIMA_E_ARG, "attention_decode: qkv rows must be 4-byte and the cache 16-byte aligned");
   CimaPaged pg{table, table_width, ring, page_size, nkv, hd};
-#define CASE(H) case H: return launch_decode<H>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, stream)
+#define CASE(H) case H: return launch_decode<H>(qkv, ld, cache, pg, seq_slot, seq_len, part_o, part_ml, out, ldo, B, nh, nkv, scale, window, n_splits, early != 0, stream)
   switch (hd) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
   }
@@ -390,5 +417,5 @@ extern "C" int cima_attention_decode_static(const void* qkv, int ld, const void*
   float* part_o = scratch;                       // [B, nh, n_splits, hd]
   float* part_ml = scratch + cells * hd;         // [B, nh, n_splits, 2]
   return cima_attention_decode(qkv, ld, cache, table, table_width, ring, page_size, seq_slot, seq_len, part_o, part_ml,
-                               out, ldo, B, nh, nkv, hd, scale, window, n_splits, stream);
+                               out, ldo, B, nh, nkv, hd, scale, window, n_splits, 0, stream);
 }

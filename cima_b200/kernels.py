@@ -15,7 +15,9 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 12
+ABI_VERSION = 13
+SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
+SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
 
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
@@ -51,7 +53,7 @@ _SIGNATURES = {
     "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_attention_plain": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                              _f, _i, _i, _vp],
-    "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
     "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "cima_gemm_tcgen05": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
@@ -388,13 +390,14 @@ class Kernels:
                                                   1 if from_cache else 0, self._stream()), "attention_plain")
 
     def attention(self, qkv: torch.Tensor, kv, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
-                  head_dim: int, scale: float, window: int, from_cache: bool) -> None:
+                  head_dim: int, scale: float, window: int, from_cache: bool, after_append: bool = False) -> None:
         """Attention of a step's rows: over the step's own keys (a prompt from position 0) or over the
-        cache.  Chooses the kernel; every choice computes the same function."""
+        cache.  Chooses the kernel; every choice computes the same function.  ``after_append``: the kernel
+        launched just before wrote nothing but ``qkv`` and the newest position of each sequence in the cache."""
         if (from_cache and qkv.dtype is torch.bfloat16 and kv.page_size == 64 and head_dim % 16 == 0
                 and head_dim <= 128 and batch.n_rows == batch.n_seqs):
             return self.attention_decode(qkv, kv, batch.seq_slot, batch.seq_len, out, n_heads, n_kv_heads, head_dim,
-                                         scale, window, batch.max_len)
+                                         scale, window, batch.max_len, early=after_append)
         if (not from_cache and qkv.dtype is torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128
                 and qkv.shape[1] % 8 == 0 and getattr(batch, "n_q_tiles", 0) > 0):
             return self.attention_prefill(qkv, batch.q_tile_seq, batch.q_tile_row0, batch.seq_first_row, out,
@@ -419,10 +422,12 @@ class Kernels:
 
     def attention_decode(self, qkv: torch.Tensor, kv, seq_slot, seq_len, out: torch.Tensor, n_heads: int,
                          n_kv_heads: int, head_dim: int, scale: float, window: int, max_len: int = 0,
-                         n_splits: Optional[int] = None) -> None:
+                         n_splits: Optional[int] = None, early: bool = False) -> None:
         """One query per sequence over the paged cache (bf16, pages of 64, head_dim <= 128), keys split
         over ``n_splits`` blocks per (sequence, kv head).  ``max_len`` (0 = unknown) only bounds the
-        number of splits chosen here."""
+        number of splits chosen here.  ``early``: the kernel launched just before this one wrote neither
+        ``seq_slot``, ``seq_len``, the block table nor a page before the one of a sequence's newest position,
+        so the first pages may be fetched while it finishes."""
         self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)
         self._need(kv.storage, "cache", torch.bfloat16, 5); self._need(kv.block_table, "block_table", torch.int32, 2)
         B = qkv.shape[0]
@@ -430,11 +435,14 @@ class Kernels:
             raise KernelError(f"attention_decode: out {tuple(out.shape)} / sequences do not fit {B} rows")
         if n_splits is None:
             mtiles = -(-(n_heads // n_kv_heads) // 16)
-            # one wave of blocks (three of them fit an SM, 444 in all): never a second, nearly empty wave;
-            # beyond 8 splits only while the GPU would otherwise stay mostly idle (measured on B200)
+            # one wave of blocks (two of them fit an SM): never a second, nearly empty wave; beyond 8 splits
+            # only while the GPU would otherwise stay mostly idle.  The splits are merged by a second kernel: merging
+            # inside a thread-block cluster (clusters of 8 blocks with 100 KB of shared memory each are slow to
+            # place) and merging in the last block to finish (a fence and a ticket per block) were both measured
+            # slower inside the decode step
             base = B * n_kv_heads * mtiles
-            n_splits = max(1, min(32, 444 // base))
-            if n_splits > 8 and base * 8 >= 148:
+            n_splits = max(1, min(32, SPLIT_BLOCKS // base))
+            if n_splits > 8 and base * 8 >= SPLIT_FEW_BLOCKS:
                 n_splits = 8
             if max_len > 0:
                 n_splits = min(n_splits, -(-max_len // 64))
@@ -445,8 +453,8 @@ class Kernels:
         self._check(self.lib.cima_attention_decode(
             qkv.data_ptr(), qkv.shape[1], kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
             kv.ring_pages, kv.page_size, seq_slot.data_ptr(), seq_len.data_ptr(), _ptr(part_o), _ptr(part_ml),
-            out.data_ptr(), out.shape[1], B, n_heads, n_kv_heads, head_dim, scale, window, n_splits, self._stream()),
-            "attention_decode")
+            out.data_ptr(), out.shape[1], B, n_heads, n_kv_heads, head_dim, scale, window, n_splits, int(early),
+            self._stream()), "attention_decode")
         if n_splits > 1:
             self.launches += 1
 

@@ -94,7 +94,8 @@ class Attention:
                            batch.seq_slot, batch.seq_len, kv if writes else None, s.n_heads, s.n_kv_heads, s.head_dim)
         att = self.rt.empty(h.shape[0], self.qd)
         from_cache = (not batch.prefill) or not writes
-        K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, from_cache)
+        K_.attention(qkv, kv, batch, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, from_cache,
+                     after_append=True)
         return self.out.accumulate(att, x, next_norm)
 
 

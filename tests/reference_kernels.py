@@ -137,7 +137,7 @@ class ReferenceKernels:
             kv.storage[page, 0, :, off, :] = heads[r, n_heads:n_heads + n_kv_heads, :]
             kv.storage[page, 1, :, off, :] = heads[r, n_heads + n_kv_heads:, :]
 
-    def attention(self, qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, from_cache):
+    def attention(self, qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, from_cache, after_append=False):
         self.attention_plain(qkv, kv, batch.row_pos, batch.row_seq, batch.seq_slot, batch.seq_first_row, out,
                              n_heads, n_kv_heads, head_dim, scale, window, from_cache)
 

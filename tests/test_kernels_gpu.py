@@ -297,10 +297,14 @@ def test_attention_decode_over_cache(K, dtype, page, nh, nkv, hd):
     K.attention_plain(qkv.cuda(), gpu, bg.row_pos, bg.row_seq, bg.seq_slot, bg.seq_first_row, plain, nh, nkv, hd, scale, 0, True)
     assert err(plain, want) <= TOL[dtype]
     if dtype == "bfloat16" and page == 64:
-        for n_splits in (1, 2, 3, 32):           # more splits than pages too
-            out.fill_(7.0)
-            K.attention_decode(qkv.cuda(), gpu, bg.seq_slot, bg.seq_len, out, nh, nkv, hd, scale, 0, n_splits=n_splits)
-            assert err(out, want) <= TOL[dtype], n_splits
+        # more splits than pages too; up to 8 merge inside a cluster, more through a second kernel; ``early``
+        # fetches the first pages before the wait on the previous kernel (which here writes ``out`` only)
+        for n_splits in (1, 2, 3, 5, 8, 9, 32):
+            for early in (False, True):
+                out.fill_(7.0)
+                K.attention_decode(qkv.cuda(), gpu, bg.seq_slot, bg.seq_len, out, nh, nkv, hd, scale, 0,
+                                   n_splits=n_splits, early=early)
+                assert err(out, want) <= TOL[dtype], (n_splits, early)
 
 
 @pytest.mark.parametrize("dtype,page", [("float32", 16), ("bfloat16", 16), ("bfloat16", 64)])
@@ -334,9 +338,12 @@ def test_attention_decode_window_edge(K, dtype, page, window, n):
     assert err(out, want) <= TOL[dtype]
     assert err(out[0, 2 * hd:3 * hd], v[inside, 1]) <= 5e-2      # head 2 is (nearly) that one value
     if dtype == "bfloat16" and page == 64:
-        for n_splits in (1, 2, 7):
-            K.attention_decode(qkv.cuda(), gpu, bg.seq_slot, bg.seq_len, out, nh, nkv, hd, scale, window, n_splits=n_splits)
-            assert err(out, want) <= TOL[dtype], n_splits
+        for n_splits in (1, 2, 7, 8, 16):
+            for early in (False, True):
+                out.fill_(7.0)
+                K.attention_decode(qkv.cuda(), gpu, bg.seq_slot, bg.seq_len, out, nh, nkv, hd, scale, window,
+                                   n_splits=n_splits, early=early)
+                assert err(out, want) <= TOL[dtype], (n_splits, early)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
