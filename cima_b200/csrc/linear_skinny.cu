@@ -317,7 +317,7 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
 }
 
 // Blocks per cluster for a matrix of `tiles` 16-feature tiles and K: the largest power of two that keeps all
-// blocks resident at once (four blocks of 256 threads per SM) and leaves every warp at least two chunks of 128.
+// blocks resident at once (four blocks of 256 threads per SM) and leaves every warp at least one chunk of 128.
 // Measured inside the decode step of a 3584-wide model on B200 (tokens per second at batch 8, K 18944, 224
 // tiles): 2 blocks 2496, 4 blocks 2414, 1, 3, 5, 6 or 8 blocks 2230 to 2290: a second, partly filled wave
 // costs more than its parallelism brings, and clusters of odd size were slower than their neighbours.
@@ -332,7 +332,7 @@ static int cluster_size(int tiles, int K) {
     resident = sms * 4;
   }
   int s = 1;
-  while (s < 8 && tiles * (2 * s) <= resident && (2 * s) * 2 * SK_WARPS * 128 <= K) s *= 2;
+  while (s < 8 && tiles * (2 * s) <= resident && (2 * s) * SK_WARPS * 128 <= K) s *= 2;
   return s;
 }
 

@@ -1,9 +1,10 @@
 // Token selection on the device.
 //
-// argmax: one block per row of float32 logits; ties go to the higher index, the order the
+// argmax: a cluster of blocks per row of float32 logits; ties go to the higher index, the order the
 // reference gets from packing (orderable float bits << 32 | index) into one u64 maximum
 // (src/kernels.cu:244-262).
 #include "common.cuh"
+#include <cooperative_groups.h>
 
 __device__ __forceinline__ unsigned long long cima_pack_key(float v, int i) {
   unsigned int b = __float_as_uint(v);
@@ -28,24 +29,64 @@ __device__ __forceinline__ unsigned long long cima_block_max_u64(unsigned long l
   return t;
 }
 
-__global__ void __launch_bounds__(1024)
+// A row is shared by the ARGMAX_BLOCKS blocks of a thread-block cluster (a block alone takes 75 us for a
+// vocabulary of 152,064: one SM's load latency, not the memory's bandwidth, is the bound); block 0 takes the
+// maximum of the blocks' maxima through distributed shared memory.  A maximum of packed keys does not depend
+// on the order in which it is taken.
+constexpr int ARGMAX_BLOCKS = 8;
+
+__global__ void __launch_bounds__(512)
 k_argmax(const float* __restrict__ logits, int ld, int V, int* __restrict__ tokens) {
   cima_pdl_wait();
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
   __shared__ unsigned long long red[32];
-  const float* x = logits + (size_t)blockIdx.x * ld;
+  __shared__ unsigned long long mine;
+  const int C = gridDim.x, c = blockIdx.x;
+  const float* x = logits + (size_t)blockIdx.y * ld;
+  const int per = (((V + C - 1) / C) + 3) & ~3;         // a multiple of 4, so that a block's share starts aligned
+  const int lo = min(V, c * per), hi = min(V, lo + per);
   unsigned long long best = 0ULL;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const unsigned long long k = cima_pack_key(x[i], i);
-    best = k > best ? k : best;
+  if ((((uintptr_t)x) & 15) == 0) {
+    const int n4 = (hi - lo) >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x + lo);
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      const float4 v = __ldg(x4 + i);
+      const int at = lo + 4 * i;
+      unsigned long long k = cima_pack_key(v.x, at);
+      best = k > best ? k : best;
+      k = cima_pack_key(v.y, at + 1); best = k > best ? k : best;
+      k = cima_pack_key(v.z, at + 2); best = k > best ? k : best;
+      k = cima_pack_key(v.w, at + 3); best = k > best ? k : best;
+    }
+    for (int i = lo + 4 * n4 + threadIdx.x; i < hi; i += blockDim.x) {
+      const unsigned long long k = cima_pack_key(x[i], i);
+      best = k > best ? k : best;
+    }
+  } else {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const unsigned long long k = cima_pack_key(x[i], i);
+      best = k > best ? k : best;
+    }
   }
   best = cima_block_max_u64(best, red);
-  if (threadIdx.x == 0) tokens[blockIdx.x] = (int)(unsigned int)best;
+  if (threadIdx.x == 0) mine = best;
+  cluster.sync();
+  if (c == 0 && threadIdx.x == 0) {
+    for (int r = 1; r < C; r++) {
+      const unsigned long long k = *cluster.map_shared_rank(&mine, r);
+      best = k > best ? k : best;
+    }
+    tokens[blockIdx.y] = (int)(unsigned int)best;
+  }
+  cluster.sync();                                        // a block's shared memory must outlive block 0's reads
 }
 
 extern "C" int cima_argmax(const float* logits, int ld, int n, int V, int* tokens, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (V <= 0 || ld < V) return cima_fail(CIMA_E_SIZE, "argmax: vocabulary %d must be positive and fit the row stride %d", V, ld);
-  { int rc_ = cima_launch(k_argmax, dim3(n), dim3(1024), (size_t)(0), stream, 1, logits, ld, V, tokens); if (rc_) return rc_; }
+  if (n > 65535) return cima_fail(CIMA_E_SIZE, "argmax: %d rows exceed one launch", n);
+  { int rc_ = cima_launch(k_argmax, dim3(ARGMAX_BLOCKS, n), dim3(512), (size_t)(0), stream, ARGMAX_BLOCKS, logits, ld, V, tokens); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
