@@ -60,8 +60,8 @@ constexpr int SK_PAD = 17;       // row stride of the reduction buffer (bank spr
 // also leaves xw = bf16(x * w) (w = the weight of the norm that follows) and partial sums of x^2; the product
 // after the norm (NORM = true) reads xw as plain bf16 activations and applies the row's factor to its finished
 // sums.  Against bf16(x * inv * w) as operand this differs by bfloat16 rounding only, and no separate norm
-// kernel runs between the two.  The partial sums (ssq [M, parts]) are fetched before the K loop and summed
-// after it in a fixed order.  An accumulating product leaves, for the rows it has updated, one partial sum
+// kernel runs between the two.  The partial sums (ssq [M, parts]) are added in a fixed order at the kernel's
+// start.  An accumulating product leaves, for the rows it has updated, one partial sum
 // per 16-feature tile (ssq_out [M, tiles]) and xw_out [M, N] = bf16(x_new * w_next).
 struct SkinnyNorm {
   const float* ssq;      // [M, parts] (NORM kernels)
@@ -175,19 +175,22 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
   const int k_first = (crank * SK_WARPS + warp) * CHUNK;
   if (k_first < K) load_w(k_first, 0);
   cima_pdl_wait();
-  // Folded norm: the rows' partial sums of squares are fetched now and added up after the K loop, so
-  // that their latency hides behind the weight stream; the factor inv = 1 / sqrt(sum / K + eps) of a
-  // row is applied to its finished dot products (the operand of the tensor core is bf16(x * w)).
+  // Folded norm: a row's factor inv = 1 / sqrt(sum / K + eps) is made now, from the partial sums of squares that
+  // the writer of the rows left, by the warp whose number is the row's: its loads (eight per lane, independent)
+  // are answered by L2 while the warp's first weights are still on their way from memory.  The factor is applied
+  // to the finished dot products (the operand of the tensor core is bf16(x * w)).
   __shared__ float inv_s[NT * 8];
-  constexpr int PARTS_MAX = 256;                         // partial sums per row staged in shared memory
-  __shared__ float ssq_s[NORM ? NT * 8 : 1][NORM ? PARTS_MAX : 1];
   if (NORM) {
-    for (int m = warp; m < M; m += SK_WARPS)
-      for (int pidx = lane; pidx < nm.parts && pidx < PARTS_MAX; pidx += 32) {
-        const unsigned dst = (unsigned)__cvta_generic_to_shared(&ssq_s[m][pidx]);
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(nm.ssq + (size_t)m * nm.parts + pidx));
-      }
-    asm volatile("cp.async.commit_group;" ::);
+    for (int m = warp; m < M; m += SK_WARPS) {
+      const float* ps = nm.ssq + (size_t)m * nm.parts;
+      float p[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) p[i] = lane + 32 * i < nm.parts ? __ldg(ps + lane + 32 * i) : 0.f;
+      float a = ((p[0] + p[1]) + (p[2] + p[3])) + ((p[4] + p[5]) + (p[6] + p[7]));     // a fixed order
+      for (int pidx = 256 + lane; pidx < nm.parts; pidx += 32) a += __ldg(ps + pidx);
+      for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+      if (lane == 0) inv_s[m] = 1.0f / sqrtf(a / (float)K + nm.eps);
+    }
   }
   if (k_first < K) {
     multiply(k_first, 0);
@@ -206,17 +209,6 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
   }
 
   cima_pdl_trigger();      // the weights are read: the next kernel may be scheduled while the sums are merged
-  if (NORM) {
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncwarp();
-    for (int m = warp; m < M; m += SK_WARPS) {
-      float a = 0.f;
-      for (int pidx = lane; pidx < nm.parts; pidx += 32)
-        a += pidx < PARTS_MAX ? ssq_s[m][pidx] : nm.ssq[(size_t)m * nm.parts + pidx];
-      for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-      if (lane == 0) inv_s[m] = 1.0f / sqrtf(a / (float)K + nm.eps);
-    }
-  }
   // partial sums -> shared memory: red[warp][a][col = j*8 + 2t (+1)][row = g (+8)]
   constexpr int COLS = NT * 8;
   float* mine = red + (size_t)warp * MT * COLS * SK_PAD;

@@ -16,7 +16,6 @@ import torch
 from ..kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
 
 FOLDED_NORM_ROWS = 16    # most rows of the skinny kernel's folded RMSNorm
-FOLDED_NORM_FEATURES = 65536
 TCGEN05_ROWS = 256       # from this many rows on, the gated product runs on the tcgen05 kernel
 SKINNY_ROWS = 8          # measured on B200: above 8 rows the library product streams the weights faster
 
@@ -43,10 +42,8 @@ class Linear:
     # ------------------------------------------------------------------ products
     def _folds(self, a, rows: int) -> bool:
         """Whether ``a`` is a pending RMSNorm that the skinny kernel can fold in."""
-        # every 16-feature tile of the product re-reads the rows' partial sums: worth it for a layer's
-        # projections, not for a head of a hundred thousand features (measured on B200)
         return (hasattr(a, "tensor") and a.ssq is not None and a.xw is not None and self._skinny(rows)
-                and rows <= FOLDED_NORM_ROWS and a.norm.spec.kind == "rmsnorm" and self.N <= FOLDED_NORM_FEATURES)
+                and rows <= FOLDED_NORM_ROWS and a.norm.spec.kind == "rmsnorm")
 
     def store(self, a, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """a W^T + bias in the activation dtype (``a``: activations, or a pending norm)."""
