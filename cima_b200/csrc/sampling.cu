@@ -141,12 +141,13 @@ __device__ float sample_mass(const SampleRow& r, unsigned long long T, float* re
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 k_sample(const float* __restrict__ logits, int ld, int V, const int* __restrict__ row_slot,
          const float* __restrict__ params, unsigned long long* __restrict__ rng, int* __restrict__ ring,
-         int* __restrict__ ring_count, float* __restrict__ work, int* __restrict__ tokens) {
+         int* __restrict__ ring_count, float* __restrict__ work, int* __restrict__ tokens, int only_unresolved) {
   cima_pdl_wait();
   __shared__ float redf[32];
   __shared__ unsigned long long redk[32];
   __shared__ float s_u;
   const int row = blockIdx.x;
+  if (only_unresolved && tokens[row] >= 0) return;      // the fast kernel has settled this row
   const int slot = row_slot[row];
   const float temperature = params[row * 4 + 0];
   const int top_k = (int)params[row * 4 + 1];
@@ -247,6 +248,232 @@ k_sample(const float* __restrict__ logits, int ld, int V, const int* __restrict_
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same chain, fast, for the common case that few tokens are kept (the reference's default top_k is 40).
+// A row is shared by the 8 blocks of a thread-block cluster; every block keeps its slice of the penalised
+// logits in shared memory.  The k-th largest key is found by a radix select (one histogram of 256 bins per
+// byte of the key, merged over the cluster through distributed shared memory; it stops as soon as a bin holds
+// exactly what is still wanted), the kept tokens are gathered and sorted in block 0, and one thread then does
+// what the reference's host loop does, in its order and in float32: probabilities, their sum, the top-p cut,
+// the renormalised draw (src/models/mod.rs:100-130).
+//
+// With top_k = 0 or above 1024 the 1024 largest tokens stand in for the whole row (the sum of all masses is
+// taken over the whole row): if the top-p cut and the draw both fall inside them the row is settled, else the
+// kernel writes token -1, leaves the sequence's state alone, and k_sample (only_unresolved) does the row.
+// ---------------------------------------------------------------------------------------------
+constexpr int FAST_BLOCKS = 8;
+constexpr int FAST_THREADS = 512;
+constexpr int FAST_MAXK = 1024;
+
+__device__ __forceinline__ float cima_key_value(unsigned long long key) {
+  const unsigned int hi = (unsigned int)(key >> 32);
+  return __uint_as_float((hi & 0x80000000u) ? (hi ^ 0x80000000u) : ~hi);
+}
+
+__global__ void __launch_bounds__(FAST_THREADS)
+k_sample_fast(const float* __restrict__ logits, int ld, int V, const int* __restrict__ row_slot,
+              const float* __restrict__ params, unsigned long long* __restrict__ rng, int* __restrict__ ring,
+              int* __restrict__ ring_count, int* __restrict__ tokens) {
+  cima_pdl_wait();
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  extern __shared__ float sl[];                       // this block's slice of the row; later the probabilities
+  __shared__ int hist[256];
+  __shared__ int merged[256];
+  __shared__ unsigned long long cand[FAST_MAXK];      // this block's kept keys, any order
+  __shared__ unsigned long long sorted[FAST_MAXK];    // block 0: all kept keys
+  __shared__ unsigned long long redk[32];
+  __shared__ float redf[32];
+  __shared__ unsigned long long s_best;
+  __shared__ int ncand, s_sel, s_above, s_cnt, s_total_n;
+  __shared__ float s_mass, s_total_all;
+  const int C = FAST_BLOCKS, c = blockIdx.x, row = blockIdx.y, tid = threadIdx.x;
+  const int slot = row_slot[row];
+  const float temperature = params[row * 4 + 0];
+  const int top_k = (int)params[row * 4 + 1];
+  const float top_p = params[row * 4 + 2];
+  const float rp = params[row * 4 + 3];
+  const float* x = logits + (size_t)row * ld;
+  int* myring = ring + (size_t)slot * SAMPLE_RING;
+  const int per = (((V + C - 1) / C) + 3) & ~3;
+  const int lo = min(V, c * per), hi = min(V, lo + per), n_loc = hi - lo;
+
+  // 1. the slice, then the penalty on it, entry by entry as the host loop does
+  for (int i = tid; i < n_loc; i += FAST_THREADS) sl[i] = x[lo + i];
+  const int pushed = ring_count[slot];
+  __syncthreads();
+  if (tid == 0 && rp != 1.0f) {
+    const int n = pushed < SAMPLE_RING ? pushed : SAMPLE_RING;
+    for (int j = 0; j < n; j++) {
+      const int t = myring[(pushed - n + j) % SAMPLE_RING];
+      if (t >= lo && t < hi) sl[t - lo] = sl[t - lo] > 0.f ? sl[t - lo] / rp : sl[t - lo] * rp;
+    }
+  }
+  __syncthreads();
+  // 2. the largest key of the row
+  unsigned long long best = 0ULL;
+  for (int i = tid; i < n_loc; i += FAST_THREADS) {
+    const unsigned long long k = cima_pack_key(sl[i], lo + i);
+    best = k > best ? k : best;
+  }
+  best = cima_block_max_u64(best, redk);
+  if (tid == 0) s_best = best;
+  cluster.sync();
+  for (int r = 0; r < C; r++) {
+    const unsigned long long k = *cluster.map_shared_rank(&s_best, r);
+    best = k > best ? k : best;
+  }
+  if (temperature <= 0.f) {
+    if (c == 0 && tid == 0) {
+      const int token = (int)(unsigned int)best;
+      tokens[row] = token;
+      myring[pushed % SAMPLE_RING] = token;
+      ring_count[slot] = pushed + 1;
+    }
+    cluster.sync();                                   // a block's shared memory must outlive the others' reads
+    return;
+  }
+  const float maxl = cima_key_value(best);
+  const float inv_t = 1.0f / fmaxf(temperature, 1e-4f);
+  const int kk = (top_k <= 0 || top_k > V) ? V : top_k;
+  const bool exact = kk <= FAST_MAXK;                 // the kept set is gathered whole
+  const int want = exact ? kk : FAST_MAXK;
+
+  // 3. T = the want-th largest key, byte by byte from the top
+  unsigned long long prefix = 0ULL;
+  int remaining = want;
+  for (int b = 7; b >= 0; b--) {
+    if (b == 3) continue;                             // indices stay below 2^24: this byte is zero in every key
+    const int shift = 8 * b;
+    for (int j = tid; j < 256; j += FAST_THREADS) hist[j] = 0;
+    __syncthreads();
+    for (int i = tid; i < n_loc; i += FAST_THREADS) {
+      const unsigned long long k = cima_pack_key(sl[i], lo + i);
+      if (b == 7 || (k >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&hist[(int)((k >> shift) & 255ULL)], 1);
+    }
+    __syncthreads();
+    cluster.sync();
+    if (tid < 256) {
+      int sum = 0;
+      for (int r = 0; r < C; r++) sum += cluster.map_shared_rank(hist, r)[tid];
+      merged[tid] = sum;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int cum = 0, bin = 255;
+      for (; bin > 0; bin--) {
+        if (cum + merged[bin] >= remaining) break;
+        cum += merged[bin];
+      }
+      s_sel = bin; s_above = cum; s_cnt = merged[bin];
+    }
+    __syncthreads();
+    prefix |= (unsigned long long)s_sel << shift;
+    remaining -= s_above;
+    const bool settled = s_cnt == remaining;          // the whole bin is kept: every lower bit of T is zero
+    cluster.sync();                                   // everyone has read this block's histogram
+    if (settled) break;
+  }
+  const unsigned long long T = prefix;
+
+  // 4. the kept keys of this slice; the mass of the whole slice when the kept set is not gathered whole
+  if (tid == 0) ncand = 0;
+  __syncthreads();
+  float mass = 0.f;
+  for (int i = tid; i < n_loc; i += FAST_THREADS) {
+    const float v = sl[i];
+    const unsigned long long k = cima_pack_key(v, lo + i);
+    if (k >= T) {
+      const int at = atomicAdd(&ncand, 1);
+      if (at < FAST_MAXK) cand[at] = k;
+    }
+    if (!exact) mass += expf((v - maxl) * inv_t);
+  }
+  if (!exact) {
+    mass = cima_block_sum(mass, redf);
+    if (tid == 0) s_mass = mass;
+  }
+  __syncthreads();
+  cluster.sync();
+  if (c == 0) {
+    int at = 0;
+    float total_all = 0.f;
+    for (int r = 0; r < C; r++) {                     // ranks in order: a fixed sum, a fixed layout
+      const int n_r = min(*cluster.map_shared_rank(&ncand, r), FAST_MAXK);
+      const unsigned long long* src = cluster.map_shared_rank(cand, r);
+      for (int j = tid; j < n_r && at + j < FAST_MAXK; j += FAST_THREADS) sorted[at + j] = src[j];
+      at = min(at + n_r, FAST_MAXK);
+      if (!exact) total_all += *cluster.map_shared_rank(&s_mass, r);
+    }
+    if (tid == 0) { s_total_n = at; s_total_all = total_all; }
+  }
+  cluster.sync();                                     // the others may go: block 0 has what it needs
+  if (c != 0) return;
+  __syncthreads();
+  const int n = s_total_n;
+  int P = 1;
+  while (P < n) P <<= 1;
+  for (int i = n + tid; i < P; i += FAST_THREADS) sorted[i] = 0ULL;
+  __syncthreads();
+  // 5. bitonic sort, largest key first: the reference's order (value descending, index descending)
+  for (int k2 = 2; k2 <= P; k2 <<= 1)
+    for (int j = k2 >> 1; j > 0; j >>= 1) {
+      for (int i = tid; i < P; i += FAST_THREADS) {
+        const int o = i ^ j;
+        if (o > i) {
+          const unsigned long long a = sorted[i], bq = sorted[o];
+          const bool desc = (i & k2) == 0;
+          if (desc ? a < bq : a > bq) { sorted[i] = bq; sorted[o] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  float* pr = sl;                                     // probabilities of the kept, in order (the slice is spent)
+  const float v0 = cima_key_value(sorted[0]);
+  for (int i = tid; i < n; i += FAST_THREADS) pr[i] = expf((cima_key_value(sorted[i]) - v0) * inv_t);
+  __syncthreads();
+  if (tid != 0) return;
+  // 6. the host loop of the reference, in its order and in float32
+  float total = 0.f;
+  if (exact) { for (int i = 0; i < n; i++) total += pr[i]; } else total = s_total_all;
+  int cut = exact ? n : -1;
+  float cum = 0.f;
+  for (int i = 0; i < n; i++) {
+    const float p = pr[i] / total;
+    pr[i] = p;
+    cum += p;
+    if (cum >= top_p) { cut = i + 1; break; }
+  }
+  unsigned long long st = rng[slot];
+  st ^= st >> 12; st ^= st << 25; st ^= st >> 27;
+  const float u = (float)((st * 0x2545F4914F6CDD1DULL) >> 40) / 16777216.0f;
+  int token = -1;
+  if (cut > 0) {
+    float renorm = 0.f;
+    for (int i = 0; i < cut; i++) renorm += pr[i];
+    float r = u * renorm;
+    token = (int)(unsigned int)sorted[cut - 1];
+    for (int i = 0; i < cut; i++) {
+      r -= pr[i];
+      if (r <= 0.f) { token = (int)(unsigned int)sorted[i]; break; }
+    }
+  } else if (top_p >= 1.0f) {
+    // nothing is cut and the kept set is the whole row, of which only the head is here: settled if the
+    // draw falls into the head
+    float r = u;
+    for (int i = 0; i < n; i++) {
+      r -= pr[i];
+      if (r <= 0.f) { token = (int)(unsigned int)sorted[i]; break; }
+    }
+  }
+  tokens[row] = token;
+  if (token >= 0) {
+    rng[slot] = st;
+    myring[pushed % SAMPLE_RING] = token;
+    ring_count[slot] = pushed + 1;
+  }
+}
+
 // logits [n, V] float32 (row stride ld); row_slot [n]; params [n, 4] = temperature, top_k, top_p,
 // repeat_penalty; rng [slots] u64; ring [slots, 64]; ring_count [slots]; work [n, V] float32 scratch.
 extern "C" int cima_sample(const float* logits, int ld, int n, int V, const int* row_slot, const float* params,
@@ -255,6 +482,24 @@ extern "C" int cima_sample(const float* logits, int ld, int n, int V, const int*
   if (n <= 0) return 0;
   if (V <= 0 || ld < V) return cima_fail(CIMA_E_SIZE, "sample: vocabulary %d must be positive and fit the row stride %d", V, ld);
   if (V >= (1 << 24)) return cima_fail(CIMA_E_SIZE, "sample: vocabulary %d exceeds 2^24 (counts are summed in float32)", V);
-  { int rc_ = cima_launch(k_sample, dim3(n), dim3(SAMPLE_THREADS), (size_t)(0), stream, 1, logits, ld, V, row_slot, params, rng, ring, ring_count, work, tokens); if (rc_) return rc_; }
+  if (n > 65535) return cima_fail(CIMA_E_SIZE, "sample: %d rows exceed one launch", n);
+  // the fast kernel keeps an eighth of a row (at least 1024 floats) in shared memory; rows too long for that
+  // go straight to the general kernel
+  const int per = (((V + FAST_BLOCKS - 1) / FAST_BLOCKS) + 3) & ~3;
+  const size_t smem = (size_t)(per > FAST_MAXK ? per : FAST_MAXK) * sizeof(float);
+  int only_unresolved = 0;
+  if (smem <= 160 * 1024) {
+    static bool raised = false;
+    if (!raised) {
+      cudaError_t e = cudaFuncSetAttribute(k_sample_fast, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      if (e != cudaSuccess) return cima_fail((int)e, "sample: cannot raise shared memory: %s", cudaGetErrorString(e));
+      raised = true;
+    }
+    { int rc_ = cima_launch(k_sample_fast, dim3(FAST_BLOCKS, n), dim3(FAST_THREADS), smem, stream, FAST_BLOCKS, logits, ld, V, row_slot, params, rng, ring, ring_count, tokens); if (rc_) return rc_; }
+    int rc = cima_launch_result();
+    if (rc) return rc;
+    only_unresolved = 1;
+  }
+  { int rc_ = cima_launch(k_sample, dim3(n), dim3(SAMPLE_THREADS), (size_t)(0), stream, 1, logits, ld, V, row_slot, params, rng, ring, ring_count, work, tokens, only_unresolved); if (rc_) return rc_; }
   return cima_launch_result();
 }
