@@ -257,9 +257,10 @@ k_sample(const float* __restrict__ logits, int ld, int V, const int* __restrict_
 // what the reference's host loop does, in its order and in float32: probabilities, their sum, the top-p cut,
 // the renormalised draw (src/models/mod.rs:100-130).
 //
-// With top_k = 0 or above 1024 the 1024 largest tokens stand in for the whole row (the sum of all masses is
-// taken over the whole row): if the top-p cut and the draw both fall inside them the row is settled, else the
-// kernel writes token -1, leaves the sequence's state alone, and k_sample (only_unresolved) does the row.
+// With top_k = 0 (or at least the vocabulary) the 1024 largest tokens stand in for the whole row (the sum of
+// all masses is taken over the whole row): if the top-p cut and the draw both fall inside them the row is
+// settled, else the kernel writes token -1, leaves the sequence's state alone, and k_sample (only_unresolved)
+// does the row.  A top_k between 1025 and the vocabulary goes to k_sample at once.
 // ---------------------------------------------------------------------------------------------
 constexpr int FAST_BLOCKS = 8;
 constexpr int FAST_THREADS = 512;
@@ -338,6 +339,12 @@ k_sample_fast(const float* __restrict__ logits, int ld, int V, const int* __rest
   const int kk = (top_k <= 0 || top_k > V) ? V : top_k;
   const bool exact = kk <= FAST_MAXK;                 // the kept set is gathered whole
   const int want = exact ? kk : FAST_MAXK;
+  if (!exact && kk < V) {
+    // more than 1024 kept, but not the whole row: the sum of the kept masses is not at hand here
+    if (c == 0 && tid == 0) tokens[row] = -1;
+    cluster.sync();
+    return;
+  }
 
   // 3. T = the want-th largest key, byte by byte from the top
   unsigned long long prefix = 0ULL;
