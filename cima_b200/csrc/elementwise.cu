@@ -47,28 +47,102 @@ extern "C" int cima_embed(const int* ids, const void* table, int table_dtype, fl
 // ---------------------------------------------------------------- RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w
 // One block per row.  Sum of squares, reciprocal root and the products are float32; one rounding
 // at the store.  1/sqrtf rather than rsqrtf: the latter is an approximation.
-template <typename TO>
-__global__ void k_rmsnorm(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ y,
-                          int H, float eps) {
+// With ADD the row is first updated, x += d (the residual sum in float32), and the norm is of the updated row:
+// bit for bit what add_residual followed by rmsnorm gives, in one pass over the row less.
+//
+// Rows of up to 8192 values whose width is a multiple of 4 are read once, 16 bytes at a time, and kept in
+// registers between the sum and the scaling; other rows take the loop that reads them twice.  Both walk the
+// row in the same order per thread (element i belongs to thread (i / 4) % 256 on the first path, i % 256 on
+// the second), so which path a width takes is fixed by the width alone.
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_VEC = 8;                  // float4 per thread: 256 * 8 * 4 = 8192 values
+
+template <typename TO> __device__ __forceinline__ void cima_store4(TO* p, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void cima_store4<float>(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void cima_store4<__nv_bfloat16>(__nv_bfloat16* p, float a, float b, float c, float d) {
+  uint2 v;
+  *reinterpret_cast<__nv_bfloat162*>(&v.x) = __floats2bfloat162_rn(a, b);
+  *reinterpret_cast<__nv_bfloat162*>(&v.y) = __floats2bfloat162_rn(c, d);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+template <typename TA> __device__ __forceinline__ float4 cima_load4(const TA* p);
+template <> __device__ __forceinline__ float4 cima_load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 cima_load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename TA, bool ADD, bool VEC>
+__global__ void __launch_bounds__(NORM_THREADS)
+k_rmsnorm(float* __restrict__ x, const TA* __restrict__ d, const float* __restrict__ w, TA* __restrict__ y,
+          int H, float eps) {
   cima_pdl_wait();
   __shared__ float red[32];
-  const float* xi = x + (size_t)blockIdx.x * H;
-  TO* yo = y + (size_t)blockIdx.x * H;
+  float* xi = x + (size_t)blockIdx.x * H;
+  const TA* di = ADD ? d + (size_t)blockIdx.x * H : nullptr;
+  TA* yo = y + (size_t)blockIdx.x * H;
+  if (VEC) {
+    float4 v[NORM_VEC];
+    const int H4 = H >> 2;
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < NORM_VEC; j++) {
+      const int i4 = threadIdx.x + j * NORM_THREADS;
+      if (i4 < H4) {
+        v[j] = *reinterpret_cast<const float4*>(xi + 4 * i4);
+        if (ADD) {
+          const float4 a = cima_load4<TA>(di + 4 * i4);
+          v[j].x += a.x; v[j].y += a.y; v[j].z += a.z; v[j].w += a.w;
+          *reinterpret_cast<float4*>(xi + 4 * i4) = v[j];
+        }
+        acc += v[j].x * v[j].x; acc += v[j].y * v[j].y; acc += v[j].z * v[j].z; acc += v[j].w * v[j].w;
+      }
+    }
+    const float total = cima_block_sum(acc, red);
+    const float inv = 1.0f / sqrtf(total / (float)H + eps);
+#pragma unroll
+    for (int j = 0; j < NORM_VEC; j++) {
+      const int i4 = threadIdx.x + j * NORM_THREADS;
+      if (i4 < H4) {
+        const float4 ww = *reinterpret_cast<const float4*>(w + 4 * i4);
+        cima_store4<TA>(yo + 4 * i4, v[j].x * inv * ww.x, v[j].y * inv * ww.y, v[j].z * inv * ww.z, v[j].w * inv * ww.w);
+      }
+    }
+    return;
+  }
   float acc = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) { const float v = xi[i]; acc += v * v; }
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = xi[i];
+    if (ADD) { v += cima_to_f32<TA>(di[i]); xi[i] = v; }
+    acc += v * v;
+  }
   const float total = cima_block_sum(acc, red);
   const float inv = 1.0f / sqrtf(total / (float)H + eps);
-  for (int i = threadIdx.x; i < H; i += blockDim.x) yo[i] = cima_from_f32<TO>(xi[i] * inv * w[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) yo[i] = cima_from_f32<TA>(xi[i] * inv * w[i]);
+}
+
+template <typename TA, bool ADD>
+static int launch_rmsnorm(float* x, const void* d, const float* w, void* y, int T, int H, float eps, cudaStream_t stream) {
+  const bool vec = H % 4 == 0 && H <= NORM_THREADS * NORM_VEC * 4 &&
+                   (((uintptr_t)x | (uintptr_t)w) & 15) == 0 && (((uintptr_t)y | (uintptr_t)d) & (4 * sizeof(TA) - 1)) == 0;
+  int rc;
+  if (vec) rc = cima_launch(k_rmsnorm<TA, ADD, true>, dim3(T), dim3(NORM_THREADS), (size_t)0, stream, 1, x, (const TA*)d, w, (TA*)y, H, eps);
+  else rc = cima_launch(k_rmsnorm<TA, ADD, false>, dim3(T), dim3(NORM_THREADS), (size_t)0, stream, 1, x, (const TA*)d, w, (TA*)y, H, eps);
+  if (rc) return rc;
+  return cima_launch_result();
 }
 
 extern "C" int cima_rmsnorm(const float* x, const float* w, void* y, int y_dtype, int T, int H, float eps,
                             cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0) return cima_fail(CIMA_E_SIZE, "rmsnorm: width %d must be positive", H);
-  if (y_dtype == CIMA_F32) { int rc_ = cima_launch(k_rmsnorm<float>, dim3(T), dim3(256), (size_t)(0), stream, 1, x, w, (float*)y, H, eps); if (rc_) return rc_; }
-  else if (y_dtype == CIMA_BF16) { int rc_ = cima_launch(k_rmsnorm<__nv_bfloat16>, dim3(T), dim3(256), (size_t)(0), stream, 1, x, w, (__nv_bfloat16*)y, H, eps); if (rc_) return rc_; }
-  else return cima_fail(CIMA_E_DTYPE, "rmsnorm: output dtype code %d is neither float32 nor bfloat16", y_dtype);
-  return cima_launch_result();
+  if (y_dtype == CIMA_F32) return launch_rmsnorm<float, false>(const_cast<float*>(x), nullptr, w, y, T, H, eps, stream);
+  if (y_dtype == CIMA_BF16) return launch_rmsnorm<__nv_bfloat16, false>(const_cast<float*>(x), nullptr, w, y, T, H, eps, stream);
+  return cima_fail(CIMA_E_DTYPE, "rmsnorm: output dtype code %d is neither float32 nor bfloat16", y_dtype);
 }
 
 // ---------------------------------------------------------------- gated activation: a = silu(g) * u
@@ -141,35 +215,14 @@ extern "C" int cima_add_residual(float* x, const void* d, int d_dtype, size_t to
 }
 
 // ---------------------------------------------------------------- residual + norm: x += d; h = RMSNorm(x)
-// One block per row, the same order of summation as k_rmsnorm: bit for bit what add_residual followed by
-// rmsnorm gives, in one pass over the row less.
-template <typename TA>
-__global__ void k_add_rmsnorm(float* __restrict__ x, const TA* __restrict__ d, const float* __restrict__ w,
-                              TA* __restrict__ h, int H, float eps) {
-  cima_pdl_wait();
-  __shared__ float red[32];
-  float* xi = x + (size_t)blockIdx.x * H;
-  const TA* di = d + (size_t)blockIdx.x * H;
-  TA* ho = h + (size_t)blockIdx.x * H;
-  float acc = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float v = xi[i] + cima_to_f32<TA>(di[i]);
-    xi[i] = v;
-    acc += v * v;
-  }
-  const float total = cima_block_sum(acc, red);
-  const float inv = 1.0f / sqrtf(total / (float)H + eps);
-  for (int i = threadIdx.x; i < H; i += blockDim.x) ho[i] = cima_from_f32<TA>(xi[i] * inv * w[i]);
-}
-
+// k_rmsnorm with ADD (see there).
 extern "C" int cima_add_rmsnorm(float* x, const void* d, const float* w, void* h, int dtype, int T, int H, float eps,
                                 cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0) return cima_fail(CIMA_E_SIZE, "add_rmsnorm: width %d must be positive", H);
-  if (dtype == CIMA_F32) { int rc_ = cima_launch(k_add_rmsnorm<float>, dim3(T), dim3(256), (size_t)0, stream, 1, x, (const float*)d, w, (float*)h, H, eps); if (rc_) return rc_; }
-  else if (dtype == CIMA_BF16) { int rc_ = cima_launch(k_add_rmsnorm<__nv_bfloat16>, dim3(T), dim3(256), (size_t)0, stream, 1, x, (const __nv_bfloat16*)d, w, (__nv_bfloat16*)h, H, eps); if (rc_) return rc_; }
-  else return cima_fail(CIMA_E_DTYPE, "add_rmsnorm: dtype code %d is neither float32 nor bfloat16", dtype);
-  return cima_launch_result();
+  if (dtype == CIMA_F32) return launch_rmsnorm<float, true>(x, d, w, h, T, H, eps, stream);
+  if (dtype == CIMA_BF16) return launch_rmsnorm<__nv_bfloat16, true>(x, d, w, h, T, H, eps, stream);
+  return cima_fail(CIMA_E_DTYPE, "add_rmsnorm: dtype code %d is neither float32 nor bfloat16", dtype);
 }
 
 // ---------------------------------------------------------------- row gather: out[i,:] = x[rows[i],:]
