@@ -1,0 +1,513 @@
+// Causal (and windowed) attention of ragged prompts on the fifth-generation tensor cores, head_dim 128.
+//
+// One block computes 128 query rows of one head.  Both products of a tile of 64 keys run as tcgen05.mma with
+// their results in tensor memory:
+//     S = Q K^T      128 x 64, K-major operands straight from the q/k/v buffer by TMA
+//     O += P V       P is written to shared memory by the softmax threads in the layout the tensor core reads
+//                    (K-major, 128-byte swizzle); V is taken TRANSPOSED ([dims, keys], keys contiguous; the
+//                    small kernel below makes it), so that this operand is K-major too
+// Warp roles (192 threads): warps 0..3 softmax, one thread per query row (a row's maximum and sum need no
+// shuffles; each warp reads the 32 TMEM lanes it may access); warp 4 TMA producer; warp 5 TMEM allocation and
+// MMA issue.  S has two buffers in TMEM, so the tensor cores compute S of the next tile while the softmax of the
+// current one runs.  Two blocks share an SM (112 KB of shared memory and 256 TMEM columns each): a softmax warp
+// alone on its scheduler issues one instruction every four cycles, two hide each other's latencies, and the
+// tensor cores serve one block while the other exponentiates.  Scores, maxima, exponentials and sums are float32 in the base-2 domain; P is rounded to
+// bfloat16 only as operand of P V, the row sums are taken before that rounding.  O is rescaled in TMEM only
+// when a row's maximum has grown by more than 2^8 over the reference of its exponentials.
+//
+// Every wait on an mbarrier is bounded (2 s); a wait that runs out sets *error_flag, and all roles leave their
+// loops, free the tensor memory and return.
+//
+// The reference's prefill attention is k_attn_prefill_f16 (src/kernels.cu:915-1000): one warp per query row,
+// online softmax on CUDA cores; it has no tensor-core attention.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+
+namespace {
+
+constexpr int HD = 128;            // head_dim of this kernel
+constexpr int BM = 128;            // query rows per block = TMEM lanes
+constexpr int BN = 64;             // keys per tile
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int HALF_BYTES = 128 * 64 * 2;     // 128 rows of 64 bf16: one 128-byte-swizzled block, 16 KB
+constexpr int KHALF_BYTES = BN * 64 * 2;     // 64 keys of 64 dims: 8 KB
+constexpr unsigned long long WAIT_NS = 2000000000ull;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(void* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when it ran out (the flag is set, the caller leaves its loop).
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, int* error_flag, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer();
+  for (unsigned it = 0;; it++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if (globaltimer() - t0 > WAIT_NS) {
+        *abort_flag = 1;
+        atomicExch(error_flag, 1);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, int x, int y, void* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+// K-major operand tile, rows of 128 bytes, 128-byte swizzle, groups of 8 rows 1024 bytes apart (see
+// gemm_tcgen05.cu for the fields).
+__device__ __forceinline__ unsigned long long umma_smem_desc(unsigned smem_addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)(1u) << 16;
+  d |= (unsigned long long)(1024u >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+__device__ __forceinline__ unsigned umma_idesc(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(M >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(void* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+// The same without the wait: several loads may be in flight; tmem_ld_wait() before their values are used.
+__device__ __forceinline__ void tmem_ld32_issue(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ex2(float x) {          // 2^x, float32, about 2 ulp; 2^(-inf) = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct AttnArgs {
+  const int* tile_seq;          // [tiles] sequence of the block of 128 query rows
+  const int* tile_row0;         // [tiles] first query position of the block
+  const int* seq_first_row;     // [seqs + 1]
+  const int* seq_vt_col;        // [seqs] first column of the sequence in the transposed V
+  __nv_bfloat16* out;           // [T, ldo]
+  int ldo, nh, nkv, window;
+  float scale;
+  int* error_flag;
+};
+
+// Keys of a query block: tiles [first, last] of 128 keys.
+__device__ __forceinline__ void key_tiles(int q0, int len, int window, int& first, int& last) {
+  const int q_hi = min(q0 + BM, len) - 1;                      // last query row of the block
+  const int lo = window > 0 ? max(0, q0 - window + 1) : 0;      // first key any row of the block sees
+  first = lo / BN;
+  last = q_hi / BN;
+}
+
+__global__ void __launch_bounds__(THREADS, 2)
+k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_vt, AttnArgs a) {
+  cima_pdl_wait();
+  extern __shared__ __align__(1024) unsigned char smem[];      // tiles of 1024-byte groups: checked below
+  unsigned char* sq = smem;                                    // Q: 2 halves (dims 0..63, 64..127) of 16 KB
+  unsigned char* sk = sq + 2 * HALF_BYTES;                     // K: [2 stages][2 halves of 64 dims][64 keys]
+  unsigned char* sv = sk + 4 * KHALF_BYTES;                    // V^T: [2 stages][128 dims][64 keys]
+  unsigned char* sp = sv + 2 * HALF_BYTES;                     // P: [128 query rows][64 keys]
+  unsigned long long* bars = (unsigned long long*)(sp + HALF_BYTES);
+  unsigned long long* q_full = bars;                           // [1]
+  unsigned long long* kv_full = bars + 1;                      // [2]
+  unsigned long long* kv_empty = bars + 3;                     // [2]
+  unsigned long long* s_full = bars + 5;                       // [2]
+  unsigned long long* s_empty = bars + 7;                      // [2]
+  unsigned long long* p_full = bars + 9;                       // [1]
+  unsigned long long* pv_done = bars + 10;                     // [1]
+  unsigned* tmem_slot = (unsigned*)(bars + 11);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+  const int seq = a.tile_seq[blockIdx.x], q0 = a.tile_row0[blockIdx.x];
+  const int row_base = a.seq_first_row[seq];
+  const int len = a.seq_first_row[seq + 1] - row_base;
+  int first, last;
+  key_tiles(q0, len, a.window, first, last);
+  const int n = last - first + 1;
+
+  if (threadIdx.x == 0 && (smem_u32(smem) & 1023u)) atomicExch(a.error_flag, 2);   // never seen; the tiles would be misread
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; s++) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4); }
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const unsigned tmem_base = *tmem_slot;
+  const unsigned tm_s[2] = {tmem_base, tmem_base + 64u};
+  const unsigned tm_o = tmem_base + 128u;
+
+  if (warp == 4) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * HALF_BYTES);
+      tma_load_2d(sq, &map_qkv, h * HD, row_base + q0, q_full);
+      tma_load_2d(sq + HALF_BYTES, &map_qkv, h * HD + 64, row_base + q0, q_full);
+      for (int j = 0; j < n; j++) {
+        const int s = j & 1, k0 = (first + j) * BN;
+        if (j >= 2 && !mbar_wait(&kv_empty[s], ((j >> 1) - 1) & 1, a.error_flag, abort_flag)) break;
+        mbar_expect_tx(&kv_full[s], 2 * KHALF_BYTES + HALF_BYTES);
+        tma_load_2d(sk + (size_t)(2 * s) * KHALF_BYTES, &map_k, (a.nh + kvh) * HD, row_base + k0, &kv_full[s]);
+        tma_load_2d(sk + (size_t)(2 * s + 1) * KHALF_BYTES, &map_k, (a.nh + kvh) * HD + 64, row_base + k0, &kv_full[s]);
+        tma_load_2d(sv + (size_t)s * HALF_BYTES, &map_vt, a.seq_vt_col[seq] + k0, kvh * HD, &kv_full[s]);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------------------------------------------------------- MMA issue (one thread)
+    if (lane == 0) {
+      const unsigned idesc_s = umma_idesc(BM, BN), idesc_o = umma_idesc(BM, HD);
+      auto issue_s = [&](int j) {                       // S(j) = Q K(j)^T into buffer j & 1
+        const int s = j & 1;
+#pragma unroll
+        for (int kb = 0; kb < 2; kb++) {
+          const unsigned long long qd = umma_smem_desc(smem_u32(sq + (size_t)kb * HALF_BYTES));
+          const unsigned long long kd = umma_smem_desc(smem_u32(sk + (size_t)(2 * s + kb) * KHALF_BYTES));
+#pragma unroll
+          for (int k = 0; k < 64 / UMMA_K; k++)
+            umma_bf16(tm_s[s], qd + (unsigned long long)(k * 2), kd + (unsigned long long)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+        }
+        umma_commit(&s_full[s]);
+      };
+      bool ok = mbar_wait(q_full, 0, a.error_flag, abort_flag) && mbar_wait(&kv_full[0], 0, a.error_flag, abort_flag);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        issue_s(0);
+      }
+      for (int j = 0; j < n && ok; j++) {
+        if (j + 1 < n) {
+          const int s1 = (j + 1) & 1;
+          ok = mbar_wait(&kv_full[s1], ((j + 1) >> 1) & 1, a.error_flag, abort_flag);
+          if (ok && j + 1 >= 2) ok = mbar_wait(&s_empty[s1], (((j + 1) >> 1) - 1) & 1, a.error_flag, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_s(j + 1);
+        }
+        ok = mbar_wait(p_full, j & 1, a.error_flag, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int s = j & 1;
+        {                                               // O += P V(j): 64 keys
+          const unsigned long long pd = umma_smem_desc(smem_u32(sp));
+          const unsigned long long vd = umma_smem_desc(smem_u32(sv + (size_t)s * HALF_BYTES));
+#pragma unroll
+          for (int k = 0; k < BN / UMMA_K; k++)
+            umma_bf16(tm_o, pd + (unsigned long long)(k * 2), vd + (unsigned long long)(k * 2), idesc_o, (j | k) ? 1u : 0u);
+        }
+        umma_commit(&kv_empty[s]);
+        umma_commit(pv_done);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax: thread = query row
+    const int r = warp * 32 + lane;                     // row of the block = TMEM lane
+    const int pos = q0 + r;                             // its position in the sequence
+    const unsigned lane_off = (unsigned)(warp * 32) << 16;
+    const float sc2 = a.scale * 1.4426950408889634f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n && ok; j++) {
+      const int s = j & 1, k0 = (first + j) * BN;
+      ok = mbar_wait(&s_full[s], (j >> 1) & 1, a.error_flag, abort_flag);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // does any key of this tile need the mask for any row of the block?
+      const bool masked = k0 + BN > q0 + 1 || k0 + BN > len || (a.window > 0 && k0 < q0 + BM - a.window);
+      const int key_hi = min(pos, len - 1);             // last key this row sees
+      const int key_lo = a.window > 0 ? pos - a.window + 1 : 0;
+      // the row's scores: the loads in flight together, one wait
+      constexpr int NC = BN / 32;
+      unsigned raw[NC][32];
+#pragma unroll
+      for (int c = 0; c < NC; c++) tmem_ld32_issue(tm_s[s] + lane_off + (unsigned)(c * 32), raw[c]);
+      tmem_ld_wait();
+      // S's buffer may be overwritten by the tile after next
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[s]);
+      // maxima of the raw scores (the scale is positive): four chains instead of one
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (masked) {
+#pragma unroll
+        for (int c = 0; c < NC; c++)
+#pragma unroll
+          for (int e = 0; e < 32; e++) {
+            const int key = k0 + c * 32 + e;
+            if (key > key_hi || key < key_lo) raw[c][e] = 0xff800000u;            // -inf
+            mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(raw[c][e]));
+          }
+      } else {
+#pragma unroll
+        for (int c = 0; c < NC; c++)
+#pragma unroll
+          for (int e = 0; e < 32; e++) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(raw[c][e]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc2;
+      // The reference point of the exponentials moves only when the row's maximum has grown by more than 2^8
+      // since it was set: O and the sum stay consistent with whatever reference they were made with, the
+      // probabilities stay below 2^8 (no harm in float32 or bfloat16), and O is rarely rescaled.
+      float alpha = 1.0f;
+      if (mx > m_run + 8.0f) {                          // also the first tile with a visible key (m_run = -inf)
+        alpha = ex2(m_run - mx);                        // 2^(-inf) = 0 while nothing was seen
+        m_run = mx;
+      }
+      const float neg_m = m_run == -INFINITY ? 0.f : -m_run;
+      l_run *= alpha;
+      // probabilities 2^(s * scale - m), summed in float32, packed as bfloat16 pairs in place
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < NC; c++)
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const float p0 = ex2(fmaf(__uint_as_float(raw[c][e]), sc2, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(raw[c][e + 1]), sc2, neg_m));
+          ps4[(e >> 1) & 3] += p0 + p1;
+          const __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+          raw[c][e >> 1] = *reinterpret_cast<const unsigned*>(&h2);
+        }
+      l_run += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+      // P's place and O are free once the previous tile's P V has completed
+      if (j > 0) {
+        ok = mbar_wait(pv_done, (j - 1) & 1, a.error_flag, abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+          for (int c = 0; c < 4; c++) {
+            float o[32];
+            tmem_ld32(tm_o + lane_off + (unsigned)(c * 32), o);
+#pragma unroll
+            for (int e = 0; e < 32; e++) o[e] *= alpha;
+            tmem_st32(tm_o + lane_off + (unsigned)(c * 32), o);
+          }
+        }
+      }
+      unsigned char* prow = sp + (size_t)(r >> 3) * 1024 + (size_t)(r & 7) * 128;
+#pragma unroll
+      for (int c = 0; c < NC; c++) {
+        // keys c*32 .. c*32+31 of the row: 16-byte pieces c * 4 .. + 3 of its 128 bytes, swizzled by the row
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const int piece = c * 4 + q;
+          *reinterpret_cast<uint4*>(prow + ((piece ^ (r & 7)) << 4)) =
+              make_uint4(raw[c][4 * q], raw[c][4 * q + 1], raw[c][4 * q + 2], raw[c][4 * q + 3]);
+        }
+      }
+      // P is written: make it visible to the tensor core's reads
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok && n > 0) ok = mbar_wait(pv_done, (n - 1) & 1, a.error_flag, abort_flag);
+    if (ok && n > 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      __nv_bfloat16* dst = a.out + (size_t)(row_base + pos) * a.ldo + (size_t)h * HD;
+#pragma unroll 1
+      for (int c = 0; c < 4; c++) {
+        float o[32];
+        tmem_ld32(tm_o + lane_off + (unsigned)(c * 32), o);
+        if (pos < len) {
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            uint4 t;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+            for (int k = 0; k < 4; k++) h2[k] = __floats2bfloat162_rn(o[8 * q + 2 * k] * inv, o[8 * q + 2 * k + 1] * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = t;
+          }
+        }
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 5) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
+  }
+}
+
+// V of a step's rows, transposed for the kernel above: vt[kvh * 128 + d][seq_vt_col[seq] + key] = v[key][d];
+// keys from a sequence's end to the next multiple of 128 are zero (P is zero there, and zero times what an
+// uninitialised buffer may hold need not be zero).  One block per (block of 128 keys, kv head).
+__global__ void __launch_bounds__(256)
+k_transpose_v(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ tile_seq,
+              const int* __restrict__ tile_row0, const int* __restrict__ seq_first_row,
+              const int* __restrict__ seq_vt_col, __nv_bfloat16* __restrict__ vt, int vt_cols, int nh, int nkv) {
+  cima_pdl_wait();
+  __shared__ __nv_bfloat16 tile[128][HD + 8];
+  const int seq = tile_seq[blockIdx.x], k0 = tile_row0[blockIdx.x], kvh = blockIdx.y;
+  const int row_base = seq_first_row[seq];
+  const int len = seq_first_row[seq + 1] - row_base;
+  const __nv_bfloat16* src = qkv + (size_t)(row_base + k0) * ld + (size_t)(nh + nkv + kvh) * HD;
+  for (int idx = threadIdx.x; idx < 128 * (HD / 8); idx += blockDim.x) {
+    const int key = idx / (HD / 8), d8 = (idx % (HD / 8)) * 8;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (k0 + key < len) v = *reinterpret_cast<const uint4*>(src + (size_t)key * ld + d8);
+    *reinterpret_cast<uint4*>(&tile[key][d8]) = v;
+  }
+  __syncthreads();
+  __nv_bfloat16* dst = vt + (size_t)(kvh * HD) * vt_cols + seq_vt_col[seq] + k0;
+  for (int idx = threadIdx.x; idx < HD * (128 / 8); idx += blockDim.x) {
+    const int d = idx % HD, k8 = (idx / HD) * 8;         // a warp's lanes walk along d: no bank conflicts in `tile`
+    uint4 v;
+    __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
+#pragma unroll
+    for (int q = 0; q < 8; q++) e[q] = tile[k8 + q][d];
+    *reinterpret_cast<uint4*>(dst + (size_t)d * vt_cols + k8) = v;
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+// A [rows, cols] bf16 matrix with row pitch ld seen through boxes of 64 columns x 128 rows, 128-byte swizzle,
+// zeros outside.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_rows = 128) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return cima_fail(CIMA_E_ARG, "attention_prefill_tc: the driver does not offer cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return cima_fail(CIMA_E_ARG, "attention_prefill_tc: cuTensorMapEncodeTiled failed with %d (base %p, %lld x %lld, pitch %lld)", (int)r, base, rows, cols, ld);
+  return 0;
+}
+
+}  // namespace
+
+// qkv [T, ld] bf16: q heads, k heads, v heads of each row, q and k already rotated.  tile_seq / tile_row0: the
+// blocks of 128 query rows, heaviest first.  seq_vt_col [seqs]: first column of each sequence in vt (a multiple
+// of 128); vt [nkv * 128, vt_cols] bf16 is scratch that this call fills (V transposed).  out [T, ldo].
+// head_dim is 128.  error_flag: device int that a wait that ran out sets to 1 (never cleared here).
+extern "C" int cima_attention_prefill_tc(const void* qkv, int ld, const int* tile_seq, const int* tile_row0,
+                                         const int* seq_first_row, const int* seq_vt_col, void* vt, int vt_cols,
+                                         void* out, int ldo, int T, int n_tiles, int nh, int nkv, int hd, float scale,
+                                         int window, int* error_flag, cudaStream_t stream) {
+  if (T <= 0 || n_tiles <= 0) return 0;
+  if (hd != HD) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: head_dim %d; this kernel takes 128", hd);
+  if (nh <= 0 || nkv <= 0 || nh % nkv) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: %d heads are not a multiple of %d kv heads", nh, nkv);
+  if (ld % 8 || ldo % 8 || vt_cols % 128 || vt_cols <= 0) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: row strides (%d, %d) must be multiples of 8 and the transposed V's columns (%d) of 128", ld, ldo, vt_cols);
+  if (ld < (nh + 2 * nkv) * hd) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: row stride %d is smaller than (heads + 2 kv heads) * head_dim", ld);
+  if ((((uintptr_t)qkv | (uintptr_t)vt | (uintptr_t)out) & 15)) return cima_fail(CIMA_E_ARG, "attention_prefill_tc: qkv, vt and out must be 16-byte aligned");
+  if (!error_flag) return cima_fail(CIMA_E_ARG, "attention_prefill_tc: an error flag on the device is needed");
+  if (nh > 65535 || nkv > 65535) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: %d heads exceed one launch", nh);
+  CUtensorMap mq, mk, mv;
+  int rc = make_map(&mq, qkv, T, (long long)(nh + 2 * nkv) * hd, ld);
+  if (rc) return rc;
+  rc = make_map(&mk, qkv, T, (long long)(nh + 2 * nkv) * hd, ld, BN);
+  if (rc) return rc;
+  rc = make_map(&mv, vt, (long long)nkv * hd, vt_cols, vt_cols);
+  if (rc) return rc;
+  { int rc_ = cima_launch(k_transpose_v, dim3(n_tiles, nkv), dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)qkv, ld, tile_seq, tile_row0, seq_first_row, seq_vt_col, (__nv_bfloat16*)vt, vt_cols, nh, nkv); if (rc_) return rc_; }
+  rc = cima_launch_result();
+  if (rc) return rc;
+  const size_t smem = 2 * (size_t)HALF_BYTES + 4 * (size_t)KHALF_BYTES + 2 * (size_t)HALF_BYTES + HALF_BYTES + 16 * 8 + 16;
+  static bool raised = false;
+  if (!raised) {
+    cudaError_t e = cudaFuncSetAttribute(k_attention_prefill_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cima_fail((int)e, "attention_prefill_tc: cannot raise shared memory to %zu bytes: %s", smem, cudaGetErrorString(e));
+    raised = true;
+  }
+  AttnArgs a{tile_seq, tile_row0, seq_first_row, seq_vt_col, (__nv_bfloat16*)out, ldo, nh, nkv, window, scale, error_flag};
+  { int rc_ = cima_launch(k_attention_prefill_tc, dim3(n_tiles, nh), dim3(THREADS), smem, stream, 1, mq, mk, mv, a); if (rc_) return rc_; }
+  return cima_launch_result();
+}

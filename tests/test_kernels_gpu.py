@@ -171,7 +171,14 @@ def batch_of(seqs, device):
         first.append(first[-1] + n)
     t = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
     tiles = sorted(((i, r0) for i, s in enumerate(seqs) for r0 in range(0, s[2], 64)), key=lambda x: -x[1])
+    tc = [x for x in tiles if x[1] % 128 == 0]
+    vt_col, cols = [], 0
+    for s in seqs:
+        vt_col.append(cols)
+        cols += -(-s[2] // 128) * 128
     return SimpleNamespace(n_q_tiles=len(tiles) if all(s[1] == 0 for s in seqs) else 0,
+                           n_q_tiles_tc=len(tc), q_tile_tc_seq=t([x[0] for x in tc]), q_tile_tc_row0=t([x[1] for x in tc]),
+                           seq_vt_col=t(vt_col), vt_cols=cols,
                            q_tile_seq=t([x[0] for x in tiles]), q_tile_row0=t([x[1] for x in tiles]),
                            row_pos=t(row_pos), row_seq=t(row_seq), seq_slot=t([s[0] for s in seqs]),
                            seq_first_row=t(first), seq_len=t([s[1] + s[2] for s in seqs]),
@@ -370,6 +377,28 @@ def test_attention_prefill_over_the_step(K, dtype, nh, nkv, hd, window):
     plain = torch.empty_like(out)
     K.attention_plain(qkv.cuda(), None, bg.row_pos, bg.row_seq, bg.seq_slot, bg.seq_first_row, plain, nh, nkv, hd, scale, window, False)
     assert err(plain, want) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("lens", [[130, 1, 67, 300], [128], [1], [257, 256, 255], [700, 40]])
+@pytest.mark.parametrize("nh,nkv,window", [(7, 1, 0), (4, 2, 0), (28, 4, 0), (4, 2, 50), (2, 2, 200), (3, 1, 128), (2, 1, 1)])
+def test_attention_prefill_tcgen05(K, lens, nh, nkv, window):
+    """The tcgen05 attention of ragged prompts (head_dim 128) against the float64 statement: sequences that
+    end inside a block of 128, a far key that stands out, windows with edges inside and between tiles."""
+    hd = 128
+    seqs = [(i, 0, n) for i, n in enumerate(lens)]
+    T = sum(lens)
+    scale = 1.0 / math.sqrt(hd)
+    qkv = g(T, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, seed=nh + T)
+    if lens[-1] > 6 and (window == 0 or window >= lens[-1]):
+        # in the last sequence, key 5 stands out for the last query of head 0 (a far key among hundreds)
+        qkv[T - lens[-1] + 5, nh * hd:(nh + 1) * hd] = qkv[T - 1, :hd] * 6.0
+    bc, bg = batch_of(seqs, "cpu"), batch_of(seqs, "cuda")
+    want = torch.zeros(T, nh * hd, dtype=torch.float64)
+    REF.attention_plain(qkv, None, bc.row_pos, bc.row_seq, bc.seq_slot, bc.seq_first_row, want, nh, nkv, hd, scale, window, False)
+    out = torch.full((T, nh * hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.attention_prefill_tc(qkv.cuda(), bg, out, nh, nkv, hd, scale, window)
+    assert K.device_errors() == 0
+    assert err(out, want) <= TOL["bfloat16"]
 
 
 # ---------------------------------------------------------------------------- sampling
