@@ -181,13 +181,15 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
   unsigned char* sp = sv + 2 * HALF_BYTES;                     // P: [128 query rows][64 keys]
   unsigned long long* bars = (unsigned long long*)(sp + HALF_BYTES);
   unsigned long long* q_full = bars;                           // [1]
-  unsigned long long* kv_full = bars + 1;                      // [2]
-  unsigned long long* kv_empty = bars + 3;                     // [2]
-  unsigned long long* s_full = bars + 5;                       // [2]
-  unsigned long long* s_empty = bars + 7;                      // [2]
-  unsigned long long* p_full = bars + 9;                       // [1]
-  unsigned long long* pv_done = bars + 10;                     // [1]
-  unsigned* tmem_slot = (unsigned*)(bars + 11);
+  unsigned long long* k_full = bars + 1;                       // [2]
+  unsigned long long* k_empty = bars + 3;                      // [2]  K's place is free once S of its tile is done,
+  unsigned long long* v_full = bars + 5;                       // [2]  long before V's (after P V): the two rings run
+  unsigned long long* v_empty = bars + 7;                      // [2]  apart, so K is fetched two tiles ahead
+  unsigned long long* s_full = bars + 9;                       // [2]
+  unsigned long long* s_empty = bars + 11;                     // [2]
+  unsigned long long* p_full = bars + 13;                      // [1]
+  unsigned long long* pv_done = bars + 14;                     // [1]
+  unsigned* tmem_slot = (unsigned*)(bars + 15);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -202,7 +204,10 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
   if (threadIdx.x == 0 && (smem_u32(smem) & 1023u)) atomicExch(a.error_flag, 2);   // never seen; the tiles would be misread
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; s++) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4); }
+    for (int s = 0; s < 2; s++) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
+    }
     mbar_init(p_full, 4);
     mbar_init(pv_done, 1);
     *abort_flag = 0;
@@ -221,18 +226,25 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
   const unsigned tm_o = tmem_base + 128u;
 
   if (warp == 4) {
-    // ---------------------------------------------------------------- TMA producer
+    // ---------------------------------------------------------------- TMA producers: lane 0 Q and K, lane 1 V
     if (lane == 0) {
       mbar_expect_tx(q_full, 2 * HALF_BYTES);
       tma_load_2d(sq, &map_qkv, h * HD, row_base + q0, q_full);
       tma_load_2d(sq + HALF_BYTES, &map_qkv, h * HD + 64, row_base + q0, q_full);
       for (int j = 0; j < n; j++) {
         const int s = j & 1, k0 = (first + j) * BN;
-        if (j >= 2 && !mbar_wait(&kv_empty[s], ((j >> 1) - 1) & 1, a.error_flag, abort_flag)) break;
-        mbar_expect_tx(&kv_full[s], 2 * KHALF_BYTES + HALF_BYTES);
-        tma_load_2d(sk + (size_t)(2 * s) * KHALF_BYTES, &map_k, (a.nh + kvh) * HD, row_base + k0, &kv_full[s]);
-        tma_load_2d(sk + (size_t)(2 * s + 1) * KHALF_BYTES, &map_k, (a.nh + kvh) * HD + 64, row_base + k0, &kv_full[s]);
-        tma_load_2d(sv + (size_t)s * HALF_BYTES, &map_vt, a.seq_vt_col[seq] + k0, kvh * HD, &kv_full[s]);
+        if (j >= 2 && !mbar_wait(&k_empty[s], ((j >> 1) - 1) & 1, a.error_flag, abort_flag)) break;
+        mbar_expect_tx(&k_full[s], 2 * KHALF_BYTES);
+        tma_load_2d(sk + (size_t)(2 * s) * KHALF_BYTES, &map_k, (a.nh + kvh) * HD, row_base + k0, &k_full[s]);
+        tma_load_2d(sk + (size_t)(2 * s + 1) * KHALF_BYTES, &map_k, (a.nh + kvh) * HD + 64, row_base + k0, &k_full[s]);
+      }
+    } else if (lane == 1) {
+      const int col0 = a.seq_vt_col[seq];
+      for (int j = 0; j < n; j++) {
+        const int s = j & 1, k0 = (first + j) * BN;
+        if (j >= 2 && !mbar_wait(&v_empty[s], ((j >> 1) - 1) & 1, a.error_flag, abort_flag)) break;
+        mbar_expect_tx(&v_full[s], HALF_BYTES);
+        tma_load_2d(sv + (size_t)s * HALF_BYTES, &map_vt, col0 + k0, kvh * HD, &v_full[s]);
       }
     }
   } else if (warp == 5) {
@@ -250,8 +262,9 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
             umma_bf16(tm_s[s], qd + (unsigned long long)(k * 2), kd + (unsigned long long)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
         }
         umma_commit(&s_full[s]);
+        umma_commit(&k_empty[s]);                       // K's place is free when these have read it
       };
-      bool ok = mbar_wait(q_full, 0, a.error_flag, abort_flag) && mbar_wait(&kv_full[0], 0, a.error_flag, abort_flag);
+      bool ok = mbar_wait(q_full, 0, a.error_flag, abort_flag) && mbar_wait(&k_full[0], 0, a.error_flag, abort_flag);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         issue_s(0);
@@ -259,13 +272,13 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
       for (int j = 0; j < n && ok; j++) {
         if (j + 1 < n) {
           const int s1 = (j + 1) & 1;
-          ok = mbar_wait(&kv_full[s1], ((j + 1) >> 1) & 1, a.error_flag, abort_flag);
+          ok = mbar_wait(&k_full[s1], ((j + 1) >> 1) & 1, a.error_flag, abort_flag);
           if (ok && j + 1 >= 2) ok = mbar_wait(&s_empty[s1], (((j + 1) >> 1) - 1) & 1, a.error_flag, abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           issue_s(j + 1);
         }
-        ok = mbar_wait(p_full, j & 1, a.error_flag, abort_flag);
+        ok = mbar_wait(&v_full[j & 1], (j >> 1) & 1, a.error_flag, abort_flag) && mbar_wait(p_full, j & 1, a.error_flag, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int s = j & 1;
@@ -276,7 +289,7 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
           for (int k = 0; k < BN / UMMA_K; k++)
             umma_bf16(tm_o, pd + (unsigned long long)(k * 2), vd + (unsigned long long)(k * 2), idesc_o, (j | k) ? 1u : 0u);
         }
-        umma_commit(&kv_empty[s]);
+        umma_commit(&v_empty[s]);
         umma_commit(pv_done);
       }
     }
@@ -501,6 +514,7 @@ extern "C" int cima_attention_prefill_tc(const void* qkv, int ld, const int* til
   rc = cima_launch_result();
   if (rc) return rc;
   const size_t smem = 2 * (size_t)HALF_BYTES + 4 * (size_t)KHALF_BYTES + 2 * (size_t)HALF_BYTES + HALF_BYTES + 16 * 8 + 16;
+  static_assert(15 * 8 + 8 <= 16 * 8 + 16, "barriers and flags fit their place");
   static bool raised = false;
   if (!raised) {
     cudaError_t e = cudaFuncSetAttribute(k_attention_prefill_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
