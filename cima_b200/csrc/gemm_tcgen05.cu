@@ -25,107 +25,22 @@
 // The reference has no kernel of this kind: its only tensor-core path is cublasGemmEx
 // (src/cuda.rs:2484-2541), its own k_gemm_f16 is a 16x16 shared-memory tile on CUDA cores
 // (src/kernels.cu:1410-1431).
-#include "common.cuh"
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
+#include "tcgen05.cuh"
 
 namespace {
+
+using namespace cima_tc;
 
 constexpr int BM = 128;          // rows of P per tile = TMEM lanes
 constexpr int BK = 64;           // k per stage: 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr unsigned long long WAIT_NS = 2000000000ull;
 
 enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3 };
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long globaltimer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
 
-__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait: false when it ran out (the flag is set, the caller leaves its loop).
-__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, int* error_flag, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer();
-  for (unsigned it = 0;; it++) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 255u) == 255u) {
-      if (*abort_flag) return false;
-      if (globaltimer() - t0 > WAIT_NS) {
-        *abort_flag = 1;
-        atomicExch(error_flag, 1);
-        return false;
-      }
-    }
-  }
-}
 
-__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, int x, int y, void* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(smem_u32(smem)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
 
-// Shared-memory operand descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle, groups of 8 rows
-// 1024 bytes apart.  Fields: start address >> 4 [0,14), leading byte offset >> 4 [16,30) (unused for this
-// layout), stride byte offset >> 4 [32,46), descriptor version 1 [46,48), layout type 2 = SWIZZLE_128B [61,64).
-__device__ __forceinline__ unsigned long long umma_smem_desc(unsigned smem_addr) {
-  unsigned long long d = 0;
-  d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
-  d |= (unsigned long long)(1u) << 16;
-  d |= (unsigned long long)(1024u >> 4) << 32;
-  d |= 1ull << 46;
-  d |= 2ull << 61;
-  return d;
-}
-// Instruction descriptor, kind::f16: D float32 [4,6) = 1, A and B bfloat16 [7,10) = [10,13) = 1, both K-major,
-// N >> 3 at [17,23), M >> 4 at [24,29).
-__device__ __forceinline__ unsigned umma_idesc(int M, int N) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(N >> 3) << 17) | ((unsigned)(M >> 4) << 24);
-}
-__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc,
-                                          unsigned idesc, unsigned accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(void* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
-  unsigned r[32];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
-}
 
 struct GemmArgs {
   int p_rows, q_rows, K;      // extents of P, Q and of the sum
@@ -138,9 +53,6 @@ struct GemmArgs {
   int* error_flag;
 };
 
-__device__ __forceinline__ void mbar_arrive(void* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 // Persistent: the grid has at most one block per SM; a block takes tiles blockIdx.x, blockIdx.x + gridDim.x, ...
 // Tile t -> (t % p_tiles, t / p_tiles): the blocks that run together cover all tiles of P (few) times a few
@@ -319,36 +231,8 @@ k_gemm_tcgen05(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  });
-  return fn;
-}
 
-// A [rows, K] bf16 row-major matrix seen through boxes of 64 k x box_rows rows, 128-byte swizzle, zeros outside.
-int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return cima_fail(CIMA_E_ARG, "gemm_tcgen05: the driver does not offer cuTensorMapEncodeTiled");
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return cima_fail(CIMA_E_ARG, "gemm_tcgen05: cuTensorMapEncodeTiled failed with %d (base %p, rows %d, K %d, box %d)", (int)r, base, rows, K, box_rows);
-  return 0;
-}
 
 int sm_count() {
   static int n = 0;
@@ -407,9 +291,9 @@ extern "C" int cima_gemm_tcgen05(const void* P, const void* Q, const float* bias
   const int q_feat = epi == EPI_SWIGLU ? up_offset : q_rows;
   const int tiles_q = (q_feat + qh - 1) / qh;
   CUtensorMap mp, mq;
-  int rc = make_map(&mp, P, p_rows, K, BM);
+  int rc = make_map(&mp, P, p_rows, K, K, BM);
   if (rc) return rc;
-  rc = make_map(&mq, Q, q_rows, K, qh);
+  rc = make_map(&mq, Q, q_rows, K, K, qh);
   if (rc) return rc;
   GemmArgs a{p_rows, q_rows, K, up_offset, bias, out, ldo, transposed, bias_on_p, error_flag};
   switch (bn) {
