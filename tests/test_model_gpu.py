@@ -157,3 +157,39 @@ def test_step_refuses_mixed_batches_and_overflow():
     finally:
         m.cache.close(s)
     m.cache.check()
+
+
+ODD = [dict(hidden_size=100, num_attention_heads=5, num_key_value_heads=5, head_dim=16, intermediate_size=130, vocab_size=333),
+       dict(hidden_size=104, num_attention_heads=2, num_key_value_heads=1, head_dim=48, intermediate_size=99, vocab_size=1001)]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("over", ODD)
+def test_widths_that_are_no_multiple_of_eight(over, dtype, tmp_path):
+    """Hidden and intermediate widths and a vocabulary that fit none of the 16-byte paths: a prompt whole,
+    then ten tokens one by one, against the plain implementation."""
+    import cima_b200
+    from cima_b200.engine import load_model
+    cfg = dict(model_type="qwen2", architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, rope_theta=10000.0,
+               rms_norm_eps=1e-6, tie_word_embeddings=False, use_sliding_window=False, max_position_embeddings=256, **over)
+    folder = str(tmp_path / "m")
+    cima_b200.write_random_model(folder, cfg, seed=3)
+    c, W = plain_load(folder)
+    toks = random_tokens(cfg["vocab_size"], 70, 0)
+    want = plain_forward(W, c, toks).float()
+    m = load_model(folder, dtype=dtype, max_tokens=512, device="cuda:0", verbose=False)
+    (slot,) = m.cache.open(1)
+    try:
+        assert close(m.step([StepEntry(slot, toks[:60], list(range(60)))]).cpu(), want[:60], TOL[dtype])
+        for t in range(60, 70):
+            assert close(m.step([StepEntry(slot, [toks[t]], [0])]).cpu()[0], want[t], TOL[dtype]), t
+    finally:
+        m.cache.close([slot])
+
+
+def test_a_head_size_outside_the_steps_of_16_is_refused(tmp_path):
+    import cima_b200
+    cfg = dict(model_type="qwen2", architectures=["Qwen2ForCausalLM"], num_hidden_layers=1, hidden_size=100,
+               num_attention_heads=5, num_key_value_heads=5, head_dim=20, intermediate_size=64, vocab_size=50)
+    with pytest.raises(ValueError, match="head_dim 20 must be a multiple of 16"):
+        cima_b200.write_random_model(str(tmp_path / "m"), cfg, seed=0)
