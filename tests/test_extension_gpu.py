@@ -1,7 +1,9 @@
 """Generality of the parts: a toy mixer with state of its own, defined here, is registered, built
 into a toy architecture (also registered here) and stepped, without any change to the package.
 The toy model also runs one layer twice (each run with storage of its own) and lets one attention
-layer read another layer's keys and values."""
+layer read another layer's keys and values.  A second toy architecture has a feed-forward with routing
+(top-1 of three experts) and a position encoding of its own (partial rotary with scaled frequencies) in
+some layers and the package's parts in the others."""
 import json
 import math
 import os
@@ -131,3 +133,141 @@ def test_toy_mixer_with_state_registers_builds_and_steps(dtype, tol):
         model.cache.close(slots)
     assert (lg[0] - toy_plain(W, TOY, toks2).float()[39]).abs().max().item() <= tol
     assert (lg[1] - want[89]).abs().max().item() <= tol
+
+
+# ---------------------------------------------------------------------------------------------
+# A feed-forward with routing and another position encoding, both defined here.
+# ---------------------------------------------------------------------------------------------
+class Top1Experts:
+    """x += expert_e(h) for the expert e whose router logit is largest (ties to the lower index); every expert is
+    a small gated MLP.  Router logits in float32.  Plain tensor operations: it shows the interface, not speed."""
+
+    def __init__(self, spec, layer, rt):
+        self.spec, self.layer, self.rt = spec, layer, rt
+        self.E = spec.params["experts"]
+
+    def plan(self, prefix, names):
+        s = self.spec
+        p = {f"{prefix}moe.router.weight": TensorSpec((self.E, s.hidden))}
+        for e in range(self.E):
+            p[f"{prefix}moe.{e}.gate.weight"] = TensorSpec((s.intermediate, s.hidden))
+            p[f"{prefix}moe.{e}.up.weight"] = TensorSpec((s.intermediate, s.hidden))
+            p[f"{prefix}moe.{e}.down.weight"] = TensorSpec((s.hidden, s.intermediate))
+        return p
+
+    def load(self, tensors, prefix, names):
+        self.router = tensors[f"{prefix}moe.router.weight"].to(self.rt.device, torch.float32)
+        self.w = [tuple(self.rt.matrix(tensors[f"{prefix}moe.{e}.{n}.weight"]) for n in ("gate", "up", "down"))
+                  for e in range(self.E)]
+
+    def nbytes(self):
+        return self.router.numel() * 4 + sum(t.numel() * t.element_size() for w in self.w for t in w)
+
+    def forward(self, h, x, batch):
+        choice = torch.argmax(h.float() @ self.router.t(), dim=1)        # first maximum = lower index
+        for e, (wg, wu, wd) in enumerate(self.w):
+            rows = torch.nonzero(choice == e).flatten()
+            if rows.numel():
+                he = h[rows].to(wg.dtype)
+                g, u = (he @ wg.t()).float(), (he @ wu.t()).float()
+                a = (g / (1 + torch.exp(-g)) * u).to(wd.dtype)
+                x[rows] += (a @ wd.t()).float()
+
+
+class ScaledRope:
+    """Rotary encoding over the first rotary_dim dimensions with every frequency divided by ``factor``."""
+
+    def __init__(self, spec, rt):
+        self.spec, self.rotary_dim = spec, spec.rotary_dim
+        i = torch.arange(spec.rotary_dim // 2, dtype=torch.float64)
+        inv = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / spec.rotary_dim) / spec.params["factor"]
+        self.inv_freq = inv.to(torch.float32).to(rt.device).contiguous()
+
+
+def toy2_spec(cfg) -> ModelSpec:
+    H, nh, nkv, hd = cfg["hidden_size"], cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
+    names = {"q": "attn.q", "k": "attn.k", "v": "attn.v", "o": "attn.o", "gate": "ffn.gate", "up": "ffn.up",
+             "down": "ffn.down", "mixer_norm": "norm1", "ffn_norm": "norm2"}
+    norm = NormSpec("rmsnorm", H, cfg["eps"])
+    layers = []
+    for i in range(cfg["layers"]):
+        pos = (PositionSpec("toy_scaled_rope", hd, cfg["rotary_dim"], cfg["theta"], {"factor": cfg["factor"]}) if i % 2 == 0
+               else PositionSpec("rope", hd, hd, cfg["theta"]))
+        mixer = MixerSpec("attention", H, nh, nkv, hd, True, False, 0, 1.0 / math.sqrt(hd), pos)
+        ffn = (FeedForwardSpec("toy_top1_experts", H, cfg["expert_intermediate"], "silu", False, {"experts": cfg["experts"]})
+               if i % 2 == 0 else FeedForwardSpec("gated_mlp", H, cfg["intermediate"], "silu"))
+        layers.append(BlockSpec("prenorm", mixer, ffn, norm, norm, f"blocks.{i}.", names))
+    return ModelSpec("ToyRoutedForCausalLM", cfg["vocab_size"], H, cfg["max_positions"], layers, list(range(cfg["layers"])),
+                     norm, False, "embed.weight", "final_norm.weight", "head.weight")
+
+
+TOY2 = dict(architectures=["ToyRoutedForCausalLM"], model_type="toyrouted", hidden_size=80, vocab_size=211, heads=5,
+            kv_heads=1, head_dim=32, rotary_dim=16, factor=4.0, intermediate=120, expert_intermediate=48, experts=3,
+            eps=1e-6, theta=5000.0, max_positions=256, layers=3)
+
+
+def toy2_plain(W, cfg, tokens):
+    W = {k: v.double() for k, v in W.items()}
+    T = len(tokens)
+    nh, nkv, hd, rd = cfg["heads"], cfg["kv_heads"], cfg["head_dim"], cfg["rotary_dim"]
+    posn = torch.arange(T)
+
+    def scaled_partial_rope(u):
+        i = torch.arange(rd // 2, dtype=torch.float64)
+        ang = posn.double()[:, None] * (cfg["theta"] ** (-2.0 * i / rd) / cfg["factor"])[None, :]
+        a, b = u[..., :rd // 2], u[..., rd // 2:rd]
+        c, s = ang.cos()[:, None], ang.sin()[:, None]
+        return torch.cat([a * c - b * s, a * s + b * c, u[..., rd:]], dim=-1)
+
+    x = plain_embed(W["embed.weight"], tokens)
+    for i in range(cfg["layers"]):
+        p = f"blocks.{i}."
+        h = plain_rmsnorm(x, W[p + "norm1.weight"], cfg["eps"])
+        q = plain_linear(h, W[p + "attn.q.weight"], W[p + "attn.q.bias"]).view(T, nh, hd)
+        k = plain_linear(h, W[p + "attn.k.weight"], W[p + "attn.k.bias"]).view(T, nkv, hd)
+        v = plain_linear(h, W[p + "attn.v.weight"], W[p + "attn.v.bias"]).view(T, nkv, hd)
+        if i % 2 == 0:
+            q, k = scaled_partial_rope(q), scaled_partial_rope(k)
+        else:
+            q, k = plain_rope(q, posn, cfg["theta"]), plain_rope(k, posn, cfg["theta"])
+        x = x + plain_linear(plain_attention(q, k, v).reshape(T, nh * hd), W[p + "attn.o.weight"])
+        h = plain_rmsnorm(x, W[p + "norm2.weight"], cfg["eps"])
+        if i % 2 == 0:
+            choice = torch.argmax(h @ W[p + "moe.router.weight"].t(), dim=1)
+            y = torch.zeros_like(x)
+            for t in range(T):
+                e = int(choice[t])
+                y[t] = plain_swiglu_mlp(h[t:t + 1], W[p + f"moe.{e}.gate.weight"], W[p + f"moe.{e}.up.weight"],
+                                        W[p + f"moe.{e}.down.weight"])[0]
+            x = x + y
+        else:
+            x = x + plain_swiglu_mlp(h, W[p + "ffn.gate.weight"], W[p + "ffn.up.weight"], W[p + "ffn.down.weight"])
+    return plain_linear(plain_rmsnorm(x, W["final_norm.weight"], cfg["eps"]), W["head.weight"]), None
+
+
+def test_toy_routed_feed_forward_and_another_position_encoding():
+    """A feed-forward with routing and a position encoding of the test's own (partial rotary with scaled
+    frequencies) are registered from here, built layer by layer beside the package's own parts, and stepped in
+    every cutting.  32-bit only: a near-tie between two router logits may fall the other way in bfloat16, which
+    says nothing about the interface."""
+    from cima_b200.parts import register_feed_forward, register_position
+    register_feed_forward("toy_top1_experts", Top1Experts)
+    register_position("toy_scaled_rope", ScaledRope)
+    register_architecture(ArchitectureEntry("ToyRoutedForCausalLM", "toyrouted", parse=lambda raw: raw, spec=toy2_spec))
+    folder = tempfile.mkdtemp(prefix="cima_toy2_")
+    write_random_model(folder, TOY2, build_plan(toy2_spec(TOY2)), seed=9)
+    from safetensors.torch import load_file
+    W = load_file(os.path.join(folder, "model.safetensors"))
+    model = load_model(folder, dtype="float32", max_tokens=1024, verbose=False)
+    toks = random_tokens(TOY2["vocab_size"], 100, seed=4)
+    want = toy2_plain(W, TOY2, toks)[0].float()
+    assert (run_whole(model, toks) - want).abs().max().item() <= 2e-5
+    assert (run_tail_one_by_one(model, toks, 32) - want).abs().max().item() <= 2e-5
+    toks2 = random_tokens(TOY2["vocab_size"], 33, seed=5)
+    slots = model.cache.open(2)
+    try:
+        lg = model.step([StepEntry(slots[0], toks2, [32]), StepEntry(slots[1], toks, [99])]).float().cpu()
+    finally:
+        model.cache.close(slots)
+    assert (lg[0] - toy2_plain(W, TOY2, toks2)[0].float()[32]).abs().max().item() <= 2e-5
+    assert (lg[1] - want[99]).abs().max().item() <= 2e-5
