@@ -1,5 +1,5 @@
 """One launch (three, the first two as warm-up) of the tcgen05 prefill attention on random q/k/v of a 2,048-token
-prompt with the 7B head shapes: the workload of profiles/prefill_2048_attention_prefill_tcgen05.md.  Not a test."""
+prompt with the 7B head shapes: the small workload on which this kernel is profiled.  Not a test."""
 import sys, os
 sys.path.insert(0, os.getcwd())
 import torch
