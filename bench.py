@@ -143,7 +143,9 @@ def main(argv=None) -> int:
     torch.cuda.empty_cache()
     max_batch = max(a.batch, 1 if a.no_points else 64)
     per_seq = a.prompt + a.steps + a.warmup + 64
-    model.make_cache(max_tokens=max_batch * (-(-per_seq // 64) * 64), max_seqs=max_batch, extra_state=sampler_state())
+    # room for the batches of the decode runs, and for the one 2,048-token prompt of the prefill figure
+    model.make_cache(max_tokens=max(max_batch * (-(-per_seq // 64) * 64), 2048 + 64), max_seqs=max_batch,
+                     extra_state=sampler_state())
     # e2e below is measured with every step's input tokens copied from pinned host memory (pipeline off);
     # "e2e_pipelined" is the default mode of the library, where the next step is queued before the host has
     # read the current one's tokens and its inputs never leave the device
