@@ -268,10 +268,12 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   }
 }
 
-// out[b, h, :] = sum_s e^(m_s - M) o_s / sum_s e^(m_s - M) l_s, splits in order.
-// One block per (head, sequence): the weights e^(m_s - M) are made once (one thread per split) and
-// kept in shared memory; then a thread per dimension sums the splits' accumulators, whose loads
-// are independent of one another.
+// out[b, h, :] = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s.
+// One block per (head, sequence).  The first warp loads every split's (m, l) at once (a lane per split, all loads
+// independent), makes the weights 2^(m_s - M) and their sum with l by a shuffle tree (a fixed order, whatever the
+// timing), and leaves them in shared memory; then a thread per dimension sums the splits' accumulators, eight
+// independent loads at a time.  (A loop of one thread over the splits' l, as this kernel once had, costs a trip to
+// L2 per split: 8 us at 32 splits.)
 __global__ void __launch_bounds__(128)
 k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                     __nv_bfloat16* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
@@ -281,37 +283,40 @@ k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ 
   const int b = blockIdx.y, h = blockIdx.x;
   const size_t base = ((size_t)b * nh + h) * n_splits;
   if (threadIdx.x < 32) {
-    float m[MAX_SPLITS / 32];
+    float m[MAX_SPLITS / 32], l[MAX_SPLITS / 32];
     float M = -INFINITY;
 #pragma unroll
     for (int i = 0; i < MAX_SPLITS / 32; i++) {
       const int s = threadIdx.x + 32 * i;
-      m[i] = s < n_splits ? part_ml[(base + s) * 2] : -INFINITY;
+      const float2 ml = s < n_splits ? *reinterpret_cast<const float2*>(part_ml + (base + s) * 2) : make_float2(-INFINITY, 0.f);
+      m[i] = ml.x;
+      l[i] = ml.y;
       M = fmaxf(M, m[i]);
     }
     for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
     const float Ms = M == -INFINITY ? 0.f : M;
+    float L = 0.f;
 #pragma unroll
     for (int i = 0; i < MAX_SPLITS / 32; i++) {
       const int s = threadIdx.x + 32 * i;
-      if (s < n_splits) w[s] = ex2(m[i] - Ms);
+      const float ws = ex2(m[i] - Ms);                 // 0 for a split beyond n_splits or without keys
+      if (s < n_splits) w[s] = ws;
+      L += ws * l[i];
     }
-    __syncwarp();
-    if (threadIdx.x == 0) {
-      float L = 0.f;                                   // splits in order, one thread: a fixed sum
-      for (int s = 0; s < n_splits; s++) L += w[s] * part_ml[(base + s) * 2 + 1];
-      s_inv = L > 0.f ? 1.0f / L : 0.f;
-    }
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    if (threadIdx.x == 0) s_inv = L > 0.f ? 1.0f / L : 0.f;
   }
   __syncthreads();
   const float inv = s_inv;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float acc = 0.f;
     int s = 0;
-    for (; s + 4 <= n_splits; s += 4) {
-      const float o0 = part_o[(base + s) * hd + d], o1 = part_o[(base + s + 1) * hd + d];
-      const float o2 = part_o[(base + s + 2) * hd + d], o3 = part_o[(base + s + 3) * hd + d];
-      acc += w[s] * o0; acc += w[s + 1] * o1; acc += w[s + 2] * o2; acc += w[s + 3] * o3;
+    for (; s + 8 <= n_splits; s += 8) {
+      float o[8];
+#pragma unroll
+      for (int q = 0; q < 8; q++) o[q] = part_o[(base + s + q) * hd + d];
+#pragma unroll
+      for (int q = 0; q < 8; q++) acc += w[s + q] * o[q];
     }
     for (; s < n_splits; s++) acc += w[s] * part_o[(base + s) * hd + d];
     out[(size_t)b * ldo + (size_t)h * hd + d] = __float2bfloat16_rn(acc * inv);
