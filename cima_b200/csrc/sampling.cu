@@ -259,8 +259,8 @@ k_sample(const float* __restrict__ logits, int ld, int V, const int* __restrict_
 //
 // With top_k = 0 (or at least the vocabulary) the 1024 largest tokens stand in for the whole row (the sum of
 // all masses is taken over the whole row): if the top-p cut and the draw both fall inside them the row is
-// settled, else the kernel writes token -1, leaves the sequence's state alone, and k_sample (only_unresolved)
-// does the row.  A top_k between 1025 and the vocabulary goes to k_sample at once.
+// settled; else, and for a top_k between 1025 and the vocabulary, the blocks search the whole row together
+// (the bisection of k_sample, over the slices in shared memory: about 2 us a pass instead of 20).
 // ---------------------------------------------------------------------------------------------
 constexpr int FAST_BLOCKS = 8;
 constexpr int FAST_THREADS = 512;
@@ -278,7 +278,8 @@ k_sample_fast(const float* __restrict__ logits, int ld, int V, const int* __rest
   cima_pdl_wait();
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
-  extern __shared__ float sl[];                       // this block's slice of the row; later the probabilities
+  extern __shared__ float sl[];                       // this block's slice of the (penalised) row
+  __shared__ float pr_s[FAST_MAXK];                   // block 0: probabilities of the kept tokens, in order
   __shared__ int hist[256];
   __shared__ int merged[256];
   __shared__ unsigned long long cand[FAST_MAXK];      // this block's kept keys, any order
@@ -288,6 +289,8 @@ k_sample_fast(const float* __restrict__ logits, int ld, int V, const int* __rest
   __shared__ unsigned long long s_best;
   __shared__ int ncand, s_sel, s_above, s_cnt, s_total_n;
   __shared__ float s_mass, s_total_all;
+  __shared__ float s_part[2];
+  __shared__ int s_resolved;
   const int C = FAST_BLOCKS, c = blockIdx.x, row = blockIdx.y, tid = threadIdx.x;
   const int slot = row_slot[row];
   const float temperature = params[row * 4 + 0];
@@ -339,146 +342,244 @@ k_sample_fast(const float* __restrict__ logits, int ld, int V, const int* __rest
   const int kk = (top_k <= 0 || top_k > V) ? V : top_k;
   const bool exact = kk <= FAST_MAXK;                 // the kept set is gathered whole
   const int want = exact ? kk : FAST_MAXK;
-  if (!exact && kk < V) {
-    // more than 1024 kept, but not the whole row: the sum of the kept masses is not at hand here
-    if (c == 0 && tid == 0) tokens[row] = -1;
-    cluster.sync();
-    return;
-  }
+  // more than 1024 kept, but not the whole row: the head cannot stand in (the sum of the kept masses is not at
+  // hand there); the search over the whole row below does it
+  const bool try_head = exact || kk == V;
 
-  // 3. T = the want-th largest key, byte by byte from the top
-  unsigned long long prefix = 0ULL;
-  int remaining = want;
-  for (int b = 7; b >= 0; b--) {
-    if (b == 3) continue;                             // indices stay below 2^24: this byte is zero in every key
-    const int shift = 8 * b;
-    for (int j = tid; j < 256; j += FAST_THREADS) hist[j] = 0;
-    __syncthreads();
-    for (int i = tid; i < n_loc; i += FAST_THREADS) {
-      const unsigned long long k = cima_pack_key(sl[i], lo + i);
-      if (b == 7 || (k >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&hist[(int)((k >> shift) & 255ULL)], 1);
-    }
-    __syncthreads();
-    cluster.sync();
-    if (tid < 256) {
-      int sum = 0;
-      for (int r = 0; r < C; r++) sum += cluster.map_shared_rank(hist, r)[tid];
-      merged[tid] = sum;
-    }
-    __syncthreads();
-    if (tid == 0) {
-      int cum = 0, bin = 255;
-      for (; bin > 0; bin--) {
-        if (cum + merged[bin] >= remaining) break;
-        cum += merged[bin];
-      }
-      s_sel = bin; s_above = cum; s_cnt = merged[bin];
-    }
-    __syncthreads();
-    prefix |= (unsigned long long)s_sel << shift;
-    remaining -= s_above;
-    const bool settled = s_cnt == remaining;          // the whole bin is kept: every lower bit of T is zero
-    cluster.sync();                                   // everyone has read this block's histogram
-    if (settled) break;
-  }
-  const unsigned long long T = prefix;
-
-  // 4. the kept keys of this slice; the mass of the whole slice when the kept set is not gathered whole
-  if (tid == 0) ncand = 0;
-  __syncthreads();
-  float mass = 0.f;
-  for (int i = tid; i < n_loc; i += FAST_THREADS) {
-    const float v = sl[i];
-    const unsigned long long k = cima_pack_key(v, lo + i);
-    if (k >= T) {
-      const int at = atomicAdd(&ncand, 1);
-      if (at < FAST_MAXK) cand[at] = k;
-    }
-    if (!exact) mass += expf((v - maxl) * inv_t);
-  }
-  if (!exact) {
-    mass = cima_block_sum(mass, redf);
-    if (tid == 0) s_mass = mass;
-  }
-  __syncthreads();
-  cluster.sync();
-  if (c == 0) {
-    int at = 0;
-    float total_all = 0.f;
-    for (int r = 0; r < C; r++) {                     // ranks in order: a fixed sum, a fixed layout
-      const int n_r = min(*cluster.map_shared_rank(&ncand, r), FAST_MAXK);
-      const unsigned long long* src = cluster.map_shared_rank(cand, r);
-      for (int j = tid; j < n_r && at + j < FAST_MAXK; j += FAST_THREADS) sorted[at + j] = src[j];
-      at = min(at + n_r, FAST_MAXK);
-      if (!exact) total_all += *cluster.map_shared_rank(&s_mass, r);
-    }
-    if (tid == 0) { s_total_n = at; s_total_all = total_all; }
-  }
-  cluster.sync();                                     // the others may go: block 0 has what it needs
-  if (c != 0) return;
-  __syncthreads();
-  const int n = s_total_n;
-  int P = 1;
-  while (P < n) P <<= 1;
-  for (int i = n + tid; i < P; i += FAST_THREADS) sorted[i] = 0ULL;
-  __syncthreads();
-  // 5. bitonic sort, largest key first: the reference's order (value descending, index descending)
-  for (int k2 = 2; k2 <= P; k2 <<= 1)
-    for (int j = k2 >> 1; j > 0; j >>= 1) {
-      for (int i = tid; i < P; i += FAST_THREADS) {
-        const int o = i ^ j;
-        if (o > i) {
-          const unsigned long long a = sorted[i], bq = sorted[o];
-          const bool desc = (i & k2) == 0;
-          if (desc ? a < bq : a > bq) { sorted[i] = bq; sorted[o] = a; }
-        }
+  if (try_head) {
+    // 3. T = the want-th largest key, byte by byte from the top
+    unsigned long long prefix = 0ULL;
+    int remaining = want;
+    for (int b = 7; b >= 0; b--) {
+      if (b == 3) continue;                             // indices stay below 2^24: this byte is zero in every key
+      const int shift = 8 * b;
+      for (int j = tid; j < 256; j += FAST_THREADS) hist[j] = 0;
+      __syncthreads();
+      for (int i = tid; i < n_loc; i += FAST_THREADS) {
+        const unsigned long long k = cima_pack_key(sl[i], lo + i);
+        if (b == 7 || (k >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&hist[(int)((k >> shift) & 255ULL)], 1);
       }
       __syncthreads();
+      cluster.sync();
+      if (tid < 256) {
+        int sum = 0;
+        for (int r = 0; r < C; r++) sum += cluster.map_shared_rank(hist, r)[tid];
+        merged[tid] = sum;
+      }
+      __syncthreads();
+      if (tid == 0) {
+        int cum = 0, bin = 255;
+        for (; bin > 0; bin--) {
+          if (cum + merged[bin] >= remaining) break;
+          cum += merged[bin];
+        }
+        s_sel = bin; s_above = cum; s_cnt = merged[bin];
+      }
+      __syncthreads();
+      prefix |= (unsigned long long)s_sel << shift;
+      remaining -= s_above;
+      const bool settled = s_cnt == remaining;          // the whole bin is kept: every lower bit of T is zero
+      cluster.sync();                                   // everyone has read this block's histogram
+      if (settled) break;
     }
-  float* pr = sl;                                     // probabilities of the kept, in order (the slice is spent)
-  const float v0 = cima_key_value(sorted[0]);
-  for (int i = tid; i < n; i += FAST_THREADS) pr[i] = expf((cima_key_value(sorted[i]) - v0) * inv_t);
-  __syncthreads();
-  if (tid != 0) return;
-  // 6. the host loop of the reference, in its order and in float32
-  float total = 0.f;
-  if (exact) { for (int i = 0; i < n; i++) total += pr[i]; } else total = s_total_all;
-  int cut = exact ? n : -1;
-  float cum = 0.f;
-  for (int i = 0; i < n; i++) {
-    const float p = pr[i] / total;
-    pr[i] = p;
-    cum += p;
-    if (cum >= top_p) { cut = i + 1; break; }
+    const unsigned long long T = prefix;
+
+    // 4. the kept keys of this slice; the mass of the whole slice when the kept set is not gathered whole
+    if (tid == 0) ncand = 0;
+    __syncthreads();
+    float mass = 0.f;
+    for (int i = tid; i < n_loc; i += FAST_THREADS) {
+      const float v = sl[i];
+      const unsigned long long k = cima_pack_key(v, lo + i);
+      if (k >= T) {
+        const int at = atomicAdd(&ncand, 1);
+        if (at < FAST_MAXK) cand[at] = k;
+      }
+      if (!exact) mass += expf((v - maxl) * inv_t);
+    }
+    if (!exact) {
+      mass = cima_block_sum(mass, redf);
+      if (tid == 0) s_mass = mass;
+    }
+    __syncthreads();
+    cluster.sync();
+    if (c == 0) {
+      int at = 0;
+      float total_all = 0.f;
+      for (int r = 0; r < C; r++) {                     // ranks in order: a fixed sum, a fixed layout
+        const int n_r = min(*cluster.map_shared_rank(&ncand, r), FAST_MAXK);
+        const unsigned long long* src = cluster.map_shared_rank(cand, r);
+        for (int j = tid; j < n_r && at + j < FAST_MAXK; j += FAST_THREADS) sorted[at + j] = src[j];
+        at = min(at + n_r, FAST_MAXK);
+        if (!exact) total_all += *cluster.map_shared_rank(&s_mass, r);
+      }
+      if (tid == 0) { s_total_n = at; s_total_all = total_all; }
+    }
+    cluster.sync();                                     // block 0 has the kept keys (and the row's mass)
+    if (c == 0) {
+      __syncthreads();
+      const int n = s_total_n;
+      int P = 1;
+      while (P < n) P <<= 1;
+      for (int i = n + tid; i < P; i += FAST_THREADS) sorted[i] = 0ULL;
+      __syncthreads();
+      // 5. bitonic sort, largest key first: the reference's order (value descending, index descending)
+      for (int k2 = 2; k2 <= P; k2 <<= 1)
+        for (int j = k2 >> 1; j > 0; j >>= 1) {
+          for (int i = tid; i < P; i += FAST_THREADS) {
+            const int o = i ^ j;
+            if (o > i) {
+              const unsigned long long a = sorted[i], bq = sorted[o];
+              const bool desc = (i & k2) == 0;
+              if (desc ? a < bq : a > bq) { sorted[i] = bq; sorted[o] = a; }
+            }
+          }
+          __syncthreads();
+        }
+      float* pr = pr_s;
+      const float v0 = cima_key_value(sorted[0]);
+      for (int i = tid; i < n; i += FAST_THREADS) pr[i] = expf((cima_key_value(sorted[i]) - v0) * inv_t);
+      __syncthreads();
+      if (tid == 0) {
+        // 6. the host loop of the reference, in its order and in float32
+        float total = 0.f;
+        if (exact) { for (int i = 0; i < n; i++) total += pr[i]; } else total = s_total_all;
+        int cut = exact ? n : -1;
+        float cum = 0.f;
+        for (int i = 0; i < n; i++) {
+          const float p = pr[i] / total;
+          pr[i] = p;
+          cum += p;
+          if (cum >= top_p) { cut = i + 1; break; }
+        }
+        unsigned long long st = rng[slot];
+        st ^= st >> 12; st ^= st << 25; st ^= st >> 27;
+        const float u = (float)((st * 0x2545F4914F6CDD1DULL) >> 40) / 16777216.0f;
+        int token = -1;
+        if (cut > 0) {
+          float renorm = 0.f;
+          for (int i = 0; i < cut; i++) renorm += pr[i];
+          float r = u * renorm;
+          token = (int)(unsigned int)sorted[cut - 1];
+          for (int i = 0; i < cut; i++) {
+            r -= pr[i];
+            if (r <= 0.f) { token = (int)(unsigned int)sorted[i]; break; }
+          }
+        } else if (top_p >= 1.0f) {
+          // nothing is cut and the kept set is the whole row, of which only the head is here: settled if the
+          // draw falls into the head
+          float r = u;
+          for (int i = 0; i < n; i++) {
+            r -= pr[i];
+            if (r <= 0.f) { token = (int)(unsigned int)sorted[i]; break; }
+          }
+        }
+        if (token >= 0) {
+          tokens[row] = token;
+          rng[slot] = st;
+          myring[pushed % SAMPLE_RING] = token;
+          ring_count[slot] = pushed + 1;
+        }
+        s_resolved = token >= 0;
+      }
+    }
+
   }
-  unsigned long long st = rng[slot];
+  // ---- what the head could not settle: the search over the whole row, by all blocks of the cluster.  The order
+  // (value descending, index descending) is the order of the 64-bit keys; the k-th largest key, the top-p floor
+  // and the drawn token are each the largest key T for which "the tokens with key >= T are at least k" (or
+  // "weigh at least so much") holds, found bit by bit from the top; each bit is one pass over the slices in
+  // shared memory and one exchange through the cluster.  Sums run in a fixed order (thread, block, rank).
+  if (try_head) {
+    cluster.sync();                                   // block 0 has said whether the head settled the row
+    const int resolved = *cluster.map_shared_rank(&s_resolved, 0);
+    cluster.sync();                                   // ... and everyone has heard it
+    if (resolved) return;
+  }
+  int pass = 0;
+  auto cl_count = [&](unsigned long long T) -> int {
+    int cnt = 0;
+    for (int i = tid; i < n_loc; i += FAST_THREADS) cnt += cima_pack_key(sl[i], lo + i) >= T ? 1 : 0;
+    const float tot = cima_block_sum((float)cnt, redf);          // below 2^24: exact
+    if (tid == 0) s_part[pass & 1] = tot;
+    cluster.sync();
+    float sum = 0.f;
+    for (int r = 0; r < C; r++) sum += cluster.map_shared_rank(s_part, r)[pass & 1];
+    pass++;
+    return (int)(sum + 0.5f);
+  };
+  auto cl_mass = [&](unsigned long long T) -> float {
+    float m = 0.f;
+    for (int i = tid; i < n_loc; i += FAST_THREADS) {
+      const float v = sl[i];
+      if (cima_pack_key(v, lo + i) >= T) m += expf((v - maxl) * inv_t);
+    }
+    m = cima_block_sum(m, redf);
+    if (tid == 0) s_part[pass & 1] = m;
+    cluster.sync();
+    float sum = 0.f;
+    for (int r = 0; r < C; r++) sum += cluster.map_shared_rank(s_part, r)[pass & 1];
+    pass++;
+    return sum;
+  };
+  int idx_bits = 1;
+  while ((1 << idx_bits) < V) idx_bits++;
+  unsigned long long floor_key = 0ULL;
+  if (kk < V) {
+    for (int b = 63; b >= 0; b--) {
+      if (b < 32 && b >= idx_bits) continue;               // index bits that no token has
+      const unsigned long long cand = floor_key | (1ULL << b);
+      const int cnt = cl_count(cand);
+      if (cnt >= kk) floor_key = cand;
+      if (cnt == kk) break;                                 // the kept set is settled
+    }
+  }
+  const float total = cl_mass(floor_key);
+  if (top_p < 1.0f) {
+    unsigned long long T = 0ULL;
+    for (int b = 63; b >= 0; b--) {
+      if (b < 32 && b >= idx_bits) continue;
+      const unsigned long long cand = T | (1ULL << b);
+      if (cand <= floor_key) { T = cand; continue; }
+      if (cand > best) continue;
+      if (cl_mass(cand) / total >= top_p) T = cand;
+    }
+    floor_key = T > floor_key ? T : floor_key;
+  }
+  const float kept = cl_mass(floor_key) / total;
+  unsigned long long st = rng[slot];                        // every block draws the same number
   st ^= st >> 12; st ^= st << 25; st ^= st >> 27;
-  const float u = (float)((st * 0x2545F4914F6CDD1DULL) >> 40) / 16777216.0f;
-  int token = -1;
-  if (cut > 0) {
-    float renorm = 0.f;
-    for (int i = 0; i < cut; i++) renorm += pr[i];
-    float r = u * renorm;
-    token = (int)(unsigned int)sorted[cut - 1];
-    for (int i = 0; i < cut; i++) {
-      r -= pr[i];
-      if (r <= 0.f) { token = (int)(unsigned int)sorted[i]; break; }
-    }
-  } else if (top_p >= 1.0f) {
-    // nothing is cut and the kept set is the whole row, of which only the head is here: settled if the
-    // draw falls into the head
-    float r = u;
-    for (int i = 0; i < n; i++) {
-      r -= pr[i];
-      if (r <= 0.f) { token = (int)(unsigned int)sorted[i]; break; }
-    }
+  const float target = (float)((st * 0x2545F4914F6CDD1DULL) >> 40) / 16777216.0f * kept;
+  unsigned long long T = 0ULL;
+  for (int b = 63; b >= 0; b--) {
+    if (b < 32 && b >= idx_bits) continue;
+    const unsigned long long cand = T | (1ULL << b);
+    if (cand <= floor_key) { T = cand; continue; }
+    if (cand > best) continue;
+    if (cl_mass(cand) / total >= target) T = cand;
   }
-  tokens[row] = token;
-  if (token >= 0) {
+  if (T < floor_key) T = floor_key;
+  // the token is the one with the smallest key >= T (T itself whenever T is a token's key)
+  unsigned long long m = 0ULL;
+  for (int i = tid; i < n_loc; i += FAST_THREADS) {
+    const unsigned long long k = cima_pack_key(sl[i], lo + i);
+    if (k >= T) { const unsigned long long cm = ~k; m = cm > m ? cm : m; }
+  }
+  m = cima_block_max_u64(m, redk);
+  if (tid == 0) s_best = m;
+  cluster.sync();                                     // (every block has read rng[slot] by now)
+  if (c == 0 && tid == 0) {
+    for (int r = 1; r < C; r++) {
+      const unsigned long long k = *cluster.map_shared_rank(&s_best, r);
+      m = k > m ? k : m;
+    }
+    const int token = (int)(unsigned int)(~m);
+    tokens[row] = token;
     rng[slot] = st;
     myring[pushed % SAMPLE_RING] = token;
     ring_count[slot] = pushed + 1;
   }
+  cluster.sync();                                     // a block's shared memory must outlive block 0's reads
 }
 
 // logits [n, V] float32 (row stride ld); row_slot [n]; params [n, 4] = temperature, top_k, top_p,
@@ -490,11 +591,10 @@ extern "C" int cima_sample(const float* logits, int ld, int n, int V, const int*
   if (V <= 0 || ld < V) return cima_fail(CIMA_E_SIZE, "sample: vocabulary %d must be positive and fit the row stride %d", V, ld);
   if (V >= (1 << 24)) return cima_fail(CIMA_E_SIZE, "sample: vocabulary %d exceeds 2^24 (counts are summed in float32)", V);
   if (n > 65535) return cima_fail(CIMA_E_SIZE, "sample: %d rows exceed one launch", n);
-  // the fast kernel keeps an eighth of a row (at least 1024 floats) in shared memory; rows too long for that
-  // go straight to the general kernel
+  // the fast kernel keeps an eighth of a row in shared memory; rows too long for that go to the general kernel,
+  // one block per row
   const int per = (((V + FAST_BLOCKS - 1) / FAST_BLOCKS) + 3) & ~3;
-  const size_t smem = (size_t)(per > FAST_MAXK ? per : FAST_MAXK) * sizeof(float);
-  int only_unresolved = 0;
+  const size_t smem = (size_t)(per > 4 ? per : 4) * sizeof(float);
   if (smem <= 160 * 1024) {
     static bool raised = false;
     if (!raised) {
@@ -503,10 +603,22 @@ extern "C" int cima_sample(const float* logits, int ld, int n, int V, const int*
       raised = true;
     }
     { int rc_ = cima_launch(k_sample_fast, dim3(FAST_BLOCKS, n), dim3(FAST_THREADS), smem, stream, FAST_BLOCKS, logits, ld, V, row_slot, params, rng, ring, ring_count, tokens); if (rc_) return rc_; }
-    int rc = cima_launch_result();
-    if (rc) return rc;
-    only_unresolved = 1;
+    return cima_launch_result();
   }
+  const int only_unresolved = 0;
   { int rc_ = cima_launch(k_sample, dim3(n), dim3(SAMPLE_THREADS), (size_t)(0), stream, 1, logits, ld, V, row_slot, params, rng, ring, ring_count, work, tokens, only_unresolved); if (rc_) return rc_; }
+  return cima_launch_result();
+}
+
+// The general kernel alone (one block per row, any vocabulary below 2^24), whatever the size: what cima_sample
+// takes for rows too long for the fast kernel's shared memory, callable by itself so that it can be tested at
+// small sizes.
+extern "C" int cima_sample_general(const float* logits, int ld, int n, int V, const int* row_slot, const float* params,
+                                   unsigned long long* rng, int* ring, int* ring_count, float* work, int* tokens,
+                                   cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (V <= 0 || ld < V) return cima_fail(CIMA_E_SIZE, "sample: vocabulary %d must be positive and fit the row stride %d", V, ld);
+  if (V >= (1 << 24)) return cima_fail(CIMA_E_SIZE, "sample: vocabulary %d exceeds 2^24 (counts are summed in float32)", V);
+  { int rc_ = cima_launch(k_sample, dim3(n), dim3(SAMPLE_THREADS), (size_t)(0), stream, 1, logits, ld, V, row_slot, params, rng, ring, ring_count, work, tokens, 0); if (rc_) return rc_; }
   return cima_launch_result();
 }

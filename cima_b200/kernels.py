@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 14
+ABI_VERSION = 15
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -61,6 +61,7 @@ _SIGNATURES = {
     "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
     "cima_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    "cima_sample_general": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
 }
 
 
@@ -509,9 +510,11 @@ class Kernels:
 
     def sample(self, logits: torch.Tensor, row_slot: torch.Tensor, params: torch.Tensor, rng: torch.Tensor,
                ring: torch.Tensor, count: torch.Tensor, work: torch.Tensor, tokens: torch.Tensor,
-               all_greedy: bool = False) -> None:
+               all_greedy: bool = False, general: bool = False) -> None:
         """The whole sampling chain per row; per-slot state (rng, ring, count) is read and advanced.
-        ``all_greedy`` (no row penalises or draws) takes the argmax kernel and leaves the state alone."""
+        ``all_greedy`` (no row penalises or draws) takes the argmax kernel and leaves the state alone.
+        ``general``: the one-block-per-row kernel whatever the size (it otherwise serves only vocabularies too long
+        for the fast kernel's shared memory)."""
         self._need(logits, "logits", torch.float32, 2); self._need(tokens, "tokens", torch.int32, 1)
         n, V = logits.shape
         if tokens.numel() < n:
@@ -524,6 +527,6 @@ class Kernels:
         self._need(work, "work", torch.float32, 2)
         if params.shape != (n, 4) or ring.shape[1] != 64 or work.shape[0] < n or work.shape[1] != V:
             raise KernelError("sample: params must be [rows, 4], the ring [slots, 64], the scratch [>= rows, vocab]")
-        self._check(self.lib.cima_sample(logits.data_ptr(), V, n, V, row_slot.data_ptr(), params.data_ptr(),
-                                         rng.data_ptr(), ring.data_ptr(), count.data_ptr(), work.data_ptr(),
-                                         tokens.data_ptr(), self._stream()), "sample")
+        fn = self.lib.cima_sample_general if general else self.lib.cima_sample
+        self._check(fn(logits.data_ptr(), V, n, V, row_slot.data_ptr(), params.data_ptr(), rng.data_ptr(),
+                       ring.data_ptr(), count.data_ptr(), work.data_ptr(), tokens.data_ptr(), self._stream()), "sample")

@@ -176,7 +176,7 @@ class ReferenceKernels:
             best = torch.nonzero(row == row.max()).max()
             tokens[i] = int(best)
 
-    def sample(self, logits, row_slot, params, rng, ring, count, work, tokens, all_greedy=False):
+    def sample(self, logits, row_slot, params, rng, ring, count, work, tokens, all_greedy=False, general=False):
         if all_greedy:
             return self.argmax(logits, tokens)
         for i in range(logits.shape[0]):
