@@ -82,3 +82,32 @@ def test_long_context_decode_against_whole_prompt(folder):
     finally:
         m32.cache.close([slot])
     assert (whole - ref).abs().max().item() <= tol and (tail - ref).abs().max().item() <= tol
+
+
+WIDER = {"14b": dict(hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, intermediate_size=13824),
+         "32b": dict(hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, intermediate_size=27648)}
+
+
+@pytest.mark.parametrize("name", ["14b", "32b"])
+def test_wider_layer_shapes(name, tmp_path):
+    """One layer of the Qwen2.5-14B and -32B shapes (hidden 5120: 320 partial sums per row for the folded norm,
+    more than the 256 a lane's registers take; 40/8 heads; intermediate 13,824 or 27,648): a prompt whole, its
+    last 16 tokens one by one, and a 300-token prompt (the tcgen05 attention) in bfloat16 against float32."""
+    shape = dict(SHAPE, num_hidden_layers=1, vocab_size=5000, **WIDER[name])
+    folder = str(tmp_path / name)
+    cima_b200.write_random_model(folder, shape, seed=13)
+    cfg, W = plain_load(folder)
+    toks = random_tokens(shape["vocab_size"], 72, seed=2)
+    want = plain_forward(W, cfg, toks).float()
+    long_toks = random_tokens(shape["vocab_size"], 300, seed=4)
+    m32 = load_model(folder, dtype="float32", max_tokens=1024, verbose=False)
+    assert (run_whole(m32, toks) - want).abs().max().item() <= 1e-4
+    long32 = run_whole(m32, long_toks)
+    del m32
+    torch.cuda.empty_cache()
+    m16 = load_model(folder, dtype="bfloat16", max_tokens=1024, verbose=False)
+    tol = REL_BF16 * want.std().item()
+    assert (run_whole(m16, toks) - want).abs().max().item() <= tol
+    assert (run_tail_one_by_one(m16, toks, 16) - want).abs().max().item() <= tol
+    assert (run_whole(m16, long_toks) - long32).abs().max().item() <= REL_BF16 * long32.std().item()
+    m16.check_device()
