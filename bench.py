@@ -104,6 +104,8 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration's 28 (named in config)")
+    ap.add_argument("--shape", default="qwen2.5-7b", help="another shape of cima_b200.config.shapes.SHAPES (the metric is "
+                    "defined on the default, Qwen2.5-7B)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
     a = ap.parse_args(argv)
@@ -126,6 +128,9 @@ def main(argv=None) -> int:
 
     pk = peaks()
     raw = dict(QWEN25_7B)
+    if a.shape != "qwen2.5-7b":
+        from cima_b200.config.shapes import SHAPES
+        raw = dict(SHAPES[a.shape])
     layers_full = raw["num_hidden_layers"]
     if a.layers:
         raw["num_hidden_layers"] = a.layers
@@ -255,7 +260,7 @@ def main(argv=None) -> int:
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
         "ms_per_step": secs / a.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0,0.02) seed 0, uniform random token ids",
-        "config": {"model": "Qwen2.5-7B shape", "global_batch": a.batch, "seq_len": SLOT_TOKENS, "parallelism": "single GPU",
+        "config": {"model": "Qwen2.5-7B shape" if a.shape == "qwen2.5-7b" else a.shape + " shape", "global_batch": a.batch, "seq_len": SLOT_TOKENS, "parallelism": "single GPU",
                    "prompt_tokens": a.prompt, "layers": cfg.num_hidden_layers, "layers_of_config": layers_full,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
