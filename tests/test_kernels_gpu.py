@@ -94,13 +94,21 @@ def test_linear_plain(K, M, N, K_, combo):
         assert err(acc, 1 + a.double() @ w.double().t()) <= 2e-5 * max(1.0, want.abs().max().item())
 
 
-def test_linear_plain_rows_are_independent(K):
-    a, w = g(70, 200, seed=1), g(300, 200, seed=2)
-    full = torch.empty(70, 300, device="cuda")
-    K.linear_plain(a.cuda(), w.cuda(), None, full)
-    one = torch.empty(1, 300, device="cuda")
-    K.linear_plain(a[33:34].contiguous().cuda(), w.cuda(), None, one)
-    assert torch.equal(full[33:34], one)
+@pytest.mark.parametrize("rows", [1, 5, 8])
+@pytest.mark.parametrize("N,K_", [(300, 200), (65, 7), (1000, 3584)])
+def test_linear_plain_rows_are_independent(K, rows, N, K_):
+    """The same bits for a row whether it comes among 70 (the tiled kernel) or among at most 8 (the kernel of
+    the decode steps, one thread per output feature): both add the products of an output in ascending k."""
+    a, w, b = g(70, K_, seed=1), g(N, K_, seed=2), g(N, seed=3)
+    full = torch.empty(70, N, device="cuda")
+    K.linear_plain(a.cuda(), w.cuda(), b.cuda(), full)
+    few = torch.empty(rows, N, device="cuda")
+    K.linear_plain(a[33:33 + rows].contiguous().cuda(), w.cuda(), b.cuda(), few)
+    assert torch.equal(full[33:33 + rows], few)
+    acc_full, acc_few = torch.ones(70, N, device="cuda"), torch.ones(rows, N, device="cuda")
+    K.linear_plain(a.cuda(), w.cuda(), None, acc_full, accumulate=True)
+    K.linear_plain(a[33:33 + rows].contiguous().cuda(), w.cuda(), None, acc_few, accumulate=True)
+    assert torch.equal(acc_full[33:33 + rows], acc_few)
 
 
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 31, 64])
