@@ -160,9 +160,12 @@ static int launch_few(const void* A, const void* W, const float* bias, void* out
 template <typename TA, typename TW, typename TO>
 static int launch_plain(const void* A, const void* W, const float* bias, void* out, int mode, int M, int N, int K,
                         int lda, int ldo, cudaStream_t stream) {
-  if (M <= FEW_ROWS) {
-    if (mode == LIN_STORE) return launch_few<TA, TW, TO, LIN_STORE>(A, W, bias, out, M, N, K, lda, ldo, stream);
-    return launch_few<TA, TW, TO, LIN_ACCUM>(A, W, bias, out, M, N, K, lda, ldo, stream);
+  // (only the all-float32 combination, the 32-bit path's: each instantiation of that kernel costs seconds to compile)
+  if constexpr (sizeof(TA) == 4 && sizeof(TW) == 4 && sizeof(TO) == 4) {
+    if (M <= FEW_ROWS) {
+      if (mode == LIN_STORE) return launch_few<TA, TW, TO, LIN_STORE>(A, W, bias, out, M, N, K, lda, ldo, stream);
+      return launch_few<TA, TW, TO, LIN_ACCUM>(A, W, bias, out, M, N, K, lda, ldo, stream);
+    }
   }
   dim3 grid((N + 63) / 64, (M + 63) / 64);
   if (mode == LIN_STORE)
