@@ -1,8 +1,8 @@
-// Matrix product for few rows (decode): out[m,n] = sum_k X[m,k] * W[n,k], M <= 64, bfloat16 operands,
+// Matrix product for few rows (decode): out[m,n] = sum_k X[m,k] * W[n,k], M <= 16, bfloat16 operands,
 // float32 accumulation.  The step is bound by reading W once from HBM, so the kernel is built
 // around the weight stream: every thread keeps several 16-byte loads of W in flight, the weights
 // are the 16-row operand of the tensor-core instruction and the few activation rows are its 8-wide
-// operand ("swap A/B"), so M = 1..8 costs one instruction per 16x16 weights and M = 64 costs eight.
+// operand ("swap A/B"), so M = 1..8 costs one instruction per 16x16 weights and M = 9..16 two.
 //
 // Work split.  One block owns 16 output features (or 16 gate and the 16 matching up features for
 // the gated epilogue).  Its 8 warps split K in interleaved chunks; their partial sums are added in
@@ -353,18 +353,18 @@ static int launch_skinny(const void* X, const void* W, const float* bias, void* 
 template <int NT, bool NORM>
 static int dispatch_mode(int mode, const void* X, const void* W, const float* bias, void* out, int M, int N, int K,
                          int ldx, int ldo, const SkinnyNorm& nm, cudaStream_t stream) {
-  constexpr int U = NT <= 2 ? 4 : 2;
+  constexpr int U = 4;
   switch (mode) {
     case SK_STORE: return launch_skinny<NT, 1, U, SK_STORE, NORM>(X, W, bias, out, M, N, K, ldx, ldo, 0, nm, stream);
     case SK_ACCUM: return launch_skinny<NT, 1, U, SK_ACCUM, NORM>(X, W, bias, out, M, N, K, ldx, ldo, 0, nm, stream);
     case SK_STORE_F32: return launch_skinny<NT, 1, U, SK_STORE_F32, NORM>(X, W, bias, out, M, N, K, ldx, ldo, 0, nm, stream);
-    case SK_SWIGLU: return launch_skinny<NT, 2, (NT <= 2 ? 2 : 1), SK_SWIGLU, NORM>(X, W, bias, out, M, N, K, ldx, ldo, N, nm, stream);
+    case SK_SWIGLU: return launch_skinny<NT, 2, 2, SK_SWIGLU, NORM>(X, W, bias, out, M, N, K, ldx, ldo, N, nm, stream);
     default: return cima_fail(CIMA_E_ARG, "linear_skinny: mode %d is not one of 0..3", mode);
   }
 }
 
 static int skinny_checks(const void* X, const void* W, const float* bias, int mode, int M, int N, int K, int ldx) {
-  if (M > 64) return cima_fail(CIMA_E_SIZE, "linear_skinny: %d rows; this kernel takes at most 64", M);
+  if (M > 16) return cima_fail(CIMA_E_SIZE, "linear_skinny: %d rows; this kernel takes at most 16 (more rows re-read the activations too often: the library product streams the weights faster there)", M);
   if (N <= 0 || K <= 0) return cima_fail(CIMA_E_SIZE, "linear_skinny: N %d and K %d must be positive", N, K);
   if (K % 8 || ldx % 8) return cima_fail(CIMA_E_SIZE, "linear_skinny: K %d and the row stride %d must be multiples of 8 (16-byte loads)", K, ldx);
   if (((uintptr_t)X | (uintptr_t)W) & 15) return cima_fail(CIMA_E_ARG, "linear_skinny: X and W must be 16-byte aligned");
@@ -374,7 +374,7 @@ static int skinny_checks(const void* X, const void* W, const float* bias, int mo
 
 // X [M, K] bf16 (row stride ldx), W [N, K] bf16 (for mode 2: [2N, K], gate rows then up rows),
 // bias float32 [N] or null, out [M, N] (row stride ldo) in the dtype of the mode.
-// Accepts 1 <= M <= 64, any N, K a multiple of 8 (16-byte rows), 16-byte aligned X, W and ldx % 8 == 0.
+// Accepts 1 <= M <= 16, any N, K a multiple of 8 (16-byte rows), 16-byte aligned X, W and ldx % 8 == 0.
 // ssq_out (mode 1 only, may be null): [M, ceil(N / 16)] partial sums of squares of the updated rows.
 // w_next / xw_out (mode 1 with ssq_out, may be null): weight [N] of the norm that follows, and where to put
 // bf16(updated row * that weight), [M, N] with row stride ldo.
@@ -388,9 +388,7 @@ extern "C" int cima_linear_skinny(const void* X, const void* W, const float* bia
   SkinnyNorm nm{nullptr, 0, 0.f, mode == SK_ACCUM ? ssq_out : nullptr,
                 mode == SK_ACCUM ? w_next : nullptr, mode == SK_ACCUM ? (__nv_bfloat16*)xw_out : nullptr};
   if (M <= 8) return dispatch_mode<1, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
-  if (M <= 16) return dispatch_mode<2, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
-  if (M <= 32) return dispatch_mode<4, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
-  return dispatch_mode<8, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
+  return dispatch_mode<2, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
 }
 
 // The same with RMSNorm folded in: xw [M, K] bf16 = bf16(x * w) as cima_embed or an accumulating product left

@@ -1,7 +1,7 @@
 """y = a W^T (+ bias): the one place that chooses how a matrix product runs.
 
 * 32-bit path, or a weight that is stored in 32-bit: the plain FFMA kernel (``linear_plain``).
-* bfloat16, at most ``SKINNY_ROWS`` rows, K a multiple of 8: the hand-written skinny kernel with its
+* bfloat16, at most ``SKINNY_ROWS`` rows (the kernel takes up to 16), K a multiple of 8: the hand-written skinny kernel with its
   fused epilogues (bias, residual accumulate, gated activation, float32 store).
 * bfloat16, more rows: the library matrix product (cuBLAS through ``torch.mm``), where the reference
   also calls its library (``cublasGemmEx`` for rows > 1, src/models/transformer.rs:1068-1084,

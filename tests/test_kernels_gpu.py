@@ -111,7 +111,7 @@ def test_linear_plain_rows_are_independent(K, rows, N, K_):
     assert torch.equal(acc_full[33:33 + rows], acc_few)
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16, 31, 64])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N,K_", [(200, 328), (1000, 192), (4608, 3584), (17, 8)])
 def test_linear_skinny_modes(K, M, N, K_):
     from cima_b200.kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
@@ -139,10 +139,10 @@ def test_linear_skinny_modes(K, M, N, K_):
 
 def test_linear_skinny_row_does_not_depend_on_batch(K):
     from cima_b200.kernels import SK_STORE_F32
-    a, w = g(64, 448, dtype=torch.bfloat16, seed=1), g(1000, 448, dtype=torch.bfloat16, seed=2)
-    full = torch.empty(64, 1000, device="cuda")
+    a, w = g(16, 448, dtype=torch.bfloat16, seed=1), g(1000, 448, dtype=torch.bfloat16, seed=2)
+    full = torch.empty(16, 1000, device="cuda")
     K.linear_skinny(a.cuda(), w.cuda(), None, full, SK_STORE_F32)
-    for m in (1, 5, 16, 40):
+    for m in (1, 5, 8, 9, 13):
         part = torch.empty(m, 1000, device="cuda")
         K.linear_skinny(a[:m].contiguous().cuda(), w.cuda(), None, part, SK_STORE_F32)
         assert torch.equal(part, full[:m])
@@ -150,9 +150,9 @@ def test_linear_skinny_row_does_not_depend_on_batch(K):
 
 def test_linear_skinny_refuses(K):
     from cima_b200.kernels import KernelError, SK_STORE
-    a, w = g(65, 64, dtype=torch.bfloat16).cuda(), g(32, 64, dtype=torch.bfloat16).cuda()
-    with pytest.raises(KernelError, match="at most 64"):
-        K.linear_skinny(a, w, None, torch.empty(65, 32, dtype=torch.bfloat16, device="cuda"), SK_STORE)
+    a, w = g(17, 64, dtype=torch.bfloat16).cuda(), g(32, 64, dtype=torch.bfloat16).cuda()
+    with pytest.raises(KernelError, match="at most 16"):
+        K.linear_skinny(a, w, None, torch.empty(17, 32, dtype=torch.bfloat16, device="cuda"), SK_STORE)
     a, w = g(2, 12, dtype=torch.bfloat16).cuda(), g(32, 12, dtype=torch.bfloat16).cuda()
     with pytest.raises(KernelError, match="multiples of 8"):
         K.linear_skinny(a, w, None, torch.empty(2, 32, dtype=torch.bfloat16, device="cuda"), SK_STORE)
