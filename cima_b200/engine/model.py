@@ -96,6 +96,20 @@ class Model:
                              shares=shares, extra_state=extra_state)
         return self.cache
 
+    def forecast(self, max_tokens: int, max_seqs: Optional[int] = None, page_size: int = 64,
+                 extra_state: Sequence[StateRequest] = ()):
+        """Bytes that the weights, a cache of ``max_tokens`` positions and a step's scratch will take."""
+        from .fit import forecast
+        sched = self.spec.schedule
+        shares = [site for site, layer in enumerate(sched) if self.spec.layers[layer].mixer.cache_from is not None]
+        widest = 0
+        for b in self.spec.layers:
+            widest = max(widest, 2 * getattr(b.feed_forward, "intermediate", 0),
+                         (b.mixer.n_heads + 2 * b.mixer.n_kv_heads) * b.mixer.head_dim)
+        return forecast(self.plan(), [self.blocks[layer].cache_requests(site) for site, layer in enumerate(sched)],
+                        self.rt.dtype, max_tokens, self.spec.hidden, self.spec.vocab, widest, page_size, shares,
+                        extra_state, max_seqs or 0)
+
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the tokens the entries bring, from the cache earlier steps left; float32 logits
@@ -178,7 +192,9 @@ def load_model(folder: str, dtype="bfloat16", max_tokens: int = 4096, max_seqs: 
     rt = Runtime(kernels=kernels if kernels is not None else Kernels(verbose=verbose),
                  dtype=parse_dtype(dtype), device=device)
     model = Model(spec, rt)
-    model.load(load_tensors(folder, model.plan(), ignore=model.ignorable()))
     from ..sampling.sampler import sampler_state
+    from .fit import check_fit
+    check_fit(model.forecast(max_tokens, max_seqs, extra_state=sampler_state()), device)     # before anything is allocated
+    model.load(load_tensors(folder, model.plan(), ignore=model.ignorable()))
     model.make_cache(max_tokens, max_seqs, extra_state=sampler_state())
     return model
