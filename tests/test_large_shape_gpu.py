@@ -111,3 +111,29 @@ def test_wider_layer_shapes(name, tmp_path):
     assert (run_tail_one_by_one(m16, toks, 16) - want).abs().max().item() <= tol
     assert (run_whole(m16, long_toks) - long32).abs().max().item() <= REL_BF16 * long32.std().item()
     m16.check_device()
+
+
+def test_ragged_long_prompts_in_one_step(folder):
+    """Five prompts of 1 to 700 tokens in one step (the longest decides that the tcgen05 attention runs: blocks
+    of 128 query rows, sequences that end inside a block, one of a single token), bfloat16 against float32, at
+    every sequence's last position and at a few inside."""
+    from cima_b200.engine import StepEntry
+    lens = [700, 130, 1, 257, 300]
+    seqs = [random_tokens(SHAPE["vocab_size"], n, seed=40 + n) for n in lens]
+    wants = [sorted({0, n // 2, max(0, n - 2), n - 1}) for n in lens]
+
+    def run(dtype):
+        m = load_model(folder, dtype=dtype, max_tokens=2048, verbose=False)
+        slots = m.cache.open(len(seqs))
+        try:
+            out = m.step([StepEntry(s, t, w) for s, t, w in zip(slots, seqs, wants)]).float().cpu()
+            m.check_device()
+        finally:
+            m.cache.close(slots)
+        del m
+        torch.cuda.empty_cache()
+        return out
+
+    got16, got32 = run("bfloat16"), run("float32")
+    assert got16.shape == got32.shape == (sum(len(w) for w in wants), SHAPE["vocab_size"])
+    assert (got16 - got32).abs().max().item() <= REL_BF16 * got32.std().item()
