@@ -11,6 +11,9 @@
 // (the down projection) would leave most of the GPU idle that way, so the blocks of a thread-block
 // cluster (1 to 8, chosen from the matrix's shape alone) split K further; block 0 of the
 // cluster adds the blocks' sums in rank order through distributed shared memory and stores.
+// A warp issues the loads of its first chunk of W before it waits for the kernel in front of it
+// (programmatic dependent launch): weights depend on no kernel, and the stream then starts while that
+// kernel's last blocks are finishing.
 //
 // Operand order.  mma.m16n8k16 wants, per thread, k = {2t, 2t+1, 2t+8, 2t+9} of rows g and g+8.
 // A sum over k does not care in which order k is visited as long as both operands agree, so a
@@ -18,9 +21,9 @@
 // first four to one instruction and the last four to the next: all loads are 16-byte and
 // row-contiguous, no shared-memory staging of W is needed.
 //
-// Epilogues (the reference's GEMV has the same three, src/kernels.cu:502-538):
+// Epilogues (the reference's GEMV has the first three, src/kernels.cu:502-538):
 //   0 store bf16 (+ bias)      1 accumulate into the float32 residual      2 silu(gate) * up -> bf16
-//   3 store float32 (+ bias), used for logits
+//   3 store float32 (+ bias), used for logits      4 q/k/v with rotation and cache append (see SkinnyRope)
 #include "common.cuh"
 #include <cooperative_groups.h>
 namespace cg = cooperative_groups;
