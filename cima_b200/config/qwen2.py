@@ -8,8 +8,11 @@ q/k/v bias following from ``model_type`` starting with "qwen2" (:257).
 Beyond the reference, which does not read them (its window is hard-wired 0,
 src/models/transformer.rs:1184-1199): ``use_sliding_window``, ``sliding_window``
 and ``max_window_layers`` select a windowed attention for the layers from
-``max_window_layers`` on; ``hidden_act`` other than "silu" and a non-null
-``rope_scaling`` are refused rather than ignored.
+``max_window_layers`` on, or for the layers that ``layer_types`` calls
+"sliding_attention" where that list is given; ``rope_parameters`` (the newer
+spelling: ``{"rope_theta": ..., "rope_type": "default"}``) gives the base when
+``rope_theta`` is absent; ``hidden_act`` other than "silu" and a rotary
+scaling of any type but "default" are refused rather than ignored.
 """
 from __future__ import annotations
 
@@ -17,7 +20,7 @@ import json
 import math
 import os
 from dataclasses import dataclass, asdict
-from typing import Any, Dict, Optional
+from typing import Any, Dict, Optional, Tuple
 
 from .specs import (BlockSpec, FeedForwardSpec, MixerSpec, ModelSpec, NormSpec,
                     PositionSpec)
@@ -79,6 +82,7 @@ class Qwen2Config:
     max_window_layers: int
     hidden_act: str = "silu"
     model_type: str = "qwen2"
+    layer_types: Optional[Tuple[str, ...]] = None      # per layer "full_attention" | "sliding_attention", if given
 
     ARCHITECTURE = "Qwen2ForCausalLM"
 
@@ -111,10 +115,20 @@ class Qwen2Config:
         act = cfg.get("hidden_act", "silu")
         if act != "silu":
             raise ConfigError(f"config.json: hidden_act '{act}' is not supported (only 'silu')")
-        if cfg.get("rope_scaling") is not None:
-            raise ConfigError("config.json: rope_scaling is set; scaled rotary embeddings are not supported")
+        for key in ("rope_scaling", "rope_parameters"):
+            rope = cfg.get(key)
+            if rope is None:
+                continue
+            if not isinstance(rope, dict):
+                raise ConfigError(f"config.json: attribute '{key}' is not an object: {rope!r}")
+            kind = rope.get("rope_type", rope.get("type", "default"))
+            if kind != "default":
+                raise ConfigError(f"config.json: {key} asks for '{kind}' rotary embeddings; only 'default' is supported")
         eps = _opt_float(cfg, "rms_norm_eps", 1e-6)
-        theta = _opt_float(cfg, "rope_theta", 10000.0)
+        if cfg.get("rope_theta") is None and isinstance(cfg.get("rope_parameters"), dict):
+            theta = _opt_float(cfg["rope_parameters"], "rope_theta", 10000.0)
+        else:
+            theta = _opt_float(cfg, "rope_theta", 10000.0)
         if eps <= 0 or theta <= 0:
             raise ConfigError(f"config.json: rms_norm_eps ({eps}) and rope_theta ({theta}) must be positive")
         max_pos = _opt_int(cfg, "max_position_embeddings", 4096)
@@ -127,13 +141,22 @@ class Qwen2Config:
             raise ConfigError("config.json: use_sliding_window is true but sliding_window is missing or not positive")
         if max_win_layers < 0:
             raise ConfigError(f"config.json: max_window_layers ({max_win_layers}) is negative")
+        layer_types = cfg.get("layer_types")
+        if layer_types is not None:
+            kinds = ("full_attention", "sliding_attention")
+            if not isinstance(layer_types, list) or len(layer_types) != layers or any(t not in kinds for t in layer_types):
+                raise ConfigError(f"config.json: layer_types must name one of {kinds} for each of the {layers} layers")
+            if "sliding_attention" in layer_types and window <= 0:
+                raise ConfigError("config.json: layer_types has sliding_attention but sliding_window is missing or not positive")
+            layer_types = tuple(layer_types)
         return cls(vocab_size=vocab, hidden_size=hidden, intermediate_size=inter,
                    num_hidden_layers=layers, num_attention_heads=heads,
                    num_key_value_heads=kv_heads, head_dim=head_dim,
                    max_position_embeddings=max_pos, rms_norm_eps=eps, rope_theta=theta,
                    tie_word_embeddings=_opt_bool(cfg, "tie_word_embeddings", False),
                    use_sliding_window=use_win, sliding_window=window,
-                   max_window_layers=max_win_layers, hidden_act=act, model_type=model_type)
+                   max_window_layers=max_win_layers, hidden_act=act, model_type=model_type,
+                   layer_types=layer_types)
 
     @classmethod
     def load(cls, folder: str) -> "Qwen2Config":
@@ -151,12 +174,18 @@ class Qwen2Config:
 
     def to_dict(self) -> Dict[str, Any]:
         d = asdict(self)
+        if self.layer_types is None:
+            del d["layer_types"]
+        else:
+            d["layer_types"] = list(self.layer_types)
         d["architectures"] = [self.ARCHITECTURE]
         d["torch_dtype"] = "bfloat16"
         return d
 
     # ------------------------------------------------------------------ layers
     def layer_window(self, layer: int) -> int:
+        if self.layer_types is not None:
+            return self.sliding_window if self.layer_types[layer] == "sliding_attention" else 0
         if self.use_sliding_window and layer >= self.max_window_layers:
             return self.sliding_window
         return 0
@@ -189,4 +218,5 @@ class Qwen2Config:
                          schedule=list(range(self.num_hidden_layers)),
                          final_norm=NormSpec(kind="rmsnorm", size=self.hidden_size, eps=self.rms_norm_eps),
                          tie_head=self.tie_word_embeddings, embed_name="model.embed_tokens.weight",
-                         final_norm_name="model.norm.weight", head_name="lm_head.weight")
+                         final_norm_name="model.norm.weight", head_name="lm_head.weight",
+                         head_may_be_absent=True)

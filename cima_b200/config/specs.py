@@ -89,6 +89,9 @@ class ModelSpec:
     final_norm_name: str
     head_name: str
     embed_scale: float = 1.0
+    # A checkpoint of an untied model that stores no head tensor: the table serves as the head
+    # (the reference decides so, src/models/transformer.rs:810, and warns, :839-841).
+    head_may_be_absent: bool = False
 
     def describe(self) -> str:
         kinds = [f"{self.layers[i].mixer.kind}"

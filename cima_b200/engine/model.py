@@ -8,6 +8,8 @@ batch of sequences here.
 """
 from __future__ import annotations
 
+import dataclasses
+import sys
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -18,7 +20,7 @@ from ..config.specs import ModelSpec
 from ..parts import Linear, Runtime, build_block, build_norm
 from ..parts.linear import FOLDED_NORM_ROWS
 from ..parts.norm import RowsInfo
-from ..weights.loader import TensorSpec, load_tensors
+from ..weights.loader import TensorSpec, load_tensors, tensor_names
 from .batch import StepBatch, StepEntry, build_batch
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -182,13 +184,24 @@ class Model:
         return self.head.logits(self.final_norm(x))
 
 
+def settle_head(spec: ModelSpec, stored: Sequence[str], warn=None) -> ModelSpec:
+    """The spec with the head tied to the table if the architecture allows a checkpoint without a head
+    tensor and this one has none (src/models/transformer.rs:810: tied = the flag, or no lm_head.weight)."""
+    if spec.tie_head or not spec.head_may_be_absent or spec.head_name in stored:
+        return spec
+    if warn is not None:
+        warn(f"{spec.head_name} absent: the embedding table serves as the head")
+    return dataclasses.replace(spec, tie_head=True)
+
+
 def load_model(folder: str, dtype="bfloat16", max_tokens: int = 4096, max_seqs: Optional[int] = None,
                device="cuda:0", kernels=None, verbose: bool = True) -> Model:
     """A model from a folder with config.json and model.safetensors, its class chosen by config.json."""
     from ..kernels import Kernels
     raw = read_config_json(folder)
     entry = lookup_architecture(raw)
-    spec = entry.spec(entry.parse(raw))
+    spec = settle_head(entry.spec(entry.parse(raw)), tensor_names(folder),
+                       warn=(lambda m: print(f"[cima_b200] {m}", file=sys.stderr, flush=True)) if verbose else None)
     rt = Runtime(kernels=kernels if kernels is not None else Kernels(verbose=verbose),
                  dtype=parse_dtype(dtype), device=device)
     model = Model(spec, rt)

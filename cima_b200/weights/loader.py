@@ -58,6 +58,16 @@ def stored_to_kept(t: torch.Tensor) -> torch.Tensor:
     return t.to(torch.int32)
 
 
+def tensor_names(folder: str) -> List[str]:
+    """Names of all tensors that the folder's safetensors files hold (headers only)."""
+    where = open_model_files(folder)
+    try:
+        return sorted(where)
+    finally:
+        for sf in {id(f): f for f, _ in where.values()}.values():
+            sf.close()
+
+
 def load_tensors(folder: str, plan: Dict[str, TensorSpec], ignore: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
     """Tensors of ``plan`` from ``folder`` (CPU).  ``ignore`` holds glob patterns of names that
     may be present without being used (a tied model that also stores its head, say)."""

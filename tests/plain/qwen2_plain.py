@@ -99,7 +99,10 @@ def plain_layer_window(cfg: dict, layer: int) -> int:
     1184-1199); its attention kernels take a per-call ``window``
     (src/kernels.cu:459).  This build reads config.json's own keys: with
     ``use_sliding_window`` true, layers from ``max_window_layers`` on look at the
-    last ``sliding_window`` keys; otherwise every layer sees all keys."""
+    last ``sliding_window`` keys; otherwise every layer sees all keys.  A
+    ``layer_types`` list, where given, names the windowed layers itself."""
+    if cfg.get("layer_types") is not None:
+        return int(cfg["sliding_window"]) if cfg["layer_types"][layer] == "sliding_attention" else 0
     if not cfg.get("use_sliding_window", False):
         return 0
     if layer >= int(cfg.get("max_window_layers", cfg["num_hidden_layers"])):
@@ -115,7 +118,7 @@ def plain_block(x, W, cfg, layer, positions):
     nkv = cfg.get("num_key_value_heads", nh)
     hd = cfg.get("head_dim", cfg["hidden_size"] // nh)
     eps = cfg.get("rms_norm_eps", 1e-6)
-    theta = cfg.get("rope_theta", 10000.0)
+    theta = cfg.get("rope_theta") or (cfg.get("rope_parameters") or {}).get("rope_theta", 10000.0)
     T = x.shape[0]
     h = plain_rmsnorm(x, W[p + "input_layernorm.weight"], eps)
     q = plain_linear(h, W[p + "self_attn.q_proj.weight"], W[p + "self_attn.q_proj.bias"]).view(T, nh, hd)

@@ -64,6 +64,25 @@ def test_spec_carries_every_size_and_the_window_per_layer():
     assert b.tie_head is False and Qwen2Config.from_dict(TINY_A).model_spec().tie_head is True
 
 
+def test_layer_types_and_the_newer_spelling_of_the_rotary_base():
+    raw = dict(TINY_C, layer_types=["sliding_attention", "full_attention", "full_attention", "sliding_attention"])
+    c = Qwen2Config.from_dict(raw)
+    assert [b.mixer.window for b in c.model_spec().layers] == [40, 0, 0, 40]
+    assert Qwen2Config.from_dict(c.to_dict()) == c
+    with pytest.raises(ConfigError, match="layer_types"):
+        Qwen2Config.from_dict(dict(TINY_C, layer_types=["full_attention"]))
+    with pytest.raises(ConfigError, match="layer_types"):
+        Qwen2Config.from_dict(dict(TINY_C, layer_types=["full_attention", "linear_attention", "full_attention", "full_attention"]))
+    with pytest.raises(ConfigError, match="sliding_window"):
+        Qwen2Config.from_dict(dict(TINY_A, layer_types=["sliding_attention", "full_attention"]))
+    raw = {k: v for k, v in TINY_B.items() if k != "rope_theta"}
+    c = Qwen2Config.from_dict(dict(raw, rope_parameters={"rope_theta": 250000.0, "rope_type": "default"}))
+    assert c.rope_theta == 250000.0 and c.model_spec().layers[0].mixer.position.theta == 250000.0
+    assert Qwen2Config.from_dict(dict(TINY_B, rope_scaling={"rope_type": "default"})).rope_theta == TINY_B["rope_theta"]
+    with pytest.raises(ConfigError, match="rope_parameters"):
+        Qwen2Config.from_dict(dict(raw, rope_parameters={"rope_theta": 1e6, "rope_type": "linear", "factor": 2.0}))
+
+
 def test_registry_lookup_and_unknown_names():
     assert "Qwen2ForCausalLM" in registered_architectures()
     assert lookup_architecture(TINY_A).name == "Qwen2ForCausalLM"

@@ -47,3 +47,39 @@ def test_bfloat16_plumbing_with_folded_norms():
     tail = run_tail_one_by_one(model, toks, 20)
     assert (whole - want).abs().max().item() <= 2e-2
     assert (tail - want).abs().max().item() <= 2e-2
+
+
+def test_a_checkpoint_without_a_head_uses_the_table(tmp_path, capsys):
+    """An untied configuration whose file holds no lm_head.weight: the table is the head, with a warning
+    (src/models/transformer.rs:810, :839-841); a tied configuration that also stores a head ignores it."""
+    import json
+    import cima_b200
+    from cima_b200.engine import load_model
+    from cima_b200.weights import SafetensorsFile, write_safetensors
+    from reference_kernels import ReferenceKernels
+    src = model_folder("B")                                   # untied, stores lm_head.weight
+    sf = SafetensorsFile(f"{src}/model.safetensors")
+    tensors = {n: sf.read(n).clone() for n in sf.names()}
+    sf.close()
+    cfg = dict(TINY["B"])
+    toks = random_tokens(cfg["vocab_size"], 20, seed=1)
+
+    def folder(name, cfg_, tensors_):
+        d = tmp_path / name
+        d.mkdir()
+        (d / "config.json").write_text(json.dumps(cfg_))
+        write_safetensors(str(d / "model.safetensors"), tensors_)
+        return str(d)
+
+    headless = folder("headless", cfg, {n: t for n, t in tensors.items() if n != "lm_head.weight"})
+    model = load_model(headless, dtype="float32", max_tokens=256, device="cpu", kernels=ReferenceKernels())
+    assert "lm_head.weight absent" in capsys.readouterr().err
+    c, W = plain_load(headless)
+    assert torch.allclose(run_whole(model, toks), plain_forward(W, c, toks).float(), atol=2e-4, rtol=1e-4)
+    tied_with_head = folder("tied", dict(cfg, tie_word_embeddings=True), tensors)
+    model = load_model(tied_with_head, dtype="float32", max_tokens=256, device="cpu", kernels=ReferenceKernels())
+    c, W = plain_load(tied_with_head)
+    got = run_whole(model, toks)
+    assert torch.allclose(got, plain_forward(W, c, toks).float(), atol=2e-4, rtol=1e-4)
+    head = plain_forward(dict(W, **{"model.embed_tokens.weight": W["model.embed_tokens.weight"]}), dict(c, tie_word_embeddings=False), toks)
+    assert not torch.allclose(got, head.float(), atol=1e-2)   # the stored head was not used
