@@ -219,4 +219,4 @@ class Qwen2Config:
                          final_norm=NormSpec(kind="rmsnorm", size=self.hidden_size, eps=self.rms_norm_eps),
                          tie_head=self.tie_word_embeddings, embed_name="model.embed_tokens.weight",
                          final_norm_name="model.norm.weight", head_name="lm_head.weight",
-                         head_may_be_absent=True)
+                         head_may_be_absent=True, optional_prefixes=("model.",))

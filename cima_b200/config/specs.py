@@ -13,7 +13,7 @@ to these classes.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional
+from typing import Any, Dict, List, Optional, Tuple
 
 
 @dataclass(frozen=True)
@@ -92,6 +92,9 @@ class ModelSpec:
     # A checkpoint of an untied model that stores no head tensor: the table serves as the head
     # (the reference decides so, src/models/transformer.rs:810, and warns, :839-841).
     head_may_be_absent: bool = False
+    # Prefixes of the tensor names above that a checkpoint may leave out (a bare backbone stores
+    # "layers.0..." for "model.layers.0..."; the reference tries both, src/models/transformer.rs:472-488).
+    optional_prefixes: Tuple[str, ...] = ()
 
     def describe(self) -> str:
         kinds = [f"{self.layers[i].mixer.kind}"

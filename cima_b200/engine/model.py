@@ -187,7 +187,8 @@ class Model:
 def settle_head(spec: ModelSpec, stored: Sequence[str], warn=None) -> ModelSpec:
     """The spec with the head tied to the table if the architecture allows a checkpoint without a head
     tensor and this one has none (src/models/transformer.rs:810: tied = the flag, or no lm_head.weight)."""
-    if spec.tie_head or not spec.head_may_be_absent or spec.head_name in stored:
+    names = [spec.head_name] + [spec.head_name[len(p):] for p in spec.optional_prefixes if spec.head_name.startswith(p)]
+    if spec.tie_head or not spec.head_may_be_absent or any(n in stored for n in names):
         return spec
     if warn is not None:
         warn(f"{spec.head_name} absent: the embedding table serves as the head")
@@ -208,6 +209,7 @@ def load_model(folder: str, dtype="bfloat16", max_tokens: int = 4096, max_seqs: 
     from ..sampling.sampler import sampler_state
     from .fit import check_fit
     check_fit(model.forecast(max_tokens, max_seqs, extra_state=sampler_state()), device)     # before anything is allocated
-    model.load(load_tensors(folder, model.plan(), ignore=model.ignorable()))
+    model.load(load_tensors(folder, model.plan(), ignore=model.ignorable(),
+                            optional_prefixes=spec.optional_prefixes))
     model.make_cache(max_tokens, max_seqs, extra_state=sampler_state())
     return model

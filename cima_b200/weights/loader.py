@@ -68,23 +68,34 @@ def tensor_names(folder: str) -> List[str]:
             sf.close()
 
 
-def load_tensors(folder: str, plan: Dict[str, TensorSpec], ignore: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
-    """Tensors of ``plan`` from ``folder`` (CPU).  ``ignore`` holds glob patterns of names that
-    may be present without being used (a tied model that also stores its head, say)."""
+def load_tensors(folder: str, plan: Dict[str, TensorSpec], ignore: Iterable[str] = (),
+                 optional_prefixes: Iterable[str] = ()) -> Dict[str, torch.Tensor]:
+    """Tensors of ``plan`` from ``folder`` (CPU), keyed by the plan's names.  ``ignore`` holds glob
+    patterns of names that may be present without being used (a tied model that also stores its head,
+    say).  ``optional_prefixes``: prefixes of plan names that a checkpoint may leave out, as the
+    reference looks a tensor up under several prefixes (src/models/transformer.rs:472-488): with
+    "model.", a file that stores ``layers.0.mlp.up_proj.weight`` serves ``model.layers.0.mlp.up_proj.weight``."""
     where = open_model_files(folder)
     try:
-        ignore = list(ignore)
-        missing: List[str] = [n for n in plan if n not in where]
-        unexpected = [n for n in where if n not in plan and not any(fnmatch.fnmatch(n, p) for p in ignore)]
+        ignore, optional_prefixes = list(ignore), list(optional_prefixes)
+        stored_as: Dict[str, str] = {}
+        for n in plan:
+            for cand in [n] + [n[len(p):] for p in optional_prefixes if n.startswith(p)]:
+                if cand in where:
+                    stored_as[n] = cand
+                    break
+        used = set(stored_as.values())
+        missing: List[str] = [n for n in plan if n not in stored_as]
+        unexpected = [n for n in where if n not in used and not any(fnmatch.fnmatch(n, p) for p in ignore)]
         wrong = []
         for n, spec in plan.items():
-            if n in where:
-                found = where[n][0].tensors[n]["shape"]
+            if n in stored_as:
+                found = where[stored_as[n]][0].tensors[stored_as[n]]["shape"]
                 if tuple(found) != tuple(spec.shape):
-                    wrong.append((n, found, spec.shape))
+                    wrong.append((stored_as[n], found, spec.shape))
         if missing or unexpected or wrong:
             raise WeightError(folder, sorted(missing), sorted(unexpected), sorted(wrong), len(where))
-        return {n: stored_to_kept(where[n][0].read(n)) for n in plan}
+        return {n: stored_to_kept(where[stored_as[n]][0].read(stored_as[n])) for n in plan}
     finally:
         for sf in {id(f): f for f, _ in where.values()}.values():
             sf.close()

@@ -106,6 +106,27 @@ def test_tied_model_may_hold_a_head_untied_must(tmp_path):
         load_tensors(str(tmp_path), plan_a)
 
 
+def test_a_checkpoint_may_leave_out_the_model_prefix(tmp_path):
+    """A bare backbone stores ``layers.0...``; the plan's names are served by it when the architecture allows
+    the prefix to be absent, and the error still lists what is wrong under the stored names."""
+    spec = Qwen2Config.from_dict(TINY_A).model_spec()
+    plan = build_plan(spec)
+    cima_b200.write_random_model(str(tmp_path), TINY_A, seed=1)
+    t = load_tensors(str(tmp_path), plan)
+    bare = {(n[len("model."):] if n.startswith("model.") else n): v for n, v in t.items()}
+    write_safetensors(str(tmp_path / "model.safetensors"), bare)
+    with pytest.raises(WeightError, match="missing"):
+        load_tensors(str(tmp_path), plan)
+    got = load_tensors(str(tmp_path), plan, optional_prefixes=spec.optional_prefixes)
+    assert set(got) == set(plan) and all(torch.equal(got[n], t[n]) for n in plan)
+    bare["layers.1.mlp.up_proj.weight"] = bare["layers.1.mlp.up_proj.weight"][:, :-1].contiguous()
+    bare["extra.weight"] = torch.zeros(2)
+    write_safetensors(str(tmp_path / "model.safetensors"), bare)
+    with pytest.raises(WeightError) as e:
+        load_tensors(str(tmp_path), plan, optional_prefixes=spec.optional_prefixes)
+    assert e.value.unexpected == ["extra.weight"] and e.value.wrong_shape[0][0] == "layers.1.mlp.up_proj.weight"
+
+
 def test_random_weights_depend_on_seed_and_name_only(tmp_path):
     cima_b200.write_random_model(str(tmp_path / "a"), TINY_A, seed=1)
     cima_b200.write_random_model(str(tmp_path / "b"), TINY_A, seed=1)
