@@ -160,14 +160,17 @@ def test_step_refuses_mixed_batches_and_overflow():
 
 
 ODD = [dict(hidden_size=100, num_attention_heads=5, num_key_value_heads=5, head_dim=16, intermediate_size=130, vocab_size=333),
-       dict(hidden_size=104, num_attention_heads=2, num_key_value_heads=1, head_dim=48, intermediate_size=99, vocab_size=1001)]
+       dict(hidden_size=104, num_attention_heads=2, num_key_value_heads=1, head_dim=48, intermediate_size=99, vocab_size=1001),
+       # head sizes above the tensor-core attention kernels' 128: the plain attention serves both precisions
+       dict(hidden_size=96, num_attention_heads=2, num_key_value_heads=1, head_dim=160, intermediate_size=72, vocab_size=300),
+       dict(hidden_size=64, num_attention_heads=3, num_key_value_heads=3, head_dim=256, intermediate_size=48, vocab_size=129)]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("over", ODD)
-def test_widths_that_are_no_multiple_of_eight(over, dtype, tmp_path):
-    """Hidden and intermediate widths and a vocabulary that fit none of the 16-byte paths: a prompt whole,
-    then ten tokens one by one, against the plain implementation."""
+def test_widths_and_head_sizes_off_the_fast_paths(over, dtype, tmp_path):
+    """Hidden and intermediate widths and a vocabulary that fit none of the 16-byte paths, and head sizes up to
+    the largest allowed: a prompt whole, then ten tokens one by one, against the plain implementation."""
     import cima_b200
     from cima_b200.engine import load_model
     cfg = dict(model_type="qwen2", architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, rope_theta=10000.0,
