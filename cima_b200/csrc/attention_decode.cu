@@ -61,6 +61,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 constexpr int MAX_SPLITS = 64;
 constexpr int STAGES = 3;         // pages in flight per block (two blocks of 3 x 34 KB fit an SM at head_dim 128)
 
+// The splits that get pages of a sequence with ``len`` positions: at most one per page of the visible keys.
+__device__ __forceinline__ int live_splits(int len, int window, int n_splits) {
+  const int lo = (window > 0 && len > window) ? len - window : 0;
+  return min(n_splits, (len - 1) / PS - lo / PS + 1);
+}
+
 // early: the sequence's lengths, slots and block table, and every page before the one that holds the newest
 // position, are not written by the kernel launched just before this one (the q/k/v projection with its cache
 // append writes the newest position only); the first pages are then fetched before the wait on that kernel.
@@ -91,9 +97,14 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   const int slot = seq_slot[b];
   const int lo = (window > 0 && len > window) ? len - window : 0;
   const int pf = lo / PS, pl = (len - 1) / PS;
-  const int npages = pl - pf + 1;                      // shared evenly: split s takes pages [s n / S, (s + 1) n / S)
-  const int p0 = pf + (int)((long long)split * npages / n_splits);
-  const int p1 = pf + (int)((long long)(split + 1) * npages / n_splits);
+  const int npages = pl - pf + 1;
+  // The pages are shared evenly among S = min(n_splits, pages) splits: split s takes pages [s n / S, (s + 1) n / S).
+  // A launch sized for a long context (a captured step keeps its grid while the sequences grow) leaves the
+  // blocks beyond S without work; the merge reads the first S partial results only (live_splits there).
+  const int S = live_splits(len, window, n_splits);
+  if (split >= S) return;
+  const int p0 = pf + (int)((long long)split * npages / S);
+  const int p1 = pf + (int)((long long)(split + 1) * npages / S);
 
   auto page_of = [&](int page_index) -> int {
     int e = page_index;
@@ -268,20 +279,21 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   }
 }
 
-// out[b, h, :] = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s.
+// out[b, h, :] = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s over the splits that have pages.
 // One block per (head, sequence).  The first warp loads every split's (m, l) at once (a lane per split, all loads
 // independent), makes the weights 2^(m_s - M) and their sum with l by a shuffle tree (a fixed order, whatever the
 // timing), and leaves them in shared memory; then a thread per dimension sums the splits' accumulators, eight
 // independent loads at a time.  (A loop of one thread over the splits' l, as this kernel once had, costs a trip to
 // L2 per split: 8 us at 32 splits.)
 __global__ void __launch_bounds__(128)
-k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                    __nv_bfloat16* __restrict__ out, int ldo, int nh, int hd, int n_splits) {
+k_attention_combine(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ seq_len,
+                    __nv_bfloat16* __restrict__ out, int ldo, int nh, int hd, int window, int splits_launched) {
   cima_pdl_wait();
   __shared__ float w[MAX_SPLITS];
   __shared__ float s_inv;
   const int b = blockIdx.y, h = blockIdx.x;
-  const size_t base = ((size_t)b * nh + h) * n_splits;
+  const size_t base = ((size_t)b * nh + h) * splits_launched;
+  const int n_splits = live_splits(seq_len[b], window, splits_launched);
   if (threadIdx.x < 32) {
     float m[MAX_SPLITS / 32], l[MAX_SPLITS / 32];
     float M = -INFINITY;
@@ -344,7 +356,7 @@ int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, cons
                                            window, n_splits, early); if (rc_) return rc_; }
   int rc = cima_launch_result();
   if (rc || n_splits == 1) return rc;
-  { int rc_ = cima_launch(k_attention_combine, dim3(dim3(nh, B)), dim3(128), (size_t)(0), stream, 1, part_o, part_ml, (__nv_bfloat16*)out, ldo, nh, HD, n_splits); if (rc_) return rc_; }
+  { int rc_ = cima_launch(k_attention_combine, dim3(dim3(nh, B)), dim3(128), (size_t)(0), stream, 1, part_o, part_ml, seq_len, (__nv_bfloat16*)out, ldo, nh, HD, window, n_splits); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
