@@ -35,6 +35,16 @@ class LM:
     def spec(self):
         return self.model.spec
 
+    @property
+    def config(self):
+        """The typed configuration that config.json was parsed into."""
+        return self.model.config
+
+    def step(self, entries):
+        """The model's step function (``cima_b200.engine.StepEntry`` per sequence): float32 logits at the wanted
+        places.  The caller opens and closes the slots (``lm.model.cache``)."""
+        return self.model.step(entries)
+
     def generate(self, prompts: Sequence[Sequence[int]], options: Union[GenOptions, Sequence[GenOptions], None] = None,
                  **named):
         """Token ids in, ``GenResult`` per prompt out.  Options by the reference's names

@@ -47,6 +47,7 @@ class Model:
                 raise ValueError(f"the schedule names layer {i}; the model has {len(spec.layers)}")
         self.blocks = [build_block(b, i, rt) for i, b in enumerate(spec.layers)]
         self.final_norm = build_norm(spec.final_norm, rt)
+        self.config = None                                  # set by load_model
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
         self.cache: Optional[KVCache] = None
@@ -201,11 +202,13 @@ def load_model(folder: str, dtype="bfloat16", max_tokens: int = 4096, max_seqs: 
     from ..kernels import Kernels
     raw = read_config_json(folder)
     entry = lookup_architecture(raw)
-    spec = settle_head(entry.spec(entry.parse(raw)), tensor_names(folder),
+    config = entry.parse(raw)
+    spec = settle_head(entry.spec(config), tensor_names(folder),
                        warn=(lambda m: print(f"[cima_b200] {m}", file=sys.stderr, flush=True)) if verbose else None)
     rt = Runtime(kernels=kernels if kernels is not None else Kernels(verbose=verbose),
                  dtype=parse_dtype(dtype), device=device)
     model = Model(spec, rt)
+    model.config = config                                   # the architecture's typed configuration, as parsed
     from ..sampling.sampler import sampler_state
     from .fit import check_fit
     check_fit(model.forecast(max_tokens, max_seqs, extra_state=sampler_state()), device)     # before anything is allocated

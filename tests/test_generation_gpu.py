@@ -53,6 +53,21 @@ def test_greedy_generation_matches_plain(name, lens, steps, dtype):
     assert lm.model.cache.slots.held == 0
 
 
+def test_entry_point_exposes_config_and_step():
+    """``lm.config`` is the typed configuration, ``lm.step`` the step function that generation runs on."""
+    from cima_b200.engine import StepEntry
+    lm = cima_b200.load(model_folder("B"), dtype="float32", max_tokens=256, verbose=False)
+    assert lm.config.num_key_value_heads == 1 and lm.config.rope_theta == TINY["B"]["rope_theta"]
+    toks = random_tokens(TINY["B"]["vocab_size"], 12, seed=5)
+    cfg, W = plain_load(model_folder("B"))
+    (slot,) = lm.model.cache.open(1)
+    try:
+        got = lm.step([StepEntry(slot, toks, [11])]).cpu()
+    finally:
+        lm.model.cache.close([slot])
+    assert torch.allclose(got[0], plain_forward(W, cfg, toks)[-1].float(), atol=2e-4, rtol=1e-4)
+
+
 @pytest.mark.parametrize("name,temp", [("A", 0.8), ("B", 1.0)])
 def test_sampled_generation_matches_plain_in_float32(name, temp):
     V = TINY[name]["vocab_size"]
