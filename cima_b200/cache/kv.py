@@ -183,6 +183,12 @@ class KVCache:
         return LayerKV(storage=g.storage[li], block_table=g.block_table, page_size=self.page_size,
                        ring_pages=g.ring_pages, window=g.request.window, group=gi)
 
+    def most_tokens_going_on(self) -> Optional[int]:
+        """The most tokens that a sequence which already holds positions may add in one step whose rows read the
+        cache, or None for no limit.  A window group keeps a ring of ceil(w / page) + 1 pages: the step's keys are
+        all appended before any row reads, so a row's oldest key survives only while the step adds at most a page."""
+        return self.page_size if any(g.ring_pages for g in self.groups) else None
+
     def has_kv(self, layer: int) -> bool:
         return layer in self._layer_group
 

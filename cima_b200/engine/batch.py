@@ -27,7 +27,9 @@ class StepEntry:
 
 @dataclass
 class StepBatch:
-    prefill: bool                     # True: every sequence starts at position 0; False: one token each
+    prefill: bool                     # True: every sequence starts at position 0 (attention may read the step's own
+                                      # keys); False: the rows read the cache (one token each, or sequences that
+                                      # go on by several tokens)
     n_rows: int
     n_seqs: int
     n_want: int
@@ -67,8 +69,7 @@ def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, dev
     elif all(s == 0 for s in starts):
         prefill = True
     else:
-        raise ValueError("the sequences of a step either all start at their first token or all go on by one "
-                         f"token (token counts {counts}, positions held {list(starts)})")
+        prefill = False                   # some sequence goes on by several tokens: every row reads the cache
     B, T = len(entries), sum(counts)
     W = sum(len(e.want) for e in entries)
     q_tiles = []

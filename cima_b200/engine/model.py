@@ -125,6 +125,9 @@ class Model:
             if not cache.slots.is_held(e.slot):
                 raise ValueError(f"slot {e.slot} is not open")
         starts = [cache.length(e.slot) for e in entries]
+        limit = cache.most_tokens_going_on()
+        if limit is not None and any(starts) and max(len(e.tokens) for e in entries) > limit:
+            return self._step_in_rounds(entries, limit)
         batch = build_batch(entries, starts, self.spec.vocab, self.rt.device)
         for e, s in zip(entries, starts):
             cache.reserve(e.slot, s + len(e.tokens))
@@ -133,6 +136,32 @@ class Model:
         for e, s in zip(entries, starts):
             cache.commit(e.slot, s + len(e.tokens))
         return logits
+
+    def _step_in_rounds(self, entries: Sequence[StepEntry], most: int) -> torch.Tensor:
+        """The same step as rounds of at most ``most`` tokens a sequence (see ``KVCache.most_tokens_going_on``);
+        the logits come back in the order of the entries and of their ``want``, as from one step."""
+        for i, e in enumerate(entries):
+            for w in e.want:
+                if not (0 <= w < len(e.tokens)):
+                    raise ValueError(f"entry {i}: wanted place {w} is outside its {len(e.tokens)} tokens")
+        parts, place = [], {}                                 # (entry, index in its want) -> row among all rounds' logits
+        done_rows = 0
+        for lo in range(0, max(len(e.tokens) for e in entries), most):
+            sub = []
+            for i, e in enumerate(entries):
+                if lo >= len(e.tokens):
+                    continue
+                want = []
+                for k, w in enumerate(e.want):
+                    if lo <= w < lo + most:
+                        place[(i, k)] = done_rows + sum(len(x.want) for x in sub) + len(want)
+                        want.append(w - lo)
+                sub.append(StepEntry(e.slot, e.tokens[lo:lo + most], want))
+            parts.append(self.step(sub))
+            done_rows += parts[-1].shape[0]
+        order = [place[(i, k)] for i, e in enumerate(entries) for k in range(len(e.want))]
+        logits = torch.cat(parts)
+        return logits[torch.as_tensor(order, dtype=torch.long, device=logits.device)] if order else logits
 
     def check_device(self) -> None:
         """Raise if a bounded wait inside a kernel ran out since the last check (synchronises)."""

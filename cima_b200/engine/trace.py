@@ -6,6 +6,8 @@ Steps come as JSON lines on standard input:
 
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
 
+The requests of a step usually either all start or all go on by one token; any other mix is taken too (a
+request may go on by several tokens), through the general rows-from-the-cache path of the step function.
 For a step that wants logits, ``<out>/<step>.f32`` holds them as little-endian float32
 [wanted, vocab] in the order of the entries and of their ``want``.  After every step a line
 ``done <step>`` is printed and flushed.

@@ -78,6 +78,29 @@ def run_tail_one_by_one(model, tokens, tail):
         model.cache.close([slot])
 
 
+def run_in_pieces(model, seqs, cuts):
+    """Sequences as one batch fed in pieces: step k brings tokens [cuts[i][k-1], cuts[i][k]) of sequence i (a
+    sequence whose cuts are used up sits the step out).  All logits per sequence."""
+    slots = model.cache.open(len(seqs))
+    try:
+        outs = [[] for _ in seqs]
+        bounds = [[0] + list(c) + [len(q)] for q, c in zip(seqs, cuts)]
+        for k in range(max(len(b) for b in bounds) - 1):
+            live = [i for i, b in enumerate(bounds) if k + 1 < len(b) and b[k + 1] > b[k]]
+            if not live:
+                continue
+            entries = [StepEntry(slots[i], seqs[i][bounds[i][k]:bounds[i][k + 1]], list(range(bounds[i][k + 1] - bounds[i][k])))
+                       for i in live]
+            lg = model.step(entries).float().cpu()
+            r = 0
+            for i in live:
+                n = bounds[i][k + 1] - bounds[i][k]
+                outs[i].append(lg[r:r + n]); r += n
+        return [torch.cat(o) for o in outs]
+    finally:
+        model.cache.close(slots)
+
+
 def run_batched(model, seqs, decode_from):
     """Sequences as one batch: tokens [0, decode_from[i]) as prompts in one step, then one token each
     per step until each sequence's own end; shorter ones end earlier.  Returns logits per sequence."""

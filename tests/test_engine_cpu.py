@@ -5,6 +5,7 @@ import pytest
 
 from helpers import TINY, cpu_model, model_folder, random_tokens, run_batched, run_tail_one_by_one, run_whole
 from qwen2_plain import plain_forward, plain_load
+from cima_b200.engine import StepEntry
 
 
 @pytest.mark.parametrize("name,length", [("A", 21), ("B", 70), ("C", 150)])
@@ -33,6 +34,35 @@ def test_unequal_batches_reuse_slots():
             assert torch.allclose(g, plain_forward(W, cfg, q).float(), atol=2e-4, rtol=1e-4)
         model.cache.check()
         assert model.cache.slots.held == 0
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_sequences_may_go_on_by_several_tokens(name):
+    """A step may bring several tokens to a sequence that already holds some (a prompt fed in pieces, a second turn
+    of a conversation), beside sequences that start or go on by one: the logits are those of the whole sequence.
+    In C the later layers keep a ring of pages for their window: pieces longer than a page are fed in rounds."""
+    from helpers import run_in_pieces
+    cfg, W = plain_load(model_folder(name))
+    model = cpu_model(name, max_tokens=1024)
+    lens = {"A": [100, 37, 64], "B": [150, 33, 90], "C": [230, 41, 130]}[name]
+    seqs = [random_tokens(cfg["vocab_size"], n, seed=20 + i) for i, n in enumerate(lens)]
+    cuts = [[20, 33, 34, lens[0] - 10], [1, 2, 30], [max(3, lens[2] - 70)]]      # the third: a start and one long piece
+    got = run_in_pieces(model, seqs, cuts)
+    for q, g in zip(seqs, got):
+        assert torch.allclose(g, plain_forward(W, cfg, q).float(), atol=2e-4, rtol=1e-4)
+    model.cache.check()
+    assert model.cache.slots.held == 0
+    # wanted places out of order and across the rounds of a long piece
+    (slot,) = model.cache.open(1)
+    try:
+        q = seqs[2]
+        model.step([StepEntry(slot, q[:5], [])])
+        want = [len(q) - 6, 0, min(70, len(q) - 7), 3]
+        lg = model.step([StepEntry(slot, q[5:], want)]).float().cpu()
+        ref = plain_forward(W, cfg, q).float()
+        assert torch.allclose(lg, ref[[5 + w for w in want]], atol=2e-4, rtol=1e-4)
+    finally:
+        model.cache.close([slot])
 
 
 def test_bfloat16_plumbing_with_folded_norms():

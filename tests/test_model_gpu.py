@@ -138,14 +138,14 @@ def test_wanted_rows_only():
     assert tuple(none.shape) == (0, 1000)
 
 
-def test_step_refuses_mixed_batches_and_overflow():
+def test_step_refuses_bad_tokens_and_overflow():
     from cima_b200.cache import CacheFull, CapacityError
     m = gpu_model("A", "float32", max_tokens=128, max_seqs=2)
     s = m.cache.open(2)
     try:
         m.step([StepEntry(s[0], [1, 2, 3], [])])
         with pytest.raises(ValueError):
-            m.step([StepEntry(s[0], [4, 5], []), StepEntry(s[1], [1, 2], [])])   # one goes on by two
+            m.step([StepEntry(s[0], [4, 5], []), StepEntry(s[0], [1, 2], [])])   # a slot twice
         with pytest.raises(ValueError):
             m.step([StepEntry(s[0], [600], [])])                                   # token id out of range
         with pytest.raises(CacheFull):
@@ -196,3 +196,21 @@ def test_a_head_size_outside_the_steps_of_16_is_refused(tmp_path):
                num_attention_heads=5, num_key_value_heads=5, head_dim=20, intermediate_size=64, vocab_size=50)
     with pytest.raises(ValueError, match="head_dim 20 must be a multiple of 16"):
         cima_b200.write_random_model(str(tmp_path / "m"), cfg, seed=0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_sequences_may_go_on_by_several_tokens(name, dtype):
+    """Prompts fed in pieces beside sequences that start or go on by one token (in C through the window's ring,
+    a long piece in rounds of a page): the logits of the whole sequences."""
+    from helpers import run_in_pieces
+    cfg = TINY[name]
+    m = model_of(name, dtype)
+    lens = {"A": [100, 37, 64], "B": [150, 33, 90], "C": [230, 41, 130]}[name]
+    seqs = [random_tokens(cfg["vocab_size"], n, seed=20 + i) for i, n in enumerate(lens)]
+    cuts = [[20, 33, 34, lens[0] - 10], [1, 2, 30], [max(3, lens[2] - 70)]]
+    got = run_in_pieces(m, seqs, cuts)
+    for q, g_ in zip(seqs, got):
+        assert close(g_, plain_logits(name, q), TOL[dtype])
+    m.cache.check()
+    assert m.cache.slots.held == 0
