@@ -1,6 +1,9 @@
-// Causal grouped-query flash attention for prompts (bfloat16): ragged batches in one launch, keys
-// and values read from the step's own qkv buffer (every sequence of a prefill step starts at
-// position 0, so key j of a sequence is its row j).
+// Causal grouped-query flash attention for several query rows per sequence (bfloat16): ragged batches in
+// one launch.  Two sources of keys and values:
+//   step  - the step's own qkv buffer (every sequence of the step starts at position 0, so key j of a
+//           sequence is its row j): prompts;
+//   cache - the layer's pages through the slot's block table (the step has appended its keys first): sequences
+//           that go on by several tokens, at positions seq_len - rows .. seq_len - 1; a key tile is a page.
 //
 // One block = 64 query rows of one sequence x one head; its 4 warps own 16 rows each.  Key tiles
 // of 64 rows stream through shared memory with cp.async (two in flight).  S = Q K^T and O += P V run
@@ -55,10 +58,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int HD>
+template <int HD, bool FROM_CACHE>
 __global__ void __launch_bounds__(WARPS * 32, 3)      // 3 blocks per SM: at most 168 registers
 k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ tile_seq,
                     const int* __restrict__ tile_row0, const int* __restrict__ seq_first_row,
+                    const __nv_bfloat16* __restrict__ cache, CimaPaged pg, const int* __restrict__ seq_slot,
+                    const int* __restrict__ seq_len,
                     __nv_bfloat16* __restrict__ out, int ldo, int T, int nh, int nkv, float scale, int window) {
   cima_pdl_wait();
   constexpr int ROW = HD + 8;
@@ -68,16 +73,18 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
   __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [2 stages][K|V][BN][ROW]
 
   const int seq = tile_seq[blockIdx.x];
-  const int q0 = tile_row0[blockIdx.x];               // first query position of this block
+  const int q0 = tile_row0[blockIdx.x];               // first query row of this block among the sequence's rows
   const int first = seq_first_row[seq];
-  const int len = seq_first_row[seq + 1] - first;
+  const int len = seq_first_row[seq + 1] - first;     // rows of the sequence in this step
+  const int start = FROM_CACHE ? seq_len[seq] - len : 0;       // position of the sequence's first row
+  const int slot = FROM_CACHE ? seq_slot[seq] : 0;
   const int h = blockIdx.y, kvh = h / (nh / nkv);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int kcol = (nh + kvh) * HD, vcol = (nh + nkv + kvh) * HD;
   const float sc2 = scale * 1.4426950408889634f;       // scores are kept in the base-2 domain
 
-  // this thread's two query rows (positions within the sequence)
+  // this thread's two query rows (among the sequence's rows; their positions are start + row)
   const int r0 = q0 + warp * 16 + g, r1 = r0 + 8;
   uint32_t q[KSTEPS][4];
   {
@@ -101,21 +108,36 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
 
   // key tiles the block needs: from the first key in any row's window to the last row's diagonal
   const int last_q = min(q0 + BM, len) - 1;
-  const int lo_key = (window > 0 && q0 + 1 > window) ? q0 + 1 - window : 0;
-  const int t0 = lo_key / BN, t1 = last_q / BN + 1;
+  const int lo_key = (window > 0 && start + q0 + 1 > window) ? start + q0 + 1 - window : 0;
+  const int t0 = lo_key / BN, t1 = (start + last_q) / BN + 1;
 
   auto issue = [&](int kt, int stage) {
     __nv_bfloat16* dst = tiles + (size_t)stage * 2 * TILE;
-    for (int c = threadIdx.x; c < BN * CPR; c += WARPS * 32) {
-      const int r = c / CPR, cc = c % CPR;
-      const int grow = first + kt * BN + r;           // global row of this key
-      if (grow < T) {
-        const __nv_bfloat16* src = qkv + (size_t)grow * ld;
-        cp_async16(dst + r * ROW + cc * 8, src + kcol + cc * 8);
-        cp_async16(dst + TILE + r * ROW + cc * 8, src + vcol + cc * 8);
-      } else {                                        // beyond the step's rows: zeros, so that 0 * V stays 0
-        *reinterpret_cast<uint4*>(dst + r * ROW + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(dst + TILE + r * ROW + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (FROM_CACHE) {
+      // tile kt is the page of positions [64 kt, 64 kt + 64): K then V, each [64][HD] contiguous.  What a page holds
+      // beyond the sequence's end is finite (zeros or an earlier sequence's keys) and lies above every row's diagonal
+      int e = kt;
+      if (pg.ring) e %= pg.ring;
+      const int page = pg.table[(size_t)slot * pg.width + e];
+      const __nv_bfloat16* src = cache + (((size_t)page * 2) * pg.kv_heads + kvh) * (size_t)(BN * HD);
+      const size_t vofs = (size_t)pg.kv_heads * BN * HD;
+      for (int c = threadIdx.x; c < BN * CPR; c += WARPS * 32) {
+        const int r = c / CPR, cc = c % CPR;
+        cp_async16(dst + r * ROW + cc * 8, src + r * HD + cc * 8);
+        cp_async16(dst + TILE + r * ROW + cc * 8, src + vofs + r * HD + cc * 8);
+      }
+    } else {
+      for (int c = threadIdx.x; c < BN * CPR; c += WARPS * 32) {
+        const int r = c / CPR, cc = c % CPR;
+        const int grow = first + kt * BN + r;         // global row of this key
+        if (grow < T) {
+          const __nv_bfloat16* src = qkv + (size_t)grow * ld;
+          cp_async16(dst + r * ROW + cc * 8, src + kcol + cc * 8);
+          cp_async16(dst + TILE + r * ROW + cc * 8, src + vcol + cc * 8);
+        } else {                                      // beyond the step's rows: zeros, so that 0 * V stays 0
+          *reinterpret_cast<uint4*>(dst + r * ROW + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(dst + TILE + r * ROW + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+        }
       }
     }
   };
@@ -158,7 +180,7 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
     // Scores in the base-2 domain: t = s * scale * log2(e), p = 2^(t - m).  Only tiles that touch the
     // diagonal or the window's lower edge need the mask (a warp-uniform choice).
     const int key_base = kt * BN;
-    const int wr0 = q0 + warp * 16;                    // this warp's first query position
+    const int wr0 = start + q0 + warp * 16;            // this warp's first query position
     const bool masked = key_base + BN - 1 > wr0 || (window > 0 && wr0 + 15 - key_base >= window);
     float mx[2] = {-INFINITY, -INFINITY};
     if (masked) {
@@ -167,7 +189,7 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
 #pragma unroll
         for (int e = 0; e < 4; e++) {
           const int key = key_base + j * 8 + 2 * t + (e & 1);
-          const int qp = (e >> 1) ? r1 : r0;
+          const int qp = start + ((e >> 1) ? r1 : r0);
           const bool seen = key <= qp && (window <= 0 || qp - key < window);
           const float v = seen ? s[j][e] * sc2 : -INFINITY;
           s[j][e] = v;
@@ -243,10 +265,11 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
   }
 }
 
-template <int HD>
+template <int HD, bool FROM_CACHE>
 int launch_prefill(const void* qkv, int ld, const int* tile_seq, const int* tile_row0, const int* seq_first_row,
+                   const void* cache, const CimaPaged& pg, const int* seq_slot, const int* seq_len,
                    void* out, int ldo, int T, int n_tiles, int nh, int nkv, float scale, int window, cudaStream_t stream) {
-  auto kern = k_attention_prefill<HD>;
+  auto kern = k_attention_prefill<HD, FROM_CACHE>;
   const size_t smem = (size_t)2 * 2 * BN * (HD + 8) * sizeof(__nv_bfloat16);
   static bool raised = false;
   if (smem > 48 * 1024 && !raised) {
@@ -255,25 +278,52 @@ int launch_prefill(const void* qkv, int ld, const int* tile_seq, const int* tile
     raised = true;
   }
   { int rc_ = cima_launch(kern, dim3(dim3(n_tiles, nh)), dim3(WARPS * 32), (size_t)(smem), stream, 1, (const __nv_bfloat16*)qkv, ld, tile_seq, tile_row0, seq_first_row,
+                                                        (const __nv_bfloat16*)cache, pg, seq_slot, seq_len,
                                                         (__nv_bfloat16*)out, ldo, T, nh, nkv, scale, window); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
 }  // namespace
 
-// tile_seq / tile_row0 [n_tiles]: the sequence and the first query position of each block of 64 rows.
+static int prefill_checks(const char* who, const void* qkv, int ld, const void* out, int ldo, int hd, int nh, int nkv) {
+  if (hd % 16 || hd < 16 || hd > 128) return cima_fail(CIMA_E_SIZE, "%s: head_dim %d; this kernel takes multiples of 16 up to 128", who, hd);
+  if (nh <= 0 || nkv <= 0 || nh % nkv || nh > 65535) return cima_fail(CIMA_E_SIZE, "%s: %d heads / %d kv heads are not accepted", who, nh, nkv);
+  if (ld % 8 || ldo % 2 || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 3))
+    return cima_fail(CIMA_E_ARG, "%s: qkv rows must be 16-byte aligned (row stride %d a multiple of 8)", who, ld);
+  return 0;
+}
+
+// tile_seq / tile_row0 [n_tiles]: the sequence and the first query row of each block of 64 rows.
 extern "C" int cima_attention_prefill(const void* qkv, int ld, const int* tile_seq, const int* tile_row0,
                                       const int* seq_first_row, void* out, int ldo, int T, int n_tiles, int nh, int nkv,
                                       int hd, float scale, int window, cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return 0;
-  if (hd % 16 || hd < 16 || hd > 128) return cima_fail(CIMA_E_SIZE, "attention_prefill: head_dim %d; this kernel takes multiples of 16 up to 128", hd);
-  if (nh <= 0 || nkv <= 0 || nh % nkv || nh > 65535) return cima_fail(CIMA_E_SIZE, "attention_prefill: %d heads / %d kv heads are not accepted", nh, nkv);
-  if (ld % 8 || ldo % 2 || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 3))
-    return cima_fail(CIMA_E_ARG, "attention_prefill: qkv rows must be 16-byte aligned (row stride %d a multiple of 8)", ld);
-#define CASE(H) case H: return launch_prefill<H>(qkv, ld, tile_seq, tile_row0, seq_first_row, out, ldo, T, n_tiles, nh, nkv, scale, window, stream)
+  if (int rc = prefill_checks("attention_prefill", qkv, ld, out, ldo, hd, nh, nkv)) return rc;
+  const CimaPaged none{nullptr, 0, 0, BN, nkv, hd};
+#define CASE(H) case H: return launch_prefill<H, false>(qkv, ld, tile_seq, tile_row0, seq_first_row, nullptr, none, nullptr, nullptr, out, ldo, T, n_tiles, nh, nkv, scale, window, stream)
   switch (hd) {
     CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
   }
 #undef CASE
   return cima_fail(CIMA_E_SIZE, "attention_prefill: head_dim %d is not instantiated", hd);
+}
+
+// The same for sequences that go on: the rows of sequence s are the positions seq_len[s] - rows .. seq_len[s] - 1,
+// and every key, the step's own included, is read from the layer's pages (64 positions each).
+extern "C" int cima_attention_extend(const void* qkv, int ld, const int* tile_seq, const int* tile_row0,
+                                     const int* seq_first_row, const void* cache, const int* table, int table_width,
+                                     int ring, int page_size, const int* seq_slot, const int* seq_len, void* out, int ldo,
+                                     int T, int n_tiles, int nh, int nkv, int hd, float scale, int window,
+                                     cudaStream_t stream) {
+  if (T <= 0 || n_tiles <= 0) return 0;
+  if (int rc = prefill_checks("attention_extend", qkv, ld, out, ldo, hd, nh, nkv)) return rc;
+  if (page_size != BN) return cima_fail(CIMA_E_SIZE, "attention_extend: page size %d; this kernel takes %d", page_size, BN);
+  if (!cache || !table || !seq_slot || !seq_len || ((uintptr_t)cache & 15)) return cima_fail(CIMA_E_ARG, "attention_extend: the cache (16-byte aligned), its block table, slots and lengths are needed");
+  const CimaPaged pg{table, table_width, ring, page_size, nkv, hd};
+#define CASE(H) case H: return launch_prefill<H, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, cache, pg, seq_slot, seq_len, out, ldo, T, n_tiles, nh, nkv, scale, window, stream)
+  switch (hd) {
+    CASE(16); CASE(32); CASE(48); CASE(64); CASE(80); CASE(96); CASE(112); CASE(128);
+  }
+#undef CASE
+  return cima_fail(CIMA_E_SIZE, "attention_extend: head_dim %d is not instantiated", hd);
 }

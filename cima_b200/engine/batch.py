@@ -42,10 +42,10 @@ class StepBatch:
     seq_first_row: torch.Tensor       # int32 [seqs + 1]
     seq_len: torch.Tensor             # int32 [seqs]
     want_rows: torch.Tensor           # int32 [wanted]
-    n_q_tiles: int = 0                # prefill only: blocks of 64 query rows, heaviest first
+    n_q_tiles: int = 0                # several rows a sequence: blocks of 64 query rows, heaviest first
     q_tile_seq: torch.Tensor = None   # int32 [n_q_tiles] sequence of the block
-    q_tile_row0: torch.Tensor = None  # int32 [n_q_tiles] first query position of the block
-    n_q_tiles_tc: int = 0             # the same in blocks of 128 rows
+    q_tile_row0: torch.Tensor = None  # int32 [n_q_tiles] first row of the block among the sequence's rows
+    n_q_tiles_tc: int = 0             # prompts only: the same in blocks of 128 rows
     q_tile_tc_seq: torch.Tensor = None
     q_tile_tc_row0: torch.Tensor = None
     seq_vt_col: torch.Tensor = None   # int32 [seqs] first column of the sequence in the transposed V
@@ -73,10 +73,11 @@ def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, dev
     B, T = len(entries), sum(counts)
     W = sum(len(e.want) for e in entries)
     q_tiles = []
-    if prefill:
-        q_tiles = sorted(((i, r0) for i, c in enumerate(counts) for r0 in range(0, c, Q_TILE)), key=lambda t: -t[1])
+    if any(c > 1 for c in counts):        # several rows of a sequence: blocks of query rows, heaviest first
+        q_tiles = sorted(((i, r0) for i, c in enumerate(counts) for r0 in range(0, c, Q_TILE)),
+                         key=lambda t: -(starts[t[0]] + t[1]))
     NT = len(q_tiles)
-    tc_tiles = [t for t in q_tiles if t[1] % Q_TILE_TC == 0]
+    tc_tiles = [t for t in q_tiles if t[1] % Q_TILE_TC == 0] if prefill else []
     NTC = len(tc_tiles)
     buf = np.empty(3 * T + 3 * B + 1 + W + 2 * NT + 2 * NTC + B, dtype=np.int32)
     tokens, row_pos, row_seq = buf[0:T], buf[T:2 * T], buf[2 * T:3 * T]

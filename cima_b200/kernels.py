@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 15
+ABI_VERSION = 16
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -56,6 +56,7 @@ _SIGNATURES = {
                              _f, _i, _i, _vp],
     "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
     "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "cima_attention_extend": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
     "cima_gemm_tcgen05": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
@@ -406,6 +407,9 @@ class Kernels:
                 and head_dim <= 128 and batch.n_rows == batch.n_seqs):
             return self.attention_decode(qkv, kv, batch.seq_slot, batch.seq_len, out, n_heads, n_kv_heads, head_dim,
                                          scale, window, batch.max_len, early=after_append)
+        if (from_cache and qkv.dtype is torch.bfloat16 and kv.page_size == 64 and head_dim % 16 == 0
+                and head_dim <= 128 and qkv.shape[1] % 8 == 0 and getattr(batch, "n_q_tiles", 0) > 0):
+            return self.attention_extend(qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window)
         if (not from_cache and qkv.dtype is torch.bfloat16 and head_dim == 128 and qkv.shape[1] % 8 == 0
                 and getattr(batch, "n_q_tiles_tc", 0) > 0 and batch.max_len >= TC_ATTENTION_MIN_LEN):
             return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window)
@@ -430,6 +434,22 @@ class Kernels:
                                                     seq_first_row.data_ptr(), out.data_ptr(), out.shape[1], T,
                                                     tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window,
                                                     self._stream()), "attention_prefill")
+
+    def attention_extend(self, qkv: torch.Tensor, kv, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
+                         head_dim: int, scale: float, window: int) -> None:
+        """Flash attention of sequences that bring several rows to a cache that already holds keys (bf16, pages of
+        64, head_dim <= 128): the rows of sequence s stand at positions seq_len[s] - rows .. seq_len[s] - 1, and all
+        keys, the step's own included, are read from the layer's pages.  ``batch`` brings the blocks of 64 rows."""
+        self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)
+        self._need(kv.storage, "cache", torch.bfloat16, 5); self._need(kv.block_table, "block_table", torch.int32, 2)
+        T = qkv.shape[0]
+        if tuple(out.shape) != (T, n_heads * head_dim) or batch.q_tile_seq.numel() != batch.q_tile_row0.numel():
+            raise KernelError(f"attention_extend: out {tuple(out.shape)} or the block list do not fit")
+        self._check(self.lib.cima_attention_extend(
+            qkv.data_ptr(), qkv.shape[1], batch.q_tile_seq.data_ptr(), batch.q_tile_row0.data_ptr(),
+            batch.seq_first_row.data_ptr(), kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
+            kv.ring_pages, kv.page_size, batch.seq_slot.data_ptr(), batch.seq_len.data_ptr(), out.data_ptr(), out.shape[1],
+            T, batch.q_tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window, self._stream()), "attention_extend")
 
     def attention_prefill_tc(self, qkv: torch.Tensor, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
                              head_dim: int, scale: float, window: int) -> None:

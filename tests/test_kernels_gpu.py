@@ -184,7 +184,8 @@ def batch_of(seqs, device):
     for s in seqs:
         vt_col.append(cols)
         cols += -(-s[2] // 128) * 128
-    return SimpleNamespace(n_q_tiles=len(tiles) if all(s[1] == 0 for s in seqs) else 0,
+    tiles.sort(key=lambda x: -(seqs[x[0]][1] + x[1]))
+    return SimpleNamespace(n_q_tiles=len(tiles) if any(s[2] > 1 for s in seqs) else 0,
                            n_q_tiles_tc=len(tc), q_tile_tc_seq=t([x[0] for x in tc]), q_tile_tc_row0=t([x[1] for x in tc]),
                            seq_vt_col=t(vt_col), vt_cols=cols,
                            q_tile_seq=t([x[0] for x in tiles]), q_tile_row0=t([x[1] for x in tiles]),
@@ -407,6 +408,35 @@ def test_attention_prefill_tcgen05(K, lens, nh, nkv, window):
     K.attention_prefill_tc(qkv.cuda(), bg, out, nh, nkv, hd, scale, window)
     assert K.device_errors() == 0
     assert err(out, want) <= TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(6, 2, 48), (28, 4, 128), (4, 4, 16)])
+@pytest.mark.parametrize("window,ring", [(0, 0), (90, 0), (40, 2)])
+def test_attention_of_sequences_that_go_on(K, nh, nkv, hd, window, ring):
+    """Several query rows per sequence over the paged cache (the step's own keys are in the pages too) against the
+    float64 statement: a sequence deep into its cache, one that starts, one across a page's edge, one with more than
+    two blocks of rows; stale keys behind every sequence's end; a window, and a window through a ring of two pages."""
+    page = 64
+    seqs = [(2, 100, 64), (0, 0, 5), (3, 63, 2)] + ([] if ring else [(1, 500, 150)])
+    width = ring or 11
+    order = torch.randperm(4 * width, generator=torch.Generator().manual_seed(5)).tolist()
+    tables = {slot: order[slot * width:(slot + 1) * width] for slot in range(4)}
+    cpu, gpu = make_kv(4 * width, nkv, page, hd, 4, width, ring, window, torch.bfloat16, tables)
+    cpu.storage.copy_(g(*cpu.storage.shape, dtype=torch.bfloat16, seed=hd + window))
+    gpu.storage.copy_(cpu.storage)
+    T = sum(s[2] for s in seqs)
+    scale = 1.0 / math.sqrt(hd)
+    qkv = g(T, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, seed=nh + T)
+    bc, bg = batch_of(seqs, "cpu"), batch_of(seqs, "cuda")
+    want = torch.zeros(T, nh * hd, dtype=torch.float64)
+    REF.attention_plain(qkv, cpu, bc.row_pos, bc.row_seq, bc.seq_slot, bc.seq_first_row, want, nh, nkv, hd, scale, window, True)
+    out = torch.full((T, nh * hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.attention_extend(qkv.cuda(), gpu, bg, out, nh, nkv, hd, scale, window)
+    assert err(out, want) <= TOL["bfloat16"]
+    # the dispatcher takes the same kernel for such a batch
+    out2 = torch.full((T, nh * hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.attention(qkv.cuda(), gpu, bg, out2, nh, nkv, hd, scale, window, True)
+    assert torch.equal(out, out2)
 
 
 # ---------------------------------------------------------------------------- sampling
