@@ -214,3 +214,27 @@ def test_sequences_may_go_on_by_several_tokens(name, dtype):
         assert close(g_, plain_logits(name, q), TOL[dtype])
     m.cache.check()
     assert m.cache.slots.held == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,first_windowed", [(1, 0), (64, 1), (65, 2), (128, 0), (16, 3)])
+def test_windows_at_the_edges_of_pages(window, first_windowed, dtype, tmp_path):
+    """Windows of one key, of exactly one and two pages, and one key more than a page, on all layers or on the later
+    ones: whole, the last 150 tokens one by one, in pieces, and in a batch of unequal lengths."""
+    import cima_b200
+    from helpers import run_in_pieces
+    from cima_b200.engine import load_model
+    cfg = dict(TINY["C"], sliding_window=window, max_window_layers=first_windowed)
+    folder = str(tmp_path / "m")
+    cima_b200.write_random_model(folder, cfg, seed=1)
+    c, W = plain_load(folder)
+    toks = random_tokens(cfg["vocab_size"], 300, 5)
+    want = plain_forward(W, c, toks).float()
+    m = load_model(folder, dtype=dtype, max_tokens=2048, device="cuda:0", verbose=False)
+    assert close(run_whole(m, toks), want, TOL[dtype])
+    assert close(run_tail_one_by_one(m, toks, 150), want, TOL[dtype])
+    assert close(run_in_pieces(m, [toks], [[10, 100, 101, 250]])[0], want, TOL[dtype])
+    for got in run_batched(m, [toks, toks[:77], toks[:130]], [200, 1, 64]):
+        assert close(got, want[:got.shape[0]], TOL[dtype])
+    m.cache.check()
+    assert m.cache.slots.held == 0
