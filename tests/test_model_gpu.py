@@ -238,3 +238,33 @@ def test_windows_at_the_edges_of_pages(window, first_windowed, dtype, tmp_path):
         assert close(got, want[:got.shape[0]], TOL[dtype])
     m.cache.check()
     assert m.cache.slots.held == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,stored", [("B", "float32"), ("A", "float32"), ("C", "mixed")])
+def test_checkpoint_stored_in_32_bit(name, stored, dtype, tmp_path):
+    """A tensor stored in 32-bit stays 32-bit on both paths (on the bfloat16 path its products run through the plain
+    kernel with bfloat16 activations).  ``mixed``: every second matrix and all vectors in 32-bit, the rest bfloat16."""
+    import json
+    from safetensors.torch import load_file, save_file
+    from cima_b200.engine import load_model
+    src = model_folder(name)
+    tensors = load_file(f"{src}/model.safetensors")
+    out = {}
+    for i, (n, t) in enumerate(sorted(tensors.items())):
+        wide = stored == "float32" or t.dim() == 1 or i % 2 == 0
+        out[n] = t.float().contiguous() if wide else t.contiguous()
+    folder = tmp_path / "m"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(TINY[name]))
+    save_file(out, str(folder / "model.safetensors"))
+    c, W = plain_load(str(folder))
+    toks = random_tokens(TINY[name]["vocab_size"], 90, 7)
+    want = plain_forward(W, c, toks).float()
+    m = load_model(str(folder), dtype=dtype, max_tokens=1024, device="cuda:0", verbose=False)
+    kept = {t.dtype for b in m.blocks for t in (b.mixer.qkv.weight, b.mixer.out.weight)}
+    assert torch.float32 in kept
+    assert close(run_whole(m, toks), want, TOL[dtype])
+    assert close(run_tail_one_by_one(m, toks, 32), want, TOL[dtype])
+    for got in run_batched(m, [toks, toks[:17], toks[:50]], [60, 1, 40]):
+        assert close(got, want[:got.shape[0]], TOL[dtype])
