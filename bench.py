@@ -21,7 +21,6 @@ import statistics
 import subprocess
 import sys
 import threading
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -120,7 +119,7 @@ def main(argv=None) -> int:
     import torch
     import cima_b200
     from cima_b200.config import Qwen2Config
-    from cima_b200.engine import Model, ModelStepper, StepEntry
+    from cima_b200.engine import Model, StepEntry
     from cima_b200.kernels import Kernels
     from cima_b200.parts import Runtime
     from cima_b200.sampling import GenOptions, sampler_state

@@ -38,10 +38,6 @@ constexpr int THREADS = 192;
 
 enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3 };
 
-
-
-
-
 struct GemmArgs {
   int p_rows, q_rows, K;      // extents of P, Q and of the sum
   int up_offset;              // EPI_SWIGLU: row of Q where the "up" half starts
@@ -231,8 +227,6 @@ k_gemm_tcgen05(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------- host side
-
-
 
 int sm_count() {
   static int n = 0;

@@ -32,11 +32,6 @@ constexpr int THREADS = 192;
 
 enum { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_STORE_F32 = 3 };
 
-
-
-
-
-
 __device__ __forceinline__ unsigned cluster_addr(const void* p, unsigned rank) {      // address of p in block `rank`
   unsigned a = smem_u32(p), r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(rank));
@@ -240,9 +235,6 @@ k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
-
-
-
 
 int sm_count() {
   static int n = 0;

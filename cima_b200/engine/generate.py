@@ -15,7 +15,7 @@ reference's loop for one sequence (src/models/mod.rs:972-1405), applied to every
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional, Protocol, Sequence, Union
 
 from ..sampling.options import GenOptions

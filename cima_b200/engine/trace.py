@@ -19,7 +19,6 @@ import os
 import sys
 from typing import Dict
 
-import numpy as np
 
 from .batch import StepEntry
 from .model import load_model

@@ -9,8 +9,8 @@ ignore_eos (false).  A failed ``set`` leaves the options untouched.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field, replace
-from typing import List
+from dataclasses import dataclass, replace
+
 
 
 class OptionError(ValueError):
