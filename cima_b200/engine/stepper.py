@@ -57,7 +57,10 @@ class ModelStepper:
             graph = self._arm(slots, last_tokens, options)
             self.reserve_ahead(slots, 1)
             chosen = graph.run()
-            out = chosen.tolist()                    # the step's result crosses to the host here
+            view = self._pinned_view(len(slots))
+            view.copy_(chosen, non_blocking=True)    # the step's result crosses to the host here, into pinned memory
+            torch.cuda.current_stream().synchronize()
+            out = view.tolist()
             self._advance_lengths(slots, 1)
             self.d2h_bytes += 4 * len(slots)
             return out
@@ -82,11 +85,7 @@ class ModelStepper:
             return None
         cache.flush()
         chosen = graph.run()
-        i = self._pin_next
-        self._pin_next ^= 1
-        if self._pinned[i] is None or self._pinned[i].numel() < len(slots):
-            self._pinned[i] = torch.empty(max(64, len(slots)), dtype=torch.int32).pin_memory()
-        view = self._pinned[i][:len(slots)]
+        view = self._pinned_view(len(slots))
         view.copy_(chosen, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
@@ -94,6 +93,14 @@ class ModelStepper:
             self._inflight[s] = self._inflight.get(s, 0) + 1
         self.d2h_bytes += 4 * len(slots)
         return {"slots": slots, "graph": graph, "tokens": view, "event": ev, "fed": None}
+
+    def _pinned_view(self, n: int) -> torch.Tensor:
+        """One of two pinned buffers in turn (a step in flight keeps its own until it is read)."""
+        i = self._pin_next
+        self._pin_next ^= 1
+        if self._pinned[i] is None or self._pinned[i].numel() < n:
+            self._pinned[i] = torch.empty(max(64, n), dtype=torch.int32).pin_memory()
+        return self._pinned[i][:n]
 
     def _read(self, flight, commit_slots) -> List[int]:
         flight["event"].synchronize()
