@@ -1,4 +1,5 @@
-// Causal (and windowed) attention of ragged prompts on the fifth-generation tensor cores, head_dim 128.
+// Causal (and windowed) attention of ragged prompts on the fifth-generation tensor cores, head_dim 64 or 128
+// (whole 128-byte rows of 64 bfloat16 for the swizzled tiles).
 //
 // One block computes 128 query rows of one head.  Both products of a tile of 64 keys run as tcgen05.mma with
 // their results in tensor memory:
@@ -26,7 +27,6 @@ namespace {
 
 using namespace cima_tc;
 
-constexpr int HD = 128;            // head_dim of this kernel
 constexpr int BM = 128;            // query rows per block = TMEM lanes
 constexpr int BN = 64;             // keys per tile
 constexpr int UMMA_K = 16;
@@ -59,15 +59,18 @@ __device__ __forceinline__ void key_tiles(int q0, int len, int window, int& firs
   last = q_hi / BN;
 }
 
+template <int HD>
 __global__ void __launch_bounds__(THREADS, 2)
 k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_vt, AttnArgs a) {
   cima_pdl_wait();
   extern __shared__ __align__(1024) unsigned char smem[];      // tiles of 1024-byte groups: checked below
-  unsigned char* sq = smem;                                    // Q: 2 halves (dims 0..63, 64..127) of 16 KB
-  unsigned char* sk = sq + 2 * HALF_BYTES;                     // K: [2 stages][2 halves of 64 dims][64 keys]
-  unsigned char* sv = sk + 4 * KHALF_BYTES;                    // V^T: [2 stages][128 dims][64 keys]
-  unsigned char* sp = sv + 2 * HALF_BYTES;                     // P: [128 query rows][64 keys]
+  constexpr int NH = HD / 64;                                  // blocks of 64 dims in a row of Q or K
+  constexpr int V_BYTES = HD * 64 * 2;                         // V^T of a tile: [HD dims][64 keys]
+  unsigned char* sq = smem;                                    // Q: NH blocks (dims 0..63, 64..127) of 16 KB
+  unsigned char* sk = sq + NH * HALF_BYTES;                    // K: [2 stages][NH blocks of 64 dims][64 keys]
+  unsigned char* sv = sk + 2 * NH * KHALF_BYTES;               // V^T: [2 stages][HD dims][64 keys]
+  unsigned char* sp = sv + 2 * V_BYTES;                        // P: [128 query rows][64 keys]
   unsigned long long* bars = (unsigned long long*)(sp + HALF_BYTES);
   unsigned long long* q_full = bars;                           // [1]
   unsigned long long* k_full = bars + 1;                       // [2]
@@ -117,23 +120,24 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
   if (warp == 4) {
     // ---------------------------------------------------------------- TMA producers: lane 0 Q and K, lane 1 V
     if (lane == 0) {
-      mbar_expect_tx(q_full, 2 * HALF_BYTES);
-      tma_load_2d(sq, &map_qkv, h * HD, row_base + q0, q_full);
-      tma_load_2d(sq + HALF_BYTES, &map_qkv, h * HD + 64, row_base + q0, q_full);
+      mbar_expect_tx(q_full, NH * HALF_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < NH; kb++) tma_load_2d(sq + (size_t)kb * HALF_BYTES, &map_qkv, h * HD + 64 * kb, row_base + q0, q_full);
       for (int j = 0; j < n; j++) {
         const int s = j & 1, k0 = (first + j) * BN;
         if (j >= 2 && !mbar_wait(&k_empty[s], ((j >> 1) - 1) & 1, a.error_flag, abort_flag)) break;
-        mbar_expect_tx(&k_full[s], 2 * KHALF_BYTES);
-        tma_load_2d(sk + (size_t)(2 * s) * KHALF_BYTES, &map_k, (a.nh + kvh) * HD, row_base + k0, &k_full[s]);
-        tma_load_2d(sk + (size_t)(2 * s + 1) * KHALF_BYTES, &map_k, (a.nh + kvh) * HD + 64, row_base + k0, &k_full[s]);
+        mbar_expect_tx(&k_full[s], NH * KHALF_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < NH; kb++)
+          tma_load_2d(sk + (size_t)(NH * s + kb) * KHALF_BYTES, &map_k, (a.nh + kvh) * HD + 64 * kb, row_base + k0, &k_full[s]);
       }
     } else if (lane == 1) {
       const int col0 = a.seq_vt_col[seq];
       for (int j = 0; j < n; j++) {
         const int s = j & 1, k0 = (first + j) * BN;
         if (j >= 2 && !mbar_wait(&v_empty[s], ((j >> 1) - 1) & 1, a.error_flag, abort_flag)) break;
-        mbar_expect_tx(&v_full[s], HALF_BYTES);
-        tma_load_2d(sv + (size_t)s * HALF_BYTES, &map_vt, col0 + k0, kvh * HD, &v_full[s]);
+        mbar_expect_tx(&v_full[s], V_BYTES);
+        tma_load_2d(sv + (size_t)s * V_BYTES, &map_vt, col0 + k0, kvh * HD, &v_full[s]);
       }
     }
   } else if (warp == 5) {
@@ -143,9 +147,9 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
       auto issue_s = [&](int j) {                       // S(j) = Q K(j)^T into buffer j & 1
         const int s = j & 1;
 #pragma unroll
-        for (int kb = 0; kb < 2; kb++) {
+        for (int kb = 0; kb < NH; kb++) {
           const unsigned long long qd = umma_smem_desc(smem_u32(sq + (size_t)kb * HALF_BYTES));
-          const unsigned long long kd = umma_smem_desc(smem_u32(sk + (size_t)(2 * s + kb) * KHALF_BYTES));
+          const unsigned long long kd = umma_smem_desc(smem_u32(sk + (size_t)(NH * s + kb) * KHALF_BYTES));
 #pragma unroll
           for (int k = 0; k < 64 / UMMA_K; k++)
             umma_bf16(tm_s[s], qd + (unsigned long long)(k * 2), kd + (unsigned long long)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
@@ -173,7 +177,7 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
         const int s = j & 1;
         {                                               // O += P V(j): 64 keys
           const unsigned long long pd = umma_smem_desc(smem_u32(sp));
-          const unsigned long long vd = umma_smem_desc(smem_u32(sv + (size_t)s * HALF_BYTES));
+          const unsigned long long vd = umma_smem_desc(smem_u32(sv + (size_t)s * V_BYTES));
 #pragma unroll
           for (int k = 0; k < BN / UMMA_K; k++)
             umma_bf16(tm_o, pd + (unsigned long long)(k * 2), vd + (unsigned long long)(k * 2), idesc_o, (j | k) ? 1u : 0u);
@@ -257,7 +261,7 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < 4; c++) {
+          for (int c = 0; c < HD / 32; c++) {
             float o[32];
             tmem_ld32(tm_o + lane_off + (unsigned)(c * 32), o);
 #pragma unroll
@@ -289,7 +293,7 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       __nv_bfloat16* dst = a.out + (size_t)(row_base + pos) * a.ldo + (size_t)h * HD;
 #pragma unroll 1
-      for (int c = 0; c < 4; c++) {
+      for (int c = 0; c < HD / 32; c++) {
         float o[32];
         tmem_ld32(tm_o + lane_off + (unsigned)(c * 32), o);
         if (pos < len) {
@@ -313,9 +317,10 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
   }
 }
 
-// V of a step's rows, transposed for the kernel above: vt[kvh * 128 + d][seq_vt_col[seq] + key] = v[key][d];
+// V of a step's rows, transposed for the kernel above: vt[kvh * HD + d][seq_vt_col[seq] + key] = v[key][d];
 // keys from a sequence's end to the next multiple of 128 are zero (P is zero there, and zero times what an
 // uninitialised buffer may hold need not be zero).  One block per (block of 128 keys, kv head).
+template <int HD>
 __global__ void __launch_bounds__(256)
 k_transpose_v(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ tile_seq,
               const int* __restrict__ tile_row0, const int* __restrict__ seq_first_row,
@@ -344,43 +349,53 @@ k_transpose_v(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __restri
   }
 }
 
+template <int HD>
+int launch_attention_tc(const void* qkv, int ld, const int* tile_seq, const int* tile_row0, const int* seq_first_row,
+                        const int* seq_vt_col, void* vt, int vt_cols, void* out, int ldo, int T, int n_tiles, int nh,
+                        int nkv, float scale, int window, int* error_flag, cudaStream_t stream) {
+  CUtensorMap mq, mk, mv;
+  int rc = make_map(&mq, qkv, T, (long long)(nh + 2 * nkv) * HD, ld);
+  if (rc) return rc;
+  rc = make_map(&mk, qkv, T, (long long)(nh + 2 * nkv) * HD, ld, BN);
+  if (rc) return rc;
+  rc = make_map(&mv, vt, (long long)nkv * HD, vt_cols, vt_cols, HD);
+  if (rc) return rc;
+  { int rc_ = cima_launch(k_transpose_v<HD>, dim3(n_tiles, nkv), dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)qkv, ld, tile_seq, tile_row0, seq_first_row, seq_vt_col, (__nv_bfloat16*)vt, vt_cols, nh, nkv); if (rc_) return rc_; }
+  rc = cima_launch_result();
+  if (rc) return rc;
+  constexpr int NH = HD / 64;
+  const size_t smem = NH * (size_t)HALF_BYTES + 2 * NH * (size_t)KHALF_BYTES + 2 * (size_t)HD * 128 + HALF_BYTES + 16 * 8 + 16;
+  static_assert(15 * 8 + 8 <= 16 * 8 + 16, "barriers and flags fit their place");
+  static bool raised = false;
+  if (!raised) {
+    cudaError_t e = cudaFuncSetAttribute(k_attention_prefill_tc<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cima_fail((int)e, "attention_prefill_tc: cannot raise shared memory to %zu bytes: %s", smem, cudaGetErrorString(e));
+    raised = true;
+  }
+  AttnArgs a{tile_seq, tile_row0, seq_first_row, seq_vt_col, (__nv_bfloat16*)out, ldo, nh, nkv, window, scale, error_flag};
+  { int rc_ = cima_launch(k_attention_prefill_tc<HD>, dim3(n_tiles, nh), dim3(THREADS), smem, stream, 1, mq, mk, mv, a); if (rc_) return rc_; }
+  return cima_launch_result();
+}
+
 }  // namespace
 
 // qkv [T, ld] bf16: q heads, k heads, v heads of each row, q and k already rotated.  tile_seq / tile_row0: the
 // blocks of 128 query rows, heaviest first.  seq_vt_col [seqs]: first column of each sequence in vt (a multiple
-// of 128); vt [nkv * 128, vt_cols] bf16 is scratch that this call fills (V transposed).  out [T, ldo].
-// head_dim is 128.  error_flag: device int that a wait that ran out sets to 1 (never cleared here).
+// of 128); vt [nkv * head_dim, vt_cols] bf16 is scratch that this call fills (V transposed).  out [T, ldo].
+// head_dim is 64 or 128.  error_flag: device int that a wait that ran out sets to 1 (never cleared here).
 extern "C" int cima_attention_prefill_tc(const void* qkv, int ld, const int* tile_seq, const int* tile_row0,
                                          const int* seq_first_row, const int* seq_vt_col, void* vt, int vt_cols,
                                          void* out, int ldo, int T, int n_tiles, int nh, int nkv, int hd, float scale,
                                          int window, int* error_flag, cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return 0;
-  if (hd != HD) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: head_dim %d; this kernel takes 128", hd);
+  if (hd != 64 && hd != 128) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: head_dim %d; this kernel takes 64 or 128", hd);
   if (nh <= 0 || nkv <= 0 || nh % nkv) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: %d heads are not a multiple of %d kv heads", nh, nkv);
   if (ld % 8 || ldo % 8 || vt_cols % 128 || vt_cols <= 0) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: row strides (%d, %d) must be multiples of 8 and the transposed V's columns (%d) of 128", ld, ldo, vt_cols);
   if (ld < (nh + 2 * nkv) * hd) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: row stride %d is smaller than (heads + 2 kv heads) * head_dim", ld);
   if ((((uintptr_t)qkv | (uintptr_t)vt | (uintptr_t)out) & 15)) return cima_fail(CIMA_E_ARG, "attention_prefill_tc: qkv, vt and out must be 16-byte aligned");
   if (!error_flag) return cima_fail(CIMA_E_ARG, "attention_prefill_tc: an error flag on the device is needed");
   if (nh > 65535 || nkv > 65535) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: %d heads exceed one launch", nh);
-  CUtensorMap mq, mk, mv;
-  int rc = make_map(&mq, qkv, T, (long long)(nh + 2 * nkv) * hd, ld);
-  if (rc) return rc;
-  rc = make_map(&mk, qkv, T, (long long)(nh + 2 * nkv) * hd, ld, BN);
-  if (rc) return rc;
-  rc = make_map(&mv, vt, (long long)nkv * hd, vt_cols, vt_cols);
-  if (rc) return rc;
-  { int rc_ = cima_launch(k_transpose_v, dim3(n_tiles, nkv), dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)qkv, ld, tile_seq, tile_row0, seq_first_row, seq_vt_col, (__nv_bfloat16*)vt, vt_cols, nh, nkv); if (rc_) return rc_; }
-  rc = cima_launch_result();
-  if (rc) return rc;
-  const size_t smem = 2 * (size_t)HALF_BYTES + 4 * (size_t)KHALF_BYTES + 2 * (size_t)HALF_BYTES + HALF_BYTES + 16 * 8 + 16;
-  static_assert(15 * 8 + 8 <= 16 * 8 + 16, "barriers and flags fit their place");
-  static bool raised = false;
-  if (!raised) {
-    cudaError_t e = cudaFuncSetAttribute(k_attention_prefill_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return cima_fail((int)e, "attention_prefill_tc: cannot raise shared memory to %zu bytes: %s", smem, cudaGetErrorString(e));
-    raised = true;
-  }
-  AttnArgs a{tile_seq, tile_row0, seq_first_row, seq_vt_col, (__nv_bfloat16*)out, ldo, nh, nkv, window, scale, error_flag};
-  { int rc_ = cima_launch(k_attention_prefill_tc, dim3(n_tiles, nh), dim3(THREADS), smem, stream, 1, mq, mk, mv, a); if (rc_) return rc_; }
-  return cima_launch_result();
+  if (hd == 64)
+    return launch_attention_tc<64>(qkv, ld, tile_seq, tile_row0, seq_first_row, seq_vt_col, vt, vt_cols, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
+  return launch_attention_tc<128>(qkv, ld, tile_seq, tile_row0, seq_first_row, seq_vt_col, vt, vt_cols, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
 }

@@ -17,7 +17,7 @@ from .csrc.build import BuildError, library_path
 F32, BF16 = 0, 1
 ABI_VERSION = 16
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
-TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 128)
+TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
 
 # epilogues of the skinny product
@@ -410,7 +410,7 @@ class Kernels:
         if (from_cache and qkv.dtype is torch.bfloat16 and kv.page_size == 64 and head_dim % 16 == 0
                 and head_dim <= 128 and qkv.shape[1] % 8 == 0 and getattr(batch, "n_q_tiles", 0) > 0):
             return self.attention_extend(qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window)
-        if (not from_cache and qkv.dtype is torch.bfloat16 and head_dim == 128 and qkv.shape[1] % 8 == 0
+        if (not from_cache and qkv.dtype is torch.bfloat16 and head_dim in (64, 128) and qkv.shape[1] % 8 == 0
                 and getattr(batch, "n_q_tiles_tc", 0) > 0 and batch.max_len >= TC_ATTENTION_MIN_LEN):
             return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window)
         if (not from_cache and qkv.dtype is torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128
@@ -454,7 +454,7 @@ class Kernels:
     def attention_prefill_tc(self, qkv: torch.Tensor, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
                              head_dim: int, scale: float, window: int) -> None:
         """Flash attention of ragged prompts that start at position 0 on the tcgen05 tensor cores (bf16,
-        head_dim 128): blocks of 128 query rows, both products with their results in tensor memory.  ``batch``
+        head_dim 64 or 128): blocks of 128 query rows, both products with their results in tensor memory.  ``batch``
         brings the blocks (``q_tile_tc_*``) and each sequence's first column in the transposed V (``seq_vt_col``,
         ``vt_cols``), which this call makes in its own scratch."""
         self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)

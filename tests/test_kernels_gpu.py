@@ -390,10 +390,10 @@ def test_attention_prefill_over_the_step(K, dtype, nh, nkv, hd, window):
 
 @pytest.mark.parametrize("lens", [[130, 1, 67, 300], [128], [1], [257, 256, 255], [700, 40]])
 @pytest.mark.parametrize("nh,nkv,window", [(7, 1, 0), (4, 2, 0), (28, 4, 0), (4, 2, 50), (2, 2, 200), (3, 1, 128), (2, 1, 1)])
-def test_attention_prefill_tcgen05(K, lens, nh, nkv, window):
-    """The tcgen05 attention of ragged prompts (head_dim 128) against the float64 statement: sequences that
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attention_prefill_tcgen05(K, lens, nh, nkv, window, hd):
+    """The tcgen05 attention of ragged prompts (head_dim 64 and 128) against the float64 statement: sequences that
     end inside a block of 128, a far key that stands out, windows with edges inside and between tiles."""
-    hd = 128
     seqs = [(i, 0, n) for i, n in enumerate(lens)]
     T = sum(lens)
     scale = 1.0 / math.sqrt(hd)
