@@ -268,3 +268,20 @@ def test_checkpoint_stored_in_32_bit(name, stored, dtype, tmp_path):
     assert close(run_tail_one_by_one(m, toks, 32), want, TOL[dtype])
     for got in run_batched(m, [toks, toks[:17], toks[:50]], [60, 1, 40]):
         assert close(got, want[:got.shape[0]], TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompts_at_head_size_64(dtype, tmp_path):
+    """Prompts past 256 tokens at head_dim 64 (in bfloat16 the tcgen05 attention serves them): two ragged prompts in
+    one step, then tokens one by one."""
+    import cima_b200
+    from cima_b200.engine import load_model
+    cfg = dict(TINY["B"], max_position_embeddings=1024, num_attention_heads=4, num_key_value_heads=2, hidden_size=256)
+    folder = str(tmp_path / "m")
+    cima_b200.write_random_model(folder, cfg, seed=2)
+    c, W = plain_load(folder)
+    seqs = [random_tokens(cfg["vocab_size"], n, seed=n) for n in (420, 300)]
+    m = load_model(folder, dtype=dtype, max_tokens=2048, device="cuda:0", verbose=False)
+    got = run_batched(m, seqs, [400, 290])
+    for q, g_ in zip(seqs, got):
+        assert close(g_, plain_forward(W, c, q).float(), TOL[dtype])
