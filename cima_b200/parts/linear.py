@@ -150,6 +150,16 @@ class GatedLinearPair:
     def nbytes(self) -> int:
         return self.lin.nbytes()
 
+    def _gated_on_tcgen05(self, rows: int) -> bool:
+        """Whether the tcgen05 product with the fused activation beats the library product plus the activation
+        kernel.  With a short sum the tile's epilogue (256 x 256 accumulators through the activation) outlasts
+        its main loop: measured at 2,048 rows, K 896 / 1,536 / 2,048 / 3,584: 55 / 93 / 136 / 366 us against
+        41 / 96 / 147 / 385; at 512 rows 31 / 36 / 54 / 101 against 17 / 32 / 52 / 105."""
+        K = self.lin.K
+        if K % 8 or K < 1536:
+            return False
+        return rows >= (TCGEN05_ROWS if K >= 3072 else 1024)
+
     def activated(self, a) -> torch.Tensor:
         """silu(a Wg^T) * (a Wu^T) in the activation dtype, [M, I]."""
         K_ = self.rt.kernels
@@ -164,8 +174,8 @@ class GatedLinearPair:
             a = a.tensor()
         if self.lin._skinny(M):
             K_.linear_skinny(a, self.lin.weight, None, out, SK_SWIGLU)
-        elif (not self.lin._plain()) and M >= TCGEN05_ROWS and self.lin.K % 8 == 0 and hasattr(K_, "gemm_tc"):
-            # many rows: the tcgen05 product with the activation in its epilogue (measured 373 us against 350 + 48 us
+        elif (not self.lin._plain()) and self._gated_on_tcgen05(M) and hasattr(K_, "gemm_tc"):
+            # many rows: the tcgen05 product with the activation in its epilogue (measured 366 us against 385 us
             # for the library product followed by the activation kernel at 2,048 x 37,888 x 3,584, and without the
             # [rows, 2I] intermediate)
             if hasattr(K_, "gemm_tc_pair"):
