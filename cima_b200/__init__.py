@@ -25,10 +25,10 @@ __version__ = "0.1.0"
 class LM:
     """A loaded model with its cache, stepper and generation loop."""
 
-    def __init__(self, model, eos_ids: Sequence[int] = (), max_batch: int = 64, pipeline: bool = True):
+    def __init__(self, model, eos_ids: Sequence[int] = (), max_batch: int = 64, pipeline: bool = True, retain: int = 0):
         from .engine import GenerationLoop, ModelStepper
         self.model = model
-        self.stepper = ModelStepper(model, max_batch=max_batch, pipeline=pipeline)
+        self.stepper = ModelStepper(model, max_batch=max_batch, pipeline=pipeline, retain=retain)
         self.loop = GenerationLoop(self.stepper, eos_ids)
 
     @property
@@ -88,12 +88,15 @@ def eos_ids_of(folder: str) -> List[int]:
 
 
 def load(folder: str, dtype: str = "bfloat16", max_tokens: int = 8192, max_seqs: Optional[int] = None,
-         max_batch: int = 64, device: str = "cuda:0", verbose: bool = True, pipeline: bool = True) -> LM:
+         max_batch: int = 64, device: str = "cuda:0", verbose: bool = True, pipeline: bool = True,
+         retain: int = 0) -> LM:
     """``pipeline``: queue the next decode step before the host has read the current one's tokens
-    (the tokens are fed forward on the device)."""
+    (the tokens are fed forward on the device).  ``retain``: how many finished sequences stay in the cache for
+    later prompts that begin with the same tokens (the next turn of a conversation runs only what is new; the
+    reference keeps its one sequence so, src/models/mod.rs:1022-1058); they give way when a batch needs the room."""
     from .engine import load_model
     model = load_model(folder, dtype=dtype, max_tokens=max_tokens, max_seqs=max_seqs, device=device, verbose=verbose)
-    return LM(model, eos_ids_of(folder), max_batch=max_batch, pipeline=pipeline)
+    return LM(model, eos_ids_of(folder), max_batch=max_batch, pipeline=pipeline, retain=retain)
 
 
 def write_random_model(folder: str, config: Union[dict, Qwen2Config], seed: int = 0) -> None:

@@ -144,6 +144,7 @@ class KVCache:
         self.groups: List[KVGroup] = []
         self._layer_group: Dict[int, Tuple[int, int]] = {}
         self.state: Dict[str, torch.Tensor] = {}
+        self.has_mixer_state = False      # a mixer keeps state of fixed size per sequence (it cannot be rewound)
         shares = dict(shares or {})
         by_key: Dict[KVRequest, List[int]] = {}
         for layer, reqs in enumerate(requests):
@@ -154,6 +155,7 @@ class KVCache:
                     by_key.setdefault(r, []).append(layer)
                 elif isinstance(r, StateRequest):
                     self._add_state(r)
+                    self.has_mixer_state = True
                 else:
                     raise TypeError(f"layer {layer}: unknown cache request {r!r}")
         for r in extra_state:
@@ -237,6 +239,31 @@ class KVCache:
 
     def length(self, slot: int) -> int:
         return int(self.lengths[slot])
+
+    def can_rewind(self, slot: int, length: int) -> bool:
+        """Whether ``slot`` may go back to its first ``length`` positions and go on from there.  Always to where it
+        is; further back only if every group keeps all keys (a ring has overwritten old ones) and no mixer keeps
+        state of its own (which belongs to the sequence's end)."""
+        held = int(self.lengths[slot])
+        if length == held:
+            return True
+        return 0 <= length < held and not self.has_mixer_state and not any(g.ring_pages for g in self.groups)
+
+    def rewind(self, slot: int, length: int) -> None:
+        """Forget the positions from ``length`` on (their pages stay with the slot and are written again)."""
+        if not self.slots.is_held(slot):
+            raise ValueError(f"slot {slot} is not open")
+        if not self.can_rewind(slot, length):
+            raise ValueError(f"slot {slot} holds {int(self.lengths[slot])} positions and cannot go back to {length}")
+        self.lengths[slot] = length
+
+    def free_tokens(self) -> int:
+        """Positions that the free pages could still hold (the scarcest group decides)."""
+        return min((g.pool.free for g in self.groups), default=self.n_pages) * self.page_size
+
+    def held_tokens(self, slot: int) -> int:
+        """Positions that the pages of ``slot`` hold room for (the group with the fewest pages decides)."""
+        return min((len(g.pages_of[slot]) for g in self.groups), default=0) * self.page_size
 
     def close(self, slots: Sequence[int]) -> None:
         """Give the slots and their pages back; later sequences use them again."""

@@ -37,6 +37,7 @@ class GenStats:
     prompt_tokens: int = 0
     gen_tokens: int = 0
     batches: int = 0
+    reused_tokens: int = 0            # prompt tokens that were not run: their keys were still in the cache
     prefill_s: float = 0.0
     decode_s: float = 0.0
     decode_steps: int = 0
@@ -123,16 +124,29 @@ class GenerationLoop:
 
     def _run_batch(self, ids, fitted, budgets, opts, results) -> None:
         st = self.stepper
-        slots = st.open(len(ids))
+        prompts = [fitted[i][0] for i in ids]
+        # a stepper that keeps finished sequences offers them to prompts that begin alike
+        keeps = getattr(st, "retain_limit", 0) > 0
+        taken = st.adopt(prompts) if keeps else [(None, 0)] * len(ids)
+        reused = [n for _, n in taken]
+        slots: List[int] = [s for s, _ in taken if s is not None]
+        done = False
         try:
+            if keeps:
+                st.make_room([len(p) + budgets[i] for p, i in zip(prompts, ids)], [s for s, _ in taken])
+            fresh = iter(st.open(sum(1 for s, _ in taken if s is None)))
+            slots = [s if s is not None else next(fresh) for s, _ in taken]
             self.stats.batches += 1
-            prompts = [fitted[i][0] for i in ids]
             stops = [set(self.eos_ids) | set(opts[i].stop) for i in ids]
             out: List[List[int]] = [[] for _ in ids]
             t0 = time.perf_counter()
-            tokens = st.prefill(slots, prompts, [opts[i] for i in ids])
+            if any(reused):
+                tokens = st.prefill(slots, prompts, [opts[i] for i in ids], reused=reused)
+            else:
+                tokens = st.prefill(slots, prompts, [opts[i] for i in ids])
             self.stats.prefill_s += time.perf_counter() - t0
             self.stats.prompt_tokens += sum(len(p) for p in prompts)
+            self.stats.reused_tokens += sum(reused)
             live = list(range(len(ids)))
             while True:
                 nxt = []
@@ -154,5 +168,9 @@ class GenerationLoop:
                 self.stats.decode_s += time.perf_counter() - t0
                 self.stats.decode_steps += 1
             self.stats.gen_tokens += sum(len(o) for o in out)
+            if keeps:
+                st.retain(slots, [list(p) + o for p, o in zip(prompts, out)])
+                done = True
         finally:
-            st.close(slots)
+            if not done:
+                st.close(slots)

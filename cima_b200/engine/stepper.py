@@ -2,7 +2,8 @@
 device sampler on the wanted logits; tokens cross to the host once per step."""
 from __future__ import annotations
 
-from typing import List, Sequence
+from collections import OrderedDict
+from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -14,10 +15,19 @@ from ..sampling.sampler import DeviceSampler
 from .batch import StepEntry
 
 
+MIN_REUSE = 16     # a finished sequence is taken up again only for at least this many tokens in common
+
+
 class ModelStepper:
-    def __init__(self, model, max_batch: int = 64, use_graphs: bool = True, pipeline: bool = True):
+    def __init__(self, model, max_batch: int = 64, use_graphs: bool = True, pipeline: bool = True, retain: int = 0):
         self.model = model
         self.pipeline = pipeline
+        # Finished sequences whose keys and values stay in the cache (slot -> the tokens they stand for), newest
+        # last, at most ``retain`` of them: a later prompt that begins with the same tokens goes on from there and
+        # runs only what is new.  The reference keeps its one sequence so (session_ids and the incremental prefill,
+        # src/models/mod.rs:1022-1058).
+        self.retain_limit = max(0, int(retain))
+        self._retained: "OrderedDict[int, List[int]]" = OrderedDict()
         self._flight = None           # the decode step that is queued but not yet read
         self._inflight = {}           # slot -> steps queued beyond the committed length
         self._pinned = [None, None]
@@ -35,19 +45,91 @@ class ModelStepper:
         self.d2h_bytes = 0
 
     def open(self, count: int) -> List[int]:
-        return self.model.cache.open(count)
+        cache = self.model.cache
+        while cache.slots.free < count and self._retained:
+            self._evict_oldest()
+        return cache.open(count)
 
     def close(self, slots: Sequence[int]) -> None:
         self._drain()
         self._armed = None
         self.model.cache.close(slots)
 
-    def prefill(self, slots, prompts, options) -> List[int]:
+    # ------------------------------------------------------------------ finished sequences kept for later prompts
+    def _evict_oldest(self) -> None:
+        slot, _ = self._retained.popitem(last=False)
+        self.model.cache.close([slot])
+
+    def adopt(self, prompts: Sequence[Sequence[int]]) -> List[Tuple[Optional[int], int]]:
+        """For each prompt (slot, n): a kept sequence whose first n tokens are the prompt's (n >= MIN_REUSE, n <
+        len(prompt) so that one token is left to run, and the cache can go back to n), taken out of the kept set;
+        (None, 0) where there is none.  Longest match first come, first served."""
+        cache = self.model.cache
+        out: List[Tuple[Optional[int], int]] = []
+        for p in prompts:
+            best, best_n = None, 0
+            for slot, held in self._retained.items():
+                cap = min(len(held), len(p) - 1)
+                n = 0
+                while n < cap and held[n] == p[n]:
+                    n += 1
+                if n >= MIN_REUSE and n > best_n and cache.can_rewind(slot, n):
+                    best, best_n = slot, n
+            if best is not None:
+                del self._retained[best]
+            out.append((best, best_n))
+        return out
+
+    def make_room(self, needs: Sequence[int], slots: Sequence[Optional[int]]) -> None:
+        """Give kept sequences up, oldest first, until the batch fits the cache: sequence i may come to hold
+        ``needs[i]`` positions and goes on in ``slots[i]`` (None: a slot yet to be opened)."""
+        cache = self.model.cache
+        page = cache.page_size
+        want = 0
+        for need, slot in zip(needs, slots):
+            pages = -(-need // page) * page
+            want += pages if slot is None else max(0, pages - cache.held_tokens(slot))
+        while self._retained and cache.free_tokens() < want:
+            self._evict_oldest()
+
+    def retain(self, slots: Sequence[int], histories: Sequence[Sequence[int]]) -> None:
+        """Instead of ``close``: keep these finished sequences (``histories``: prompt and answer) for later prompts,
+        the newest ``retain_limit`` of them; the rest is closed."""
+        self._drain()
+        self._armed = None
+        cache = self.model.cache
+        for slot, h in zip(slots, histories):
+            n = cache.length(slot)                  # positions whose keys are in the cache: the last token was never fed
+            self._retained[slot] = list(h[:n])
+        while len(self._retained) > self.retain_limit:
+            self._evict_oldest()
+
+    def drop_retained(self) -> None:
+        while self._retained:
+            self._evict_oldest()
+
+    def prefill(self, slots, prompts, options, reused: Optional[Sequence[int]] = None) -> List[int]:
+        """The prompts' step.  ``reused[i]`` > 0: slot i already holds that many of prompt i's tokens (``adopt``)."""
         self._drain()
         self._armed = None
         self.sampler.begin(slots, prompts, options)
-        entries = [StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)]
-        return self._choose(self.model.step(entries), slots, options, sum(len(p) for p in prompts))
+        reused = list(reused) if reused is not None else [0] * len(slots)
+        cache = self.model.cache
+        for s, n in zip(slots, reused):
+            if n:
+                cache.rewind(s, n)
+        out: List[Optional[int]] = [None] * len(slots)
+        # sequences that start run as one prompt step (attention over the step's own keys), those that go on as
+        # another (rows that read the cache)
+        for group in ([i for i, n in enumerate(reused) if not n], [i for i, n in enumerate(reused) if n]):
+            if not group:
+                continue
+            entries = [StepEntry(slots[i], prompts[i][reused[i]:], [len(prompts[i]) - reused[i] - 1]) for i in group]
+            toks = self._choose(self.model.step(entries), [slots[i] for i in group], [options[i] for i in group],
+                                sum(len(e.tokens) for e in entries))
+            for i, t in zip(group, toks):
+                out[i] = t
+        return out  # type: ignore[return-value]
 
     def decode(self, slots, last_tokens, options) -> List[int]:
         if not self.use_graphs:

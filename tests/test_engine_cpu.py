@@ -113,3 +113,61 @@ def test_a_checkpoint_without_a_head_uses_the_table(tmp_path, capsys):
     assert torch.allclose(got, plain_forward(W, c, toks).float(), atol=2e-4, rtol=1e-4)
     head = plain_forward(dict(W, **{"model.embed_tokens.weight": W["model.embed_tokens.weight"]}), dict(c, tie_word_embeddings=False), toks)
     assert not torch.allclose(got, head.float(), atol=1e-2)   # the stored head was not used
+
+
+def _lm(name, retain, max_tokens=1024, **kw):
+    import cima_b200
+    return cima_b200.LM(cpu_model(name, max_tokens=max_tokens, **kw), retain=retain, pipeline=False)
+
+
+@pytest.mark.parametrize("opts", [dict(temperature=0, repeat_penalty=1.0), dict(temperature=0.9, top_k=20, seed=7)])
+def test_finished_sequences_are_taken_up_again(opts):
+    """With ``retain`` a finished sequence stays in the cache; a prompt that begins with its tokens runs only what is
+    new, and the answers are those of a model that runs everything (src/models/mod.rs:1022-1058 does so for its
+    one sequence)."""
+    V = TINY["B"]["vocab_size"]
+    lm, plain = _lm("B", retain=2), _lm("B", retain=0)
+    p1 = random_tokens(V, 40, 1)
+    r1 = lm.generate([p1], max_tokens=8, **opts)[0]
+    assert lm.stats.reused_tokens == 0 and lm.model.cache.slots.held == 1
+    # the next turn: everything so far and something new
+    p2 = p1 + r1.tokens + random_tokens(V, 10, 2)
+    r2 = lm.generate([p2], max_tokens=8, **opts)[0]
+    assert lm.stats.reused_tokens == len(p1) + len(r1.tokens) - 1        # the last token of the answer was never run
+    assert r2.tokens == plain.generate([p2], max_tokens=8, **opts)[0].tokens
+    # a prompt that shares only the first 30 tokens: the sequence goes back to there
+    p3 = p2[:30] + random_tokens(V, 25, 3)
+    # ... beside one that shares nothing and one that is all old but for its last token
+    p4, p5 = random_tokens(V, 33, 4), p1[:20]
+    got = lm.generate([p3, p4, p5], max_tokens=6, **opts)
+    assert lm.stats.reused_tokens == 30                                   # p5 found its sequence taken by p3
+    want = plain.generate([p3, p4, p5], max_tokens=6, **opts)
+    assert [g.tokens for g in got] == [w.tokens for w in want]
+    assert lm.model.cache.slots.held == 2                                 # the newest two stay
+    lm.model.cache.check()
+    lm.stepper.drop_retained()
+    assert lm.model.cache.slots.held == 0
+    lm.model.cache.check()
+
+
+def test_kept_sequences_give_way_and_rings_do_not_go_back():
+    V = TINY["C"]["vocab_size"]
+    opts = dict(temperature=0, repeat_penalty=1.0)
+    # C's later layers keep a ring for their window: a sequence is taken up only where it ended
+    lm, plain = _lm("C", retain=4, max_tokens=512), _lm("C", retain=0, max_tokens=512)
+    p1 = random_tokens(V, 100, 1)
+    r1 = lm.generate([p1], max_tokens=5, **opts)[0]
+    p2 = p1 + r1.tokens[:-1] + random_tokens(V, 80, 2)                    # goes on where the cache ends
+    r2 = lm.generate([p2], max_tokens=5, **opts)[0]
+    assert lm.stats.reused_tokens == 104
+    assert r2.tokens == plain.generate([p2], max_tokens=5, **opts)[0].tokens
+    p3 = p2[:50] + random_tokens(V, 20, 3)                                # would have to go back: runs whole
+    r3 = lm.generate([p3], max_tokens=5, **opts)[0]
+    assert lm.stats.reused_tokens == 0
+    assert r3.tokens == plain.generate([p3], max_tokens=5, **opts)[0].tokens
+    # the cache holds 512 positions; the kept sequences (189 and 75 positions: 3 + 2 pages) give way to a batch of 448
+    big = [random_tokens(V, 200, 10 + i) for i in range(2)]
+    got = lm.generate(big, max_tokens=20, **opts)
+    assert [g.tokens for g in got] == [w.tokens for w in plain.generate(big, max_tokens=20, **opts)]
+    lm.model.cache.check()
+    assert lm.model.cache.slots.held == 2

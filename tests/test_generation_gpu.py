@@ -195,3 +195,30 @@ def test_pipelined_and_plain_decoding_give_the_same_tokens():
         lm.model.cache.check()
         assert lm.model.cache.slots.held == 0
     assert outs[0] == outs[1]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("pipeline", [True, False])
+def test_finished_sequences_are_taken_up_again(dtype, pipeline):
+    """``retain``: the next turn of a conversation runs only its new tokens (decoding through graphs, with and
+    without run-ahead); the answers are those of a model that runs everything."""
+    V = TINY["B"]["vocab_size"]
+    opts = dict(temperature=0, repeat_penalty=1.0)
+    lm = cima_b200.load(model_folder("B"), dtype=dtype, max_tokens=1024, verbose=False, retain=2, pipeline=pipeline)
+    plain = cima_b200.load(model_folder("B"), dtype=dtype, max_tokens=1024, verbose=False, pipeline=pipeline)
+    p1 = random_tokens(V, 40, 1)
+    r1 = lm.generate([p1], max_tokens=12, **opts)[0]
+    assert r1.tokens == plain.generate([p1], max_tokens=12, **opts)[0].tokens
+    p2 = p1 + r1.tokens + random_tokens(V, 10, 2)
+    q2 = random_tokens(V, 21, 9)
+    r2 = lm.generate([p2, q2], max_tokens=12, **opts)
+    assert lm.stats.reused_tokens == len(p1) + len(r1.tokens) - 1
+    assert [r.tokens for r in r2] == [r.tokens for r in plain.generate([p2, q2], max_tokens=12, **opts)]
+    p3 = p2[:30] + random_tokens(V, 25, 3)                    # goes back to 30 tokens in common
+    r3 = lm.generate([p3], max_tokens=12, **opts)[0]
+    assert lm.stats.reused_tokens == 30
+    assert r3.tokens == plain.generate([p3], max_tokens=12, **opts)[0].tokens
+    lm.model.cache.check()
+    assert lm.model.cache.slots.held == 2
+    lm.stepper.drop_retained()
+    assert lm.model.cache.slots.held == 0
