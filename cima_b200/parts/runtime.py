@@ -25,7 +25,10 @@ class Runtime:
         return t.to(device=self.device, dtype=torch.float32).contiguous()
 
     def matrix(self, t: torch.Tensor) -> torch.Tensor:
-        """A weight matrix on the device: float32 on the 32-bit path; otherwise in the dtype it was kept in."""
+        """A weight matrix on the device: float32 on the 32-bit path; otherwise in the dtype it was kept in
+        (bfloat16 or float32), a float16 one as bfloat16."""
         if self.full_precision:
             return t.to(device=self.device, dtype=torch.float32).contiguous()
+        if t.dtype is torch.float16:
+            return t.to(device=self.device, dtype=torch.bfloat16).contiguous()
         return t.to(device=self.device).contiguous()

@@ -7,9 +7,11 @@ reports a missing tensor with the names it tried (src/models/transformer.rs:
 490-502) and a shape mismatch with both shapes (:563-572), one at a time; a
 missing q/k/v bias is silently "no bias" there (:852-858) and is an error here.
 
-Stored dtypes are kept: bfloat16 stays bfloat16, float16 becomes bfloat16, a
-tensor stored in 32-bit (or 64-bit) floating point stays 32-bit, integer
-tensors become int32.
+Stored dtypes are kept: bfloat16 stays bfloat16, a tensor stored in 32-bit (or
+64-bit) floating point stays 32-bit, integer tensors become int32.  float16
+leaves the loader as it is stored and is settled by the model's precision
+(``Runtime.matrix``): bfloat16 on the bfloat16 path, float32 (exactly) on the
+32-bit path, which would lose three bits by way of bfloat16.
 """
 from __future__ import annotations
 
@@ -49,10 +51,8 @@ class WeightError(ValueError):
 
 def stored_to_kept(t: torch.Tensor) -> torch.Tensor:
     """The dtype rule of the loader (see module docstring)."""
-    if t.dtype in (torch.bfloat16, torch.float32):
+    if t.dtype in (torch.bfloat16, torch.float32, torch.float16):
         return t
-    if t.dtype is torch.float16:
-        return t.to(torch.bfloat16)
     if t.dtype is torch.float64:
         return t.to(torch.float32)
     return t.to(torch.int32)

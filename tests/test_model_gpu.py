@@ -241,17 +241,28 @@ def test_windows_at_the_edges_of_pages(window, first_windowed, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,stored", [("B", "float32"), ("A", "float32"), ("C", "mixed")])
+@pytest.mark.parametrize("name,stored", [("B", "float32"), ("A", "float32"), ("C", "mixed"), ("B", "float16")])
 def test_checkpoint_stored_in_32_bit(name, stored, dtype, tmp_path):
     """A tensor stored in 32-bit stays 32-bit on both paths (on the bfloat16 path its products run through the plain
-    kernel with bfloat16 activations).  ``mixed``: every second matrix and all vectors in 32-bit, the rest bfloat16."""
+    kernel with bfloat16 activations).  ``mixed``: every second matrix and all vectors in 32-bit, the rest bfloat16.
+    ``float16``: random values of 11 bits stored as float16 must reach the 32-bit path exactly (by way of bfloat16
+    they would lose three bits); the bfloat16 path rounds them to bfloat16 by design and is not compared."""
     import json
     from safetensors.torch import load_file, save_file
     from cima_b200.engine import load_model
     src = model_folder(name)
     tensors = load_file(f"{src}/model.safetensors")
     out = {}
+    if stored == "float16":
+        if dtype == "bfloat16":
+            pytest.skip("float16 weights are rounded to bfloat16 on the bfloat16 path")
+        gen = torch.Generator().manual_seed(3)
+        for n, t in sorted(tensors.items()):
+            noise = torch.randn(t.shape, generator=gen) * 0.004      # bits that bfloat16 does not hold
+            out[n] = (t.float() * (1 + noise)).to(torch.float16).contiguous()
     for i, (n, t) in enumerate(sorted(tensors.items())):
+        if stored == "float16":
+            break
         wide = stored == "float32" or t.dim() == 1 or i % 2 == 0
         out[n] = t.float().contiguous() if wide else t.contiguous()
     folder = tmp_path / "m"
@@ -264,6 +275,8 @@ def test_checkpoint_stored_in_32_bit(name, stored, dtype, tmp_path):
     m = load_model(str(folder), dtype=dtype, max_tokens=1024, device="cuda:0", verbose=False)
     kept = {t.dtype for b in m.blocks for t in (b.mixer.qkv.weight, b.mixer.out.weight)}
     assert torch.float32 in kept
+    if stored == "float16":
+        assert torch.equal(m.blocks[0].mixer.out.weight.cpu(), out["model.layers.0.self_attn.o_proj.weight"].float())
     assert close(run_whole(m, toks), want, TOL[dtype])
     assert close(run_tail_one_by_one(m, toks, 32), want, TOL[dtype])
     for got in run_batched(m, [toks, toks[:17], toks[:50]], [60, 1, 40]):

@@ -64,7 +64,11 @@ def test_dtype_rule_of_the_loader(tmp_path):
     write_safetensors(str(tmp_path / "model.safetensors"), t)
     got = load_tensors(str(tmp_path), {k: TensorSpec(tuple(v.shape)) for k, v in t.items()})
     assert got["bf"].dtype is torch.bfloat16 and got["f32"].dtype is torch.float32      # stored dtypes stay
-    assert got["f16"].dtype is torch.bfloat16 and got["f64"].dtype is torch.float32
+    assert got["f16"].dtype is torch.float16 and got["f64"].dtype is torch.float32       # float16: the model's precision settles it
+    from cima_b200.parts import Runtime
+    assert Runtime(None, torch.bfloat16, "cpu").matrix(got["f16"].view(1, 2)).dtype is torch.bfloat16
+    wide = Runtime(None, torch.float32, "cpu").matrix(got["f16"].view(1, 2))
+    assert wide.dtype is torch.float32 and torch.equal(wide.view(2), t["f16"].float())   # exactly, not by way of bfloat16
     assert got["i64"].dtype is torch.int32 and got["i64"].tolist() == [0, 1, 2]          # integer tables as int32
     assert torch.equal(got["f32"], t["f32"])
 
