@@ -179,6 +179,36 @@ def test_trace_run_three_ways(tmp_path, dtype, tol):
             fed[e["id"]] = start + len(e["tokens"])
 
 
+def test_trace_run_answers_each_step_before_the_next_is_sent(tmp_path):
+    """The driver sends a step only after ``done <step>`` of the one before: nothing may wait for more input or
+    sit in a buffer; a step's file is complete when its line arrives."""
+    name = "A"
+    V = TINY[name]["vocab_size"]
+    cfg, W = plain_load(model_folder(name))
+    toks = random_tokens(V, 12, seed=5)
+    want = plain_forward(W, cfg, toks).float()
+    p = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_folder(name), "--dtype",
+                          "float32", "--out", str(tmp_path), "--max-tokens", "64"], stdin=subprocess.PIPE,
+                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, bufsize=1)
+    try:
+        steps = [{"step": 0, "entries": [{"id": "x", "tokens": toks[:9], "want": [8]}], "end": []},
+                 {"step": 1, "entries": [{"id": "x", "tokens": [toks[9]], "want": [0]}], "end": []},
+                 {"step": 2, "entries": [{"id": "x", "tokens": toks[10:], "want": [1]}], "end": ["x"]}]
+        for s, place in zip(steps, (8, 9, 11)):
+            p.stdin.write(json.dumps(s) + "\n")
+            p.stdin.flush()
+            line = p.stdout.readline()
+            while line and not line.startswith("done"):
+                line = p.stdout.readline()
+            assert line.strip() == f"done {s['step']}"
+            assert (read_step(tmp_path, s["step"], V)[0] - want[place]).abs().max().item() <= 2e-5
+        p.stdin.close()
+        assert p.wait(timeout=120) == 0
+    finally:
+        if p.poll() is None:
+            p.kill()
+
+
 def test_pipelined_and_plain_decoding_give_the_same_tokens():
     """Run-ahead decoding (the default) against the step-by-step loop: greedy and sampled, early stops."""
     name = "B"
