@@ -5,8 +5,8 @@
 // their results in tensor memory:
 //     S = Q K^T      128 x 64, K-major operands straight from the q/k/v buffer by TMA
 //     O += P V       P is written to shared memory by the softmax threads in the layout the tensor core reads
-//                    (K-major, 128-byte swizzle); V is taken TRANSPOSED ([dims, keys], keys contiguous; the
-//                    small kernel below makes it), so that this operand is K-major too
+//                    (K-major, 128-byte swizzle); V is taken as it lies in the buffer ([keys, dims], dims
+//                    contiguous): for this product the dims are N, so the operand is MN-major
 // Warp roles (192 threads): warps 0..3 softmax, one thread per query row (a row's maximum and sum need no
 // shuffles; each warp reads the 32 TMEM lanes it may access); warp 4 TMA producer; warp 5 TMEM allocation and
 // MMA issue.  S has two buffers in TMEM, so the tensor cores compute S of the next tile while the softmax of the
@@ -44,7 +44,6 @@ struct AttnArgs {
   const int* tile_seq;          // [tiles] sequence of the block of 128 query rows
   const int* tile_row0;         // [tiles] first query position of the block
   const int* seq_first_row;     // [seqs + 1]
-  const int* seq_vt_col;        // [seqs] first column of the sequence in the transposed V
   __nv_bfloat16* out;           // [T, ldo]
   int ldo, nh, nkv, window;
   float scale;
@@ -62,14 +61,14 @@ __device__ __forceinline__ void key_tiles(int q0, int len, int window, int& firs
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 2)
 k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_k,
-                       const __grid_constant__ CUtensorMap map_vt, AttnArgs a) {
+                       AttnArgs a) {
   cima_pdl_wait();
   extern __shared__ __align__(1024) unsigned char smem[];      // tiles of 1024-byte groups: checked below
   constexpr int NH = HD / 64;                                  // blocks of 64 dims in a row of Q or K
-  constexpr int V_BYTES = HD * 64 * 2;                         // V^T of a tile: [HD dims][64 keys]
+  constexpr int V_BYTES = HD * 64 * 2;                         // V of a tile: NH blocks of [64 keys][64 dims]
   unsigned char* sq = smem;                                    // Q: NH blocks (dims 0..63, 64..127) of 16 KB
   unsigned char* sk = sq + NH * HALF_BYTES;                    // K: [2 stages][NH blocks of 64 dims][64 keys]
-  unsigned char* sv = sk + 2 * NH * KHALF_BYTES;               // V^T: [2 stages][HD dims][64 keys]
+  unsigned char* sv = sk + 2 * NH * KHALF_BYTES;               // V: [2 stages][NH blocks of 64 dims][64 keys]
   unsigned char* sp = sv + 2 * V_BYTES;                        // P: [128 query rows][64 keys]
   unsigned long long* bars = (unsigned long long*)(sp + HALF_BYTES);
   unsigned long long* q_full = bars;                           // [1]
@@ -132,18 +131,20 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
           tma_load_2d(sk + (size_t)(NH * s + kb) * KHALF_BYTES, &map_k, (a.nh + kvh) * HD + 64 * kb, row_base + k0, &k_full[s]);
       }
     } else if (lane == 1) {
-      const int col0 = a.seq_vt_col[seq];
       for (int j = 0; j < n; j++) {
         const int s = j & 1, k0 = (first + j) * BN;
         if (j >= 2 && !mbar_wait(&v_empty[s], ((j >> 1) - 1) & 1, a.error_flag, abort_flag)) break;
         mbar_expect_tx(&v_full[s], V_BYTES);
-        tma_load_2d(sv + (size_t)s * V_BYTES, &map_vt, col0 + k0, kvh * HD, &v_full[s]);
+#pragma unroll
+        for (int kb = 0; kb < NH; kb++)
+          tma_load_2d(sv + (size_t)s * V_BYTES + (size_t)kb * KHALF_BYTES, &map_k, (a.nh + a.nkv + kvh) * HD + 64 * kb,
+                      row_base + k0, &v_full[s]);
       }
     }
   } else if (warp == 5) {
     // ---------------------------------------------------------------- MMA issue (one thread)
     if (lane == 0) {
-      const unsigned idesc_s = umma_idesc(BM, BN), idesc_o = umma_idesc(BM, HD);
+      const unsigned idesc_s = umma_idesc(BM, BN), idesc_o = umma_idesc(BM, HD) | (1u << 16);   // B of P V is MN-major
       auto issue_s = [&](int j) {                       // S(j) = Q K(j)^T into buffer j & 1
         const int s = j & 1;
 #pragma unroll
@@ -177,10 +178,11 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
         const int s = j & 1;
         {                                               // O += P V(j): 64 keys
           const unsigned long long pd = umma_smem_desc(smem_u32(sp));
-          const unsigned long long vd = umma_smem_desc(smem_u32(sv + (size_t)s * V_BYTES));
+          // V as it lies in the buffer, [keys][dims]: the dims (N) are contiguous, 16 keys further is 16 rows of 128 bytes
+          const unsigned long long vd = umma_smem_desc_mn(smem_u32(sv + (size_t)s * V_BYTES), KHALF_BYTES);
 #pragma unroll
           for (int k = 0; k < BN / UMMA_K; k++)
-            umma_bf16(tm_o, pd + (unsigned long long)(k * 2), vd + (unsigned long long)(k * 2), idesc_o, (j | k) ? 1u : 0u);
+            umma_bf16(tm_o, pd + (unsigned long long)(k * 2), vd + (unsigned long long)(k * (UMMA_K * 128 >> 4)), idesc_o, (j | k) ? 1u : 0u);
         }
         umma_commit(&v_empty[s]);
         umma_commit(pv_done);
@@ -317,51 +319,14 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
   }
 }
 
-// V of a step's rows, transposed for the kernel above: vt[kvh * HD + d][seq_vt_col[seq] + key] = v[key][d];
-// keys from a sequence's end to the next multiple of 128 are zero (P is zero there, and zero times what an
-// uninitialised buffer may hold need not be zero).  One block per (block of 128 keys, kv head).
-template <int HD>
-__global__ void __launch_bounds__(256)
-k_transpose_v(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __restrict__ tile_seq,
-              const int* __restrict__ tile_row0, const int* __restrict__ seq_first_row,
-              const int* __restrict__ seq_vt_col, __nv_bfloat16* __restrict__ vt, int vt_cols, int nh, int nkv) {
-  cima_pdl_wait();
-  __shared__ __nv_bfloat16 tile[128][HD + 8];
-  const int seq = tile_seq[blockIdx.x], k0 = tile_row0[blockIdx.x], kvh = blockIdx.y;
-  const int row_base = seq_first_row[seq];
-  const int len = seq_first_row[seq + 1] - row_base;
-  const __nv_bfloat16* src = qkv + (size_t)(row_base + k0) * ld + (size_t)(nh + nkv + kvh) * HD;
-  for (int idx = threadIdx.x; idx < 128 * (HD / 8); idx += blockDim.x) {
-    const int key = idx / (HD / 8), d8 = (idx % (HD / 8)) * 8;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (k0 + key < len) v = *reinterpret_cast<const uint4*>(src + (size_t)key * ld + d8);
-    *reinterpret_cast<uint4*>(&tile[key][d8]) = v;
-  }
-  __syncthreads();
-  __nv_bfloat16* dst = vt + (size_t)(kvh * HD) * vt_cols + seq_vt_col[seq] + k0;
-  for (int idx = threadIdx.x; idx < HD * (128 / 8); idx += blockDim.x) {
-    const int d = idx % HD, k8 = (idx / HD) * 8;         // a warp's lanes walk along d: no bank conflicts in `tile`
-    uint4 v;
-    __nv_bfloat16* e = reinterpret_cast<__nv_bfloat16*>(&v);
-#pragma unroll
-    for (int q = 0; q < 8; q++) e[q] = tile[k8 + q][d];
-    *reinterpret_cast<uint4*>(dst + (size_t)d * vt_cols + k8) = v;
-  }
-}
-
 template <int HD>
 int launch_attention_tc(const void* qkv, int ld, const int* tile_seq, const int* tile_row0, const int* seq_first_row,
-                        const int* seq_vt_col, void* vt, int vt_cols, void* out, int ldo, int T, int n_tiles, int nh,
-                        int nkv, float scale, int window, int* error_flag, cudaStream_t stream) {
-  CUtensorMap mq, mk, mv;
+                        void* out, int ldo, int T, int n_tiles, int nh, int nkv, float scale, int window,
+                        int* error_flag, cudaStream_t stream) {
+  CUtensorMap mq, mk;                                  // boxes of 128 rows (Q) and of 64 rows (K and V) by 64 columns
   int rc = make_map(&mq, qkv, T, (long long)(nh + 2 * nkv) * HD, ld);
   if (rc) return rc;
   rc = make_map(&mk, qkv, T, (long long)(nh + 2 * nkv) * HD, ld, BN);
-  if (rc) return rc;
-  rc = make_map(&mv, vt, (long long)nkv * HD, vt_cols, vt_cols, HD);
-  if (rc) return rc;
-  { int rc_ = cima_launch(k_transpose_v<HD>, dim3(n_tiles, nkv), dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)qkv, ld, tile_seq, tile_row0, seq_first_row, seq_vt_col, (__nv_bfloat16*)vt, vt_cols, nh, nkv); if (rc_) return rc_; }
-  rc = cima_launch_result();
   if (rc) return rc;
   constexpr int NH = HD / 64;
   const size_t smem = NH * (size_t)HALF_BYTES + 2 * NH * (size_t)KHALF_BYTES + 2 * (size_t)HD * 128 + HALF_BYTES + 16 * 8 + 16;
@@ -372,30 +337,28 @@ int launch_attention_tc(const void* qkv, int ld, const int* tile_seq, const int*
     if (e != cudaSuccess) return cima_fail((int)e, "attention_prefill_tc: cannot raise shared memory to %zu bytes: %s", smem, cudaGetErrorString(e));
     raised = true;
   }
-  AttnArgs a{tile_seq, tile_row0, seq_first_row, seq_vt_col, (__nv_bfloat16*)out, ldo, nh, nkv, window, scale, error_flag};
-  { int rc_ = cima_launch(k_attention_prefill_tc<HD>, dim3(n_tiles, nh), dim3(THREADS), smem, stream, 1, mq, mk, mv, a); if (rc_) return rc_; }
+  AttnArgs a{tile_seq, tile_row0, seq_first_row, (__nv_bfloat16*)out, ldo, nh, nkv, window, scale, error_flag};
+  { int rc_ = cima_launch(k_attention_prefill_tc<HD>, dim3(n_tiles, nh), dim3(THREADS), smem, stream, 1, mq, mk, a); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
 }  // namespace
 
 // qkv [T, ld] bf16: q heads, k heads, v heads of each row, q and k already rotated.  tile_seq / tile_row0: the
-// blocks of 128 query rows, heaviest first.  seq_vt_col [seqs]: first column of each sequence in vt (a multiple
-// of 128); vt [nkv * head_dim, vt_cols] bf16 is scratch that this call fills (V transposed).  out [T, ldo].
-// head_dim is 64 or 128.  error_flag: device int that a wait that ran out sets to 1 (never cleared here).
+// blocks of 128 query rows, heaviest first.  out [T, ldo].  head_dim is 64 or 128.
+// error_flag: device int that a wait that ran out sets to 1 (never cleared here).
 extern "C" int cima_attention_prefill_tc(const void* qkv, int ld, const int* tile_seq, const int* tile_row0,
-                                         const int* seq_first_row, const int* seq_vt_col, void* vt, int vt_cols,
-                                         void* out, int ldo, int T, int n_tiles, int nh, int nkv, int hd, float scale,
-                                         int window, int* error_flag, cudaStream_t stream) {
+                                         const int* seq_first_row, void* out, int ldo, int T, int n_tiles, int nh,
+                                         int nkv, int hd, float scale, int window, int* error_flag, cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return 0;
   if (hd != 64 && hd != 128) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: head_dim %d; this kernel takes 64 or 128", hd);
   if (nh <= 0 || nkv <= 0 || nh % nkv) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: %d heads are not a multiple of %d kv heads", nh, nkv);
-  if (ld % 8 || ldo % 8 || vt_cols % 128 || vt_cols <= 0) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: row strides (%d, %d) must be multiples of 8 and the transposed V's columns (%d) of 128", ld, ldo, vt_cols);
+  if (ld % 8 || ldo % 8) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: row strides (%d, %d) must be multiples of 8", ld, ldo);
   if (ld < (nh + 2 * nkv) * hd) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: row stride %d is smaller than (heads + 2 kv heads) * head_dim", ld);
-  if ((((uintptr_t)qkv | (uintptr_t)vt | (uintptr_t)out) & 15)) return cima_fail(CIMA_E_ARG, "attention_prefill_tc: qkv, vt and out must be 16-byte aligned");
+  if ((((uintptr_t)qkv | (uintptr_t)out) & 15)) return cima_fail(CIMA_E_ARG, "attention_prefill_tc: qkv and out must be 16-byte aligned");
   if (!error_flag) return cima_fail(CIMA_E_ARG, "attention_prefill_tc: an error flag on the device is needed");
   if (nh > 65535 || nkv > 65535) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: %d heads exceed one launch", nh);
   if (hd == 64)
-    return launch_attention_tc<64>(qkv, ld, tile_seq, tile_row0, seq_first_row, seq_vt_col, vt, vt_cols, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
-  return launch_attention_tc<128>(qkv, ld, tile_seq, tile_row0, seq_first_row, seq_vt_col, vt, vt_cols, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
+    return launch_attention_tc<64>(qkv, ld, tile_seq, tile_row0, seq_first_row, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
+  return launch_attention_tc<128>(qkv, ld, tile_seq, tile_row0, seq_first_row, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
 }

@@ -67,6 +67,18 @@ __device__ __forceinline__ unsigned long long umma_smem_desc(unsigned smem_addr)
   d |= 2ull << 61;
   return d;
 }
+// The same for an operand whose M/N index is the contiguous one (MN-major): rows of 128 bytes hold 64 values
+// along M/N for one k, 8 such rows (k .. k + 7) form a swizzle group of 1024 bytes (stride byte offset), and the
+// next 64 values along M/N start ``lbo_bytes`` further (leading byte offset).
+__device__ __forceinline__ unsigned long long umma_smem_desc_mn(unsigned smem_addr, unsigned lbo_bytes) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (unsigned long long)(1024u >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
 // Instruction descriptor, kind::f16: D float32 [4,6) = 1, A and B bfloat16 [7,10) = [10,13) = 1, both K-major,
 // N >> 3 at [17,23), M >> 4 at [24,29).
 __device__ __forceinline__ unsigned umma_idesc(int M, int N) {

@@ -14,8 +14,7 @@ import torch
 
 
 Q_TILE = 64        # query rows per block of the prefill attention kernel
-Q_TILE_TC = 128    # ... and of its tcgen05 variant, which also wants V transposed, a sequence's keys starting
-                   # at a column that is a multiple of 128
+Q_TILE_TC = 128    # ... and of its tcgen05 variant
 
 
 @dataclass
@@ -48,8 +47,6 @@ class StepBatch:
     n_q_tiles_tc: int = 0             # prompts only: the same in blocks of 128 rows
     q_tile_tc_seq: torch.Tensor = None
     q_tile_tc_row0: torch.Tensor = None
-    seq_vt_col: torch.Tensor = None   # int32 [seqs] first column of the sequence in the transposed V
-    vt_cols: int = 0                  # columns of the transposed V (every sequence padded to 128)
     host_seq_slot: np.ndarray = None
     host_seq_first_row: np.ndarray = None
     host_seq_len: np.ndarray = None
@@ -79,7 +76,7 @@ def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, dev
     NT = len(q_tiles)
     tc_tiles = [t for t in q_tiles if t[1] % Q_TILE_TC == 0] if prefill else []
     NTC = len(tc_tiles)
-    buf = np.empty(3 * T + 3 * B + 1 + W + 2 * NT + 2 * NTC + B, dtype=np.int32)
+    buf = np.empty(3 * T + 3 * B + 1 + W + 2 * NT + 2 * NTC, dtype=np.int32)
     tokens, row_pos, row_seq = buf[0:T], buf[T:2 * T], buf[2 * T:3 * T]
     o = 3 * T
     seq_slot, seq_first, seq_len = buf[o:o + B], buf[o + B:o + 2 * B + 1], buf[o + 2 * B + 1:o + 3 * B + 1]
@@ -89,13 +86,9 @@ def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, dev
         buf[w0 + W:w0 + W + NT] = [t[0] for t in q_tiles]
         buf[w0 + W + NT:w0 + W + 2 * NT] = [t[1] for t in q_tiles]
     t0 = w0 + W + 2 * NT
-    vt_cols = 0
     if NTC:
         buf[t0:t0 + NTC] = [t[0] for t in tc_tiles]
         buf[t0 + NTC:t0 + 2 * NTC] = [t[1] for t in tc_tiles]
-    for i, c in enumerate(counts):
-        buf[t0 + 2 * NTC + i] = vt_cols
-        vt_cols += -(-c // Q_TILE_TC) * Q_TILE_TC
     r = w = 0
     for i, (e, s, c) in enumerate(zip(entries, starts, counts)):
         tk = np.asarray(e.tokens, dtype=np.int64)
@@ -125,5 +118,4 @@ def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, dev
                      seq_len=dev[o + 2 * B + 1:o + 3 * B + 1], want_rows=dev[w0:w0 + W],
                      n_q_tiles=NT, q_tile_seq=dev[w0 + W:w0 + W + NT], q_tile_row0=dev[w0 + W + NT:w0 + W + 2 * NT],
                      n_q_tiles_tc=NTC, q_tile_tc_seq=dev[t0:t0 + NTC], q_tile_tc_row0=dev[t0 + NTC:t0 + 2 * NTC],
-                     seq_vt_col=dev[t0 + 2 * NTC:t0 + 2 * NTC + B], vt_cols=vt_cols if prefill else 0,
                      host_seq_slot=seq_slot.copy(), host_seq_first_row=seq_first.copy(), host_seq_len=seq_len.copy())

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 16
+ABI_VERSION = 17
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -57,7 +57,7 @@ _SIGNATURES = {
     "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
     "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "cima_attention_extend": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
-    "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
+    "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
     "cima_gemm_tcgen05": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
@@ -455,24 +455,18 @@ class Kernels:
                              head_dim: int, scale: float, window: int) -> None:
         """Flash attention of ragged prompts that start at position 0 on the tcgen05 tensor cores (bf16,
         head_dim 64 or 128): blocks of 128 query rows, both products with their results in tensor memory.  ``batch``
-        brings the blocks (``q_tile_tc_*``) and each sequence's first column in the transposed V (``seq_vt_col``,
-        ``vt_cols``), which this call makes in its own scratch."""
+        brings the blocks (``q_tile_tc_*``)."""
         self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)
         T = qkv.shape[0]
-        if tuple(out.shape) != (T, n_heads * head_dim) or batch.n_q_tiles_tc <= 0 or batch.vt_cols <= 0:
+        if tuple(out.shape) != (T, n_heads * head_dim) or batch.n_q_tiles_tc <= 0:
             raise KernelError(f"attention_prefill_tc: out {tuple(out.shape)} or the block list do not fit")
-        need = n_kv_heads * head_dim * batch.vt_cols
-        vt = self._scratch_bufs.get("vt")
-        if vt is None or vt.numel() < need or vt.device != qkv.device:
-            vt = self._scratch_bufs["vt"] = torch.empty(need, dtype=torch.bfloat16, device=qkv.device)
         if self._error_flag is None:
             self._error_flag = torch.zeros(1, dtype=torch.int32, device=qkv.device)
         self._check(self.lib.cima_attention_prefill_tc(
             qkv.data_ptr(), qkv.shape[1], batch.q_tile_tc_seq.data_ptr(), batch.q_tile_tc_row0.data_ptr(),
-            batch.seq_first_row.data_ptr(), batch.seq_vt_col.data_ptr(), vt.data_ptr(), batch.vt_cols, out.data_ptr(),
+            batch.seq_first_row.data_ptr(), out.data_ptr(),
             out.shape[1], T, batch.n_q_tiles_tc, n_heads, n_kv_heads, head_dim, scale, window,
             self._error_flag.data_ptr(), self._stream()), "attention_prefill_tc")
-        self.launches += 1
 
     def attention_decode(self, qkv: torch.Tensor, kv, seq_slot, seq_len, out: torch.Tensor, n_heads: int,
                          n_kv_heads: int, head_dim: int, scale: float, window: int, max_len: int = 0,

@@ -23,18 +23,17 @@ def test_prefill_batch_layout():
     # blocks of 128 rows for the tcgen05 kernel, and a sequence's first column in the transposed V
     tc = list(zip(b.q_tile_tc_seq.tolist(), b.q_tile_tc_row0.tolist()))
     assert len(tc) == b.n_q_tiles_tc == 2 + 1 + 3 and all(r0 % Q_TILE_TC == 0 for _, r0 in tc)
-    assert b.seq_vt_col.tolist() == [0, 256, 384] and b.vt_cols == 768          # every sequence padded to 128 columns
 
 
 def test_decode_batch_and_what_is_refused():
     b = build_batch([StepEntry(2, [5], [0]), StepEntry(9, [6], [0])], [40, 7], vocab=10, device="cpu")
-    assert not b.prefill and b.n_q_tiles == 0 and b.n_q_tiles_tc == 0 and b.vt_cols == 0
+    assert not b.prefill and b.n_q_tiles == 0 and b.n_q_tiles_tc == 0
     assert b.row_pos.tolist() == [40, 7] and b.seq_len.tolist() == [41, 8] and b.want_all_in_order
     with pytest.raises(ValueError, match="twice"):
         build_batch([StepEntry(1, [1]), StepEntry(1, [2])], [0, 0], 10, "cpu")
     # a sequence that goes on by several tokens beside one that starts: rows that read the cache, no prompt blocks
     b = build_batch([StepEntry(1, [1, 2, 3], [2]), StepEntry(2, [2, 4])], [7, 0], 10, "cpu")
-    assert not b.prefill and b.n_rows == 5 and b.n_seqs == 2 and b.n_q_tiles_tc == 0 and b.vt_cols == 0
+    assert not b.prefill and b.n_rows == 5 and b.n_seqs == 2 and b.n_q_tiles_tc == 0
     assert list(zip(b.q_tile_seq.tolist(), b.q_tile_row0.tolist())) == [(0, 0), (1, 0)]     # blocks of rows, heaviest first
     assert b.row_pos.tolist() == [7, 8, 9, 0, 1] and b.seq_len.tolist() == [10, 2] and b.want_rows.tolist() == [2]
     with pytest.raises(ValueError, match="token ids"):

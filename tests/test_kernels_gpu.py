@@ -180,14 +180,9 @@ def batch_of(seqs, device):
     t = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
     tiles = sorted(((i, r0) for i, s in enumerate(seqs) for r0 in range(0, s[2], 64)), key=lambda x: -x[1])
     tc = [x for x in tiles if x[1] % 128 == 0]
-    vt_col, cols = [], 0
-    for s in seqs:
-        vt_col.append(cols)
-        cols += -(-s[2] // 128) * 128
     tiles.sort(key=lambda x: -(seqs[x[0]][1] + x[1]))
     return SimpleNamespace(n_q_tiles=len(tiles) if any(s[2] > 1 for s in seqs) else 0,
                            n_q_tiles_tc=len(tc), q_tile_tc_seq=t([x[0] for x in tc]), q_tile_tc_row0=t([x[1] for x in tc]),
-                           seq_vt_col=t(vt_col), vt_cols=cols,
                            q_tile_seq=t([x[0] for x in tiles]), q_tile_row0=t([x[1] for x in tiles]),
                            row_pos=t(row_pos), row_seq=t(row_seq), seq_slot=t([s[0] for s in seqs]),
                            seq_first_row=t(first), seq_len=t([s[1] + s[2] for s in seqs]),

@@ -15,7 +15,7 @@ out = torch.empty(T, nh * hd, device=dev, dtype=torch.bfloat16)
 t32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
 tiles = sorted(((i, r0) for i, n in enumerate(lens) for r0 in range(0, n, 128)), key=lambda x: -x[1])
 b = SimpleNamespace(n_q_tiles_tc=len(tiles), q_tile_tc_seq=t32([x[0] for x in tiles]), q_tile_tc_row0=t32([x[1] for x in tiles]),
-                    seq_first_row=t32([0, T]), seq_vt_col=t32([0]), vt_cols=T)
+                    seq_first_row=t32([0, T]))
 for _ in range(3):
     K.attention_prefill_tc(qkv, b, out, nh, nkv, hd, 0.088, 0)
 torch.cuda.synchronize()
