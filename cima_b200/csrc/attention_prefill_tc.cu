@@ -16,6 +16,10 @@
 // bfloat16 only as operand of P V, the row sums are taken before that rounding.  O is rescaled in TMEM only
 // when a row's maximum has grown by more than 2^8 over the reference of its exponentials.
 //
+// Two sources of keys and values, as in the mma.sync kernel: the step's own q/k/v buffer (prompts that start at
+// position 0), or the layer's pages in the cache (sequences that go on by many tokens: their rows stand at positions
+// seq_len - rows .. seq_len - 1, a tile of 64 keys is a page, fetched by TMA through the slot's block table).
+//
 // Every wait on an mbarrier is bounded (2 s); a wait that runs out sets *error_flag, and all roles leave their
 // loops, free the tensor memory and return.
 //
@@ -42,23 +46,27 @@ __device__ __forceinline__ float ex2(float x) {          // 2^x, float32, about 
 
 struct AttnArgs {
   const int* tile_seq;          // [tiles] sequence of the block of 128 query rows
-  const int* tile_row0;         // [tiles] first query position of the block
+  const int* tile_row0;         // [tiles] first query row of the block among the sequence's rows
   const int* seq_first_row;     // [seqs + 1]
+  const int* seq_len;           // keys from the cache: [seqs] positions held after the step
+  const int* seq_slot;          //                      [seqs]
+  const int* table;             //                      [slots, table_width] pages
+  int table_width, ring;
   __nv_bfloat16* out;           // [T, ldo]
   int ldo, nh, nkv, window;
   float scale;
   int* error_flag;
 };
 
-// Keys of a query block: tiles [first, last] of 128 keys.
-__device__ __forceinline__ void key_tiles(int q0, int len, int window, int& first, int& last) {
-  const int q_hi = min(q0 + BM, len) - 1;                      // last query row of the block
-  const int lo = window > 0 ? max(0, q0 - window + 1) : 0;      // first key any row of the block sees
+// Keys of a query block whose rows stand at positions p0 .. (at most p0 + 127, below len): tiles [first, last] of 64.
+__device__ __forceinline__ void key_tiles(int p0, int len, int window, int& first, int& last) {
+  const int q_hi = min(p0 + BM, len) - 1;                      // last query position of the block
+  const int lo = window > 0 ? max(0, p0 - window + 1) : 0;      // first key any row of the block sees
   first = lo / BN;
   last = q_hi / BN;
 }
 
-template <int HD>
+template <int HD, bool FROM_CACHE>
 __global__ void __launch_bounds__(THREADS, 2)
 k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_k,
                        AttnArgs a) {
@@ -85,9 +93,12 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
-  const int seq = a.tile_seq[blockIdx.x], q0 = a.tile_row0[blockIdx.x];
+  const int seq = a.tile_seq[blockIdx.x], r0 = a.tile_row0[blockIdx.x];
   const int row_base = a.seq_first_row[seq];
-  const int len = a.seq_first_row[seq + 1] - row_base;
+  const int rows = a.seq_first_row[seq + 1] - row_base;       // rows of the sequence in this step
+  const int len = FROM_CACHE ? a.seq_len[seq] : rows;         // positions it holds after the step
+  const int q0 = len - rows + r0;                             // position of the block's first query row
+  const int slot = FROM_CACHE ? a.seq_slot[seq] : 0;
   int first, last;
   key_tiles(q0, len, a.window, first, last);
   const int n = last - first + 1;
@@ -118,27 +129,35 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
 
   if (warp == 4) {
     // ---------------------------------------------------------------- TMA producers: lane 0 Q and K, lane 1 V
+    auto page_of = [&](int tile) -> int {               // the page that holds positions [64 tile, 64 tile + 64)
+      int e = tile;
+      if (a.ring) e %= a.ring;
+      return a.table[(size_t)slot * a.table_width + e];
+    };
     if (lane == 0) {
       mbar_expect_tx(q_full, NH * HALF_BYTES);
 #pragma unroll
-      for (int kb = 0; kb < NH; kb++) tma_load_2d(sq + (size_t)kb * HALF_BYTES, &map_qkv, h * HD + 64 * kb, row_base + q0, q_full);
+      for (int kb = 0; kb < NH; kb++) tma_load_2d(sq + (size_t)kb * HALF_BYTES, &map_qkv, h * HD + 64 * kb, row_base + r0, q_full);
       for (int j = 0; j < n; j++) {
         const int s = j & 1, k0 = (first + j) * BN;
         if (j >= 2 && !mbar_wait(&k_empty[s], ((j >> 1) - 1) & 1, a.error_flag, abort_flag)) break;
         mbar_expect_tx(&k_full[s], NH * KHALF_BYTES);
+        // from the cache, map_k covers the layer's pages as rows of head_dim values: page, k or v, kv head, position
+        const int x = FROM_CACHE ? 0 : (a.nh + kvh) * HD, y = FROM_CACHE ? (page_of(first + j) * 2 * a.nkv + kvh) * BN : row_base + k0;
 #pragma unroll
         for (int kb = 0; kb < NH; kb++)
-          tma_load_2d(sk + (size_t)(NH * s + kb) * KHALF_BYTES, &map_k, (a.nh + kvh) * HD + 64 * kb, row_base + k0, &k_full[s]);
+          tma_load_2d(sk + (size_t)(NH * s + kb) * KHALF_BYTES, &map_k, x + 64 * kb, y, &k_full[s]);
       }
     } else if (lane == 1) {
       for (int j = 0; j < n; j++) {
         const int s = j & 1, k0 = (first + j) * BN;
         if (j >= 2 && !mbar_wait(&v_empty[s], ((j >> 1) - 1) & 1, a.error_flag, abort_flag)) break;
         mbar_expect_tx(&v_full[s], V_BYTES);
+        const int x = FROM_CACHE ? 0 : (a.nh + a.nkv + kvh) * HD;
+        const int y = FROM_CACHE ? ((page_of(first + j) * 2 + 1) * a.nkv + kvh) * BN : row_base + k0;
 #pragma unroll
         for (int kb = 0; kb < NH; kb++)
-          tma_load_2d(sv + (size_t)s * V_BYTES + (size_t)kb * KHALF_BYTES, &map_k, (a.nh + a.nkv + kvh) * HD + 64 * kb,
-                      row_base + k0, &v_full[s]);
+          tma_load_2d(sv + (size_t)s * V_BYTES + (size_t)kb * KHALF_BYTES, &map_k, x + 64 * kb, y, &v_full[s]);
       }
     }
   } else if (warp == 5) {
@@ -293,7 +312,7 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
     if (ok && n > 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-      __nv_bfloat16* dst = a.out + (size_t)(row_base + pos) * a.ldo + (size_t)h * HD;
+      __nv_bfloat16* dst = a.out + (size_t)(row_base + r0 + r) * a.ldo + (size_t)h * HD;
 #pragma unroll 1
       for (int c = 0; c < HD / 32; c++) {
         float o[32];
@@ -319,30 +338,50 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
   }
 }
 
-template <int HD>
+struct CacheSource {              // keys and values from a layer's pages; cache == nullptr: from the q/k/v buffer
+  const void* cache;
+  long long n_pages;
+  const int *table, *seq_slot, *seq_len;
+  int table_width, ring;
+};
+
+template <int HD, bool FROM_CACHE>
 int launch_attention_tc(const void* qkv, int ld, const int* tile_seq, const int* tile_row0, const int* seq_first_row,
-                        void* out, int ldo, int T, int n_tiles, int nh, int nkv, float scale, int window,
-                        int* error_flag, cudaStream_t stream) {
+                        const CacheSource& c, void* out, int ldo, int T, int n_tiles, int nh, int nkv, float scale,
+                        int window, int* error_flag, cudaStream_t stream) {
   CUtensorMap mq, mk;                                  // boxes of 128 rows (Q) and of 64 rows (K and V) by 64 columns
   int rc = make_map(&mq, qkv, T, (long long)(nh + 2 * nkv) * HD, ld);
   if (rc) return rc;
-  rc = make_map(&mk, qkv, T, (long long)(nh + 2 * nkv) * HD, ld, BN);
+  if (FROM_CACHE) rc = make_map(&mk, c.cache, c.n_pages * 2 * nkv * BN, HD, HD, BN);
+  else rc = make_map(&mk, qkv, T, (long long)(nh + 2 * nkv) * HD, ld, BN);
   if (rc) return rc;
   constexpr int NH = HD / 64;
   const size_t smem = NH * (size_t)HALF_BYTES + 2 * NH * (size_t)KHALF_BYTES + 2 * (size_t)HD * 128 + HALF_BYTES + 16 * 8 + 16;
   static_assert(15 * 8 + 8 <= 16 * 8 + 16, "barriers and flags fit their place");
   static bool raised = false;
   if (!raised) {
-    cudaError_t e = cudaFuncSetAttribute(k_attention_prefill_tc<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(k_attention_prefill_tc<HD, FROM_CACHE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return cima_fail((int)e, "attention_prefill_tc: cannot raise shared memory to %zu bytes: %s", smem, cudaGetErrorString(e));
     raised = true;
   }
-  AttnArgs a{tile_seq, tile_row0, seq_first_row, (__nv_bfloat16*)out, ldo, nh, nkv, window, scale, error_flag};
-  { int rc_ = cima_launch(k_attention_prefill_tc<HD>, dim3(n_tiles, nh), dim3(THREADS), smem, stream, 1, mq, mk, a); if (rc_) return rc_; }
+  AttnArgs a{tile_seq, tile_row0, seq_first_row, c.seq_len, c.seq_slot, c.table, c.table_width, c.ring,
+             (__nv_bfloat16*)out, ldo, nh, nkv, window, scale, error_flag};
+  { int rc_ = cima_launch(k_attention_prefill_tc<HD, FROM_CACHE>, dim3(n_tiles, nh), dim3(THREADS), smem, stream, 1, mq, mk, a); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
 }  // namespace
+
+static int tc_checks(const char* who, const void* qkv, int ld, const void* out, int ldo, int nh, int nkv, int hd, const int* error_flag) {
+  if (hd != 64 && hd != 128) return cima_fail(CIMA_E_SIZE, "%s: head_dim %d; this kernel takes 64 or 128", who, hd);
+  if (nh <= 0 || nkv <= 0 || nh % nkv) return cima_fail(CIMA_E_SIZE, "%s: %d heads are not a multiple of %d kv heads", who, nh, nkv);
+  if (ld % 8 || ldo % 8) return cima_fail(CIMA_E_SIZE, "%s: row strides (%d, %d) must be multiples of 8", who, ld, ldo);
+  if (ld < (nh + 2 * nkv) * hd) return cima_fail(CIMA_E_SIZE, "%s: row stride %d is smaller than (heads + 2 kv heads) * head_dim", who, ld);
+  if ((((uintptr_t)qkv | (uintptr_t)out) & 15)) return cima_fail(CIMA_E_ARG, "%s: qkv and out must be 16-byte aligned", who);
+  if (!error_flag) return cima_fail(CIMA_E_ARG, "%s: an error flag on the device is needed", who);
+  if (nh > 65535 || nkv > 65535) return cima_fail(CIMA_E_SIZE, "%s: %d heads exceed one launch", who, nh);
+  return 0;
+}
 
 // qkv [T, ld] bf16: q heads, k heads, v heads of each row, q and k already rotated.  tile_seq / tile_row0: the
 // blocks of 128 query rows, heaviest first.  out [T, ldo].  head_dim is 64 or 128.
@@ -351,14 +390,28 @@ extern "C" int cima_attention_prefill_tc(const void* qkv, int ld, const int* til
                                          const int* seq_first_row, void* out, int ldo, int T, int n_tiles, int nh,
                                          int nkv, int hd, float scale, int window, int* error_flag, cudaStream_t stream) {
   if (T <= 0 || n_tiles <= 0) return 0;
-  if (hd != 64 && hd != 128) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: head_dim %d; this kernel takes 64 or 128", hd);
-  if (nh <= 0 || nkv <= 0 || nh % nkv) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: %d heads are not a multiple of %d kv heads", nh, nkv);
-  if (ld % 8 || ldo % 8) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: row strides (%d, %d) must be multiples of 8", ld, ldo);
-  if (ld < (nh + 2 * nkv) * hd) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: row stride %d is smaller than (heads + 2 kv heads) * head_dim", ld);
-  if ((((uintptr_t)qkv | (uintptr_t)out) & 15)) return cima_fail(CIMA_E_ARG, "attention_prefill_tc: qkv and out must be 16-byte aligned");
-  if (!error_flag) return cima_fail(CIMA_E_ARG, "attention_prefill_tc: an error flag on the device is needed");
-  if (nh > 65535 || nkv > 65535) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: %d heads exceed one launch", nh);
+  if (int rc = tc_checks("attention_prefill_tc", qkv, ld, out, ldo, nh, nkv, hd, error_flag)) return rc;
+  const CacheSource none{nullptr, 0, nullptr, nullptr, nullptr, 0, 0};
   if (hd == 64)
-    return launch_attention_tc<64>(qkv, ld, tile_seq, tile_row0, seq_first_row, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
-  return launch_attention_tc<128>(qkv, ld, tile_seq, tile_row0, seq_first_row, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
+    return launch_attention_tc<64, false>(qkv, ld, tile_seq, tile_row0, seq_first_row, none, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
+  return launch_attention_tc<128, false>(qkv, ld, tile_seq, tile_row0, seq_first_row, none, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
+}
+
+// The same for sequences that go on: the rows of sequence s are the positions seq_len[s] - rows .. seq_len[s] - 1, and
+// every key, the step's own included, is read from the layer's pages: cache [n_pages, 2, nkv, 64, head_dim] bf16.
+extern "C" int cima_attention_extend_tc(const void* qkv, int ld, const int* tile_seq, const int* tile_row0,
+                                        const int* seq_first_row, const void* cache, long long n_pages, const int* table,
+                                        int table_width, int ring, int page_size, const int* seq_slot, const int* seq_len,
+                                        void* out, int ldo, int T, int n_tiles, int nh, int nkv, int hd, float scale,
+                                        int window, int* error_flag, cudaStream_t stream) {
+  if (T <= 0 || n_tiles <= 0) return 0;
+  if (int rc = tc_checks("attention_extend_tc", qkv, ld, out, ldo, nh, nkv, hd, error_flag)) return rc;
+  if (page_size != BN) return cima_fail(CIMA_E_SIZE, "attention_extend_tc: page size %d; this kernel takes %d", page_size, BN);
+  if (!cache || !table || !seq_slot || !seq_len || ((uintptr_t)cache & 15) || n_pages <= 0)
+    return cima_fail(CIMA_E_ARG, "attention_extend_tc: the cache (16-byte aligned), its block table, slots and lengths are needed");
+  if (n_pages * 2 * nkv * BN >= (1ll << 31)) return cima_fail(CIMA_E_SIZE, "attention_extend_tc: %lld pages exceed a tensor map's 32-bit row coordinate", n_pages);
+  const CacheSource c{cache, n_pages, table, seq_slot, seq_len, table_width, ring};
+  if (hd == 64)
+    return launch_attention_tc<64, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, c, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
+  return launch_attention_tc<128, true>(qkv, ld, tile_seq, tile_row0, seq_first_row, c, out, ldo, T, n_tiles, nh, nkv, scale, window, error_flag, stream);
 }

@@ -44,7 +44,8 @@ class StepBatch:
     n_q_tiles: int = 0                # several rows a sequence: blocks of 64 query rows, heaviest first
     q_tile_seq: torch.Tensor = None   # int32 [n_q_tiles] sequence of the block
     q_tile_row0: torch.Tensor = None  # int32 [n_q_tiles] first row of the block among the sequence's rows
-    n_q_tiles_tc: int = 0             # prompts only: the same in blocks of 128 rows
+    max_rows: int = 0                 # most rows that one sequence brings
+    n_q_tiles_tc: int = 0             # the same in blocks of 128 rows
     q_tile_tc_seq: torch.Tensor = None
     q_tile_tc_row0: torch.Tensor = None
     host_seq_slot: np.ndarray = None
@@ -74,7 +75,7 @@ def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, dev
         q_tiles = sorted(((i, r0) for i, c in enumerate(counts) for r0 in range(0, c, Q_TILE)),
                          key=lambda t: -(starts[t[0]] + t[1]))
     NT = len(q_tiles)
-    tc_tiles = [t for t in q_tiles if t[1] % Q_TILE_TC == 0] if prefill else []
+    tc_tiles = [t for t in q_tiles if t[1] % Q_TILE_TC == 0]
     NTC = len(tc_tiles)
     buf = np.empty(3 * T + 3 * B + 1 + W + 2 * NT + 2 * NTC, dtype=np.int32)
     tokens, row_pos, row_seq = buf[0:T], buf[T:2 * T], buf[2 * T:3 * T]
@@ -112,7 +113,7 @@ def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, dev
         dev = host.clone()
     all_in_order = W == T and bool(np.array_equal(want_rows, np.arange(T)))
     return StepBatch(prefill=prefill, n_rows=T, n_seqs=B, n_want=W, max_len=int(seq_len.max()),
-                     want_all_in_order=all_in_order,
+                     want_all_in_order=all_in_order, max_rows=max(counts),
                      tokens=dev[0:T], row_pos=dev[T:2 * T], row_seq=dev[2 * T:3 * T],
                      seq_slot=dev[o:o + B], seq_first_row=dev[o + B:o + 2 * B + 1],
                      seq_len=dev[o + 2 * B + 1:o + 3 * B + 1], want_rows=dev[w0:w0 + W],

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 17
+ABI_VERSION = 18
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -57,6 +57,8 @@ _SIGNATURES = {
     "cima_attention_decode": [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
     "cima_attention_prefill": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
     "cima_attention_extend": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "cima_attention_extend_tc": [_vp, _i, _vp, _vp, _vp, _vp, ctypes.c_longlong, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                                 _f, _i, _vp, _vp],
     "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
     "cima_gemm_tcgen05": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
@@ -407,11 +409,14 @@ class Kernels:
                 and head_dim <= 128 and batch.n_rows == batch.n_seqs):
             return self.attention_decode(qkv, kv, batch.seq_slot, batch.seq_len, out, n_heads, n_kv_heads, head_dim,
                                          scale, window, batch.max_len, early=after_append)
+        many = (qkv.dtype is torch.bfloat16 and head_dim in (64, 128) and qkv.shape[1] % 8 == 0
+                and getattr(batch, "n_q_tiles_tc", 0) > 0 and getattr(batch, "max_rows", 0) >= TC_ATTENTION_MIN_LEN)
+        if from_cache and many and kv.page_size == 64 and kv.storage.numel() // head_dim < 2 ** 31:
+            return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window, kv=kv)
         if (from_cache and qkv.dtype is torch.bfloat16 and kv.page_size == 64 and head_dim % 16 == 0
                 and head_dim <= 128 and qkv.shape[1] % 8 == 0 and getattr(batch, "n_q_tiles", 0) > 0):
             return self.attention_extend(qkv, kv, batch, out, n_heads, n_kv_heads, head_dim, scale, window)
-        if (not from_cache and qkv.dtype is torch.bfloat16 and head_dim in (64, 128) and qkv.shape[1] % 8 == 0
-                and getattr(batch, "n_q_tiles_tc", 0) > 0 and batch.max_len >= TC_ATTENTION_MIN_LEN):
+        if not from_cache and many:
             return self.attention_prefill_tc(qkv, batch, out, n_heads, n_kv_heads, head_dim, scale, window)
         if (not from_cache and qkv.dtype is torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 128
                 and qkv.shape[1] % 8 == 0 and getattr(batch, "n_q_tiles", 0) > 0):
@@ -452,16 +457,27 @@ class Kernels:
             T, batch.q_tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window, self._stream()), "attention_extend")
 
     def attention_prefill_tc(self, qkv: torch.Tensor, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
-                             head_dim: int, scale: float, window: int) -> None:
-        """Flash attention of ragged prompts that start at position 0 on the tcgen05 tensor cores (bf16,
-        head_dim 64 or 128): blocks of 128 query rows, both products with their results in tensor memory.  ``batch``
-        brings the blocks (``q_tile_tc_*``)."""
+                             head_dim: int, scale: float, window: int, kv=None) -> None:
+        """Flash attention of ragged prompts on the tcgen05 tensor cores (bf16, head_dim 64 or 128): blocks of 128
+        query rows, both products with their results in tensor memory.  ``batch`` brings the blocks
+        (``q_tile_tc_*``).  Without ``kv`` the sequences start at position 0 and the keys are the step's own rows;
+        with ``kv`` (a layer's pages, to which the step has appended) the rows of sequence s stand at positions
+        seq_len[s] - rows .. seq_len[s] - 1 and all keys come from the pages."""
         self._need(qkv, "qkv", torch.bfloat16, 2); self._need(out, "out", torch.bfloat16, 2)
         T = qkv.shape[0]
         if tuple(out.shape) != (T, n_heads * head_dim) or batch.n_q_tiles_tc <= 0:
             raise KernelError(f"attention_prefill_tc: out {tuple(out.shape)} or the block list do not fit")
         if self._error_flag is None:
             self._error_flag = torch.zeros(1, dtype=torch.int32, device=qkv.device)
+        if kv is not None:
+            self._need(kv.storage, "cache", torch.bfloat16, 5); self._need(kv.block_table, "block_table", torch.int32, 2)
+            self._check(self.lib.cima_attention_extend_tc(
+                qkv.data_ptr(), qkv.shape[1], batch.q_tile_tc_seq.data_ptr(), batch.q_tile_tc_row0.data_ptr(),
+                batch.seq_first_row.data_ptr(), kv.storage.data_ptr(), kv.storage.shape[0], kv.block_table.data_ptr(),
+                kv.block_table.shape[1], kv.ring_pages, kv.page_size, batch.seq_slot.data_ptr(), batch.seq_len.data_ptr(),
+                out.data_ptr(), out.shape[1], T, batch.n_q_tiles_tc, n_heads, n_kv_heads, head_dim, scale, window,
+                self._error_flag.data_ptr(), self._stream()), "attention_extend_tc")
+            return
         self._check(self.lib.cima_attention_prefill_tc(
             qkv.data_ptr(), qkv.shape[1], batch.q_tile_tc_seq.data_ptr(), batch.q_tile_tc_row0.data_ptr(),
             batch.seq_first_row.data_ptr(), out.data_ptr(),

@@ -33,7 +33,7 @@ def test_decode_batch_and_what_is_refused():
         build_batch([StepEntry(1, [1]), StepEntry(1, [2])], [0, 0], 10, "cpu")
     # a sequence that goes on by several tokens beside one that starts: rows that read the cache, no prompt blocks
     b = build_batch([StepEntry(1, [1, 2, 3], [2]), StepEntry(2, [2, 4])], [7, 0], 10, "cpu")
-    assert not b.prefill and b.n_rows == 5 and b.n_seqs == 2 and b.n_q_tiles_tc == 0
+    assert not b.prefill and b.n_rows == 5 and b.n_seqs == 2 and b.n_q_tiles_tc == 2 and b.max_rows == 3
     assert list(zip(b.q_tile_seq.tolist(), b.q_tile_row0.tolist())) == [(0, 0), (1, 0)]     # blocks of rows, heaviest first
     assert b.row_pos.tolist() == [7, 8, 9, 0, 1] and b.seq_len.tolist() == [10, 2] and b.want_rows.tolist() == [2]
     with pytest.raises(ValueError, match="token ids"):

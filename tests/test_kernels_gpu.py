@@ -187,7 +187,7 @@ def batch_of(seqs, device):
                            row_pos=t(row_pos), row_seq=t(row_seq), seq_slot=t([s[0] for s in seqs]),
                            seq_first_row=t(first), seq_len=t([s[1] + s[2] for s in seqs]),
                            n_rows=len(row_pos), n_seqs=len(seqs), prefill=all(s[1] == 0 for s in seqs),
-                           max_len=max(s[1] + s[2] for s in seqs))
+                           max_len=max(s[1] + s[2] for s in seqs), max_rows=max(s[2] for s in seqs))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -431,6 +431,34 @@ def test_attention_of_sequences_that_go_on(K, nh, nkv, hd, window, ring):
     # the dispatcher takes the same kernel for such a batch
     out2 = torch.full((T, nh * hd), 7.0, dtype=torch.bfloat16, device="cuda")
     K.attention(qkv.cuda(), gpu, bg, out2, nh, nkv, hd, scale, window, True)
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 128), (6, 1, 64)])
+@pytest.mark.parametrize("window", [0, 90, 300])
+def test_attention_of_sequences_that_go_on_by_many_rows_tcgen05(K, nh, nkv, hd, window):
+    """The tcgen05 attention with its keys from the cache's pages (by TMA through the block table): a sequence of 260
+    rows deep into its cache, one that starts, one of 130 rows; stale keys behind every end; windows."""
+    page = 64
+    seqs = [(2, 100, 260), (0, 0, 5), (1, 380, 130)]
+    width = 9
+    order = torch.randperm(4 * width, generator=torch.Generator().manual_seed(6)).tolist()
+    tables = {slot: order[slot * width:(slot + 1) * width] for slot in range(4)}
+    cpu, gpu = make_kv(4 * width, nkv, page, hd, 4, width, 0, window, torch.bfloat16, tables)
+    cpu.storage.copy_(g(*cpu.storage.shape, dtype=torch.bfloat16, seed=hd + window + 1))
+    gpu.storage.copy_(cpu.storage)
+    T = sum(s[2] for s in seqs)
+    scale = 1.0 / math.sqrt(hd)
+    qkv = g(T, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, seed=nh + T)
+    bc, bg = batch_of(seqs, "cpu"), batch_of(seqs, "cuda")
+    want = torch.zeros(T, nh * hd, dtype=torch.float64)
+    REF.attention_plain(qkv, cpu, bc.row_pos, bc.row_seq, bc.seq_slot, bc.seq_first_row, want, nh, nkv, hd, scale, window, True)
+    out = torch.full((T, nh * hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.attention_prefill_tc(qkv.cuda(), bg, out, nh, nkv, hd, scale, window, kv=gpu)
+    assert K.device_errors() == 0
+    assert err(out, want) <= TOL["bfloat16"]
+    out2 = torch.full((T, nh * hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.attention(qkv.cuda(), gpu, bg, out2, nh, nkv, hd, scale, window, True)      # the dispatcher's choice for such a batch
     assert torch.equal(out, out2)
 
 
