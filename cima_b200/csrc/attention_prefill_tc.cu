@@ -4,17 +4,20 @@
 // One block computes 128 query rows of one head.  Both products of a tile of 64 keys run as tcgen05.mma with
 // their results in tensor memory:
 //     S = Q K^T      128 x 64, K-major operands straight from the q/k/v buffer by TMA
-//     O += P V       P is written to shared memory by the softmax threads in the layout the tensor core reads
-//                    (K-major, 128-byte swizzle); V is taken as it lies in the buffer ([keys, dims], dims
-//                    contiguous): for this product the dims are N, so the operand is MN-major
+//     O += P V       P stays in tensor memory: a softmax thread writes its row's 64 probabilities (bfloat16, 32
+//                    words) over the first columns of the S it has just read, and the tensor core takes them from
+//                    there as the A operand; V is taken as it lies in the buffer ([keys, dims], dims contiguous):
+//                    for this product the dims are N, so the operand is MN-major
 // Warp roles (192 threads): warps 0..3 softmax, one thread per query row (a row's maximum and sum need no
 // shuffles; each warp reads the 32 TMEM lanes it may access); warp 4 TMA producer; warp 5 TMEM allocation and
 // MMA issue.  S has two buffers in TMEM, so the tensor cores compute S of the next tile while the softmax of the
-// current one runs.  Two blocks share an SM (112 KB of shared memory and 256 TMEM columns each): a softmax warp
-// alone on its scheduler issues one instruction every four cycles, two hide each other's latencies, and the
-// tensor cores serve one block while the other exponentiates.  Scores, maxima, exponentials and sums are float32 in the base-2 domain; P is rounded to
-// bfloat16 only as operand of P V, the row sums are taken before that rounding.  O is rescaled in TMEM only
-// when a row's maximum has grown by more than 2^8 over the reference of its exponentials.
+// current one runs (a buffer is free for the tile after next once P V of its tile has completed).  Two blocks
+// share an SM (98 KB of shared memory at head_dim 128 and 256 TMEM columns each): a softmax warp alone on its
+// scheduler issues one instruction every four cycles, two hide each other's latencies, and the tensor cores
+// serve one block while the other exponentiates.  Scores, maxima, exponentials and sums are float32 in the
+// base-2 domain; P is rounded to bfloat16 only as operand of P V, the row sums are taken before that rounding.
+// O is rescaled in TMEM only when a row's maximum has grown by more than 2^8 over the reference of its
+// exponentials.
 //
 // Two sources of keys and values, as in the mma.sync kernel: the step's own q/k/v buffer (prompts that start at
 // position 0), or the layer's pages in the cache (sequences that go on by many tokens: their rows stand at positions
@@ -77,18 +80,16 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
   unsigned char* sq = smem;                                    // Q: NH blocks (dims 0..63, 64..127) of 16 KB
   unsigned char* sk = sq + NH * HALF_BYTES;                    // K: [2 stages][NH blocks of 64 dims][64 keys]
   unsigned char* sv = sk + 2 * NH * KHALF_BYTES;               // V: [2 stages][NH blocks of 64 dims][64 keys]
-  unsigned char* sp = sv + 2 * V_BYTES;                        // P: [128 query rows][64 keys]
-  unsigned long long* bars = (unsigned long long*)(sp + HALF_BYTES);
+  unsigned long long* bars = (unsigned long long*)(sv + 2 * V_BYTES);
   unsigned long long* q_full = bars;                           // [1]
   unsigned long long* k_full = bars + 1;                       // [2]
   unsigned long long* k_empty = bars + 3;                      // [2]  K's place is free once S of its tile is done,
   unsigned long long* v_full = bars + 5;                       // [2]  long before V's (after P V): the two rings run
   unsigned long long* v_empty = bars + 7;                      // [2]  apart, so K is fetched two tiles ahead
   unsigned long long* s_full = bars + 9;                       // [2]
-  unsigned long long* s_empty = bars + 11;                     // [2]
-  unsigned long long* p_full = bars + 13;                      // [1]
-  unsigned long long* pv_done = bars + 14;                     // [1]
-  unsigned* tmem_slot = (unsigned*)(bars + 15);
+  unsigned long long* p_full = bars + 11;                      // [1]
+  unsigned long long* pv_done = bars + 12;                     // [1]
+  unsigned* tmem_slot = (unsigned*)(bars + 13);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -108,7 +109,7 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
     mbar_init(q_full, 1);
     for (int s = 0; s < 2; s++) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-      mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], 4);
+      mbar_init(&s_full[s], 1);
     }
     mbar_init(p_full, 4);
     mbar_init(pv_done, 1);
@@ -186,7 +187,8 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
         if (j + 1 < n) {
           const int s1 = (j + 1) & 1;
           ok = mbar_wait(&k_full[s1], ((j + 1) >> 1) & 1, a.error_flag, abort_flag);
-          if (ok && j + 1 >= 2) ok = mbar_wait(&s_empty[s1], (((j + 1) >> 1) - 1) & 1, a.error_flag, abort_flag);
+          // buffer s1 held S of tile j - 1 and then its P: free once P V of tile j - 1 has completed
+          if (ok && j + 1 >= 2) ok = mbar_wait(pv_done, (j - 1) & 1, a.error_flag, abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           issue_s(j + 1);
@@ -195,13 +197,12 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int s = j & 1;
-        {                                               // O += P V(j): 64 keys
-          const unsigned long long pd = umma_smem_desc(smem_u32(sp));
+        {                                               // O += P V(j): 64 keys; P from tensor memory (the first 32 columns of S's buffer)
           // V as it lies in the buffer, [keys][dims]: the dims (N) are contiguous, 16 keys further is 16 rows of 128 bytes
           const unsigned long long vd = umma_smem_desc_mn(smem_u32(sv + (size_t)s * V_BYTES), KHALF_BYTES);
 #pragma unroll
           for (int k = 0; k < BN / UMMA_K; k++)
-            umma_bf16(tm_o, pd + (unsigned long long)(k * 2), vd + (unsigned long long)(k * (UMMA_K * 128 >> 4)), idesc_o, (j | k) ? 1u : 0u);
+            umma_bf16_ts(tm_o, tm_s[s] + (unsigned)(k * (UMMA_K / 2)), vd + (unsigned long long)(k * (UMMA_K * 128 >> 4)), idesc_o, (j | k) ? 1u : 0u);
         }
         umma_commit(&v_empty[s]);
         umma_commit(pv_done);
@@ -230,10 +231,6 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
 #pragma unroll
       for (int c = 0; c < NC; c++) tmem_ld32_issue(tm_s[s] + lane_off + (unsigned)(c * 32), raw[c]);
       tmem_ld_wait();
-      // S's buffer may be overwritten by the tile after next
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[s]);
       // maxima of the raw scores (the scale is positive): four chains instead of one
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (masked) {
@@ -275,12 +272,12 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
           raw[c][e >> 1] = *reinterpret_cast<const unsigned*>(&h2);
         }
       l_run += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
-      // P's place and O are free once the previous tile's P V has completed
-      if (j > 0) {
+      // O may be touched once the previous tile's P V has completed
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
         ok = mbar_wait(pv_done, (j - 1) & 1, a.error_flag, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+        {
 #pragma unroll 1
           for (int c = 0; c < HD / 32; c++) {
             float o[32];
@@ -291,23 +288,27 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
           }
         }
       }
-      unsigned char* prow = sp + (size_t)(r >> 3) * 1024 + (size_t)(r & 7) * 128;
+      // P of the row, 64 bfloat16 as 32 words, over the first 32 columns of its S (this thread alone reads and
+      // writes its lane of the buffer): the A operand of P V, read by the tensor core from tensor memory
+      {
+        unsigned pk[32];
 #pragma unroll
-      for (int c = 0; c < NC; c++) {
-        // keys c*32 .. c*32+31 of the row: 16-byte pieces c * 4 .. + 3 of its 128 bytes, swizzled by the row
+        for (int c = 0; c < NC; c++)
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-          const int piece = c * 4 + q;
-          *reinterpret_cast<uint4*>(prow + ((piece ^ (r & 7)) << 4)) =
-              make_uint4(raw[c][4 * q], raw[c][4 * q + 1], raw[c][4 * q + 2], raw[c][4 * q + 3]);
-        }
+          for (int e = 0; e < 16; e++) pk[c * 16 + e] = raw[c][e];
+        tmem_st32_words(tm_s[s] + lane_off, pk);
       }
-      // P is written: make it visible to the tensor core's reads
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      // a warp is at most one tile ahead of the slowest: were it to arrive for this tile before all four have arrived
+      // for the last one, that phase of the barrier would complete without the slowest warp's P
+      if (j > 0 && !mbar_wait(p_full, (j - 1) & 1, a.error_flag, abort_flag)) { ok = false; break; }
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
+    // A wait on a parity answers for the last phase of that parity.  This warp has S of tile n - 1, so P V of tile
+    // n - 3 is complete, but that of tile n - 2 need not be: asked for tile n - 1 alone, the barrier would answer for
+    // tile n - 3.  (Inside the loop a warp with S of tile j asks for tile j - 1 and cannot be answered for j - 3.)
+    if (ok && n > 1) ok = mbar_wait(pv_done, (n - 2) & 1, a.error_flag, abort_flag);
     if (ok && n > 0) ok = mbar_wait(pv_done, (n - 1) & 1, a.error_flag, abort_flag);
     if (ok && n > 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -356,8 +357,8 @@ int launch_attention_tc(const void* qkv, int ld, const int* tile_seq, const int*
   else rc = make_map(&mk, qkv, T, (long long)(nh + 2 * nkv) * HD, ld, BN);
   if (rc) return rc;
   constexpr int NH = HD / 64;
-  const size_t smem = NH * (size_t)HALF_BYTES + 2 * NH * (size_t)KHALF_BYTES + 2 * (size_t)HD * 128 + HALF_BYTES + 16 * 8 + 16;
-  static_assert(15 * 8 + 8 <= 16 * 8 + 16, "barriers and flags fit their place");
+  const size_t smem = NH * (size_t)HALF_BYTES + 2 * NH * (size_t)KHALF_BYTES + 2 * (size_t)HD * 128 + 14 * 8 + 16;
+  static_assert(13 * 8 + 8 <= 14 * 8 + 16, "barriers and flags fit their place");
   static bool raised = false;
   if (!raised) {
     cudaError_t e = cudaFuncSetAttribute(k_attention_prefill_tc<HD, FROM_CACHE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
