@@ -48,6 +48,10 @@ class GenStats:
 
 
 class Stepper(Protocol):
+    """What the loop needs of a stepper.  One that keeps finished sequences for later prompts also has
+    ``retain_limit`` (> 0), ``adopt(prompts) -> [(slot | None, tokens in common)]``, ``make_room(needs, slots)``,
+    ``retain(slots, histories)`` and takes ``prefill(..., reused=[...])`` (see ``ModelStepper``); the loop uses them
+    only when ``retain_limit`` is positive."""
     max_batch: int                    # most sequences in one batch
     max_position: int                 # most positions a sequence may hold
     cache_tokens: int                 # positions the cache holds in all
