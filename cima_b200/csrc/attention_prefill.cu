@@ -72,13 +72,16 @@ k_attention_prefill(const __nv_bfloat16* __restrict__ qkv, int ld, const int* __
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [2 stages][K|V][BN][ROW]
 
-  const int seq = tile_seq[blockIdx.x];
-  const int q0 = tile_row0[blockIdx.x];               // first query row of this block among the sequence's rows
+  // blocks are numbered (tile, head) with the head running fastest, the tiles heaviest first: the hardware hands
+  // blocks out in that order, so every head's heaviest tile starts before any lighter one
+  const int tile = blockIdx.x / nh;
+  const int seq = tile_seq[tile];
+  const int q0 = tile_row0[tile];                     // first query row of this block among the sequence's rows
   const int first = seq_first_row[seq];
   const int len = seq_first_row[seq + 1] - first;     // rows of the sequence in this step
   const int start = FROM_CACHE ? seq_len[seq] - len : 0;       // position of the sequence's first row
   const int slot = FROM_CACHE ? seq_slot[seq] : 0;
-  const int h = blockIdx.y, kvh = h / (nh / nkv);
+  const int h = blockIdx.x % nh, kvh = h / (nh / nkv);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int kcol = (nh + kvh) * HD, vcol = (nh + nkv + kvh) * HD;
@@ -269,6 +272,7 @@ template <int HD, bool FROM_CACHE>
 int launch_prefill(const void* qkv, int ld, const int* tile_seq, const int* tile_row0, const int* seq_first_row,
                    const void* cache, const CimaPaged& pg, const int* seq_slot, const int* seq_len,
                    void* out, int ldo, int T, int n_tiles, int nh, int nkv, float scale, int window, cudaStream_t stream) {
+  if ((long long)n_tiles * nh > 0x7fffffffll) return cima_fail(CIMA_E_SIZE, "attention_prefill: %d blocks of rows x %d heads exceed one launch", n_tiles, nh);
   auto kern = k_attention_prefill<HD, FROM_CACHE>;
   const size_t smem = (size_t)2 * 2 * BN * (HD + 8) * sizeof(__nv_bfloat16);
   static bool raised = false;
@@ -277,7 +281,7 @@ int launch_prefill(const void* qkv, int ld, const int* tile_seq, const int* tile
     if (e != cudaSuccess) return cima_fail((int)e, "attention_prefill: cannot raise shared memory to %zu bytes: %s", smem, cudaGetErrorString(e));
     raised = true;
   }
-  { int rc_ = cima_launch(kern, dim3(dim3(n_tiles, nh)), dim3(WARPS * 32), (size_t)(smem), stream, 1, (const __nv_bfloat16*)qkv, ld, tile_seq, tile_row0, seq_first_row,
+  { int rc_ = cima_launch(kern, dim3((unsigned)n_tiles * (unsigned)nh), dim3(WARPS * 32), (size_t)(smem), stream, 1, (const __nv_bfloat16*)qkv, ld, tile_seq, tile_row0, seq_first_row,
                                                         (const __nv_bfloat16*)cache, pg, seq_slot, seq_len,
                                                         (__nv_bfloat16*)out, ldo, T, nh, nkv, scale, window); if (rc_) return rc_; }
   return cima_launch_result();

@@ -93,8 +93,10 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
-  const int seq = a.tile_seq[blockIdx.x], r0 = a.tile_row0[blockIdx.x];
+  // blocks are numbered (tile, head) with the head running fastest, the tiles heaviest first: the hardware hands
+  // blocks out in that order, so every head's heaviest tile starts before any lighter one
+  const int tile = blockIdx.x / a.nh, h = blockIdx.x % a.nh, kvh = h / (a.nh / a.nkv);
+  const int seq = a.tile_seq[tile], r0 = a.tile_row0[tile];
   const int row_base = a.seq_first_row[seq];
   const int rows = a.seq_first_row[seq + 1] - row_base;       // rows of the sequence in this step
   const int len = FROM_CACHE ? a.seq_len[seq] : rows;         // positions it holds after the step
@@ -350,6 +352,7 @@ template <int HD, bool FROM_CACHE>
 int launch_attention_tc(const void* qkv, int ld, const int* tile_seq, const int* tile_row0, const int* seq_first_row,
                         const CacheSource& c, void* out, int ldo, int T, int n_tiles, int nh, int nkv, float scale,
                         int window, int* error_flag, cudaStream_t stream) {
+  if ((long long)n_tiles * nh > 0x7fffffffll) return cima_fail(CIMA_E_SIZE, "attention_prefill_tc: %d blocks of rows x %d heads exceed one launch", n_tiles, nh);
   CUtensorMap mq, mk;                                  // boxes of 128 rows (Q) and of 64 rows (K and V) by 64 columns
   int rc = make_map(&mq, qkv, T, (long long)(nh + 2 * nkv) * HD, ld);
   if (rc) return rc;
@@ -367,7 +370,7 @@ int launch_attention_tc(const void* qkv, int ld, const int* tile_seq, const int*
   }
   AttnArgs a{tile_seq, tile_row0, seq_first_row, c.seq_len, c.seq_slot, c.table, c.table_width, c.ring,
              (__nv_bfloat16*)out, ldo, nh, nkv, window, scale, error_flag};
-  { int rc_ = cima_launch(k_attention_prefill_tc<HD, FROM_CACHE>, dim3(n_tiles, nh), dim3(THREADS), smem, stream, 1, mq, mk, a); if (rc_) return rc_; }
+  { int rc_ = cima_launch(k_attention_prefill_tc<HD, FROM_CACHE>, dim3((unsigned)n_tiles * (unsigned)nh), dim3(THREADS), smem, stream, 1, mq, mk, a); if (rc_) return rc_; }
   return cima_launch_result();
 }
 
