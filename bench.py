@@ -118,12 +118,8 @@ def main(argv=None) -> int:
     import numpy as np
     import torch
     import cima_b200
-    from cima_b200.config import Qwen2Config
-    from cima_b200.engine import Model, StepEntry
-    from cima_b200.kernels import Kernels
-    from cima_b200.parts import Runtime
-    from cima_b200.sampling import GenOptions, sampler_state
-    from cima_b200.weights import random_tensor
+    from cima_b200.engine import StepEntry
+    from cima_b200.sampling import GenOptions
 
     pk = peaks()
     raw = dict(QWEN25_7B)
@@ -133,27 +129,20 @@ def main(argv=None) -> int:
     layers_full = raw["num_hidden_layers"]
     if a.layers:
         raw["num_hidden_layers"] = a.layers
-    cfg = Qwen2Config.from_dict(raw)
     dev = "cuda:0"
     torch.cuda.set_device(0)
-    K = Kernels(verbose=True)
-    rt = Runtime(kernels=K, dtype=torch.bfloat16, device=dev)
-    model = Model(cfg.model_spec(), rt)
-    plan = model.plan()
-    # random weights straight on the device, tensor by tensor (seeded by name, as the random-weights mode)
-    tensors = {n: random_tensor(s, 0, n, torch.bfloat16, device=dev) for n, s in plan.items()}
-    model.load(tensors)
-    del tensors
-    torch.cuda.empty_cache()
     max_batch = max(a.batch, 1 if a.no_points else 64)
     per_seq = a.prompt + a.steps + a.warmup + 64
-    # room for the batches of the decode runs, and for the one 2,048-token prompt of the prefill figure
-    model.make_cache(max_tokens=max(max_batch * (-(-per_seq // 64) * 64), 2048 + 64), max_seqs=max_batch,
-                     extra_state=sampler_state())
+    # Random weights drawn on the device, tensor by tensor (seeded by name, as the random-weights mode); a cache with
+    # room for the batches of the decode runs and for the one 2,048-token prompt of the prefill figure.
     # e2e below is measured with every step's input tokens copied from pinned host memory (pipeline off);
-    # "e2e_pipelined" is the default mode of the library, where the next step is queued before the host has
+    # "pipelined" is the default mode of the library, where the next step is queued before the host has
     # read the current one's tokens and its inputs never leave the device
-    lm = cima_b200.LM(model, eos_ids=(), max_batch=max_batch, pipeline=False)
+    lm = cima_b200.load(config=raw, seed=0, draw="device", dtype="bfloat16", device=dev, max_seqs=max_batch,
+                        max_tokens=max(max_batch * (-(-per_seq // 64) * 64), 2048 + 64), max_batch=max_batch,
+                        pipeline=False, verbose=True)
+    model, cfg = lm.model, lm.config
+    K = model.rt.kernels
     st = lm.stepper
     greedy = GenOptions(temperature=0.0, repeat_penalty=1.0, max_tokens=a.steps, ignore_eos=True)
     rng = np.random.default_rng(0)

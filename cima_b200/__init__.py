@@ -3,6 +3,8 @@
     import cima_b200
     lm = cima_b200.load("model_dir", dtype="bfloat16", max_tokens=8192)
     results = lm.generate([[1, 2, 3], [4, 5]], temperature=0, max_tokens=32)
+    lm = cima_b200.load(config={...config.json keys...}, seed=0)     # random weights, no folder
+    weights = lm.state_dict()                                         # tensors by their checkpoint names
 
 A model folder holds ``config.json`` and ``model.safetensors``; the model class is chosen by
 config.json through the architecture registry.  ``cima_b200.write_random_model`` makes such a folder
@@ -25,11 +27,16 @@ __version__ = "0.1.0"
 class LM:
     """A loaded model with its cache, stepper and generation loop."""
 
-    def __init__(self, model, eos_ids: Sequence[int] = (), max_batch: int = 64, pipeline: bool = True, retain: int = 0):
+    def __init__(self, model, eos_ids: Sequence[int] = (), max_batch: int = 64, pipeline: bool = True, retain: int = 0,
+                 use_graphs: bool = True):
         from .engine import GenerationLoop, ModelStepper
         self.model = model
-        self.stepper = ModelStepper(model, max_batch=max_batch, pipeline=pipeline, retain=retain)
+        self.stepper = ModelStepper(model, max_batch=max_batch, use_graphs=use_graphs, pipeline=pipeline, retain=retain)
         self.loop = GenerationLoop(self.stepper, eos_ids)
+
+    def state_dict(self):
+        """The model's tensors by their checkpoint names, as kept on the device (``Model.state_dict``)."""
+        return self.model.state_dict()
 
     @property
     def spec(self):
@@ -87,16 +94,30 @@ def eos_ids_of(folder: str) -> List[int]:
     return out
 
 
-def load(folder: str, dtype: str = "bfloat16", max_tokens: int = 8192, max_seqs: Optional[int] = None,
+def _eos_ids_of_config(raw) -> List[int]:
+    v = raw.get("eos_token_id") if isinstance(raw, dict) else None
+    return [t for t in (v if isinstance(v, list) else [v]) if isinstance(t, int) and not isinstance(t, bool)]
+
+
+def load(folder: Optional[str] = None, dtype: str = "bfloat16", max_tokens: int = 8192, max_seqs: Optional[int] = None,
          max_batch: int = 64, device: str = "cuda:0", verbose: bool = True, pipeline: bool = True,
-         retain: int = 0) -> LM:
-    """``pipeline``: queue the next decode step before the host has read the current one's tokens
+         retain: int = 0, use_graphs: bool = True, config=None, seed: int = 0, draw: str = "cpu") -> LM:
+    """A model from ``folder`` (config.json, model.safetensors), or from ``config`` (a config.json dict or a typed
+    configuration) and ``seed`` with random weights in memory (``draw``: see ``engine.load_model``).
+    ``pipeline``: queue the next decode step before the host has read the current one's tokens
     (the tokens are fed forward on the device).  ``retain``: how many finished sequences stay in the cache for
     later prompts that begin with the same tokens (the next turn of a conversation runs only what is new; the
-    reference keeps its one sequence so, src/models/mod.rs:1022-1058); they give way when a batch needs the room."""
+    reference keeps its one sequence so, src/models/mod.rs:1022-1058); they give way when a batch needs the room.
+    ``use_graphs``: record decode steps as CUDA graphs (a model with a part that is unfit for it decodes step by
+    step whatever is asked)."""
     from .engine import load_model
-    model = load_model(folder, dtype=dtype, max_tokens=max_tokens, max_seqs=max_seqs, device=device, verbose=verbose)
-    return LM(model, eos_ids_of(folder), max_batch=max_batch, pipeline=pipeline, retain=retain)
+    model = load_model(folder, dtype=dtype, max_tokens=max_tokens, max_seqs=max_seqs, device=device, verbose=verbose,
+                       config=config, seed=seed, draw=draw)
+    if folder is not None:
+        eos = eos_ids_of(folder)
+    else:
+        eos = _eos_ids_of_config(config.to_dict() if hasattr(config, "to_dict") else config)
+    return LM(model, eos, max_batch=max_batch, pipeline=pipeline, retain=retain, use_graphs=use_graphs)
 
 
 def write_random_model(folder: str, config: Union[dict, Qwen2Config], seed: int = 0) -> None:

@@ -230,6 +230,19 @@ class KVCache:
             raise CacheFull(f"slot {slot} cannot grow to {length} positions: {e} "
                             f"(the cache holds {self.max_tokens} positions in pages of {self.page_size})") from e
 
+    def must_fit(self, wanted: Sequence[Tuple[int, int]]) -> None:
+        """Raise (``CapacityError`` / ``CacheFull``) unless every (slot, length) of ``wanted`` can be reserved
+        together; takes nothing.  A step asks this before it reserves anything, so one that does not fit leaves
+        no sequence with pages it did not commit."""
+        for slot, length in wanted:
+            if length > self.max_position:
+                raise CapacityError(f"slot {slot}: {length} positions exceed the model's max_position {self.max_position}")
+        for g in self.groups:
+            need = sum(max(0, g.pages_needed(length) - len(g.pages_of[slot])) for slot, length in wanted)
+            if need > g.pool.free:
+                raise CacheFull(f"the step needs {need} more pages of group {g.index}, {g.pool.free} are free "
+                                f"(the cache holds {self.max_tokens} positions in pages of {self.page_size})")
+
     def commit(self, slot: int, length: int) -> None:
         """Record that ``slot`` now holds ``length`` positions (after the step that wrote them)."""
         for g in self.groups:

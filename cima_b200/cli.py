@@ -1,6 +1,7 @@
 """Command line in the manner of the reference's ``cima`` (src/main.rs:19-70, :220-270):
 
     cima run <MODEL_DIR> [TOKEN_ID ...] [--prompts FILE] [--dtype D] [--max-seq N] [--PARAM VALUE]...
+    cima run --random-shape NAME [--weights-seed S] [TOKEN_ID ...] ...
     cima bench <MODEL_DIR> [-n TOKENS] [--iters N] [--batch B] [--prompt-len P]
     cima random <OUT_DIR> --shape NAME | --config FILE [--seed S]
     cima show <MODEL_DIR>
@@ -28,6 +29,8 @@ cima_b200 — generation library for the Qwen2 dense decoder on one B200
 
 Usage:
   cima run <MODEL_DIR> [TOKEN_ID ...]   Generate from a prompt of token ids (--prompts FILE: one per line)
+       --random-shape NAME                instead of MODEL_DIR: a known shape with random weights in memory
+       --weights-seed S                   seed of those weights (default 0)
        --dtype bfloat16|float32           precision of the whole model (default bfloat16)
        --max-seq N                        positions the cache holds in all (default 8192)
        --PARAM VALUE                      generation parameters (see `cima run --help`)
@@ -36,7 +39,7 @@ Usage:
   cima random <OUT_DIR> --shape NAME | --config FILE [--seed S]
                                         Write a model folder with seeded random weights
   cima show <MODEL_DIR>                 Show the model's configuration and layers
-  cima selftest                         A tiny random model against the plain implementation
+  cima selftest                         A tiny random model: both precisions, twice, must agree
   cima help                             Show this help
 """
 
@@ -68,9 +71,18 @@ def cmd_run(args: List[str]) -> int:
         print("usage: cima run <MODEL_DIR> [TOKEN_ID ...] [--prompts FILE] [--dtype D] [--max-seq N] [--PARAM VALUE]...\n")
         print(render_help(), end="")
         return 0
-    if not args:
-        raise SystemExit("cima run: a model folder is needed")
-    model_dir, rest = args[0], list(args[1:])
+    rest = list(args)
+    shape = _flag(rest, "--random-shape")
+    weights_seed = int(_flag(rest, "--weights-seed", "0"))
+    model_dir = None
+    if shape is None:
+        if not rest or rest[0].startswith("--"):
+            raise SystemExit("cima run: a model folder (or --random-shape NAME) is needed")
+        model_dir = rest.pop(0)
+    else:
+        from .config.shapes import SHAPES
+        if shape not in SHAPES:
+            raise SystemExit(f"cima run: unknown shape '{shape}' (known: {', '.join(sorted(SHAPES))})")
     dtype = _flag(rest, "--dtype", "bfloat16")
     max_seq = int(_flag(rest, "--max-seq", "8192"))
     prompts_file = _flag(rest, "--prompts")
@@ -96,8 +108,12 @@ def cmd_run(args: List[str]) -> int:
     if not prompts:
         raise SystemExit("cima run: no prompt (token ids on the command line or --prompts FILE)")
     import cima_b200
-    print(f"loading {model_dir} …", file=sys.stderr)
-    lm = cima_b200.load(model_dir, dtype=dtype, max_tokens=max_seq)
+    if model_dir is not None:
+        print(f"loading {model_dir} …", file=sys.stderr)
+        lm = cima_b200.load(model_dir, dtype=dtype, max_tokens=max_seq)
+    else:
+        print(f"random weights of shape {shape}, seed {weights_seed} …", file=sys.stderr)
+        lm = cima_b200.load(config=SHAPES[shape], seed=weights_seed, dtype=dtype, max_tokens=max_seq)
     t0 = time.perf_counter()
     results = lm.generate(prompts, opts)
     total = time.perf_counter() - t0
@@ -174,6 +190,43 @@ def cmd_show(args: List[str]) -> int:
     return 0
 
 
+def cmd_selftest(args: List[str]) -> int:
+    """A tiny model with random weights in memory, on the GPU: the same prompts generate the same tokens twice
+    (greedy and sampled, with graphs and run-ahead), in 32-bit and in bfloat16; a step's bfloat16 logits stay
+    within rounding of the 32-bit ones; the cache ends empty.  (The reference's selftest drives its real
+    generation path over stand-in weights the same way, src/selftest.rs:184-337.)"""
+    import cima_b200
+    from .config.shapes import SHAPES
+    from .engine import StepEntry
+    prompts = [[5, 17, 3, 200, 411, 9, 1], [42], [7, 7, 7, 300, 2, 1, 0, 99, 100, 101, 511, 250, 3]]
+    chains = (dict(temperature=0.0, repeat_penalty=1.0), dict(temperature=0.8, top_k=40, top_p=0.9, repeat_penalty=1.1, seed=3))
+    logits = {}
+    for dtype in ("float32", "bfloat16"):
+        lm = cima_b200.load(config=SHAPES["tiny-a"], seed=7, dtype=dtype, max_tokens=512, verbose=False)
+        for opts in chains:
+            first = [r.tokens for r in lm.generate(prompts, max_tokens=12, **opts)]
+            again = [r.tokens for r in lm.generate(prompts, max_tokens=12, **opts)]
+            if first != again or any(len(t) != 12 for t in first):
+                print(f"selftest FAILED ({dtype}, {opts}): {first} then {again}", file=sys.stderr)
+                return 1
+        (slot,) = lm.model.cache.open(1)
+        try:
+            logits[dtype] = lm.step([StepEntry(slot, prompts[2], list(range(len(prompts[2]))))]).float().cpu()
+        finally:
+            lm.model.cache.close([slot])
+        lm.model.cache.check()
+        if lm.model.cache.slots.held:
+            print(f"selftest FAILED ({dtype}): {lm.model.cache.slots.held} slots still held", file=sys.stderr)
+            return 1
+        print(f"selftest {dtype}: ok ({lm.model.rt.kernels.launches} kernel launches)")
+    worst = (logits["float32"] - logits["bfloat16"]).abs().max().item()
+    if not worst <= 2e-2:
+        print(f"selftest FAILED: bfloat16 logits are {worst:.3g} from the 32-bit ones", file=sys.stderr)
+        return 1
+    print(f"selftest: bfloat16 within {worst:.2g} of 32-bit")
+    return 0
+
+
 def main(argv=None) -> int:
     args = list(sys.argv[1:] if argv is None else argv)
     if not args or args[0] in ("help", "--help", "-h"):
@@ -189,11 +242,7 @@ def main(argv=None) -> int:
     if cmd == "show":
         return cmd_show(rest)
     if cmd == "selftest":
-        import os
-        sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-        import __graft_entry__
-        __graft_entry__.smoke()
-        return 0
+        return cmd_selftest(rest)
     print(USAGE, end="")
     print(f"unknown command '{cmd}'", file=sys.stderr)
     return 2

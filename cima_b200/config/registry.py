@@ -11,7 +11,7 @@ from __future__ import annotations
 import json
 import os
 from dataclasses import dataclass
-from typing import Any, Callable, Dict, Optional
+from typing import Any, Callable, Dict
 
 from .specs import ModelSpec
 
@@ -22,8 +22,6 @@ class ArchitectureEntry:
     model_type: str                             # e.g. "qwen2"
     parse: Callable[[Dict[str, Any]], Any]      # config.json dict -> typed configuration
     spec: Callable[[Any], ModelSpec]            # typed configuration -> ModelSpec
-    # typed configuration, seed -> {tensor name: tensor}; used by the random-weights mode
-    random_tensors: Optional[Callable[[Any, int], Dict[str, Any]]] = None
 
 
 _BY_NAME: Dict[str, ArchitectureEntry] = {}

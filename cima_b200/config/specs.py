@@ -35,16 +35,18 @@ class PositionSpec:
 
 @dataclass(frozen=True)
 class MixerSpec:
+    """Only ``kind`` and ``hidden`` are every mixer's; the fields after them describe an attention and keep their
+    defaults for a mixer that has no heads (a recurrence, a convolution), which puts its own sizes in ``params``."""
     kind: str                    # "attention"
     hidden: int
-    n_heads: int
-    n_kv_heads: int
-    head_dim: int
-    qkv_bias: bool
-    out_bias: bool
-    window: int                  # 0 = every earlier key; w > 0 = the last w keys
-    scale: float                 # factor of q.k before the softmax
-    position: PositionSpec
+    n_heads: int = 0
+    n_kv_heads: int = 0
+    head_dim: int = 0
+    qkv_bias: bool = False
+    out_bias: bool = False
+    window: int = 0              # 0 = every earlier key; w > 0 = the last w keys
+    scale: float = 0.0           # factor of q.k before the softmax
+    position: Optional[PositionSpec] = None
     # Site (index into ModelSpec.schedule) whose keys and values this layer reads instead of
     # writing its own; None = own cache.
     cache_from: Optional[int] = None

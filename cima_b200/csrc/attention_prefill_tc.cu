@@ -26,7 +26,7 @@
 // Every wait on an mbarrier is bounded (2 s); a wait that runs out sets *error_flag, and all roles leave their
 // loops, free the tensor memory and return.
 //
-// The reference's prefill attention is k_attn_prefill_f16 (src/kernels.cu:915-1000): one warp per query row,
+// The reference's prefill attention is k_attn_prefill_tiled (src/kernels.cu:659-753): one warp per query row,
 // online softmax on CUDA cores; it has no tensor-core attention.
 #include "tcgen05.cuh"
 

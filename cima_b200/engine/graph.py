@@ -33,10 +33,13 @@ class DecodeGraph:
         self.seq_slot, self.seq_first_row, self.seq_len = m[3 * B:4 * B], m[4 * B:5 * B + 1], m[5 * B + 1:6 * B + 1]
         self.params = torch.zeros(B, 4, dtype=torch.float32, device=dev)
         self.chosen = torch.zeros(B, dtype=torch.int32, device=dev)
+        # What a recorded step may know on the host is what every replay shares: the number of sequences and their
+        # rows (one each).  Slots, positions and lengths change from replay to replay and exist on the device only
+        # (``host_seq_slot`` / ``host_seq_len`` stay None, ``max_len`` 0 = unknown).
         self.batch = StepBatch(prefill=False, n_rows=B, n_seqs=B, n_want=B, max_len=0, want_all_in_order=True,
                                tokens=self.tokens, row_pos=self.row_pos, row_seq=self.row_seq,
                                seq_slot=self.seq_slot, seq_first_row=self.seq_first_row, seq_len=self.seq_len,
-                               want_rows=self.row_seq)
+                               want_rows=self.row_seq, max_rows=1, host_seq_first_row=np.arange(B + 1, dtype=np.int32))
         self.graph = None
         self.slots: List[int] = []
 

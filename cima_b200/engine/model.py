@@ -20,7 +20,7 @@ from ..config.specs import ModelSpec
 from ..parts import Linear, Runtime, build_block, build_norm
 from ..parts.linear import FOLDED_NORM_ROWS
 from ..parts.norm import RowsInfo
-from ..weights.loader import TensorSpec, load_tensors, tensor_names
+from ..weights.loader import TensorSpec, tensor_names
 from .batch import StepBatch, StepEntry, build_batch
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
@@ -70,15 +70,37 @@ class Model:
             pats.append(self.spec.head_name)
         return pats
 
-    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+    def load(self, tensors) -> None:
+        """``tensors``: name -> tensor, a dict or a ``TensorSource`` that fetches each tensor when it is asked for
+        (every name of the plan is asked for once)."""
         s = self.spec
-        self.embedding = self.rt.matrix(tensors[s.embed_name])
+        table = tensors[s.embed_name]
+        self.embedding = self.rt.matrix(table)
+        if s.tie_head:
+            self.head = Linear(self.embedding, None, self.rt)     # one copy on the device serves both
+        del table
         for b in self.blocks:
             b.load(tensors)
         self.final_norm.load(tensors, s.final_norm_name)
-        self.head = Linear(tensors[s.embed_name] if s.tie_head else tensors[s.head_name], None, self.rt)
-        if s.tie_head and self.head.weight.dtype == self.embedding.dtype:
-            self.head.weight = self.embedding                 # one copy on the device
+        if not s.tie_head:
+            self.head = Linear(tensors[s.head_name], None, self.rt)
+
+    def state_dict(self) -> Dict[str, torch.Tensor]:
+        """Every tensor of the plan by its name, as it is kept on the device (matrices in the model's precision or
+        the 32 bits they were stored in, vectors in float32); stacked matrices come back as views of their rows."""
+        s = self.spec
+        out: Dict[str, torch.Tensor] = {s.embed_name: self.embedding}
+        for b in self.blocks:
+            out.update(b.state())
+        out.update(self.final_norm.state(s.final_norm_name))
+        if not s.tie_head:
+            out[s.head_name] = self.head.weight
+        return out
+
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step may be recorded as a CUDA graph: every layer's parts and the final norm say so."""
+        return all(getattr(b, "graph_safe", False) for b in self.blocks) and getattr(self.final_norm, "graph_safe", False)
 
     def weight_bytes(self) -> int:
         """Bytes a decode step reads of the weights: every block, final norm and head once
@@ -105,10 +127,7 @@ class Model:
         from .fit import forecast
         sched = self.spec.schedule
         shares = [site for site, layer in enumerate(sched) if self.spec.layers[layer].mixer.cache_from is not None]
-        widest = 0
-        for b in self.spec.layers:
-            widest = max(widest, 2 * getattr(b.feed_forward, "intermediate", 0),
-                         (b.mixer.n_heads + 2 * b.mixer.n_kv_heads) * b.mixer.head_dim)
+        widest = max([int(getattr(b, "scratch_row", lambda: 0)()) for b in self.blocks] + [self.spec.hidden])
         return forecast(self.plan(), [self.blocks[layer].cache_requests(site) for site, layer in enumerate(sched)],
                         self.rt.dtype, max_tokens, self.spec.hidden, self.spec.vocab, widest, page_size, shares,
                         extra_state, max_seqs or 0)
@@ -125,6 +144,8 @@ class Model:
             if not cache.slots.is_held(e.slot):
                 raise ValueError(f"slot {e.slot} is not open")
         starts = [cache.length(e.slot) for e in entries]
+        # the whole step fits or nothing is taken: a step that fails leaves the cache as it found it
+        cache.must_fit([(e.slot, s + len(e.tokens)) for e, s in zip(entries, starts)])
         limit = cache.most_tokens_going_on()
         if limit is not None and any(starts) and max(len(e.tokens) for e in entries) > limit:
             return self._step_in_rounds(entries, limit)
@@ -225,23 +246,45 @@ def settle_head(spec: ModelSpec, stored: Sequence[str], warn=None) -> ModelSpec:
     return dataclasses.replace(spec, tie_head=True)
 
 
-def load_model(folder: str, dtype="bfloat16", max_tokens: int = 4096, max_seqs: Optional[int] = None,
-               device="cuda:0", kernels=None, verbose: bool = True) -> Model:
-    """A model from a folder with config.json and model.safetensors, its class chosen by config.json."""
+def load_model(folder: Optional[str] = None, dtype="bfloat16", max_tokens: int = 4096, max_seqs: Optional[int] = None,
+               device="cuda:0", kernels=None, verbose: bool = True, config=None, seed: int = 0,
+               draw: str = "cpu") -> Model:
+    """A model from a folder with config.json and model.safetensors, or, without a folder, from ``config`` (a
+    config.json dict or the architecture's typed configuration) with random weights drawn from ``seed``; its
+    class is chosen by the configuration either way, and both go through the same steps: the fit check, the parts'
+    ``load`` from a source that hands out one tensor at a time, the cache.  ``draw``: where the random values are
+    drawn, "cpu" (the values that ``write_random_model`` stores for this seed) or "device" (the device's own
+    generator: other values, seconds instead of a minute for a 7B shape).  The reference's in-memory stand-in for
+    a checkpoint takes the same road as a file (src/selftest.rs:23-159)."""
     from ..kernels import Kernels
-    raw = read_config_json(folder)
+    from ..weights.loader import CheckpointTensors, RandomTensors
+    if (folder is None) == (config is None):
+        raise ValueError("load_model takes a model folder or a configuration, one of the two")
+    if folder is not None:
+        raw = read_config_json(folder)
+    else:
+        raw = config.to_dict() if hasattr(config, "to_dict") else dict(config)
     entry = lookup_architecture(raw)
-    config = entry.parse(raw)
-    spec = settle_head(entry.spec(config), tensor_names(folder),
-                       warn=(lambda m: print(f"[cima_b200] {m}", file=sys.stderr, flush=True)) if verbose else None)
+    typed = entry.parse(raw)
+    spec = entry.spec(typed)
+    if folder is not None:
+        spec = settle_head(spec, tensor_names(folder),
+                           warn=(lambda m: print(f"[cima_b200] {m}", file=sys.stderr, flush=True)) if verbose else None)
     rt = Runtime(kernels=kernels if kernels is not None else Kernels(verbose=verbose),
                  dtype=parse_dtype(dtype), device=device)
     model = Model(spec, rt)
-    model.config = config                                   # the architecture's typed configuration, as parsed
+    model.config = typed                                    # the architecture's typed configuration, as parsed
     from ..sampling.sampler import sampler_state
     from .fit import check_fit
     check_fit(model.forecast(max_tokens, max_seqs, extra_state=sampler_state()), device)     # before anything is allocated
-    model.load(load_tensors(folder, model.plan(), ignore=model.ignorable(),
-                            optional_prefixes=spec.optional_prefixes))
+    if folder is not None:
+        source = CheckpointTensors(folder, model.plan(), ignore=model.ignorable(), optional_prefixes=spec.optional_prefixes)
+    else:
+        if draw not in ("cpu", "device"):
+            raise ValueError(f"draw '{draw}' is neither 'cpu' nor 'device'")
+        source = RandomTensors(model.plan(), seed, torch.bfloat16, device if draw == "device" else "cpu")
+    with source:
+        model.load(source)
+    model.load_peak_host_bytes = source.peak_bytes          # most bytes of fetched tensors alive at once while loading
     model.make_cache(max_tokens, max_seqs, extra_state=sampler_state())
     return model

@@ -21,7 +21,10 @@ MIN_REUSE = 16     # a finished sequence is taken up again only for at least thi
 class ModelStepper:
     def __init__(self, model, max_batch: int = 64, use_graphs: bool = True, pipeline: bool = True, retain: int = 0):
         self.model = model
-        self.pipeline = pipeline
+        # Run-ahead queues a step that a sequence may turn out not to need.  Keys and values written so are simply
+        # beyond the sequence's end; state of fixed size that a mixer keeps per sequence would have taken one token
+        # too many, so a model with such state decodes without run-ahead.
+        self.pipeline = pipeline and not model.cache.has_mixer_state
         # Finished sequences whose keys and values stay in the cache (slot -> the tokens they stand for), newest
         # last, at most ``retain`` of them: a later prompt that begins with the same tokens goes on from there and
         # runs only what is new.  The reference keeps its one sequence so (session_ids and the incremental prefill,
@@ -32,12 +35,14 @@ class ModelStepper:
         self._inflight = {}           # slot -> steps queued beyond the committed length
         self._pinned = [None, None]
         self._pin_next = 0
-        self.use_graphs = use_graphs and torch.device(model.rt.device).type == "cuda"
+        # a part that reads the batch on the host, or says nothing about it, cannot be recorded: step by step then
+        self.use_graphs = (use_graphs and torch.device(model.rt.device).type == "cuda"
+                           and getattr(model, "graph_safe", False))
         self._graphs = {}
         self._armed = None            # (graph, slots) whose device-side inputs are those of the next step
-        self.sampler = DeviceSampler(model)
         cache = model.cache
         self.max_batch = max(1, min(max_batch, cache.n_slots))
+        self.sampler = DeviceSampler(model, max_rows=self.max_batch)
         self.max_position = min(model.spec.max_position, cache.max_tokens)
         self.cache_tokens = cache.max_tokens
         self.page_size = cache.page_size
@@ -196,8 +201,11 @@ class ModelStepper:
 
     def _drain(self) -> None:
         if self._flight is not None:
+            # the dropped step has run: the graph's positions and lengths on the device are one past the cache's
+            # committed lengths, so the next step loads them anew
             self._read(self._flight, ())
             self._flight = None
+            self._armed = None
         self._inflight.clear()
 
     def _decode_pipelined(self, slots, last_tokens, options) -> List[int]:

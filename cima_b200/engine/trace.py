@@ -46,10 +46,10 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines, out
             logits = model.step(entries)
             if logits.shape[0] > 0:
                 arr = logits.detach().float().cpu().numpy().astype("<f4", copy=False)
+                model.check_device()                    # before the file appears: a reader never sees invalid logits
                 tmp = os.path.join(out_dir, f".{step}.f32.tmp")
                 arr.tofile(tmp)
                 os.replace(tmp, os.path.join(out_dir, f"{step}.f32"))
-                model.check_device()
             elif device != "cpu":
                 import torch
                 torch.cuda.synchronize()

@@ -100,6 +100,7 @@ class Kernels:
             fn.restype = ctypes.c_int
         self.launches = 0
         self._scratch_bufs = {}
+        self._retired = []          # replaced scratch buffers, kept alive for the graphs recorded with them
         self._error_flag = None
 
     # ------------------------------------------------------------------ plumbing
@@ -353,8 +354,14 @@ class Kernels:
                                                     self._error_flag.data_ptr(), self._stream()), "gemm_tcgen05_pair")
 
     def device_errors(self) -> int:
-        """The error flag that a bounded wait inside a kernel sets when it runs out (synchronises)."""
-        return 0 if self._error_flag is None else int(self._error_flag.item())
+        """The error flag that a bounded wait inside a kernel sets when it runs out (synchronises).  Reading it
+        clears it: a later, sound step is not blamed for an earlier one."""
+        if self._error_flag is None:
+            return 0
+        v = int(self._error_flag.item())
+        if v:
+            self._error_flag.zero_()
+        return v
 
     # ------------------------------------------------------------------ attention
     def rope_append(self, qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, row_pos, row_seq, seq_slot,
@@ -524,9 +531,12 @@ class Kernels:
 
     def _scratch(self, name: str, numel: int, device) -> torch.Tensor:
         """Float32 scratch that lives as long as this object (grown on demand, outside graph capture:
-        a captured step always follows an eager one of the same sizes)."""
+        a captured step always follows an eager one of the same sizes).  A buffer that a larger one replaces is
+        kept, not freed: a captured step holds the address it was recorded with and goes on writing there."""
         t = self._scratch_bufs.get(name)
         if t is None or t.numel() < numel or t.device != torch.device(device):
+            if t is not None:
+                self._retired.append(t)
             t = self._scratch_bufs[name] = torch.empty(numel, dtype=torch.float32, device=device)
         return t
 

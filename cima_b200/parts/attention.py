@@ -48,18 +48,35 @@ class Attention:
 
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str, names: Dict[str, str]) -> None:
         s = self.spec
-        ws = [tensors[f"{prefix}{names[k]}.weight"] for k in ("q", "k", "v")]
-        if len({w.dtype for w in ws}) > 1:
-            ws = [w.float() for w in ws]
         bias = None
         if s.qkv_bias:
             bias = torch.cat([tensors[f"{prefix}{names[k]}.bias"].float() for k in ("q", "k", "v")])
-        self.qkv = Linear(torch.cat(ws, dim=0), bias, self.rt)
+        self.qkv = Linear([tensors[f"{prefix}{names[k]}.weight"] for k in ("q", "k", "v")], bias, self.rt)
         ob = tensors[f"{prefix}{names['o']}.bias"] if s.out_bias else None
         self.out = Linear(tensors[f"{prefix}{names['o']}.weight"], ob, self.rt)
 
     def nbytes(self) -> int:
         return self.qkv.nbytes() + self.out.nbytes()
+
+    def state(self, prefix: str, names: Dict[str, str]) -> Dict[str, torch.Tensor]:
+        """The tensors of ``plan`` back out of the stacked matrices, as they are kept on the device."""
+        out: Dict[str, torch.Tensor] = {}
+        r = 0
+        for key, rows in (("q", self.qd), ("k", self.kvd), ("v", self.kvd)):
+            out[f"{prefix}{names[key]}.weight"] = self.qkv.weight[r:r + rows]
+            if self.qkv.bias is not None:
+                out[f"{prefix}{names[key]}.bias"] = self.qkv.bias[r:r + rows]
+            r += rows
+        out[f"{prefix}{names['o']}.weight"] = self.out.weight
+        if self.out.bias is not None:
+            out[f"{prefix}{names['o']}.bias"] = self.out.bias
+        return out
+
+    def scratch_row(self) -> int:
+        """Values of the widest activation row a step of this part holds (its q | k | v row)."""
+        return self.qd + 2 * self.kvd
+
+    graph_safe = True              # a decode step reads nothing of the batch on the host
 
     # ------------------------------------------------------------------ cache
     def cache_requests(self, site: int) -> List[object]:

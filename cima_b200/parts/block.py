@@ -43,6 +43,30 @@ class PreNormBlock:
     def cache_requests(self, site: int) -> List[object]:
         return list(self.mixer.cache_requests(site))
 
+    def state(self) -> Dict[str, torch.Tensor]:
+        """The layer's tensors by name as they are kept on the device (the inverse of ``load``).  A part offers
+        ``state`` with the arguments of its ``plan``; one that does not cannot be written out."""
+        s = self.spec
+        out: Dict[str, torch.Tensor] = {}
+        for part, args in ((self.mixer_norm, (f"{s.prefix}{s.names['mixer_norm']}.weight",)), (self.mixer, (s.prefix, s.names)),
+                           (self.ffn_norm, (f"{s.prefix}{s.names['ffn_norm']}.weight",)), (self.feed_forward, (s.prefix, s.names))):
+            if not hasattr(part, "state"):
+                raise NotImplementedError(f"{type(part).__name__} of layer {self.layer} offers no state(): its tensors "
+                                          f"cannot be given back by name")
+            out.update(part.state(*args))
+        return out
+
+    def scratch_row(self) -> int:
+        """Values of the widest activation row that a step holds inside this layer (sizes the memory forecast)."""
+        return max(int(getattr(p, "scratch_row", lambda: 0)()) for p in (self.mixer, self.feed_forward))
+
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step of this layer may be recorded as a CUDA graph: every part says so itself
+        (``graph_safe = True``: it reads nothing of the batch on the host and keeps its buffers' addresses); a part
+        that says nothing is taken as unfit, and the stepper then decodes step by step."""
+        return all(getattr(p, "graph_safe", False) for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward))
+
     def nbytes(self) -> int:
         return self.mixer_norm.nbytes() + self.mixer.nbytes() + self.ffn_norm.nbytes() + self.feed_forward.nbytes()
 

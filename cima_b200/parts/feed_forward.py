@@ -38,6 +38,16 @@ class GatedMLP:
     def nbytes(self) -> int:
         return self.gate_up.nbytes() + self.down.nbytes()
 
+    def state(self, prefix: str, names: Dict[str, str]) -> Dict[str, torch.Tensor]:
+        w, I = self.gate_up.lin.weight, self.spec.intermediate
+        return {f"{prefix}{names['gate']}.weight": w[:I], f"{prefix}{names['up']}.weight": w[I:],
+                f"{prefix}{names['down']}.weight": self.down.weight}
+
+    def scratch_row(self) -> int:
+        return 2 * self.spec.intermediate
+
+    graph_safe = True
+
     takes_pending_norm = True
     takes_next_norm = True
 

@@ -21,9 +21,10 @@ SKINNY_ROWS = 8          # measured on B200: above 8 rows the library product st
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor], rt):
+    def __init__(self, weight, bias: Optional[torch.Tensor], rt):
+        """``weight``: a matrix [N, K], or a list of matrices of one width that are stacked by rows."""
         self.rt = rt
-        self.weight = rt.matrix(weight)                    # [N, K]
+        self.weight = rt.matrix_rows(weight) if isinstance(weight, (list, tuple)) else rt.matrix(weight)    # [N, K]
         self.bias = rt.vector(bias) if bias is not None else None
         self.N, self.K = self.weight.shape
         self._bias_act = None
@@ -141,9 +142,7 @@ class GatedLinearPair:
     decode GEMV mode 2, src/kernels.cu:533-537)."""
 
     def __init__(self, gate: torch.Tensor, up: torch.Tensor, rt):
-        if gate.dtype != up.dtype:
-            gate, up = gate.float(), up.float()
-        self.lin = Linear(torch.cat([gate, up], dim=0), None, rt)
+        self.lin = Linear([gate, up], None, rt)
         self.rt = rt
         self.I = gate.shape[0]
 

@@ -54,6 +54,11 @@ class RMSNorm:
     def nbytes(self) -> int:
         return self.weight.numel() * 4
 
+    def state(self, name: str) -> Dict[str, torch.Tensor]:
+        return {name: self.weight}
+
+    graph_safe = True
+
     def lazy(self, x: torch.Tensor, ssq=None, xw=None) -> NormedInput:
         return NormedInput(self, x, ssq, xw)
 

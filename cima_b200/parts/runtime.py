@@ -32,3 +32,20 @@ class Runtime:
         if t.dtype is torch.float16:
             return t.to(device=self.device, dtype=torch.bfloat16).contiguous()
         return t.to(device=self.device).contiguous()
+
+    def matrix_rows(self, pieces) -> torch.Tensor:
+        """Several matrices of one width stacked by rows into one device matrix (q | k | v, gate | up), each piece
+        uploaded into its place: the host never holds the stacked copy.  Pieces kept in different dtypes meet in
+        float32, as does everything on the 32-bit path."""
+        pieces = list(pieces)
+        kept = {torch.bfloat16 if (p.dtype is torch.float16 and not self.full_precision) else p.dtype for p in pieces}
+        dtype = torch.float32 if (self.full_precision or len(kept) > 1) else kept.pop()
+        rows = sum(p.shape[0] for p in pieces)
+        out = torch.empty((rows, pieces[0].shape[1]), dtype=dtype, device=self.device)
+        r = 0
+        for p in pieces:
+            if p.shape[1] != out.shape[1]:
+                raise ValueError(f"matrices of widths {p.shape[1]} and {out.shape[1]} cannot be stacked by rows")
+            out[r:r + p.shape[0]].copy_(p)
+            r += p.shape[0]
+        return out

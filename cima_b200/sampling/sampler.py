@@ -25,8 +25,12 @@ def sampler_state() -> List[StateRequest]:
 
 
 class DeviceSampler:
-    def __init__(self, model):
+    def __init__(self, model, max_rows: int = 0):
+        """``max_rows``: the most rows one call will bring (the largest batch); the scratch is sized for it at the
+        first call, so that a captured decode step and later, larger batches share one buffer."""
         self.model = model
+        self.max_rows = max(0, int(max_rows))
+        self._retired = []
         self.kernels = model.rt.kernels
         st = model.cache.state
         self.rng, self.ring, self.count = st["sampler.rng"], st["sampler.ring"], st["sampler.count"]
@@ -62,6 +66,11 @@ class DeviceSampler:
                tokens: torch.Tensor, all_greedy: bool) -> None:
         """tokens[i] = the choice for row i of ``logits``; the choice is pushed to the slot's history."""
         n, V = logits.shape
+        if all_greedy:
+            self.kernels.sample(logits, row_slot, params, self.rng, self.ring, self.count, None, tokens, True)
+            return
         if self._work is None or self._work.shape[0] < n or self._work.shape[1] != V:
-            self._work = torch.empty((max(n, 1), V), dtype=torch.float32, device=logits.device)
+            if self._work is not None:
+                self._retired.append(self._work)      # a captured step may still write there: kept, not freed
+            self._work = torch.empty((max(n, self.max_rows, 1), V), dtype=torch.float32, device=logits.device)
         self.kernels.sample(logits, row_slot, params, self.rng, self.ring, self.count, self._work, tokens, all_greedy)

@@ -24,17 +24,28 @@ def _tensor_seed(seed: int, name: str) -> int:
     return int.from_bytes(h[:8], "little") & ((1 << 63) - 1)
 
 
+_SLAB = 1 << 24     # elements drawn at a time: bounds the float32 scratch of a large tensor to 64 MiB
+
+
 def random_tensor(spec: TensorSpec, seed: int, name: str, dtype=torch.bfloat16, device="cpu") -> torch.Tensor:
+    """The tensor ``name`` drawn from the generator seeded by (seed, name), in slabs of ``_SLAB`` values in float32
+    that are rounded into ``dtype`` as they come.  On the CPU a slab (a multiple of 16 values) continues the
+    generator's sequence exactly where the last one ended, so the values do not depend on the slab size."""
+    if spec.init not in ("normal", "ones_normal"):
+        raise ValueError(f"unknown init '{spec.init}' for tensor '{name}'")
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, name))
-    t = torch.empty(spec.shape, dtype=torch.float32, device=device)
-    # large tensors are drawn in slabs to bound the float32 scratch
-    t.normal_(0.0, spec.std, generator=g)
-    if spec.init == "ones_normal":
-        t += 1.0
-    elif spec.init != "normal":
-        raise ValueError(f"unknown init '{spec.init}' for tensor '{name}'")
-    return t.to(dtype)
+    out = torch.empty(spec.shape, dtype=dtype, device=device)
+    flat = out.view(-1)
+    n = flat.numel()
+    scratch = torch.empty(min(n, _SLAB), dtype=torch.float32, device=device)
+    for lo in range(0, n, _SLAB):
+        part = scratch[:min(_SLAB, n - lo)]
+        part.normal_(0.0, spec.std, generator=g)
+        if spec.init == "ones_normal":
+            part += 1.0
+        flat[lo:lo + part.numel()].copy_(part)
+    return out
 
 
 def random_tensors(plan: Dict[str, TensorSpec], seed: int, dtype=torch.bfloat16, device="cpu") -> Dict[str, torch.Tensor]:

@@ -55,6 +55,21 @@ class CausalMean:
             state[slot] = c[-1]
 
 
+class CausalMeanOnDevice(CausalMean):
+    """The same mixer, fit for a recorded decode step: when every sequence brings one row it finds its state through
+    the batch's device arrays only (no host value enters the recorded work); other steps take the host's road."""
+    graph_safe = True
+
+    def forward(self, h, x, batch, cache, site):
+        if batch.n_rows != batch.n_seqs:
+            return super().forward(h, x, batch, cache, site)
+        state = cache.state[f"causal_mean.sum.{site}"]
+        slots = batch.seq_slot.long()
+        c = h.float() + state.index_select(0, slots)
+        x += self.gain * c / (batch.row_pos.float() + 1.0)[:, None]
+        state.index_copy_(0, slots, c)
+
+
 def toy_spec(cfg) -> ModelSpec:
     H, nh, nkv, hd = cfg["hidden_size"], cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
     pos = PositionSpec("rope", hd, hd, cfg["theta"])
@@ -65,7 +80,7 @@ def toy_spec(cfg) -> ModelSpec:
     layers = []
     for i, kind in enumerate(cfg["layer_kinds"]):
         if kind == "causal_mean":
-            mixer = MixerSpec("causal_mean", H, 0, 0, 0, False, False, 0, 0.0, PositionSpec("none", 0, 0, 1.0))
+            mixer = MixerSpec(cfg.get("mean_kind", "causal_mean"), H)       # no heads: only kind and width
         else:
             mixer = MixerSpec("attention", H, nh, nkv, hd, True, False, 0, 1.0 / math.sqrt(hd), pos,
                               cache_from=cfg["reads_site"] if kind == "attention_shared" else None)
@@ -271,3 +286,74 @@ def test_toy_routed_feed_forward_and_another_position_encoding():
         model.cache.close(slots)
     assert (lg[0] - toy2_plain(W, TOY2, toks2)[0].float()[32]).abs().max().item() <= 2e-5
     assert (lg[1] - want[99]).abs().max().item() <= 2e-5
+
+
+# ---------------------------------------------------------------------------------------------
+# Generation with the toy architectures through the package's entry point.
+# ---------------------------------------------------------------------------------------------
+def toy_generate(plain, W, cfg, prompt, n):
+    seq, out = list(prompt), []
+    for _ in range(n):
+        lg = plain(W, cfg, seq)
+        lg = (lg[0] if isinstance(lg, tuple) else lg)[-1].float()
+        best = max(range(lg.numel()), key=lambda i: (float(lg[i]), i))        # ties to the higher index
+        out.append(best)
+        seq.append(best)
+    return out
+
+
+@pytest.mark.parametrize("mean_kind,pipeline", [("causal_mean", True), ("causal_mean_on_device", True),
+                                                ("causal_mean_on_device", False)])
+def test_toy_architecture_with_state_generates_through_the_entry_point(mean_kind, pipeline):
+    """``cima_b200.load(...).generate`` with the stateful toy mixer: the variant that reads the batch on the host is
+    decoded step by step (it does not declare itself fit for recording), the other through recorded steps; neither
+    runs ahead (a step too many would leave its running sum one token ahead of the cache).  A finished sequence is
+    kept (``retain``) and the next turn goes on from its keys and its state; every token equals the plain model's."""
+    register_mixer("causal_mean", CausalMean)
+    register_mixer("causal_mean_on_device", CausalMeanOnDevice)
+    register_architecture(ArchitectureEntry("ToyMixForCausalLM", "toymix", parse=lambda raw: raw, spec=toy_spec))
+    cfg = dict(TOY, mean_kind=mean_kind)
+    folder = tempfile.mkdtemp(prefix="cima_toy_gen_")
+    cima_b200.write_random_model(folder, cfg, seed=5)
+    from safetensors.torch import load_file
+    W = load_file(os.path.join(folder, "model.safetensors"))
+    lm = cima_b200.load(folder, dtype="float32", max_tokens=2048, verbose=False, pipeline=pipeline, retain=1)
+    assert lm.stepper.use_graphs == (mean_kind == "causal_mean_on_device")
+    assert lm.stepper.pipeline is False and lm.model.cache.has_mixer_state
+    prompts = [random_tokens(300, n, seed=10 + n) for n in (23, 5, 40)]
+    got = lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=9)
+    for p, r in zip(prompts, got):
+        assert r.tokens == toy_generate(toy_plain, W, TOY, p, 9)
+    # the next turn of the last conversation: only the new tokens run, from the kept keys and the kept running sums
+    turn2 = prompts[2] + got[2].tokens + random_tokens(300, 7, seed=99)
+    r2 = lm.generate([turn2], temperature=0, repeat_penalty=1.0, max_tokens=9)[0]
+    assert lm.stats.reused_tokens == len(prompts[2]) + len(got[2].tokens) - 1
+    assert r2.tokens == toy_generate(toy_plain, W, TOY, turn2, 9)
+    # a prompt that shares only a part of the kept sequence cannot go back there (the state belongs to its end)
+    turn3 = turn2[:30] + random_tokens(300, 6, seed=98)
+    r3 = lm.generate([turn3], temperature=0, repeat_penalty=1.0, max_tokens=5)[0]
+    assert lm.stats.reused_tokens == 0 and r3.tokens == toy_generate(toy_plain, W, TOY, turn3, 5)
+    lm.stepper.drop_retained()
+    lm.model.cache.check()
+    assert lm.model.cache.slots.held == 0
+
+
+@pytest.mark.parametrize("pipeline", [True, False])
+def test_toy_routed_architecture_generates_through_the_entry_point(pipeline):
+    """The routed feed-forward says nothing about recording, so the model decodes step by step; greedy tokens of a
+    batch of unequal prompts equal the plain model's (32-bit)."""
+    from cima_b200.parts import register_feed_forward, register_position
+    register_feed_forward("toy_top1_experts", Top1Experts)
+    register_position("toy_scaled_rope", ScaledRope)
+    register_architecture(ArchitectureEntry("ToyRoutedForCausalLM", "toyrouted", parse=lambda raw: raw, spec=toy2_spec))
+    lm = cima_b200.load(config=TOY2, seed=9, dtype="float32", max_tokens=1024, verbose=False, pipeline=pipeline)
+    assert not lm.stepper.use_graphs
+    folder = tempfile.mkdtemp(prefix="cima_toy2_gen_")
+    cima_b200.write_random_model(folder, TOY2, seed=9)
+    from safetensors.torch import load_file
+    W = load_file(os.path.join(folder, "model.safetensors"))
+    prompts = [random_tokens(TOY2["vocab_size"], n, seed=30 + n) for n in (12, 1, 33)]
+    got = lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=8)
+    for p, r in zip(prompts, got):
+        assert r.tokens == toy_generate(toy2_plain, W, TOY2, p, 8)
+    assert lm.model.cache.slots.held == 0

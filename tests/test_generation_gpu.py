@@ -252,3 +252,163 @@ def test_finished_sequences_are_taken_up_again(dtype, pipeline):
     assert lm.model.cache.slots.held == 2
     lm.stepper.drop_retained()
     assert lm.model.cache.slots.held == 0
+
+
+@pytest.mark.parametrize("name,n_prompts,pipeline", [("A", 20, True), ("B", 64, True), ("B", 20, False), ("A", 64, False)])
+def test_many_prompts_generate_as_the_plain_loop_does(name, n_prompts, pipeline):
+    """20 and 64 prompts of unequal lengths through ``generate`` in 32-bit (decode graphs of 9 to 64 sequences, with
+    run-ahead and without): greedy, and the reference's default sampling chain on a part of them, token for token
+    what the plain implementation generates; some stop early on stop tokens, so that the batch shrinks on the way."""
+    V = TINY[name]["vocab_size"]
+    gen = np.random.default_rng(n_prompts)
+    prompts = [random_tokens(V, int(n), seed=500 + i) for i, n in enumerate(gen.integers(1, 40, size=n_prompts))]
+    lm = cima_b200.load(model_folder(name), dtype="float32", max_tokens=64 * 2 * n_prompts, verbose=False, pipeline=pipeline)
+    steps = 6
+    free = lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=steps)
+    want = [plain_generate(name, p, dict(temperature=0.0), steps)[0] for p in prompts]
+    assert [r.tokens for r in free] == want
+    stops = (want[3][2], want[11][4], want[0][0])
+    got = lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=steps, stop=stops)
+    for w, r in zip(want, got):
+        cut = next((j for j, t in enumerate(w) if t in stops), None)
+        assert r.tokens == (w if cut is None else w[:cut])
+    opts = dict(temperature=0.8, top_k=40, top_p=0.9, repeat_penalty=1.1, seed=11)
+    some = prompts[:12]
+    got = lm.generate(some, max_tokens=5, **opts)
+    for p, r in zip(some, got):
+        assert r.tokens == plain_generate(name, p, opts, 5)[0]
+    lm.model.cache.check()
+    assert lm.model.cache.slots.held == 0
+
+
+def test_batch_sizes_in_any_order_through_recorded_steps():
+    """Recorded decode steps keep the addresses of the scratch they were recorded with (the attention's splits, the
+    sampler's row copies).  Batches of 1, 8, 1, then 8 shrinking to 4 and 8 again, with sampling on, must give what
+    step-by-step decoding gives, and logits that a caller kept from an earlier step must stay as they were."""
+    name = "B"
+    V = TINY[name]["vocab_size"]
+    prompts = [random_tokens(V, 5 + 3 * i, seed=900 + i) for i in range(8)]
+    opts = dict(temperature=0.9, top_k=30, top_p=0.95, repeat_penalty=1.1, seed=21)
+    outs = []
+    for use_graphs in (True, False):
+        lm = cima_b200.load(model_folder(name), dtype="bfloat16", max_tokens=4096, verbose=False, use_graphs=use_graphs)
+        assert lm.stepper.use_graphs == use_graphs
+        from cima_b200.engine import StepEntry
+        (slot,) = lm.model.cache.open(1)
+        kept = lm.step([StepEntry(slot, prompts[0], [len(prompts[0]) - 1])])
+        lm.model.cache.close([slot])
+        before = kept.clone()
+        res = []
+        res.append(lm.generate(prompts[:1], max_tokens=20, **opts))
+        res.append(lm.generate(prompts, max_tokens=20, **opts))
+        res.append(lm.generate(prompts[:1], max_tokens=20, **opts))
+        # four of the eight stop after a few tokens: 8 -> 4 sequences, then 8 again
+        stops = tuple(res[1][i].tokens[3 + i] for i in range(4))
+        res.append(lm.generate(prompts, max_tokens=20, stop=stops, **opts))
+        res.append(lm.generate(prompts, max_tokens=20, **opts))
+        res.append(lm.generate(prompts[:3], temperature=0, repeat_penalty=1.0, max_tokens=20))
+        res.append(lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=20))
+        assert torch.equal(kept, before)
+        outs.append([[r.tokens for r in x] for x in res])
+        assert outs[-1][1] == outs[-1][4]
+        lm.model.cache.check()
+        assert lm.model.cache.slots.held == 0
+    assert outs[0] == outs[1]
+
+
+def test_other_tokens_than_the_chosen_ones_may_be_fed_back():
+    """A caller of the stepper that feeds back tokens of its own choosing (forced tokens) while run-ahead is on: the
+    step that was queued with the chosen tokens is dropped, and the next one starts from the cache's lengths."""
+    from cima_b200.engine import StepEntry
+    from cima_b200.sampling import GenOptions
+    name = "B"
+    V = TINY[name]["vocab_size"]
+    lm = cima_b200.load(model_folder(name), dtype="float32", max_tokens=1024, verbose=False, pipeline=True)
+    st = lm.stepper
+    greedy = GenOptions(temperature=0.0, repeat_penalty=1.0)
+    prompts = [random_tokens(V, n, seed=300 + n) for n in (9, 4)]
+    forced = [random_tokens(V, 6, seed=1), random_tokens(V, 6, seed=2)]
+    slots = st.open(2)
+    try:
+        st.prefill(slots, prompts, [greedy, greedy])
+        got = []
+        for k in range(6):
+            got.append(st.decode(slots, [forced[0][k], forced[1][k]], [greedy, greedy]))
+    finally:
+        st.close(slots)
+    cfg, W = plain_load(model_folder(name))
+    for i in range(2):
+        seq = list(prompts[i])
+        for k in range(6):
+            seq.append(forced[i][k])
+            assert got[k][i] == int(torch.argmax(plain_forward(W, cfg, seq)[-1].float()))
+    lm.model.cache.check()
+
+
+def test_cima_run_generates_what_the_plain_loop_does(tmp_path):
+    """``bin/cima run`` as a user calls it: token ids on the command line and in a prompts file, options by the
+    reference's names; the generated ids on standard output are the plain implementation's (32-bit, greedy and
+    sampled).  Then the same command on a shape with random weights in memory."""
+    name = "A"
+    folder = model_folder(name)
+    exe = [sys.executable, os.path.join(ROOT, "bin", "cima"), "run"]
+    p = subprocess.run(exe + [folder, "5", "17", "3", "--temp", "0", "--repeat-penalty", "1.0", "--max-tokens", "8", "--dtype",
+                              "float32"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [int(t) for t in p.stdout.split()] == plain_generate(name, [5, 17, 3], dict(temperature=0.0), 8)[0]
+    assert "3 prompt tok | 8 gen tok" in p.stderr
+    (tmp_path / "prompts.txt").write_text("5 17 3\n42\n7,7,7,300,2\n")
+    opts = dict(temperature=0.7, top_k=20, top_p=0.9, repeat_penalty=1.2, seed=99)
+    p = subprocess.run(exe + [folder, "--prompts", str(tmp_path / "prompts.txt"), "--temperature", "0.7", "--top-k", "20",
+                              "--top-p", "0.9", "--repeat-penalty", "1.2", "--seed", "99", "--max-tokens", "6", "--dtype", "float32"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    lines = [[int(t) for t in l.split()] for l in p.stdout.strip().split("\n")]
+    assert lines == [plain_generate(name, q, opts, 6)[0] for q in ([5, 17, 3], [42], [7, 7, 7, 300, 2])]
+    p = subprocess.run(exe + ["--random-shape", "tiny-b", "--weights-seed", "4", "1", "2", "3", "--temp", "0", "--max-tokens", "5"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert len(p.stdout.split()) == 5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_model_from_a_configuration_in_memory_equals_the_folder(dtype, tmp_path):
+    """``load(config=, seed=)`` draws the values that ``write_random_model`` stores for the seed and goes through
+    the same loader: logits bit for bit those of the folder's model; ``state_dict`` gives the tensors back by name."""
+    from cima_b200.engine import StepEntry, build_plan
+    from cima_b200.weights import random_tensors
+    cfg = TINY["C"]
+    folder = str(tmp_path / "m")
+    cima_b200.write_random_model(folder, cfg, seed=6)
+    a = cima_b200.load(folder, dtype=dtype, max_tokens=512, verbose=False)
+    b = cima_b200.load(config=cfg, seed=6, dtype=dtype, max_tokens=512, verbose=False)
+    toks = random_tokens(cfg["vocab_size"], 120, seed=8)
+    outs = []
+    for lm in (a, b):
+        (slot,) = lm.model.cache.open(1)
+        try:
+            outs.append(lm.step([StepEntry(slot, toks, list(range(len(toks))))]).clone())
+        finally:
+            lm.model.cache.close([slot])
+    assert torch.equal(outs[0], outs[1])
+    want = random_tensors(build_plan(b.spec), 6)
+    sd = b.state_dict()
+    assert sorted(sd) == sorted(want)
+    for n, t in want.items():
+        assert torch.equal(sd[n].float().cpu(), t.float()), n
+    # drawn on the device: other values, the same road
+    c = cima_b200.load(config=cfg, seed=6, dtype=dtype, max_tokens=512, verbose=False, draw="device")
+    assert len(c.generate([toks[:9]], temperature=0, max_tokens=4)[0].tokens) == 4
+
+
+def test_loading_holds_one_group_of_tensors_on_the_host_not_the_checkpoint():
+    """While a model loads, the fetched host tensors alive at once stay within the largest group that a part
+    stacks (the table, gate | up, or q | k | v), far below the checkpoint: each is uploaded and dropped."""
+    from cima_b200.engine import build_plan, load_model
+    m = load_model(model_folder("B"), dtype="bfloat16", max_tokens=256, verbose=False)
+    cfg = m.config
+    total = sum(2 * int(np.prod(s.shape)) for s in build_plan(m.spec).values())
+    H, I, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    group = max(2 * V * H, 2 * 2 * I * H, 2 * (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim * H)
+    assert 0 < m.load_peak_host_bytes <= group + 4096
+    assert m.load_peak_host_bytes < total / 3

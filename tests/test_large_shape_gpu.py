@@ -101,7 +101,15 @@ def test_wider_layer_shapes(name, tmp_path):
     want = plain_forward(W, cfg, toks).float()
     long_toks = random_tokens(shape["vocab_size"], 300, seed=4)
     m32 = load_model(folder, dtype="float32", max_tokens=1024, verbose=False)
-    assert (run_whole(m32, toks) - want).abs().max().item() <= 1e-4
+    whole32 = run_whole(m32, toks)
+    assert (whole32 - want).abs().max().item() <= 1e-4
+    # 32-bit: the last 16 one by one and a batch of three unequal requests, bit for bit the whole prompt's logits
+    assert torch.equal(run_tail_one_by_one(m32, toks, 16), whole32)
+    others = [random_tokens(shape["vocab_size"], n, seed=50 + n) for n in (9, 40)]
+    got = run_batched(m32, [toks] + others, [60, 1, 33])
+    assert torch.equal(got[0], whole32)
+    for q, g in zip(others, got[1:]):
+        assert (g - plain_forward(W, cfg, q).float()).abs().max().item() <= 1e-4
     long32 = run_whole(m32, long_toks)
     del m32
     torch.cuda.empty_cache()
@@ -137,3 +145,138 @@ def test_ragged_long_prompts_in_one_step(folder):
     got16, got32 = run("bfloat16"), run("float32")
     assert got16.shape == got32.shape == (sum(len(w) for w in wants), SHAPE["vocab_size"])
     assert (got16 - got32).abs().max().item() <= REL_BF16 * got32.std().item()
+
+
+def test_a_300_token_prompt_at_the_7b_layer_shape_against_the_plain_implementation(folder):
+    """From 256 rows on the gated projection runs on the tcgen05 pair kernel and the attention on its tcgen05 kernel:
+    one 300-token prompt through two layers in bfloat16, directly against the plain implementation (not by way of
+    the 32-bit engine), whole and then with the 32-bit engine beside it."""
+    cfg, W = plain_load(folder)
+    toks = random_tokens(SHAPE["vocab_size"], 300, seed=6)
+    want = plain_forward(W, cfg, toks).float()
+    m16 = load_model(folder, dtype="bfloat16", max_tokens=1024, verbose=False)
+    got = run_whole(m16, toks)
+    m16.check_device()
+    assert (got - want).abs().max().item() <= REL_BF16 * want.std().item()
+    del m16
+    torch.cuda.empty_cache()
+    m32 = load_model(folder, dtype="float32", max_tokens=1024, verbose=False)
+    assert (run_whole(m32, toks) - want).abs().max().item() <= 1e-4
+
+
+def test_64_sequences_decode_together_at_the_7b_layer_shape(folder):
+    """One decode step of 64 sequences (and of 9 and 16) after prompts of unequal lengths: the schedule for more
+    than 8 rows at the benchmark's widths, bfloat16 against the 32-bit engine and, for a few sequences, against the
+    plain implementation."""
+    from cima_b200.engine import StepEntry
+    cfg, W = plain_load(folder)
+    gen = torch.Generator().manual_seed(3)
+    lens = [int(x) for x in torch.randint(1, 200, (64,), generator=gen)]
+    lens[0], lens[1], lens[2] = 1, 64, 199
+    seqs = [random_tokens(SHAPE["vocab_size"], n + 3, seed=300 + i) for i, n in enumerate(lens)]
+
+    def run(dtype, count):
+        m = load_model(folder, dtype=dtype, max_tokens=64 * 4 * 64, max_seqs=64, verbose=False)
+        slots = m.cache.open(count)
+        try:
+            for i in range(0, count, 16):
+                m.step([StepEntry(s, q[:n], []) for s, q, n in zip(slots[i:i + 16], seqs[i:i + 16], lens[i:i + 16])])
+            outs = [m.step([StepEntry(s, [q[n + k]], [0]) for s, q, n in zip(slots, seqs, lens)]).float().cpu()
+                    for k in range(3)]
+        finally:
+            m.cache.close(slots)
+        del m
+        torch.cuda.empty_cache()
+        return torch.stack(outs)                      # [3 steps, count, vocab]
+
+    want32 = run("float32", 64)
+    tol = REL_BF16 * want32.std().item()
+    for i in (0, 1, 2, 63):
+        plain = plain_forward(W, cfg, seqs[i]).float()
+        for k in range(3):
+            assert (want32[k, i] - plain[lens[i] + k]).abs().max().item() <= 1e-4
+    for count in (64, 16, 9):
+        got = run("bfloat16", count)
+        assert (got - want32[:, :count]).abs().max().item() <= tol, count
+
+
+def test_gated_feed_forward_in_row_chunks(folder, monkeypatch):
+    """A step whose [rows, 2 x intermediate] scratch would exceed its bound runs the feed-forward in row chunks: with
+    the bound set so low that a 300-token prompt takes three chunks, the 32-bit logits are bit for bit those of
+    the run in one piece, and bfloat16 stays within its tolerance of them."""
+    import cima_b200.parts.feed_forward as ff
+    toks = random_tokens(SHAPE["vocab_size"], 300, seed=8)
+    outs = {}
+    for dtype in ("float32", "bfloat16"):
+        m = load_model(folder, dtype=dtype, max_tokens=1024, verbose=False)
+        outs[dtype, "whole"] = run_whole(m, toks)
+        monkeypatch.setattr(ff, "_SCRATCH_ELEMS", 2 * SHAPE["intermediate_size"] * 128)
+        outs[dtype, "chunks"] = run_whole(m, toks)
+        monkeypatch.undo()
+        del m
+        torch.cuda.empty_cache()
+    assert torch.equal(outs["float32", "whole"], outs["float32", "chunks"])
+    tol = REL_BF16 * outs["float32", "whole"].std().item()
+    assert (outs["bfloat16", "chunks"] - outs["float32", "whole"]).abs().max().item() <= tol
+    assert (outs["bfloat16", "whole"] - outs["float32", "whole"]).abs().max().item() <= tol
+
+
+def test_the_full_vocabulary_head_argmax_and_sampler():
+    """One layer of the 7B shape with the whole vocabulary of 152,064: the head through the kernel for few rows (1 and
+    8 rows) and through the library branch (9 and 64 rows), the argmax and the sampling chain at that width (the
+    default chain and temperature only), against the plain implementation: float64 logits of the same rows, and the
+    plain sampler on the engine's own float32 logits, draw for draw."""
+    import numpy as np
+    from cima_b200.engine import StepEntry
+    from cima_b200.sampling import GenOptions
+    from qwen2_plain import PlainXorshift, plain_sample
+    shape = dict(SHAPE, num_hidden_layers=1, vocab_size=152064)
+    lm = cima_b200.load(config=shape, seed=17, dtype="bfloat16", max_tokens=64 * 2 * 64, max_seqs=64, verbose=False)
+    W = {k: v.detach().cpu().double() for k, v in lm.state_dict().items()}      # float64 once: plain_forward keeps it
+    cfg = shape
+    V = shape["vocab_size"]
+    seqs = [random_tokens(V, 3 + (i % 5), seed=700 + i) for i in range(64)]
+    plain_last = {}
+
+    def plain_row(i):
+        if i not in plain_last:
+            plain_last[i] = plain_forward(W, cfg, seqs[i])[-1].float()
+        return plain_last[i]
+
+    K = lm.model.rt.kernels
+    for count in (1, 8, 9, 64):
+        slots = lm.model.cache.open(count)
+        try:
+            lm.step([StepEntry(s, q[:-1], []) for s, q in zip(slots, seqs)])
+            logits = lm.step([StepEntry(s, [q[-1]], [0]) for s, q in zip(slots, seqs)])       # a decode step of `count` rows
+        finally:
+            lm.model.cache.close(slots)
+        host = logits.float().cpu()
+        tol = REL_BF16 * host.std().item()
+        for i in sorted({0, count // 2, count - 1}):
+            assert (host[i] - plain_row(i)).abs().max().item() <= tol, (count, i)
+        # argmax at this width: the reference's tie rule (the higher index) on the engine's own logits
+        tokens = torch.empty(count, dtype=torch.int32, device=logits.device)
+        K.argmax(logits, tokens)
+        for i in range(count):
+            row = host[i].numpy()
+            best = int(np.flatnonzero(row == row.max())[-1])
+            assert int(tokens[i]) == best, (count, i)
+    # the sampling chain through generate: every draw is the plain sampler's on the same logits.  The logits of the
+    # engine are taken from a step of the same rows; generate then must choose what the plain chain chooses on them
+    for opts in (dict(temperature=0.8, top_k=40, top_p=0.9, repeat_penalty=1.1, seed=5),
+                 dict(temperature=1.0, top_k=0, top_p=1.0, repeat_penalty=1.0, seed=6)):
+        prompts = seqs[:8]
+        slots = lm.model.cache.open(8)
+        try:
+            logits = lm.step([StepEntry(s, q, [len(q) - 1]) for s, q in zip(slots, prompts)]).float().cpu()
+        finally:
+            lm.model.cache.close(slots)
+        got = lm.generate(prompts, max_tokens=1, **opts)
+        from test_sampling_gpu import draw_is_consistent
+        for i, (p, r) in enumerate(zip(prompts, got)):
+            want = plain_sample(logits[i].tolist(), list(p), opts, PlainXorshift(opts["seed"]))
+            # over a flat row of 152,064 masses the device's tree of float32 sums and the host's running sum
+            # may land on neighbouring tokens of the sorted order: then the draw must be one the chain can make
+            assert r.tokens == [want] or (opts["top_k"] == 0 and draw_is_consistent(
+                logits[i].tolist(), list(p), opts, PlainXorshift(opts["seed"]).next_f32(), r.tokens[0])), (opts, i)

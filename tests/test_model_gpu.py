@@ -1,5 +1,6 @@
 """The engine on the GPU against the plain implementation: every way of cutting the same requests,
 in 32-bit and in bfloat16, on three tiny configurations that differ in every size and option."""
+import numpy as np
 import pytest
 import torch
 
@@ -298,3 +299,150 @@ def test_long_prompts_at_head_size_64(dtype, tmp_path):
     got = run_batched(m, seqs, [400, 290])
     for q, g_ in zip(seqs, got):
         assert close(g_, plain_forward(W, c, q).float(), TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,n_seqs", [("A", 12), ("B", 20), ("A", 64), ("B", 64)])
+def test_many_sequences_decode_together(name, n_seqs, dtype):
+    """9 to 64 sequences in one decode step (in bfloat16 that is another schedule than for up to 8: library
+    products with their own residual, norm and activation kernels, fewer splits of the attention): prompts of 1 to
+    64 tokens in one step, then a token each; the shorter ones end earlier; three rounds on a cache with exactly as
+    many slots as sequences, so that every slot and most pages are used again."""
+    V = TINY[name]["vocab_size"]
+    gen = np.random.default_rng(1000 + n_seqs)
+    m = gpu_model(name, dtype, max_tokens=64 * 2 * n_seqs, max_seqs=n_seqs)
+    for rnd in range(3):
+        lens = [int(x) for x in gen.integers(1, 65, size=n_seqs)]
+        lens[rnd % n_seqs], lens[(rnd + 5) % n_seqs] = 1, 64
+        tails = [int(x) for x in gen.integers(1, 13, size=n_seqs)]
+        tails[0], tails[-1] = 12, 2
+        seqs = [random_tokens(V, n + t, seed=7000 + 100 * rnd + i) for i, (n, t) in enumerate(zip(lens, tails))]
+        got = run_batched(m, seqs, lens)
+        for i, (q, g) in enumerate(zip(seqs, got)):
+            assert close(g, plain_logits(name, q), TOL[dtype]), (name, dtype, rnd, i, len(q))
+        if dtype == "float32" and rnd == 0:
+            for i in range(0, n_seqs, 7):
+                assert torch.equal(got[i], run_whole(m, seqs[i])), i      # alone and whole: bit for bit
+        m.cache.check()
+        assert m.cache.slots.held == 0
+
+
+def standout_model(folder):
+    """Tiny B with weights made so that single keys carry a row: five marker tokens S_i (ids 901..905) and a query
+    token Q (id 900).  An S_i's embedding has one large component in a dimension of its own (all other tokens have
+    0 there); layer 0's key projection turns any of those dimensions into one large component of the key, in the
+    rotary pair of the lowest frequency (so that the distance between query and key hardly matters); its value
+    projection turns each into a large vector of its own; Q's embedding has such a dimension that layer 0's query
+    projection turns into the matching component of every head's query.  A Q row's score with an S key then stands
+    about 4 above its scores with ordinary keys, and the S keys before it hold two thirds of its weight."""
+    import json
+    from safetensors.torch import load_file, save_file
+    name, hd = "B", 64
+    W = dict(load_file(f"{model_folder(name)}/model.safetensors"))
+    Q, dq, S, dks = 900, 7, [901, 902, 903, 904, 905], [11, 12, 13, 14, 15]
+    alpha, beta, big, vscale, r = 0.2, 0.9, 0.5, 0.15, hd // 2 - 1
+    E = W["model.embed_tokens.weight"].float().clone()
+    wq, wk, wv = (W[f"model.layers.0.self_attn.{n}_proj.weight"].float().clone() for n in "qkv")
+    n1 = W["model.layers.0.input_layernorm.weight"].float().clone()
+    gen = torch.Generator().manual_seed(1)
+    for d in [dq] + dks:
+        E[:, d] = 0
+        wq[:, d] = 0
+        wk[:, d] = 0
+        n1[d] = 1
+    E[Q, dq] = big
+    for h in range(TINY[name]["num_attention_heads"]):
+        wq[h * hd + r, dq] = alpha
+    for t, d in zip(S, dks):
+        E[t, d] = big
+        wk[r, d] = beta
+        wv[:, d] = torch.randn(hd, generator=gen) * vscale
+    W["model.embed_tokens.weight"] = E.to(torch.bfloat16)
+    for n, w in zip("qkv", (wq, wk, wv)):
+        W[f"model.layers.0.self_attn.{n}_proj.weight"] = w.to(torch.bfloat16)
+    W["model.layers.0.input_layernorm.weight"] = n1.to(torch.bfloat16)
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(TINY[name]))
+    save_file({k: v.contiguous() for k, v in W.items()}, str(folder / "model.safetensors"))
+    return Q, S
+
+
+def test_keys_that_stand_out_in_bfloat16(tmp_path):
+    """A masking fault of one key moves a bfloat16 logit by less than the model tests' tolerance while every key
+    weighs about 1/300.  Here single keys carry a fifth to a whole of a row's weight (``standout_model``), at the
+    places where tiles, pages and splits begin and end: positions 0, 63, 64, 127, 128, read by query rows at 1, 65,
+    129, 130 and the last position.  First the plain side shows that forgetting any one of those keys moves the
+    rows' logits by more than ten times the tolerance; then every cutting must agree with the plain logits."""
+    import math
+    import qwen2_plain
+    from helpers import run_in_pieces
+    from cima_b200.engine import load_model
+    Q, S = standout_model(tmp_path / "m")
+    cfg, W = plain_load(str(tmp_path / "m"))
+    toks = random_tokens(900, 200, seed=77)
+    spos, qpos = [0, 63, 64, 127, 128], [1, 65, 129, 130, 199]
+    for p, t in zip(spos, S):
+        toks[p] = t
+    for p in qpos:
+        toks[p] = Q
+    want = plain_forward(W, cfg, toks).float()
+    tol = TOL["bfloat16"]
+
+    def without_key(j):
+        def attention(q, k, v, window=0):
+            T, nh, hd = q.shape
+            out = torch.zeros_like(q)
+            for h in range(nh):
+                for p in range(T):
+                    keep = [i for i in range(p + 1) if not (i == j and p > j)]
+                    w = torch.softmax((k[keep, h // (nh // k.shape[1]), :] @ q[p, h, :]) / math.sqrt(hd), dim=0)
+                    out[p, h, :] = w @ v[keep, h // (nh // k.shape[1]), :]
+            return out
+        return attention
+
+    whole = qwen2_plain.plain_attention
+    try:
+        for j in spos:
+            qwen2_plain.plain_attention = without_key(j)
+            moved = (plain_forward(W, cfg, toks).float() - want).abs().max(dim=1).values
+            assert all(moved[p].item() > 10 * tol for p in qpos if p > j), (j, moved[qpos])
+    finally:
+        qwen2_plain.plain_attention = whole
+
+    m = load_model(str(tmp_path / "m"), dtype="bfloat16", max_tokens=4096, device="cuda:0", verbose=False)
+    assert close(run_whole(m, toks), want, tol)
+    assert close(run_tail_one_by_one(m, toks, 140), want, tol)          # decoding across the page edges 64, 128, 192
+    assert close(run_in_pieces(m, [toks], [[63, 64, 65, 128, 129]])[0], want, tol)
+    # in batches: 13 sequences (the schedule for more than 8 rows) that decode across the marked places
+    seqs = [toks, toks[:66], toks[:131], toks[:2]] + [toks[:140 + 5 * i] for i in range(9)]
+    for got in run_batched(m, seqs, [120, 64, 128, 1] + [60 + i for i in range(9)]):
+        assert close(got, want[:got.shape[0]], tol)
+    for got in run_batched(m, seqs[:5], [127, 63, 129, 1, 100]):
+        assert close(got, want[:got.shape[0]], tol)
+
+
+def test_a_step_that_does_not_fit_takes_nothing():
+    """A step whose second entry overflows the cache leaves the first entry's slot without pages it did not
+    commit; a long piece that would be run in rounds is refused before its first round."""
+    from cima_b200.cache import CacheFull
+    m = gpu_model("A", "float32", max_tokens=64 * 3, max_seqs=3)
+    s = m.cache.open(2)
+    try:
+        free = m.cache.free_tokens()
+        with pytest.raises(CacheFull):
+            m.step([StepEntry(s[0], list(range(100)), []), StepEntry(s[1], list(range(100)), [])])   # 4 pages, 3 free
+        assert m.cache.free_tokens() == free and m.cache.length(s[0]) == 0 and m.cache.held_tokens(s[0]) == 0
+        m.cache.check()
+    finally:
+        m.cache.close(s)
+    m = gpu_model("C", "float32", max_tokens=64 * 4, max_seqs=2)        # windows: a long piece runs in rounds of a page
+    s = m.cache.open(2)
+    try:
+        m.step([StepEntry(s[0], list(range(10)), []), StepEntry(s[1], list(range(10)), [])])
+        free = m.cache.free_tokens()
+        with pytest.raises(CacheFull):
+            m.step([StepEntry(s[0], list(range(150)), []), StepEntry(s[1], list(range(100)), [])])
+        assert m.cache.free_tokens() == free and m.cache.length(s[0]) == 10 and m.cache.length(s[1]) == 10
+        m.cache.check()
+    finally:
+        m.cache.close(s)

@@ -3,6 +3,7 @@ import json
 import os
 import struct
 
+import numpy as np
 import pytest
 import torch
 
@@ -162,3 +163,55 @@ def test_shards_and_duplicates(tmp_path):
     os.remove(tmp_path / "p1.safetensors")
     with pytest.raises(SafetensorsError, match="does not exist"):
         load_tensors(str(tmp_path), {"a": TensorSpec((2,))})
+
+
+def test_source_hands_out_one_tensor_at_a_time(tmp_path):
+    """``CheckpointTensors`` reads a tensor when it is asked for and counts what is alive: a consumer that drops
+    each tensor before it asks for the next (as an upload to the device does) never holds more than the largest
+    one; the whole plan is checked when the source opens, before anything is read."""
+    from helpers import TINY, model_folder
+    from cima_b200.weights import CheckpointTensors
+    cfg = Qwen2Config.from_dict(TINY["B"])
+    plan = build_plan(cfg.model_spec())
+    size = {n: 2 * int(np.prod(s.shape)) for n, s in plan.items()}
+    with CheckpointTensors(model_folder("B"), plan) as src:
+        assert sorted(src.names()) == sorted(plan) and src.live_bytes == 0
+        for n in plan:
+            t = src[n]
+            assert tuple(t.shape) == tuple(plan[n].shape) and src.live_bytes == size[n]
+            del t
+            assert src.live_bytes == 0
+        assert src.peak_bytes == max(size.values()) and src.fetched == list(plan)
+    bad = dict(plan)
+    bad["model.layers.9.mlp.up_proj.weight"] = plan["model.layers.0.mlp.up_proj.weight"]
+    with pytest.raises(WeightError, match="missing"):
+        CheckpointTensors(model_folder("B"), bad)
+
+
+def test_state_dict_of_a_seeded_model_is_the_random_weights_mode(tmp_path):
+    """A model made from a configuration and a seed in memory holds exactly ``random_tensors(plan, seed)``, and a
+    slab-wise draw gives the values of a draw in one piece."""
+    import cima_b200.weights.random_init as R
+    from helpers import TINY
+    from reference_kernels import ReferenceKernels
+    from cima_b200.engine import build_plan, load_model
+    from cima_b200.weights import TensorSpec, random_tensor, random_tensors
+    m = load_model(config=TINY["A"], seed=12, dtype="bfloat16", max_tokens=256, device="cpu", kernels=ReferenceKernels())
+    want = random_tensors(build_plan(m.spec), 12)
+    sd = m.state_dict()
+    assert sorted(sd) == sorted(want)
+    for n, t in want.items():
+        assert torch.equal(sd[n].float(), t.float()), n
+    spec = TensorSpec((1000, 77))
+    whole = random_tensor(spec, 3, "x")
+    slab = R._SLAB
+    try:
+        R._SLAB = 1600
+        assert torch.equal(random_tensor(spec, 3, "x"), whole)
+    finally:
+        R._SLAB = slab
+    g = torch.Generator()
+    g.manual_seed(R._tensor_seed(3, "x"))
+    assert torch.equal(torch.empty(1000, 77).normal_(0.0, 0.02, generator=g).to(torch.bfloat16), whole)
+    with pytest.raises(ValueError, match="one of the two"):
+        load_model(device="cpu", kernels=ReferenceKernels())
