@@ -107,6 +107,9 @@ def main(argv=None) -> int:
                     "defined on the default, Qwen2.5-7B)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--per-kernel", action="store_true", help="instead of the metric line: every launch of one decode step "
+                    "(--batch) and of one prompt step (--prompt tokens) with its time inside the step, bytes and flops "
+                    "over time against the measured peaks; use few layers (--layers 2)")
     a = ap.parse_args(argv)
     if a.impl == "reference":
         return reference_arm()
@@ -150,6 +153,26 @@ def main(argv=None) -> int:
     kv_bytes_per_token = sum(g.storage.element_size() * len(g.layers) * 2 * g.request.n_kv_heads * g.request.head_dim
                              for g in model.cache.groups)
     weight_bytes = model.weight_bytes()
+
+    if a.per_kernel:
+        from cima_b200.engine.profile import profile_decode, profile_prompt, table
+        prompts = [rng.integers(0, V, size=a.prompt).tolist() for _ in range(a.batch)]
+        slots = st.open(a.batch)
+        try:
+            opts = [greedy] * a.batch
+            first = []
+            for i in range(0, a.batch, 8):
+                first += st.prefill(slots[i:i + 8], prompts[i:i + 8], opts[i:i + 8])
+            rows = profile_decode(st, slots, first, opts)
+        finally:
+            st.close(slots)
+        print(f"decode step, batch {a.batch}, context {a.prompt}, {cfg.num_hidden_layers} of {layers_full} layers "
+              f"(time of each launch inside the recorded step; peaks {pk['source']}):")
+        print(table(rows, pk["hbm_gbs"], pk["bf16_tflops"], tokens=a.batch))
+        rows = profile_prompt(model, [a.prompt])
+        print(f"\nprompt step, one prompt of {a.prompt} tokens:")
+        print(table(rows, pk["hbm_gbs"], pk["bf16_tflops"]))
+        return 0
 
     def timed(fn, reps=1):
         torch.cuda.synchronize()

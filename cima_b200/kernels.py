@@ -99,11 +99,21 @@ class Kernels:
             fn.argtypes = sig
             fn.restype = ctypes.c_int
         self.launches = 0
+        self.library_launches = 0   # matrix products handed to the library (not counted in ``launches``)
         self._scratch_bufs = {}
         self._retired = []          # replaced scratch buffers, kept alive for the graphs recorded with them
         self._error_flag = None
+        self.profile = None         # a StepProfile while a step's launches are being counted and timed
 
     # ------------------------------------------------------------------ plumbing
+    def _admit(self, name: str, nbytes: float = 0, flops: float = 0) -> bool:
+        """Asked before every launch.  Without a profile it says yes.  With one (``self.profile``, see
+        ``cima_b200.engine.profile``) the launch is noted with the bytes it has to move and the operations it has
+        to do, and launches beyond the profile's limit are left out: a step cut after its n-th launch, timed
+        against the step cut after launch n - 1, gives launch n's time inside the step."""
+        p = self.profile
+        return True if p is None else p.admit(name, nbytes, flops)
+
     def _check(self, code: int, what: str) -> None:
         self.launches += 1
         if code != 0:
@@ -144,6 +154,7 @@ class Kernels:
             self._need(xw, "xw", torch.bfloat16, 2); self._need(w_next, "w_next", torch.float32, 1)
             if tuple(xw.shape) != (T, H) or w_next.numel() != H:
                 raise KernelError(f"embed: xw {tuple(xw.shape)} / w_next {tuple(w_next.shape)} do not fit {(T, H)}")
+        if not self._admit("embed", T * H * (table.element_size() + 4)): return
         self._check(self.lib.cima_embed(ids.data_ptr(), table.data_ptr(), dtype_code(table.dtype), x.data_ptr(),
                                         T, H, V, scale, _ptr(ssq), _ptr(w_next) if xw is not None else None, _ptr(xw),
                                         self._stream()), "embed")
@@ -153,6 +164,7 @@ class Kernels:
         T, H = x.shape
         if w.numel() != H or tuple(out.shape) != (T, H):
             raise KernelError(f"rmsnorm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not agree")
+        if not self._admit("rmsnorm", T * H * (4 + out.element_size())): return
         self._check(self.lib.cima_rmsnorm(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
                                           T, H, eps, self._stream()), "rmsnorm")
 
@@ -161,6 +173,7 @@ class Kernels:
         T, I2 = gate_up.shape
         if I2 % 2 or tuple(out.shape) != (T, I2 // 2):
             raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} and out {tuple(out.shape)} do not agree")
+        if not self._admit("swiglu", T * (I2 + I2 // 2) * out.element_size()): return
         self._check(self.lib.cima_swiglu(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), T, I2 // 2,
                                          self._stream()), "swiglu")
 
@@ -168,6 +181,7 @@ class Kernels:
         self._need(x, "x", torch.float32); self._need(delta, "delta")
         if x.shape != delta.shape:
             raise KernelError(f"add_residual: x {tuple(x.shape)} and delta {tuple(delta.shape)} differ")
+        if not self._admit("add_residual", x.numel() * (8 + delta.element_size())): return
         self._check(self.lib.cima_add_residual(x.data_ptr(), delta.data_ptr(), dtype_code(delta.dtype),
                                                x.numel(), self._stream()), "add_residual")
 
@@ -179,6 +193,7 @@ class Kernels:
         if delta.shape != x.shape or out.shape != x.shape or w.numel() != H:
             raise KernelError(f"add_rmsnorm: x {tuple(x.shape)}, delta {tuple(delta.shape)}, out {tuple(out.shape)}, "
                               f"w {tuple(w.shape)} do not agree")
+        if not self._admit("add_rmsnorm", T * H * (8 + 2 * delta.element_size())): return
         self._check(self.lib.cima_add_rmsnorm(x.data_ptr(), delta.data_ptr(), w.data_ptr(), out.data_ptr(),
                                               dtype_code(delta.dtype), T, H, eps, self._stream()), "add_rmsnorm")
 
@@ -186,6 +201,7 @@ class Kernels:
         self._need(x, "x", torch.float32, 2); self._need(rows, "rows", torch.int32, 1); self._need(out, "out", torch.float32, 2)
         if tuple(out.shape) != (rows.numel(), x.shape[1]):
             raise KernelError(f"gather_rows: out is {tuple(out.shape)}, expected {(rows.numel(), x.shape[1])}")
+        if not self._admit("gather_rows", rows.numel() * x.shape[1] * 8): return
         self._check(self.lib.cima_gather_rows(x.data_ptr(), rows.data_ptr(), out.data_ptr(), rows.numel(),
                                               x.shape[1], self._stream()), "gather_rows")
 
@@ -196,6 +212,7 @@ class Kernels:
             self._need(t, n, torch.int32, 1)
             if t.numel() != B:
                 raise KernelError(f"decode_advance: {n} has {t.numel()} entries, expected {B}")
+        if not self._admit("decode_advance", 16 * B): return
         self._check(self.lib.cima_decode_advance(chosen.data_ptr(), tokens.data_ptr(), row_pos.data_ptr(),
                                                  seq_len.data_ptr(), B, self._stream()), "decode_advance")
 
@@ -212,6 +229,7 @@ class Kernels:
             self._need(bias, "bias", torch.float32, 1)
             if bias.numel() != N:
                 raise KernelError(f"linear_plain: bias has {bias.numel()} entries, expected {N}")
+        if not self._admit("linear_plain", w.numel() * w.element_size() + (M * K + M * N) * 4, 2.0 * M * N * K): return
         # one launch takes up to 65535 * 64 rows; cut above that
         step = 65535 * 64
         for m0 in range(0, M, step):
@@ -247,6 +265,7 @@ class Kernels:
             self._need(xw_out, "xw_out", torch.bfloat16, 2); self._need(w_next, "w_next", torch.float32, 1)
             if ssq_out is None or tuple(xw_out.shape) != (M, N) or w_next.numel() != N:
                 raise KernelError("linear_skinny: xw_out goes with ssq_out and must be [rows, N], w_next [N]")
+        if not self._admit(f"linear_skinny[{mode}]", w.numel() * 2 + M * K * 2 + M * N * out.element_size(), 2.0 * M * w.shape[0] * K): return
         self._check(self.lib.cima_linear_skinny(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode,
                                                 M, N, K, K, N, _ptr(ssq_out), _ptr(w_next) if xw_out is not None else None,
                                                 _ptr(xw_out), self._stream()), "linear_skinny")
@@ -266,6 +285,7 @@ class Kernels:
                               f"{tuple(ssq.shape)}, out {tuple(out.shape)} {out.dtype} do not agree")
         if bias is not None:
             self._need(bias, "bias", torch.float32, 1)
+        if not self._admit(f"linear_skinny_norm[{mode}]", w.numel() * 2 + M * K * 2 + M * N * out.element_size(), 2.0 * M * w.shape[0] * K): return
         self._check(self.lib.cima_linear_skinny_norm(xw.data_ptr(), ssq.data_ptr(), ssq.shape[1], eps, w.data_ptr(),
                                                      _ptr(bias), out.data_ptr(), mode, M, N, K, K, N, self._stream()),
                     "linear_skinny_norm")
@@ -297,6 +317,7 @@ class Kernels:
             if ssq.shape[0] != M:
                 raise KernelError(f"qkv_rope: ssq {tuple(ssq.shape)} does not fit {M} rows")
             head = (a.data_ptr(), ssq.data_ptr(), ssq.shape[1], eps)
+        if not self._admit("qkv_rope_skinny", w.numel() * 2 + M * K * 2 + M * N * 2, 2.0 * M * N * K): return
         self._check(self.lib.cima_qkv_rope_skinny(*head, w.data_ptr(), _ptr(bias), qkv.data_ptr(), M, K, K, N,
                                                   inv_freq.data_ptr(), row_pos.data_ptr(), row_seq.data_ptr(),
                                                   seq_slot.data_ptr(), kv.storage.data_ptr(), kv.block_table.data_ptr(),
@@ -321,6 +342,7 @@ class Kernels:
             swap = M <= 64 and mode != SK_SWIGLU
         if self._error_flag is None:
             self._error_flag = torch.zeros(1, dtype=torch.int32, device=a.device)
+        if not self._admit(f"gemm_tcgen05[{mode}]", (w.numel() + M * K) * 2 + M * N * out.element_size(), 2.0 * M * w.shape[0] * K): return
         if swap:
             if mode == SK_SWIGLU:
                 raise KernelError("gemm_tc: the gated epilogue is not offered with swapped operands")
@@ -349,9 +371,16 @@ class Kernels:
             self._need(bias, "bias", torch.float32, 1)
         if self._error_flag is None:
             self._error_flag = torch.zeros(1, dtype=torch.int32, device=a.device)
+        if not self._admit(f"gemm_tcgen05_pair[{mode}]", (w.numel() + M * K) * 2 + M * N * out.element_size(), 2.0 * M * w.shape[0] * K): return
         self._check(self.lib.cima_gemm_tcgen05_pair(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, M,
                                                     w.shape[0], K, N, N if mode == SK_SWIGLU else 0,
                                                     self._error_flag.data_ptr(), self._stream()), "gemm_tcgen05_pair")
+
+    def error_flag(self, device) -> torch.Tensor:
+        """The int32 word that kernels with bounded waits set when a wait runs out (``device_errors`` reads it)."""
+        if self._error_flag is None:
+            self._error_flag = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._error_flag
 
     def device_errors(self) -> int:
         """The error flag that a bounded wait inside a kernel sets when it runs out (synchronises).  Reading it
@@ -383,6 +412,7 @@ class Kernels:
             args = (kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1], kv.ring_pages, kv.page_size)
         else:
             args = (None, None, 0, 0, 0)
+        if not self._admit("rope_append", 2 * qkv.numel() * qkv.element_size()): return
         self._check(self.lib.cima_rope_append(qkv.data_ptr(), dtype_code(qkv.dtype), qkv.shape[1], inv_freq.data_ptr(),
                                               rotary_dim, row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
                                               seq_len.data_ptr(), *args, T, n_heads, n_kv_heads, head_dim, self._stream()), "rope_append")
@@ -401,11 +431,40 @@ class Kernels:
             args = (kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1], kv.ring_pages, kv.page_size)
         else:
             args = (None, None, 0, 0, 1)
+        if not self._admit("attention_plain", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
         self._check(self.lib.cima_attention_plain(qkv.data_ptr(), dtype_code(qkv.dtype), qkv.shape[1], *args,
                                                   row_pos.data_ptr(), row_seq.data_ptr(), seq_slot.data_ptr(),
                                                   seq_first_row.data_ptr(), out.data_ptr(), out.shape[1], T,
                                                   n_heads, n_kv_heads, head_dim, scale, window,
                                                   1 if from_cache else 0, self._stream()), "attention_plain")
+
+    def _attention_work(self, qkv, n_heads, n_kv_heads, head_dim):
+        """(bytes, operations) of an attention launch while a step is profiled: the keys and values of the step's
+        sequences (``profile.kv_tokens``: positions that the step's rows read, each once) and the products over the
+        (query, key) pairs (``profile.qk_pairs``); the step's maker states both."""
+        p = self.profile
+        if p is None:
+            return 0, 0
+        elt = qkv.element_size()
+        return (2.0 * p.kv_tokens * n_kv_heads * head_dim * elt + 2.0 * qkv.shape[0] * n_heads * head_dim * elt,
+                4.0 * p.qk_pairs * n_heads * head_dim)
+
+    def library_mm(self, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
+        """out = a @ w.T (+ bias) by the library's matrix product (cuBLAS through torch), where the reference calls
+        its library too; ``out`` may be float32 for bfloat16 operands (the head).  Counted apart from this
+        library's own launches."""
+        if not self._admit("library_mm", (w.numel() + a.numel()) * a.element_size() + out.numel() * out.element_size(),
+                           2.0 * a.shape[0] * w.shape[0] * w.shape[1]):
+            return
+        self.library_launches += 1
+        if out.dtype is not a.dtype:
+            torch.mm(a, w.t(), out_dtype=out.dtype, out=out)
+            if bias is not None:
+                out += bias
+        elif bias is not None:
+            torch.addmm(bias, a, w.t(), out=out)
+        else:
+            torch.mm(a, w.t(), out=out)
 
     def attention(self, qkv: torch.Tensor, kv, batch, out: torch.Tensor, n_heads: int, n_kv_heads: int,
                   head_dim: int, scale: float, window: int, from_cache: bool, after_append: bool = False) -> None:
@@ -442,6 +501,7 @@ class Kernels:
         T = qkv.shape[0]
         if tuple(out.shape) != (T, n_heads * head_dim) or tile_seq.numel() != tile_row0.numel():
             raise KernelError(f"attention_prefill: out {tuple(out.shape)} or the block list do not fit")
+        if not self._admit("attention_prefill", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
         self._check(self.lib.cima_attention_prefill(qkv.data_ptr(), qkv.shape[1], tile_seq.data_ptr(), tile_row0.data_ptr(),
                                                     seq_first_row.data_ptr(), out.data_ptr(), out.shape[1], T,
                                                     tile_seq.numel(), n_heads, n_kv_heads, head_dim, scale, window,
@@ -457,6 +517,7 @@ class Kernels:
         T = qkv.shape[0]
         if tuple(out.shape) != (T, n_heads * head_dim) or batch.q_tile_seq.numel() != batch.q_tile_row0.numel():
             raise KernelError(f"attention_extend: out {tuple(out.shape)} or the block list do not fit")
+        if not self._admit("attention_extend", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
         self._check(self.lib.cima_attention_extend(
             qkv.data_ptr(), qkv.shape[1], batch.q_tile_seq.data_ptr(), batch.q_tile_row0.data_ptr(),
             batch.seq_first_row.data_ptr(), kv.storage.data_ptr(), kv.block_table.data_ptr(), kv.block_table.shape[1],
@@ -476,6 +537,7 @@ class Kernels:
             raise KernelError(f"attention_prefill_tc: out {tuple(out.shape)} or the block list do not fit")
         if self._error_flag is None:
             self._error_flag = torch.zeros(1, dtype=torch.int32, device=qkv.device)
+        if not self._admit("attention_prefill_tc", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
         if kv is not None:
             self._need(kv.storage, "cache", torch.bfloat16, 5); self._need(kv.block_table, "block_table", torch.int32, 2)
             self._check(self.lib.cima_attention_extend_tc(
@@ -517,6 +579,7 @@ class Kernels:
                 n_splits = 8
             if max_len > 0:
                 n_splits = min(n_splits, -(-max_len // 64))
+        if not self._admit(f"attention_decode[{n_splits} splits]", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
         part_o = part_ml = None
         if n_splits > 1:
             part_o = self._scratch("attn_o", B * n_heads * n_splits * head_dim, qkv.device)
@@ -546,6 +609,7 @@ class Kernels:
         n, V = logits.shape
         if tokens.numel() < n:
             raise KernelError(f"argmax: {tokens.numel()} token places for {n} rows")
+        if not self._admit("argmax", n * V * 4): return
         self._check(self.lib.cima_argmax(logits.data_ptr(), V, n, V, tokens.data_ptr(), self._stream()), "argmax")
 
     def sample(self, logits: torch.Tensor, row_slot: torch.Tensor, params: torch.Tensor, rng: torch.Tensor,
@@ -559,6 +623,7 @@ class Kernels:
         n, V = logits.shape
         if tokens.numel() < n:
             raise KernelError(f"sample: {tokens.numel()} token places for {n} rows")
+        if not self._admit("argmax" if all_greedy else "sample", n * V * 4): return
         if all_greedy:
             self._check(self.lib.cima_argmax(logits.data_ptr(), V, n, V, tokens.data_ptr(), self._stream()), "argmax")
             return

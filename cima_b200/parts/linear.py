@@ -64,12 +64,9 @@ class Linear:
         elif self._skinny(M):
             K_.linear_skinny(a, self.weight, self.bias, out, SK_STORE)
         else:
-            if self.bias is not None:
-                if self._bias_act is None:
-                    self._bias_act = self.bias.to(self.rt.dtype)
-                torch.addmm(self._bias_act, a, self.weight.t(), out=out)
-            else:
-                torch.mm(a, self.weight.t(), out=out)
+            if self.bias is not None and self._bias_act is None:
+                self._bias_act = self.bias.to(self.rt.dtype)
+            K_.library_mm(a, self.weight, out, self._bias_act)
         return out
 
     def accumulate(self, a: torch.Tensor, x: torch.Tensor, next_norm=None):
@@ -126,12 +123,7 @@ class Linear:
         else:
             # more rows than the skinny kernel streams well (it takes 600 us for 64 rows of a 152,064-wide head,
             # the library 180 us): the library product with a float32 result, the bias added to that
-            if a.is_cuda:
-                torch.mm(a, self.weight.t(), out_dtype=torch.float32, out=out)
-            else:                                                     # host-logic tests on CPU stand-ins
-                torch.mm(a.float(), self.weight.float().t(), out=out)
-            if self.bias is not None:
-                out += self.bias
+            K_.library_mm(a, self.weight, out, self.bias)
         return out
 
 

@@ -76,6 +76,9 @@ class ReferenceKernels:
         else:
             out.copy_(y.to(out.dtype))
 
+    def library_mm(self, a, w, out, bias=None):
+        self.linear_plain(a, w, bias, out)
+
     def linear_skinny_norm(self, xw, ssq, eps, w, bias, out, mode):
         inv = 1.0 / torch.sqrt(ssq.to(self.compute).sum(dim=1, keepdim=True) / xw.shape[1] + eps)
         h = (xw.to(self.compute) * inv).to(torch.bfloat16)
