@@ -14,7 +14,7 @@ from typing import List, Sequence
 import numpy as np
 import torch
 
-from .batch import StepBatch
+from .batch import StepBatch, StepEntry, build_batch
 
 
 class DecodeGraph:
@@ -85,3 +85,47 @@ class DecodeGraph:
         else:
             self.graph.replay()
         return self.chosen
+
+
+PROMPT_BUCKETS = (16, 32, 64)      # rows of a recorded prompt step; longer prompts hide the host's launches behind their own work
+
+
+class PromptGraph:
+    """The step of ONE short prompt recorded as a graph, for the first token's sake: a prompt of up to 64 tokens is
+    a few milliseconds of device work behind some 250 launches from the host, and the host is the slower of the two.
+    The prompt is padded at its end to the bucket's rows; the rows of the padding come after every real row, so no
+    real row sees them (attention is causal), their keys land beyond the sequence's committed length, where the
+    next tokens are written over them, and logits are gathered at the prompt's last real row only.  Padding
+    changes no result.  (The reference records its decode step only, src/models/transformer.rs:1467-1494.)"""
+
+    def __init__(self, model, rows: int):
+        self.model, self.rows = model, rows
+        dev = model.rt.device
+        self.batch = build_batch([StepEntry(0, [0] * rows, [rows - 1])], [0], model.spec.vocab, dev)
+        self.batch.host_seq_slot = self.batch.host_seq_len = None       # they change from replay to replay
+        self.host = torch.zeros(rows + 2, dtype=torch.int32).pin_memory()
+        self.graph = None
+        self.logits = None
+
+    def run(self, slot: int, tokens: Sequence[int]) -> torch.Tensor:
+        """Float32 logits [1, vocab] at the prompt's last token.  The caller has reserved ``rows`` positions for the
+        slot and commits ``len(tokens)`` afterwards."""
+        n, R = len(tokens), self.rows
+        h = self.host.numpy()
+        h[:n] = tokens
+        h[n:R] = 0
+        h[R], h[R + 1] = slot, n - 1
+        b = self.batch
+        b.tokens.copy_(self.host[:R], non_blocking=True)
+        b.seq_slot.copy_(self.host[R:R + 1], non_blocking=True)
+        b.want_rows.copy_(self.host[R + 1:R + 2], non_blocking=True)
+        if self.graph is None:
+            out = self.model.forward(b)                 # a real step, eagerly; it also warms every kernel up
+            torch.cuda.current_stream().synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.logits = self.model.forward(b)
+            self.graph = g
+            return out
+        self.graph.replay()
+        return self.logits

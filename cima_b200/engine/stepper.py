@@ -39,6 +39,7 @@ class ModelStepper:
         self.use_graphs = (use_graphs and torch.device(model.rt.device).type == "cuda"
                            and getattr(model, "graph_safe", False))
         self._graphs = {}
+        self._prompt_graphs = {}      # rows of the bucket -> PromptGraph
         self._armed = None            # (graph, slots) whose device-side inputs are those of the next step
         cache = model.cache
         self.max_batch = max(1, min(max_batch, cache.n_slots))
@@ -123,6 +124,10 @@ class ModelStepper:
         for s, n in zip(slots, reused):
             if n:
                 cache.rewind(s, n)
+        if len(slots) == 1 and not reused[0]:
+            first = self._short_prompt(slots[0], prompts[0], options[0])
+            if first is not None:
+                return [first]
         out: List[Optional[int]] = [None] * len(slots)
         # sequences that start run as one prompt step (attention over the step's own keys), those that go on as
         # another (rows that read the cache)
@@ -135,6 +140,34 @@ class ModelStepper:
             for i, t in zip(group, toks):
                 out[i] = t
         return out  # type: ignore[return-value]
+
+    def _short_prompt(self, slot: int, prompt: Sequence[int], option: GenOptions) -> Optional[int]:
+        """The first token of one short prompt through a recorded step (``PromptGraph``), or None where that does
+        not apply: graphs off, a prompt beyond the largest bucket, no room for the bucket's rows, or a mixer that
+        keeps state of its own per sequence (the padding's rows would pass through it)."""
+        from .graph import PROMPT_BUCKETS, PromptGraph
+        n = len(prompt)
+        if not self.use_graphs or n == 0 or n > PROMPT_BUCKETS[-1] or self.model.cache.has_mixer_state:
+            return None
+        rows = next(r for r in PROMPT_BUCKETS if r >= n)
+        cache = self.model.cache
+        if rows > self.max_position or cache.length(slot) != 0:
+            return None
+        vocab = self.model.spec.vocab
+        if min(prompt) < 0 or max(prompt) >= vocab:
+            raise ValueError(f"token ids must lie in [0, {vocab})")
+        try:
+            cache.must_fit([(slot, rows)])
+        except (CacheFull, CapacityError):
+            return None
+        cache.reserve(slot, rows)
+        cache.flush()
+        g = self._prompt_graphs.get(rows)
+        if g is None:
+            g = self._prompt_graphs[rows] = PromptGraph(self.model, rows)
+        logits = g.run(slot, prompt)
+        cache.commit(slot, n)
+        return self._choose(logits, [slot], [option], n)[0]
 
     def decode(self, slots, last_tokens, options) -> List[int]:
         if not self.use_graphs:

@@ -283,37 +283,36 @@ def test_many_prompts_generate_as_the_plain_loop_does(name, n_prompts, pipeline)
 
 def test_batch_sizes_in_any_order_through_recorded_steps():
     """Recorded decode steps keep the addresses of the scratch they were recorded with (the attention's splits, the
-    sampler's row copies).  Batches of 1, 8, 1, then 8 shrinking to 4 and 8 again, with sampling on, must give what
-    step-by-step decoding gives, and logits that a caller kept from an earlier step must stay as they were."""
+    sampler's row copies).  Batches of 1, 8, 1, then 8 shrinking to 4 and 8 again, with sampling on, on ONE model
+    must give what each call gives on a model of its own (which has recorded nothing before), and logits that a
+    caller kept from an earlier step must stay as they were."""
+    from cima_b200.engine import StepEntry
     name = "B"
     V = TINY[name]["vocab_size"]
     prompts = [random_tokens(V, 5 + 3 * i, seed=900 + i) for i in range(8)]
     opts = dict(temperature=0.9, top_k=30, top_p=0.95, repeat_penalty=1.1, seed=21)
-    outs = []
-    for use_graphs in (True, False):
-        lm = cima_b200.load(model_folder(name), dtype="bfloat16", max_tokens=4096, verbose=False, use_graphs=use_graphs)
-        assert lm.stepper.use_graphs == use_graphs
-        from cima_b200.engine import StepEntry
-        (slot,) = lm.model.cache.open(1)
-        kept = lm.step([StepEntry(slot, prompts[0], [len(prompts[0]) - 1])])
-        lm.model.cache.close([slot])
-        before = kept.clone()
-        res = []
-        res.append(lm.generate(prompts[:1], max_tokens=20, **opts))
-        res.append(lm.generate(prompts, max_tokens=20, **opts))
-        res.append(lm.generate(prompts[:1], max_tokens=20, **opts))
-        # four of the eight stop after a few tokens: 8 -> 4 sequences, then 8 again
-        stops = tuple(res[1][i].tokens[3 + i] for i in range(4))
-        res.append(lm.generate(prompts, max_tokens=20, stop=stops, **opts))
-        res.append(lm.generate(prompts, max_tokens=20, **opts))
-        res.append(lm.generate(prompts[:3], temperature=0, repeat_penalty=1.0, max_tokens=20))
-        res.append(lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=20))
-        assert torch.equal(kept, before)
-        outs.append([[r.tokens for r in x] for x in res])
-        assert outs[-1][1] == outs[-1][4]
-        lm.model.cache.check()
-        assert lm.model.cache.slots.held == 0
-    assert outs[0] == outs[1]
+    greedy = dict(temperature=0, repeat_penalty=1.0)
+
+    def fresh():
+        return cima_b200.load(model_folder(name), dtype="bfloat16", max_tokens=4096, verbose=False)
+
+    probe = fresh().generate(prompts, max_tokens=20, **opts)
+    stops = tuple(probe[i].tokens[3 + i] for i in range(4))       # four of the eight stop early: 8 -> 4 sequences
+    calls = [(prompts[:1], dict(opts)), (prompts, dict(opts)), (prompts[:1], dict(opts)), (prompts, dict(opts, stop=stops)),
+             (prompts, dict(opts)), (prompts[:3], dict(greedy)), (prompts, dict(greedy))]
+    want = [[r.tokens for r in fresh().generate(ps, max_tokens=20, **o)] for ps, o in calls]
+    lm = fresh()
+    assert lm.stepper.use_graphs
+    (slot,) = lm.model.cache.open(1)
+    kept = lm.step([StepEntry(slot, prompts[0], [len(prompts[0]) - 1])])
+    lm.model.cache.close([slot])
+    before = kept.clone()
+    got = [[r.tokens for r in lm.generate(ps, max_tokens=20, **o)] for ps, o in calls]
+    assert torch.equal(kept, before)
+    assert got == want
+    assert any(len(t) < 20 for t in got[3])
+    lm.model.cache.check()
+    assert lm.model.cache.slots.held == 0
 
 
 def test_other_tokens_than_the_chosen_ones_may_be_fed_back():
@@ -412,3 +411,34 @@ def test_loading_holds_one_group_of_tensors_on_the_host_not_the_checkpoint():
     group = max(2 * V * H, 2 * 2 * I * H, 2 * (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim * H)
     assert 0 < m.load_peak_host_bytes <= group + 4096
     assert m.load_peak_host_bytes < total / 3
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_prompts_through_recorded_prompt_steps(dtype):
+    """One short prompt at a time takes a recorded prompt step whose rows are padded to 16, 32 or 64: lengths at and
+    around the buckets' edges, each twice (the second time the step is replayed), then a batch, then longer ones.
+    32-bit: the tokens of the plain implementation; bfloat16: maxima of the plain logits within its rounding.
+    The padding's keys lie beyond the sequence's length and are written over by the tokens that follow."""
+    name = "B"
+    V = TINY[name]["vocab_size"]
+    cfg, W = plain_load(model_folder(name))
+    lm = cima_b200.load(model_folder(name), dtype=dtype, max_tokens=2048, verbose=False)
+    for n in (1, 2, 15, 16, 17, 31, 33, 64, 65, 100):
+        for rep in range(2):
+            p = random_tokens(V, n, seed=3000 + n + 7 * rep)
+            r = lm.generate([p], temperature=0, repeat_penalty=1.0, max_tokens=6)[0]
+            if dtype == "float32":
+                assert r.tokens == plain_generate(name, p, dict(temperature=0.0), 6)[0], (n, rep)
+            else:
+                seq = list(p)
+                for t in r.tokens:
+                    lg = plain_forward(W, cfg, seq)[-1]
+                    assert lg[t] >= lg.max() - 4e-2, (n, rep)
+                    seq.append(t)
+    assert sorted(lm.stepper._prompt_graphs) == [16, 32, 64]
+    opts = dict(temperature=0.8, top_k=40, top_p=0.9, repeat_penalty=1.1, seed=4)
+    if dtype == "float32":
+        p = random_tokens(V, 20, seed=1)
+        assert lm.generate([p], max_tokens=6, **opts)[0].tokens == plain_generate(name, p, opts, 6)[0]
+    lm.model.cache.check()
+    assert lm.model.cache.slots.held == 0

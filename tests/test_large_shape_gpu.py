@@ -217,12 +217,14 @@ def test_gated_feed_forward_in_row_chunks(folder, monkeypatch):
         torch.cuda.empty_cache()
     assert torch.equal(outs["float32", "whole"], outs["float32", "chunks"])
     # bfloat16: chunks of 128 rows take the library product and the activation kernel where the whole prompt takes
-    # the tcgen05 product, so the two differ by rounding.  Compared at the chunks' seams, the first and the last
-    # rows (about a hundred rows, the sample that this file's tolerance is used with elsewhere).
-    rows = sorted(set(range(8)) | {126, 127, 128, 129, 254, 255, 256, 257} | set(range(216, 300)))
+    # the tcgen05 product with the activation in its epilogue; everything else is the same kernels on the same
+    # values, so the two runs differ by the rounding of one layer part and stay within the tolerance of each other,
+    # and the chunked run is on average as close to the 32-bit logits as the whole one
     tol = REL_BF16 * outs["float32", "whole"].std().item()
-    assert (outs["bfloat16", "chunks"][rows] - outs["float32", "whole"][rows]).abs().max().item() <= tol
-    assert (outs["bfloat16", "whole"][rows] - outs["float32", "whole"][rows]).abs().max().item() <= tol
+    assert (outs["bfloat16", "chunks"] - outs["bfloat16", "whole"]).abs().max().item() <= tol
+    err_chunks = (outs["bfloat16", "chunks"] - outs["float32", "whole"]).abs().mean().item()
+    err_whole = (outs["bfloat16", "whole"] - outs["float32", "whole"]).abs().mean().item()
+    assert err_chunks <= 1.1 * err_whole
 
 
 def test_the_full_vocabulary_head_argmax_and_sampler():
