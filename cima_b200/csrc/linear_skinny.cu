@@ -1,8 +1,9 @@
-// Matrix product for few rows (decode): out[m,n] = sum_k X[m,k] * W[n,k], M <= 16, bfloat16 operands,
+// Matrix product for few rows (decode): out[m,n] = sum_k X[m,k] * W[n,k], M <= 8, bfloat16 operands,
 // float32 accumulation.  The step is bound by reading W once from HBM, so the kernel is built
 // around the weight stream: every thread keeps several 16-byte loads of W in flight, the weights
 // are the 16-row operand of the tensor-core instruction and the few activation rows are its 8-wide
-// operand ("swap A/B"), so M = 1..8 costs one instruction per 16x16 weights and M = 9..16 two.
+// operand ("swap A/B"), so M = 1..8 costs one instruction per 16x16 weights.  (With a second 8-row tile
+// for 9 to 16 rows the kernel lost to the library product on B200 and is not instantiated.)
 //
 // Work split.  One block owns 16 output features (or 16 gate and the 16 matching up features for
 // the gated epilogue).  Its 8 warps split K in interleaved chunks; their partial sums are added in
@@ -367,7 +368,7 @@ static int dispatch_mode(int mode, const void* X, const void* W, const float* bi
 }
 
 static int skinny_checks(const void* X, const void* W, const float* bias, int mode, int M, int N, int K, int ldx) {
-  if (M > 16) return cima_fail(CIMA_E_SIZE, "linear_skinny: %d rows; this kernel takes at most 16 (more rows re-read the activations too often: the library product streams the weights faster there)", M);
+  if (M > 8) return cima_fail(CIMA_E_SIZE, "linear_skinny: %d rows; this kernel takes at most 8 (the library product streams the weights faster for more)", M);
   if (N <= 0 || K <= 0) return cima_fail(CIMA_E_SIZE, "linear_skinny: N %d and K %d must be positive", N, K);
   if (K % 8 || ldx % 8) return cima_fail(CIMA_E_SIZE, "linear_skinny: K %d and the row stride %d must be multiples of 8 (16-byte loads)", K, ldx);
   if (((uintptr_t)X | (uintptr_t)W) & 15) return cima_fail(CIMA_E_ARG, "linear_skinny: X and W must be 16-byte aligned");
@@ -377,7 +378,7 @@ static int skinny_checks(const void* X, const void* W, const float* bias, int mo
 
 // X [M, K] bf16 (row stride ldx), W [N, K] bf16 (for mode 2: [2N, K], gate rows then up rows),
 // bias float32 [N] or null, out [M, N] (row stride ldo) in the dtype of the mode.
-// Accepts 1 <= M <= 16, any N, K a multiple of 8 (16-byte rows), 16-byte aligned X, W and ldx % 8 == 0.
+// Accepts 1 <= M <= 8, any N, K a multiple of 8 (16-byte rows), 16-byte aligned X, W and ldx % 8 == 0.
 // ssq_out (mode 1 only, may be null): [M, ceil(N / 16)] partial sums of squares of the updated rows.
 // w_next / xw_out (mode 1 with ssq_out, may be null): weight [N] of the norm that follows, and where to put
 // bf16(updated row * that weight), [M, N] with row stride ldo.
@@ -390,36 +391,34 @@ extern "C" int cima_linear_skinny(const void* X, const void* W, const float* bia
   if (xw_out && (mode != SK_ACCUM || !ssq_out || !w_next)) return cima_fail(CIMA_E_ARG, "linear_skinny: the scaled rows go with mode 1, the partial sums and the next norm's weight");
   SkinnyNorm nm{nullptr, 0, 0.f, mode == SK_ACCUM ? ssq_out : nullptr,
                 mode == SK_ACCUM ? w_next : nullptr, mode == SK_ACCUM ? (__nv_bfloat16*)xw_out : nullptr};
-  if (M <= 8) return dispatch_mode<1, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
-  return dispatch_mode<2, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
+  return dispatch_mode<1, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
 }
 
 // The same with RMSNorm folded in: xw [M, K] bf16 = bf16(x * w) as cima_embed or an accumulating product left
-// it (row stride ldx), ssq [M, parts] the partial sums of squares of the rows x, and eps.  At most 16 rows.
+// it (row stride ldx), ssq [M, parts] the partial sums of squares of the rows x, and eps.  At most 8 rows.
 extern "C" int cima_linear_skinny_norm(const void* xw, const float* ssq, int parts, float eps, const void* W,
                                        const float* bias, void* out, int mode, int M, int N, int K, int ldx, int ldo,
                                        cudaStream_t stream) {
   if (M <= 0) return 0;
-  if (M > 16) return cima_fail(CIMA_E_SIZE, "linear_skinny_norm: %d rows; the folded norm takes at most 16", M);
+  if (M > 8) return cima_fail(CIMA_E_SIZE, "linear_skinny_norm: %d rows; the folded norm takes at most 8", M);
   if (!ssq || parts <= 0) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: the partial sums of squares are needed");
   if (mode == SK_ACCUM) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: the accumulating epilogue reads activations, not the residual");
   int rc = skinny_checks(xw, W, bias, mode, M, N, K, ldx);
   if (rc) return rc;
   SkinnyNorm nm{ssq, parts, eps, nullptr, nullptr, nullptr};
-  if (M <= 8) return dispatch_mode<1, true>(mode, xw, W, bias, out, M, N, K, ldx, ldo, nm, stream);
-  return dispatch_mode<2, true>(mode, xw, W, bias, out, M, N, K, ldx, ldo, nm, stream);
+  return dispatch_mode<1, true>(mode, xw, W, bias, out, M, N, K, ldx, ldo, nm, stream);
 }
 
 // Mode 4 (see SkinnyRope): qkv [M, (nh + 2 nkv) * hd] receives the rotated q; k and v go to the cache.
 // X: bf16 activations, or (ssq != null) bf16(x * w) with the partial sums of the rows: the norm folded in.
-// At most 16 rows; head_dim a multiple of 16; every dimension of a head rotates (rotary_dim == head_dim).
+// At most 8 rows; head_dim a multiple of 16; every dimension of a head rotates (rotary_dim == head_dim).
 extern "C" int cima_qkv_rope_skinny(const void* X, const float* ssq, int parts, float eps, const void* W,
                                     const float* bias, void* qkv, int M, int K, int ldx, int ldo,
                                     const float* inv_freq, const int* row_pos, const int* row_seq,
                                     const int* seq_slot, void* cache, const int* table, int table_width, int ring,
                                     int page_size, int nh, int nkv, int hd, cudaStream_t stream) {
   if (M <= 0) return 0;
-  if (M > 16) return cima_fail(CIMA_E_SIZE, "qkv_rope_skinny: %d rows; this kernel takes at most 16", M);
+  if (M > 8) return cima_fail(CIMA_E_SIZE, "qkv_rope_skinny: %d rows; this kernel takes at most 8", M);
   if (hd <= 0 || hd % 16 || nh <= 0 || nkv <= 0) return cima_fail(CIMA_E_SIZE, "qkv_rope_skinny: head_dim %d must be a multiple of 16 and the head counts positive", hd);
   if (!cache || !table || !inv_freq || !row_pos || !row_seq || !seq_slot) return cima_fail(CIMA_E_ARG, "qkv_rope_skinny: positions, frequencies and the cache are needed");
   const int N = (nh + 2 * nkv) * hd;
@@ -430,10 +429,6 @@ extern "C" int cima_qkv_rope_skinny(const void* X, const float* ssq, int parts, 
   SkinnyNorm nm{ssq, parts, eps, nullptr, nullptr, nullptr};
   SkinnyRope rp{inv_freq, row_pos, row_seq, seq_slot, (__nv_bfloat16*)cache,
                 CimaPaged{table, table_width, ring, page_size, nkv, hd}, nh, nkv, hd};
-  if (norm) {
-    if (M <= 8) return launch_skinny<1, 1, 4, SK_QKV_ROPE, true>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
-    return launch_skinny<2, 1, 4, SK_QKV_ROPE, true>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
-  }
-  if (M <= 8) return launch_skinny<1, 1, 4, SK_QKV_ROPE, false>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
-  return launch_skinny<2, 1, 4, SK_QKV_ROPE, false>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
+  if (norm) return launch_skinny<1, 1, 4, SK_QKV_ROPE, true>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
+  return launch_skinny<1, 1, 4, SK_QKV_ROPE, false>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);
 }

@@ -15,7 +15,7 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 18
+ABI_VERSION = 19
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
@@ -60,7 +60,6 @@ _SIGNATURES = {
     "cima_attention_extend_tc": [_vp, _i, _vp, _vp, _vp, _vp, ctypes.c_longlong, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                  _f, _i, _vp, _vp],
     "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
-    "cima_gemm_tcgen05": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
     "cima_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -242,7 +241,7 @@ class Kernels:
     def linear_skinny(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
                       mode: int, ssq_out: Optional[torch.Tensor] = None, w_next: Optional[torch.Tensor] = None,
                       xw_out: Optional[torch.Tensor] = None) -> None:
-        """Few rows (<= 16), bf16 operands; ``mode`` is one of SK_*.  For SK_SWIGLU ``w`` is [2N, K].
+        """Few rows (<= 8), bf16 operands; ``mode`` is one of SK_*.  For SK_SWIGLU ``w`` is [2N, K].
         With SK_ACCUM, ``ssq_out`` [M, ceil(N / 16)] receives partial sums of squares of the updated rows and
         ``xw_out`` [M, N] bf16 the updated rows times ``w_next`` (the weight of the norm that follows)."""
         self._need(a, "a", torch.bfloat16, 2); self._need(w, "w", torch.bfloat16, 2); self._need(out, "out", None, 2)
@@ -272,7 +271,7 @@ class Kernels:
 
     def linear_skinny_norm(self, xw: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tensor,
                            bias: Optional[torch.Tensor], out: torch.Tensor, mode: int) -> None:
-        """``linear_skinny`` of RMSNorm(x) for at most 16 rows: ``xw`` [M, K] bf16 = bf16(x * norm weight) and
+        """``linear_skinny`` of RMSNorm(x) for at most 8 rows: ``xw`` [M, K] bf16 = bf16(x * norm weight) and
         ``ssq`` [M, parts], the partial sums of squares of the rows x, as ``embed`` or an accumulating
         ``linear_skinny`` left them."""
         self._need(xw, "xw", torch.bfloat16, 2); self._need(ssq, "ssq", torch.float32, 2)
@@ -292,7 +291,7 @@ class Kernels:
 
     def qkv_rope(self, a, w: torch.Tensor, bias: Optional[torch.Tensor], qkv: torch.Tensor, inv_freq: torch.Tensor,
                  row_pos, row_seq, seq_slot, kv, n_heads: int, n_kv_heads: int, head_dim: int, norm=None) -> None:
-        """The q/k/v projection of a decode step (at most 16 rows) with rotation and cache append in its
+        """The q/k/v projection of a decode step (at most 8 rows) with rotation and cache append in its
         epilogue: the rotated q lands in ``qkv`` [rows, (heads + 2 kv_heads) * head_dim], k and v in the layer's
         pages.  ``a``: bf16 activations, or with ``norm = (ssq, eps)`` the rows bf16(x * norm weight) and
         the partial sums of squares of x: the RMSNorm is folded in."""
@@ -324,42 +323,11 @@ class Kernels:
                                                   kv.block_table.shape[1], kv.ring_pages, kv.page_size, n_heads,
                                                   n_kv_heads, head_dim, self._stream()), "qkv_rope_skinny")
 
-    def gemm_tc(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int,
-                swap: Optional[bool] = None, bn: Optional[int] = None) -> None:
-        """out = epilogue(a @ w.T) on the tcgen05 tensor cores (bf16 operands, float32 accumulation in
-        tensor memory, operands by TMA).  ``mode`` as for ``linear_skinny`` (SK_*); for SK_SWIGLU ``w`` is
-        [2N, K].  ``swap`` makes the weights the 128-row operand (few rows of ``a``, at most 64... 256)."""
-        self._need(a, "a", torch.bfloat16, 2); self._need(w, "w", torch.bfloat16, 2); self._need(out, "out", None, 2)
-        M, K = a.shape
-        N = w.shape[0] // 2 if mode == SK_SWIGLU else w.shape[0]
-        want = torch.float32 if mode in (SK_ACCUM, SK_STORE_F32) else torch.bfloat16
-        if w.shape[1] != K or tuple(out.shape) != (M, N) or out.dtype is not want:
-            raise KernelError(f"gemm_tc(mode {mode}): a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} "
-                              f"{out.dtype} do not agree")
-        if bias is not None:
-            self._need(bias, "bias", torch.float32, 1)
-        if swap is None:
-            swap = M <= 64 and mode != SK_SWIGLU
-        if self._error_flag is None:
-            self._error_flag = torch.zeros(1, dtype=torch.int32, device=a.device)
-        if not self._admit(f"gemm_tcgen05[{mode}]", (w.numel() + M * K) * 2 + M * N * out.element_size(), 2.0 * M * w.shape[0] * K): return
-        if swap:
-            if mode == SK_SWIGLU:
-                raise KernelError("gemm_tc: the gated epilogue is not offered with swapped operands")
-            bn = bn or (64 if M <= 64 else 128 if M <= 128 else 256)
-            code = self.lib.cima_gemm_tcgen05(w.data_ptr(), a.data_ptr(), _ptr(bias), out.data_ptr(), mode, N, M, K,
-                                              N, 1, 1, 0, bn, self._error_flag.data_ptr(), self._stream())
-        else:
-            bn = bn or (256 if N >= 2048 else 128)
-            code = self.lib.cima_gemm_tcgen05(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, M,
-                                              w.shape[0], K, N, 0, 0, N if mode == SK_SWIGLU else 0, bn,
-                                              self._error_flag.data_ptr(), self._stream())
-        self._check(code, "gemm_tcgen05")
-
     def gemm_tc_pair(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
                      mode: int) -> None:
-        """``gemm_tc`` for many rows on pairs of SMs (tcgen05 cta_group::2, tiles of 256 x 256): each SM of a
-        pair stages only half of the weight tile.  Same modes and layouts as ``gemm_tc`` without ``swap``."""
+        """out = epilogue(a @ w.T) on the tcgen05 tensor cores, for many rows: bf16 operands by TMA, float32
+        accumulation in tensor memory, pairs of SMs on tiles of 256 x 256 (cta_group::2; each SM of a pair stages
+        only half of the weight tile).  ``mode`` as for ``linear_skinny`` (SK_*); for SK_SWIGLU ``w`` is [2N, K]."""
         self._need(a, "a", torch.bfloat16, 2); self._need(w, "w", torch.bfloat16, 2); self._need(out, "out", None, 2)
         M, K = a.shape
         N = w.shape[0] // 2 if mode == SK_SWIGLU else w.shape[0]

@@ -93,7 +93,7 @@ class Attention:
         kv = cache.layer_kv(site)
         writes = s.cache_from is None
         rows = h.shape[0]
-        if (not batch.prefill and writes and rows <= 16 and self.qkv._skinny(rows) and kv.storage.dtype is torch.bfloat16
+        if (not batch.prefill and writes and self.qkv._skinny(rows) and kv.storage.dtype is torch.bfloat16
                 and self.position.rotary_dim == s.head_dim and hasattr(K_, "qkv_rope")):
             # decoding: projection, rotation and the append to the cache as one kernel
             qkv = self.rt.empty(rows, self.qd + 2 * self.kvd)

@@ -1,7 +1,7 @@
 """y = a W^T (+ bias): the one place that chooses how a matrix product runs.
 
 * 32-bit path, or a weight that is stored in 32-bit: the plain FFMA kernel (``linear_plain``).
-* bfloat16, at most ``SKINNY_ROWS`` rows (the kernel takes up to 16), K a multiple of 8: the hand-written skinny kernel with its
+* bfloat16, at most ``SKINNY_ROWS`` rows, K a multiple of 8: the hand-written skinny kernel with its
   fused epilogues (bias, residual accumulate, gated activation, float32 store).
 * bfloat16, more rows: the library matrix product (cuBLAS through ``torch.mm``), where the reference
   also calls its library (``cublasGemmEx`` for rows > 1, src/models/transformer.rs:1068-1084,
@@ -15,9 +15,12 @@ import torch
 
 from ..kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
 
-FOLDED_NORM_ROWS = 16    # most rows of the skinny kernel's folded RMSNorm
+FOLDED_NORM_ROWS = 8     # most rows of the skinny kernel's folded RMSNorm (the kernel takes at most 8 rows)
 TCGEN05_ROWS = 256       # from this many rows on, the gated product runs on the tcgen05 kernel
-SKINNY_ROWS = 8          # measured on B200: above 8 rows the library product streams the weights faster
+# Measured on B200 inside a recorded decode step of the 7B shape: for 12 and 16 rows the skinny kernel with two
+# 8-row tiles took 77 us for gate|up, 43 us for down and 224 us for the head, the library product with its activation
+# and norm kernels 47 + 3, 29 + 3 and 181 us; the skinny kernel therefore serves 8 rows at most.
+SKINNY_ROWS = 8
 
 
 class Linear:
@@ -165,14 +168,11 @@ class GatedLinearPair:
             a = a.tensor()
         if self.lin._skinny(M):
             K_.linear_skinny(a, self.lin.weight, None, out, SK_SWIGLU)
-        elif (not self.lin._plain()) and self._gated_on_tcgen05(M) and hasattr(K_, "gemm_tc"):
+        elif (not self.lin._plain()) and self._gated_on_tcgen05(M) and hasattr(K_, "gemm_tc_pair"):
             # many rows: the tcgen05 product with the activation in its epilogue (measured 366 us against 385 us
             # for the library product followed by the activation kernel at 2,048 x 37,888 x 3,584, and without the
             # [rows, 2I] intermediate)
-            if hasattr(K_, "gemm_tc_pair"):
-                K_.gemm_tc_pair(a, self.lin.weight, None, out, SK_SWIGLU)          # pairs of SMs, 256 x 256 tiles
-            else:
-                K_.gemm_tc(a, self.lin.weight, None, out, SK_SWIGLU, swap=False, bn=256)
+            K_.gemm_tc_pair(a, self.lin.weight, None, out, SK_SWIGLU)              # pairs of SMs, 256 x 256 tiles
         else:
             K_.swiglu(self.lin.store(a), out)
         return out

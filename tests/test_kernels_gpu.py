@@ -111,7 +111,7 @@ def test_linear_plain_rows_are_independent(K, rows, N, K_):
     assert torch.equal(acc_full[33:33 + rows], acc_few)
 
 
-@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("M", [1, 3, 7, 8])
 @pytest.mark.parametrize("N,K_", [(200, 328), (1000, 192), (4608, 3584), (17, 8)])
 def test_linear_skinny_modes(K, M, N, K_):
     from cima_b200.kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
@@ -139,10 +139,10 @@ def test_linear_skinny_modes(K, M, N, K_):
 
 def test_linear_skinny_row_does_not_depend_on_batch(K):
     from cima_b200.kernels import SK_STORE_F32
-    a, w = g(16, 448, dtype=torch.bfloat16, seed=1), g(1000, 448, dtype=torch.bfloat16, seed=2)
-    full = torch.empty(16, 1000, device="cuda")
+    a, w = g(8, 448, dtype=torch.bfloat16, seed=1), g(1000, 448, dtype=torch.bfloat16, seed=2)
+    full = torch.empty(8, 1000, device="cuda")
     K.linear_skinny(a.cuda(), w.cuda(), None, full, SK_STORE_F32)
-    for m in (1, 5, 8, 9, 13):
+    for m in (1, 2, 5, 7):
         part = torch.empty(m, 1000, device="cuda")
         K.linear_skinny(a[:m].contiguous().cuda(), w.cuda(), None, part, SK_STORE_F32)
         assert torch.equal(part, full[:m])
@@ -150,9 +150,9 @@ def test_linear_skinny_row_does_not_depend_on_batch(K):
 
 def test_linear_skinny_refuses(K):
     from cima_b200.kernels import KernelError, SK_STORE
-    a, w = g(17, 64, dtype=torch.bfloat16).cuda(), g(32, 64, dtype=torch.bfloat16).cuda()
-    with pytest.raises(KernelError, match="at most 16"):
-        K.linear_skinny(a, w, None, torch.empty(17, 32, dtype=torch.bfloat16, device="cuda"), SK_STORE)
+    a, w = g(9, 64, dtype=torch.bfloat16).cuda(), g(32, 64, dtype=torch.bfloat16).cuda()
+    with pytest.raises(KernelError, match="at most 8"):
+        K.linear_skinny(a, w, None, torch.empty(9, 32, dtype=torch.bfloat16, device="cuda"), SK_STORE)
     a, w = g(2, 12, dtype=torch.bfloat16).cuda(), g(32, 12, dtype=torch.bfloat16).cuda()
     with pytest.raises(KernelError, match="multiples of 8"):
         K.linear_skinny(a, w, None, torch.empty(2, 32, dtype=torch.bfloat16, device="cuda"), SK_STORE)
@@ -475,39 +475,8 @@ def test_argmax_ties_go_to_the_higher_index(K):
     assert tok.tolist() == [900, 999, 999, 0, int(torch.nonzero(x[4] == x[4].max()).max())]
 
 
-# ---------------------------------------------------------------------------- tcgen05 matrix product
-@pytest.mark.parametrize("M,N,K_,bn,swap", [(128, 128, 64, 128, False), (200, 328, 200, 128, False),
-                                            (2048, 1000, 448, 256, False), (300, 3584, 192, 256, False),
-                                            (64, 3584, 448, 64, True), (17, 1000, 192, 64, True),
-                                            (1, 200, 8, 64, True), (130, 65, 72, 128, False)])
-def test_gemm_tcgen05_modes(K, M, N, K_, bn, swap):
-    """TMA + tcgen05.mma + TMEM product against float64, every epilogue, tails in every dimension."""
-    from cima_b200.kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
-    a = g(M, K_, dtype=torch.bfloat16, seed=M)
-    w = g(N, K_, dtype=torch.bfloat16, seed=N, scale=1.0 / math.sqrt(K_))
-    b = g(N, seed=7)
-    want = a.double() @ w.double().t()
-    out32 = torch.full((M, N), -777.0, device="cuda")
-    K.gemm_tc(a.cuda(), w.cuda(), b.cuda(), out32, SK_STORE_F32, swap=swap, bn=bn)
-    assert err(out32, want + b.double()) <= 1e-4
-    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-    K.gemm_tc(a.cuda(), w.cuda(), None, out, SK_STORE, swap=swap, bn=bn)
-    assert err(out, want) <= TOL["bfloat16"] * 4
-    x = g(M, N, seed=9)
-    xg = x.cuda()
-    K.gemm_tc(a.cuda(), w.cuda(), None, xg, SK_ACCUM, swap=swap, bn=bn)
-    assert err(xg, x.double() + want) <= 1e-4
-    if N % 2 == 0 and not swap:
-        I = N // 2
-        act = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
-        K.gemm_tc(a.cuda(), w.cuda(), None, act, SK_SWIGLU, swap=False, bn=bn)
-        gg, uu = want[:, :I], want[:, I:]
-        assert err(act, gg / (1 + torch.exp(-gg)) * uu) <= TOL["bfloat16"] * 4
-    assert K.device_errors() == 0
-
-
 # ---------------------------------------------------------------------------- norm folded into the skinny product
-@pytest.mark.parametrize("M", [1, 5, 8, 16])
+@pytest.mark.parametrize("M", [1, 5, 7, 8])
 @pytest.mark.parametrize("N,K_", [(200, 328), (4608, 3584), (1000, 192)])
 def test_skinny_accumulate_leaves_sums_of_squares_and_the_next_product_folds_the_norm(K, M, N, K_):
     """x += a W1^T leaves per-tile sums of squares of the updated rows; the next product takes the rows,
@@ -609,7 +578,7 @@ def test_gemm_tcgen05_pair_modes(K, M, N, K_):
     assert K.device_errors() == 0
 
 
-@pytest.mark.parametrize("M", [1, 5, 8, 16])
+@pytest.mark.parametrize("M", [1, 5, 7, 8])
 @pytest.mark.parametrize("nh,nkv,hd,H", [(6, 2, 48, 200), (28, 4, 128, 3584), (3, 1, 64, 192), (4, 4, 16, 64)])
 def test_qkv_rope_skinny_equals_projection_then_rope_append(K, M, nh, nkv, hd, H):
     """The decode projection with rotation and cache append in its epilogue against the two separate steps
