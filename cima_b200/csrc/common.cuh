@@ -40,6 +40,18 @@ template <typename T> __device__ __forceinline__ T cima_from_f32(float v);
 template <> __device__ __forceinline__ float cima_from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 cima_from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// The activation of a gated feed-forward's gate, float32.  The reference has SiLU only (src/kernels.cu:81-84);
+// the others are what architectures of the same build use in its place.
+enum { CIMA_ACT_SILU = 0, CIMA_ACT_GELU_TANH = 1, CIMA_ACT_GELU = 2, CIMA_ACT_RELU = 3, CIMA_ACT_COUNT = 4 };
+__device__ __forceinline__ float cima_gate_act(float g, int act) {
+  switch (act) {
+    case CIMA_ACT_GELU_TANH: return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    case CIMA_ACT_GELU: return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
+    case CIMA_ACT_RELU: return fmaxf(g, 0.f);
+    default: return g / (1.0f + expf(-g));
+  }
+}
+
 // Sum over the threads of a block in a fixed order (warp shuffles, then warp 0 over the warps'
 // partial sums), so that a row's result never depends on what else is launched with it.
 // `red` is shared memory of at least 32 floats.  Every thread gets the total.

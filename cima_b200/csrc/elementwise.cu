@@ -145,22 +145,22 @@ extern "C" int cima_rmsnorm(const float* x, const float* w, void* y, int y_dtype
   return cima_fail(CIMA_E_DTYPE, "rmsnorm: output dtype code %d is neither float32 nor bfloat16", y_dtype);
 }
 
-// ---------------------------------------------------------------- gated activation: a = silu(g) * u
+// ---------------------------------------------------------------- gated activation: a = act(g) * u (act: CIMA_ACT_*)
 // gu is [T, 2I] with the gate in columns [0, I) and the up projection in [I, 2I).
 // The bfloat16 kernel moves 16 bytes per access when I is a multiple of 8; otherwise element by element.
 template <typename TA>
-__global__ void k_swiglu(const TA* __restrict__ gu, TA* __restrict__ a, size_t total, int I) {
+__global__ void k_swiglu(const TA* __restrict__ gu, TA* __restrict__ a, size_t total, int I, int act) {
   cima_pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / I;
     const int c = (int)(idx - row * I);
     const float g = cima_to_f32<TA>(gu[row * 2 * I + c]);
     const float u = cima_to_f32<TA>(gu[row * 2 * I + I + c]);
-    a[idx] = cima_from_f32<TA>(g / (1.0f + expf(-g)) * u);
+    a[idx] = cima_from_f32<TA>(cima_gate_act(g, act) * u);
   }
 }
 
-__global__ void k_swiglu_bf16x8(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ a, size_t groups, int I8) {
+__global__ void k_swiglu_bf16x8(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ a, size_t groups, int I8, int act) {
   cima_pdl_wait();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / I8;
@@ -174,25 +174,26 @@ __global__ void k_swiglu_bf16x8(const __nv_bfloat16* __restrict__ gu, __nv_bfloa
 #pragma unroll
     for (int e = 0; e < 4; e++) {
       const float2 g = __bfloat1622float2(gp[e]), u = __bfloat1622float2(up[e]);
-      op[e] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+      op[e] = __floats2bfloat162_rn(cima_gate_act(g.x, act) * u.x, cima_gate_act(g.y, act) * u.y);
     }
     *reinterpret_cast<uint4*>(a + idx * 8) = ov;
   }
 }
 
-extern "C" int cima_swiglu(const void* gu, void* a, int dtype, int T, int I, cudaStream_t stream) {
+extern "C" int cima_swiglu(const void* gu, void* a, int dtype, int T, int I, int act, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "swiglu: activation code %d is not one of 0..%d", act, CIMA_ACT_COUNT - 1);
   if (I <= 0) return cima_fail(CIMA_E_SIZE, "swiglu: intermediate width %d must be positive", I);
   const size_t total = (size_t)T * I;
   if (dtype == CIMA_BF16 && I % 8 == 0 && (((uintptr_t)gu | (uintptr_t)a) & 15) == 0) {
     const size_t groups = total / 8;
     const int grid = (int)((groups + 255) / 256 > 148 * 16 ? 148 * 16 : (groups + 255) / 256);
-    { int rc_ = cima_launch(k_swiglu_bf16x8, dim3(grid), dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)a, groups, I / 8); if (rc_) return rc_; }
+    { int rc_ = cima_launch(k_swiglu_bf16x8, dim3(grid), dim3(256), (size_t)0, stream, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)a, groups, I / 8, act); if (rc_) return rc_; }
     return cima_launch_result();
   }
   const int grid = (int)((total + 255) / 256 > 148 * 32 ? 148 * 32 : (total + 255) / 256);
-  if (dtype == CIMA_F32) { int rc_ = cima_launch(k_swiglu<float>, dim3(grid), dim3(256), (size_t)(0), stream, 1, (const float*)gu, (float*)a, total, I); if (rc_) return rc_; }
-  else if (dtype == CIMA_BF16) { int rc_ = cima_launch(k_swiglu<__nv_bfloat16>, dim3(grid), dim3(256), (size_t)(0), stream, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)a, total, I); if (rc_) return rc_; }
+  if (dtype == CIMA_F32) { int rc_ = cima_launch(k_swiglu<float>, dim3(grid), dim3(256), (size_t)(0), stream, 1, (const float*)gu, (float*)a, total, I, act); if (rc_) return rc_; }
+  else if (dtype == CIMA_BF16) { int rc_ = cima_launch(k_swiglu<__nv_bfloat16>, dim3(grid), dim3(256), (size_t)(0), stream, 1, (const __nv_bfloat16*)gu, (__nv_bfloat16*)a, total, I, act); if (rc_) return rc_; }
   else return cima_fail(CIMA_E_DTYPE, "swiglu: dtype code %d is neither float32 nor bfloat16", dtype);
   return cima_launch_result();
 }

@@ -65,6 +65,7 @@ struct PairArgs {
   void* out;                  // out[i * ldo + j]
   int ldo;
   int* error_flag;
+  int act;                    // gated epilogue: the gate's activation (CIMA_ACT_*)
 };
 
 template <int BN, int STAGES, int EPI>
@@ -177,7 +178,7 @@ k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_cons
           float u[32];
           tmem_ld32(acc + (unsigned)(BN / 2 + c0), u);
 #pragma unroll
-          for (int e = 0; e < 32; e++) v[e] = v[e] / (1.0f + expf(-v[e])) * u[e];
+          for (int e = 0; e < 32; e++) v[e] = (a.act == CIMA_ACT_SILU ? v[e] / (1.0f + expf(-v[e])) : cima_gate_act(v[e], a.act)) * u[e];
         }
         if (i < a.p_rows) {
           const int jmax = GATED ? a.up_offset : a.q_rows;
@@ -267,10 +268,11 @@ int launch(const CUtensorMap& mp, const CUtensorMap& mq, const PairArgs& a, int 
 }  // namespace
 
 // out[i, j] = epilogue(sum_k P[i, k] Q[j, k]); P [p_rows, K], Q [q_rows, K] bf16, 16-byte aligned, K % 8 == 0.
-// Tiles of 256 rows x 256 columns per pair of SMs.  Epilogues: 0 store bf16 (+ bias), 1 accumulate into float32, 2 silu(gate) * up (Q = [gate | up]), 3 store float32.
+// Tiles of 256 rows x 256 columns per pair of SMs.  Epilogues: 0 store bf16 (+ bias), 1 accumulate into float32, 2 act(gate) * up (Q = [gate | up]; act: CIMA_ACT_*), 3 store float32.
 extern "C" int cima_gemm_tcgen05_pair(const void* P, const void* Q, const float* bias, void* out, int epi, int p_rows,
-                                      int q_rows, int K, int ldo, int up_offset, int* error_flag, cudaStream_t stream) {
+                                      int q_rows, int K, int ldo, int up_offset, int act, int* error_flag, cudaStream_t stream) {
   if (p_rows <= 0 || q_rows <= 0) return 0;
+  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair: activation code %d is not one of 0..%d", act, CIMA_ACT_COUNT - 1);
   if (K <= 0 || K % 8) return cima_fail(CIMA_E_SIZE, "gemm_tcgen05_pair: K %d must be a positive multiple of 8", K);
   if (((uintptr_t)P | (uintptr_t)Q) & 15) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair: P and Q must be 16-byte aligned");
   if (!error_flag) return cima_fail(CIMA_E_ARG, "gemm_tcgen05_pair: an error flag on the device is needed");
@@ -286,7 +288,7 @@ extern "C" int cima_gemm_tcgen05_pair(const void* P, const void* Q, const float*
   if (rc) return rc;
   rc = make_map(&mq, Q, q_rows, K, K, BN / 2);
   if (rc) return rc;
-  PairArgs a{p_rows, q_rows, K, up_offset, bias, out, ldo, error_flag};
+  PairArgs a{p_rows, q_rows, K, up_offset, bias, out, ldo, error_flag, act};
   switch (epi) {
     case EPI_STORE: return launch<BN, 6, EPI_STORE>(mp, mq, a, p_tiles, tiles_q, stream);
     case EPI_ACCUM: return launch<BN, 6, EPI_ACCUM>(mp, mq, a, p_tiles, tiles_q, stream);

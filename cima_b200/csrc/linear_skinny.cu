@@ -23,7 +23,7 @@
 // row-contiguous, no shared-memory staging of W is needed.
 //
 // Epilogues (the reference's GEMV has the first three, src/kernels.cu:502-538):
-//   0 store bf16 (+ bias)      1 accumulate into the float32 residual      2 silu(gate) * up -> bf16
+//   0 store bf16 (+ bias)      1 accumulate into the float32 residual      2 act(gate) * up -> bf16 (act: CIMA_ACT_*)
 //   3 store float32 (+ bias), used for logits      4 q/k/v with rotation and cache append (see SkinnyRope)
 #include "common.cuh"
 #include <cooperative_groups.h>
@@ -74,6 +74,7 @@ struct SkinnyNorm {
   float* ssq_out;        // [M, tiles] or null (accumulating epilogue only)
   const float* w_next;   // [N] weight of the norm that follows, with xw_out; both null = not wanted
   __nv_bfloat16* xw_out;
+  int act;               // gated epilogue: the gate's activation (CIMA_ACT_*)
 };
 
 // Mode 4: the q/k/v projection of a decode step with the rotary encoding and the append to the cache in its
@@ -305,7 +306,7 @@ k_linear_skinny(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __rest
         ((float*)out)[o] = v[0] + (bias ? bias[n] : 0.f);
       } else {
         const float gate = v[0], up = v[MT - 1];
-        ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
+        ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(cima_gate_act(gate, nm.act) * up);
       }
     }
   }
@@ -383,14 +384,15 @@ static int skinny_checks(const void* X, const void* W, const float* bias, int mo
 // w_next / xw_out (mode 1 with ssq_out, may be null): weight [N] of the norm that follows, and where to put
 // bf16(updated row * that weight), [M, N] with row stride ldo.
 extern "C" int cima_linear_skinny(const void* X, const void* W, const float* bias, void* out, int mode, int M, int N,
-                                  int K, int ldx, int ldo, float* ssq_out, const float* w_next, void* xw_out,
+                                  int K, int ldx, int ldo, float* ssq_out, const float* w_next, void* xw_out, int act,
                                   cudaStream_t stream) {
   if (M <= 0) return 0;
+  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "linear_skinny: activation code %d is not one of 0..%d", act, CIMA_ACT_COUNT - 1);
   int rc = skinny_checks(X, W, bias, mode, M, N, K, ldx);
   if (rc) return rc;
   if (xw_out && (mode != SK_ACCUM || !ssq_out || !w_next)) return cima_fail(CIMA_E_ARG, "linear_skinny: the scaled rows go with mode 1, the partial sums and the next norm's weight");
   SkinnyNorm nm{nullptr, 0, 0.f, mode == SK_ACCUM ? ssq_out : nullptr,
-                mode == SK_ACCUM ? w_next : nullptr, mode == SK_ACCUM ? (__nv_bfloat16*)xw_out : nullptr};
+                mode == SK_ACCUM ? w_next : nullptr, mode == SK_ACCUM ? (__nv_bfloat16*)xw_out : nullptr, act};
   return dispatch_mode<1, false>(mode, X, W, bias, out, M, N, K, ldx, ldo, nm, stream);
 }
 
@@ -398,14 +400,15 @@ extern "C" int cima_linear_skinny(const void* X, const void* W, const float* bia
 // it (row stride ldx), ssq [M, parts] the partial sums of squares of the rows x, and eps.  At most 8 rows.
 extern "C" int cima_linear_skinny_norm(const void* xw, const float* ssq, int parts, float eps, const void* W,
                                        const float* bias, void* out, int mode, int M, int N, int K, int ldx, int ldo,
-                                       cudaStream_t stream) {
+                                       int act, cudaStream_t stream) {
   if (M <= 0) return 0;
+  if (act < 0 || act >= CIMA_ACT_COUNT) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: activation code %d is not one of 0..%d", act, CIMA_ACT_COUNT - 1);
   if (M > 8) return cima_fail(CIMA_E_SIZE, "linear_skinny_norm: %d rows; the folded norm takes at most 8", M);
   if (!ssq || parts <= 0) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: the partial sums of squares are needed");
   if (mode == SK_ACCUM) return cima_fail(CIMA_E_ARG, "linear_skinny_norm: the accumulating epilogue reads activations, not the residual");
   int rc = skinny_checks(xw, W, bias, mode, M, N, K, ldx);
   if (rc) return rc;
-  SkinnyNorm nm{ssq, parts, eps, nullptr, nullptr, nullptr};
+  SkinnyNorm nm{ssq, parts, eps, nullptr, nullptr, nullptr, act};
   return dispatch_mode<1, true>(mode, xw, W, bias, out, M, N, K, ldx, ldo, nm, stream);
 }
 
@@ -426,7 +429,7 @@ extern "C" int cima_qkv_rope_skinny(const void* X, const float* ssq, int parts, 
   if (norm && parts <= 0) return cima_fail(CIMA_E_ARG, "qkv_rope_skinny: the folded norm needs the number of partial sums");
   int rc = skinny_checks(X, W, bias, SK_STORE, M, N, K, ldx);
   if (rc) return rc;
-  SkinnyNorm nm{ssq, parts, eps, nullptr, nullptr, nullptr};
+  SkinnyNorm nm{ssq, parts, eps, nullptr, nullptr, nullptr, 0};
   SkinnyRope rp{inv_freq, row_pos, row_seq, seq_slot, (__nv_bfloat16*)cache,
                 CimaPaged{table, table_width, ring, page_size, nkv, hd}, nh, nkv, hd};
   if (norm) return launch_skinny<1, 1, 4, SK_QKV_ROPE, true>(X, W, bias, qkv, M, N, K, ldx, ldo, 0, nm, stream, rp);

@@ -18,7 +18,7 @@ int cima_fail(int code, const char* fmt, ...) {
 }
 
 // Version of the entry points' signatures; the Python side refuses a library that answers otherwise.
-extern "C" int cima_abi_version() { return 19; }
+extern "C" int cima_abi_version() { return 20; }
 
 bool cima_pdl_enabled() {
   static int on = -1;

@@ -15,13 +15,15 @@ import torch
 from .csrc.build import BuildError, library_path
 
 F32, BF16 = 0, 1
-ABI_VERSION = 19
+ABI_VERSION = 20
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
 
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
+# activations of a gated feed-forward's gate (CIMA_ACT_* of csrc/common.cuh), by the names config files use
+ACTIVATIONS = {"silu": 0, "swish": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1, "gelu_new": 1, "gelu": 2, "relu": 3}
 
 
 class KernelError(RuntimeError):
@@ -41,14 +43,14 @@ _vp, _i, _f, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_
 _SIGNATURES = {
     "cima_embed": [_vp, _vp, _i, _vp, _i, _i, _i, _f, _vp, _vp, _vp, _vp],
     "cima_rmsnorm": [_vp, _vp, _vp, _i, _i, _i, _f, _vp],
-    "cima_swiglu": [_vp, _vp, _i, _i, _i, _vp],
+    "cima_swiglu": [_vp, _vp, _i, _i, _i, _i, _vp],
     "cima_add_residual": [_vp, _vp, _i, _sz, _vp],
     "cima_gather_rows": [_vp, _vp, _vp, _i, _i, _vp],
     "cima_add_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "cima_decode_advance": [_vp, _vp, _vp, _vp, _i, _vp],
     "cima_linear_plain": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "cima_linear_skinny": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp],
-    "cima_linear_skinny_norm": [_vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "cima_linear_skinny": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp],
+    "cima_linear_skinny_norm": [_vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "cima_qkv_rope_skinny": [_vp, _vp, _i, _f, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i,
                              _i, _i, _i, _i, _vp],
     "cima_rope_append": [_vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -60,7 +62,7 @@ _SIGNATURES = {
     "cima_attention_extend_tc": [_vp, _i, _vp, _vp, _vp, _vp, ctypes.c_longlong, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                  _f, _i, _vp, _vp],
     "cima_attention_prefill_tc": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
-    "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "cima_gemm_tcgen05_pair": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "cima_argmax": [_vp, _i, _i, _i, _vp, _vp],
     "cima_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     "cima_sample_general": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -167,13 +169,14 @@ class Kernels:
         self._check(self.lib.cima_rmsnorm(x.data_ptr(), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
                                           T, H, eps, self._stream()), "rmsnorm")
 
-    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    def swiglu(self, gate_up: torch.Tensor, out: torch.Tensor, act: int = 0) -> None:
+        """out = act(gate) * up of ``gate_up`` = [gate | up]; ``act`` one of ``ACTIVATIONS``' codes."""
         self._need(gate_up, "gate_up", None, 2); self._need(out, "out", gate_up.dtype, 2)
         T, I2 = gate_up.shape
         if I2 % 2 or tuple(out.shape) != (T, I2 // 2):
             raise KernelError(f"swiglu: gate_up {tuple(gate_up.shape)} and out {tuple(out.shape)} do not agree")
         if not self._admit("swiglu", T * (I2 + I2 // 2) * out.element_size()): return
-        self._check(self.lib.cima_swiglu(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), T, I2 // 2,
+        self._check(self.lib.cima_swiglu(gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), T, I2 // 2, act,
                                          self._stream()), "swiglu")
 
     def add_residual(self, x: torch.Tensor, delta: torch.Tensor) -> None:
@@ -240,7 +243,7 @@ class Kernels:
 
     def linear_skinny(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
                       mode: int, ssq_out: Optional[torch.Tensor] = None, w_next: Optional[torch.Tensor] = None,
-                      xw_out: Optional[torch.Tensor] = None) -> None:
+                      xw_out: Optional[torch.Tensor] = None, act: int = 0) -> None:
         """Few rows (<= 8), bf16 operands; ``mode`` is one of SK_*.  For SK_SWIGLU ``w`` is [2N, K].
         With SK_ACCUM, ``ssq_out`` [M, ceil(N / 16)] receives partial sums of squares of the updated rows and
         ``xw_out`` [M, N] bf16 the updated rows times ``w_next`` (the weight of the norm that follows)."""
@@ -267,10 +270,10 @@ class Kernels:
         if not self._admit(f"linear_skinny[{mode}]", w.numel() * 2 + M * K * 2 + M * N * out.element_size(), 2.0 * M * w.shape[0] * K): return
         self._check(self.lib.cima_linear_skinny(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode,
                                                 M, N, K, K, N, _ptr(ssq_out), _ptr(w_next) if xw_out is not None else None,
-                                                _ptr(xw_out), self._stream()), "linear_skinny")
+                                                _ptr(xw_out), act, self._stream()), "linear_skinny")
 
     def linear_skinny_norm(self, xw: torch.Tensor, ssq: torch.Tensor, eps: float, w: torch.Tensor,
-                           bias: Optional[torch.Tensor], out: torch.Tensor, mode: int) -> None:
+                           bias: Optional[torch.Tensor], out: torch.Tensor, mode: int, act: int = 0) -> None:
         """``linear_skinny`` of RMSNorm(x) for at most 8 rows: ``xw`` [M, K] bf16 = bf16(x * norm weight) and
         ``ssq`` [M, parts], the partial sums of squares of the rows x, as ``embed`` or an accumulating
         ``linear_skinny`` left them."""
@@ -286,7 +289,7 @@ class Kernels:
             self._need(bias, "bias", torch.float32, 1)
         if not self._admit(f"linear_skinny_norm[{mode}]", w.numel() * 2 + M * K * 2 + M * N * out.element_size(), 2.0 * M * w.shape[0] * K): return
         self._check(self.lib.cima_linear_skinny_norm(xw.data_ptr(), ssq.data_ptr(), ssq.shape[1], eps, w.data_ptr(),
-                                                     _ptr(bias), out.data_ptr(), mode, M, N, K, K, N, self._stream()),
+                                                     _ptr(bias), out.data_ptr(), mode, M, N, K, K, N, act, self._stream()),
                     "linear_skinny_norm")
 
     def qkv_rope(self, a, w: torch.Tensor, bias: Optional[torch.Tensor], qkv: torch.Tensor, inv_freq: torch.Tensor,
@@ -324,7 +327,7 @@ class Kernels:
                                                   n_kv_heads, head_dim, self._stream()), "qkv_rope_skinny")
 
     def gemm_tc_pair(self, a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-                     mode: int) -> None:
+                     mode: int, act: int = 0) -> None:
         """out = epilogue(a @ w.T) on the tcgen05 tensor cores, for many rows: bf16 operands by TMA, float32
         accumulation in tensor memory, pairs of SMs on tiles of 256 x 256 (cta_group::2; each SM of a pair stages
         only half of the weight tile).  ``mode`` as for ``linear_skinny`` (SK_*); for SK_SWIGLU ``w`` is [2N, K]."""
@@ -341,7 +344,7 @@ class Kernels:
             self._error_flag = torch.zeros(1, dtype=torch.int32, device=a.device)
         if not self._admit(f"gemm_tcgen05_pair[{mode}]", (w.numel() + M * K) * 2 + M * N * out.element_size(), 2.0 * M * w.shape[0] * K): return
         self._check(self.lib.cima_gemm_tcgen05_pair(a.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, M,
-                                                    w.shape[0], K, N, N if mode == SK_SWIGLU else 0,
+                                                    w.shape[0], K, N, N if mode == SK_SWIGLU else 0, act,
                                                     self._error_flag.data_ptr(), self._stream()), "gemm_tcgen05_pair")
 
     def error_flag(self, device) -> torch.Tensor:

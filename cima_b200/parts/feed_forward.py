@@ -1,6 +1,8 @@
-"""Gated feed-forward: x += (act(h Wg^T) * (h Wu^T)) Wd^T, act = SiLU g / (1 + exp(-g)) in float32
-(src/kernels.cu:81-84; src/models/transformer.rs:1219-1229 and :1273-1291).  Rows are independent,
-so a long step is cut into row chunks that bound the [rows, 2I] scratch."""
+"""Gated feed-forward: x += (act(h Wg^T) * (h Wu^T)) Wd^T in float32, act by the spec's ``activation``: SiLU
+g / (1 + exp(-g)) as the reference has it (src/kernels.cu:81-84; src/models/transformer.rs:1219-1229 and
+:1273-1291), or one of the other entries of ``kernels.ACTIVATIONS`` (tanh or erf GELU, ReLU), which every kernel
+that applies the activation takes as a parameter.  Rows are independent, so a long step is cut into row chunks
+that bound the [rows, 2I] scratch."""
 from __future__ import annotations
 
 from typing import Dict
@@ -16,8 +18,9 @@ _SCRATCH_ELEMS = 1 << 29          # elements of the [rows, 2I] gate|up scratch p
 
 class GatedMLP:
     def __init__(self, spec, layer: int, rt):
-        if spec.activation != "silu":
-            raise ValueError(f"gated_mlp: activation '{spec.activation}' is not implemented (only 'silu')")
+        from ..kernels import ACTIVATIONS
+        if spec.activation not in ACTIVATIONS:
+            raise ValueError(f"gated_mlp: activation '{spec.activation}' is not one of {sorted(ACTIVATIONS)}")
         if spec.bias:
             raise ValueError("gated_mlp: biases are not implemented")
         self.spec, self.layer, self.rt = spec, layer, rt
@@ -32,7 +35,7 @@ class GatedMLP:
 
     def load(self, tensors: Dict[str, torch.Tensor], prefix: str, names: Dict[str, str]) -> None:
         self.gate_up = GatedLinearPair(tensors[f"{prefix}{names['gate']}.weight"],
-                                       tensors[f"{prefix}{names['up']}.weight"], self.rt)
+                                       tensors[f"{prefix}{names['up']}.weight"], self.rt, self.spec.activation)
         self.down = Linear(tensors[f"{prefix}{names['down']}.weight"], None, self.rt)
 
     def nbytes(self) -> int:

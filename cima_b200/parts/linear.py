@@ -136,7 +136,11 @@ class GatedLinearPair:
     (the reference fuses the same way at load, src/models/transformer.rs:864-873, and in its
     decode GEMV mode 2, src/kernels.cu:533-537)."""
 
-    def __init__(self, gate: torch.Tensor, up: torch.Tensor, rt):
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor, rt, activation: str = "silu"):
+        from ..kernels import ACTIVATIONS
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"gated activation '{activation}' is not one of {sorted(ACTIVATIONS)}")
+        self.act = ACTIVATIONS[activation]
         self.lin = Linear([gate, up], None, rt)
         self.rt = rt
         self.I = gate.shape[0]
@@ -155,24 +159,24 @@ class GatedLinearPair:
         return rows >= (TCGEN05_ROWS if K >= 3072 else 1024)
 
     def activated(self, a) -> torch.Tensor:
-        """silu(a Wg^T) * (a Wu^T) in the activation dtype, [M, I]."""
+        """act(a Wg^T) * (a Wu^T) in the activation dtype, [M, I]."""
         K_ = self.rt.kernels
         M = a.shape[0]
         out = self.rt.empty(M, self.I)
         if M == 0:
             return out
         if self.lin._folds(a, M):
-            K_.linear_skinny_norm(a.xw, a.ssq, a.norm.spec.eps, self.lin.weight, None, out, SK_SWIGLU)
+            K_.linear_skinny_norm(a.xw, a.ssq, a.norm.spec.eps, self.lin.weight, None, out, SK_SWIGLU, act=self.act)
             return out
         if hasattr(a, "tensor"):
             a = a.tensor()
         if self.lin._skinny(M):
-            K_.linear_skinny(a, self.lin.weight, None, out, SK_SWIGLU)
+            K_.linear_skinny(a, self.lin.weight, None, out, SK_SWIGLU, act=self.act)
         elif (not self.lin._plain()) and self._gated_on_tcgen05(M) and hasattr(K_, "gemm_tc_pair"):
             # many rows: the tcgen05 product with the activation in its epilogue (measured 366 us against 385 us
             # for the library product followed by the activation kernel at 2,048 x 37,888 x 3,584, and without the
             # [rows, 2I] intermediate)
-            K_.gemm_tc_pair(a, self.lin.weight, None, out, SK_SWIGLU)              # pairs of SMs, 256 x 256 tiles
+            K_.gemm_tc_pair(a, self.lin.weight, None, out, SK_SWIGLU, act=self.act)              # pairs of SMs, 256 x 256 tiles
         else:
-            K_.swiglu(self.lin.store(a), out)
+            K_.swiglu(self.lin.store(a), out, self.act)
         return out

@@ -46,10 +46,21 @@ class ReferenceKernels:
         inv = 1.0 / torch.sqrt((xc * xc).mean(dim=-1, keepdim=True) + eps)
         out.copy_((xc * inv * w.to(self.compute)).to(out.dtype))
 
-    def swiglu(self, gate_up, out):
+    @staticmethod
+    def gate_act(g, act):
+        """The gate's activation by its code: 0 SiLU, 1 GELU with tanh, 2 GELU with erf, 3 ReLU."""
+        if act == 1:
+            return 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+        if act == 2:
+            return 0.5 * g * (1.0 + torch.erf(g * 0.7071067811865476))
+        if act == 3:
+            return torch.clamp(g, min=0.0)
+        return g / (1.0 + torch.exp(-g))
+
+    def swiglu(self, gate_up, out, act=0):
         I = gate_up.shape[1] // 2
         g, u = gate_up[:, :I].to(self.compute), gate_up[:, I:].to(self.compute)
-        out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
+        out.copy_((self.gate_act(g, act) * u).to(out.dtype))
 
     def add_residual(self, x, delta):
         x.add_(delta.float())
@@ -79,17 +90,17 @@ class ReferenceKernels:
     def library_mm(self, a, w, out, bias=None):
         self.linear_plain(a, w, bias, out)
 
-    def linear_skinny_norm(self, xw, ssq, eps, w, bias, out, mode):
+    def linear_skinny_norm(self, xw, ssq, eps, w, bias, out, mode, act=0):
         inv = 1.0 / torch.sqrt(ssq.to(self.compute).sum(dim=1, keepdim=True) / xw.shape[1] + eps)
         h = (xw.to(self.compute) * inv).to(torch.bfloat16)
-        self.linear_skinny(h, w, bias, out, mode)
+        self.linear_skinny(h, w, bias, out, mode, act=act)
 
-    def linear_skinny(self, a, w, bias, out, mode, ssq_out=None, w_next=None, xw_out=None):
+    def linear_skinny(self, a, w, bias, out, mode, ssq_out=None, w_next=None, xw_out=None, act=0):
         y = a.to(self.compute) @ w.to(self.compute).t()
         if mode == SK_SWIGLU:
             I = w.shape[0] // 2
             g, u = y[:, :I], y[:, I:]
-            out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
+            out.copy_((self.gate_act(g, act) * u).to(out.dtype))
             return
         if bias is not None:
             y = y + bias.to(self.compute)

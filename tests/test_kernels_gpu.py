@@ -62,10 +62,11 @@ def test_swiglu_and_residual_and_gather(K, dtype):
     T, I = 37, 328
     gu = g(T, 2 * I, dtype=DT[dtype], seed=3, scale=2.0)
     out = torch.empty(T, I, dtype=DT[dtype], device="cuda")
-    K.swiglu(gu.cuda(), out)
-    want = torch.empty(T, I, dtype=torch.float64)
-    REF.swiglu(gu, want)
-    assert err(out, want) <= TOL[dtype] * 4
+    for code in (0, 1, 2, 3):                           # the gate's activation: SiLU, GELU (tanh, erf), ReLU
+        K.swiglu(gu.cuda(), out, code)
+        want = torch.empty(T, I, dtype=torch.float64)
+        REF.swiglu(gu, want, code)
+        assert err(out, want) <= TOL[dtype] * 4, code
     x, d = g(T, I, seed=4), g(T, I, dtype=DT[dtype], seed=5)
     xg = x.cuda()
     K.add_residual(xg, d.cuda())
@@ -131,10 +132,13 @@ def test_linear_skinny_modes(K, M, N, K_):
     assert err(xg, x.double() + want) <= 1e-4
     if N % 2 == 0:
         I = N // 2
-        act = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
-        K.linear_skinny(a.cuda(), w.cuda(), None, act, SK_SWIGLU)
         gg, uu = want[:, :I], want[:, I:]
-        assert err(act, gg / (1 + torch.exp(-gg)) * uu) <= TOL["bfloat16"] * 4
+        for code in (0, 1, 2, 3):                       # the gate's activation: SiLU, GELU (tanh, erf), ReLU
+            act = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+            K.linear_skinny(a.cuda(), w.cuda(), None, act, SK_SWIGLU, act=code)
+            assert err(act, REF.gate_act(gg, code) * uu) <= TOL["bfloat16"] * 4, code
+        with pytest.raises(Exception, match="activation code"):
+            K.linear_skinny(a.cuda(), w.cuda(), None, act, SK_SWIGLU, act=9)
 
 
 def test_linear_skinny_row_does_not_depend_on_batch(K):
@@ -571,10 +575,11 @@ def test_gemm_tcgen05_pair_modes(K, M, N, K_):
     assert err(xg, x.double() + want) <= 1e-4
     if N % 2 == 0:
         I = N // 2
-        act = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
-        K.gemm_tc_pair(a.cuda(), w.cuda(), None, act, SK_SWIGLU)
         gg, uu = want[:, :I], want[:, I:]
-        assert err(act, gg / (1 + torch.exp(-gg)) * uu) <= TOL["bfloat16"] * 4
+        for code in (0, 1, 2, 3):                       # the gate's activation: SiLU, GELU (tanh, erf), ReLU
+            act = torch.empty(M, I, dtype=torch.bfloat16, device="cuda")
+            K.gemm_tc_pair(a.cuda(), w.cuda(), None, act, SK_SWIGLU, act=code)
+            assert err(act, REF.gate_act(gg, code) * uu) <= TOL["bfloat16"] * 4, code
     assert K.device_errors() == 0
 
 

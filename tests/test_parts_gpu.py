@@ -72,6 +72,42 @@ def test_position_encoding_alone(name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("activation", ["gelu_pytorch_tanh", "gelu", "relu", "silu"])
+@pytest.mark.parametrize("T", [1, 7, 40, 300])
+def test_gated_feed_forward_with_other_activations(activation, T, dtype):
+    """The gated feed-forward built from a spec of the test's own (sizes that no tiny configuration has, any of the
+    gate's activations), loaded from tensors of the test's making, for few rows (the skinny product with the
+    activation in its epilogue), more (the library product and the activation kernel) and 300 (which still takes
+    that road at this width): x += (act(h Wg^T) * (h Wu^T)) Wd^T against float64."""
+    import math
+    from cima_b200.config import FeedForwardSpec
+    from cima_b200.kernels import Kernels
+    from cima_b200.parts import Runtime, build_feed_forward
+    H, I = 136, 264
+    gen = torch.Generator().manual_seed(11)
+    W = {"f.g.weight": torch.randn(I, H, generator=gen) / math.sqrt(H), "f.u.weight": torch.randn(I, H, generator=gen) / math.sqrt(H),
+         "f.d.weight": torch.randn(H, I, generator=gen) / math.sqrt(I)}
+    W = {k: v.to(torch.bfloat16) for k, v in W.items()}
+    rt = Runtime(kernels=Kernels(verbose=False), dtype=DT[dtype], device="cuda:0")
+    ffn = build_feed_forward(FeedForwardSpec("gated_mlp", H, I, activation), 0, rt)
+    names = {"gate": "g", "up": "u", "down": "d"}
+    assert sorted(ffn.plan("f.", names)) == sorted(W)
+    ffn.load(W, "f.", names)
+    h, x0 = rows(T, H, 3), rows(T, H, 4)
+    x = x0.cuda()
+    ffn.forward(h.to(DT[dtype]).cuda(), x, None)
+    hd = h.to(DT[dtype]).double()
+    g_, u_ = hd @ W["f.g.weight"].double().t(), hd @ W["f.u.weight"].double().t()
+    act = {"gelu_pytorch_tanh": lambda g: 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3))),
+           "gelu": lambda g: 0.5 * g * (1 + torch.erf(g / math.sqrt(2))), "relu": lambda g: g.clamp(min=0),
+           "silu": lambda g: g / (1 + torch.exp(-g))}[activation]
+    want = x0.double() + (act(g_) * u_) @ W["f.d.weight"].double().t()
+    assert err(x, want) <= TOL[dtype]
+    with pytest.raises(ValueError, match="is not one of"):
+        build_feed_forward(FeedForwardSpec("gated_mlp", H, I, "softsign"), 0, rt)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name,layer", [("A", 0), ("B", 2), ("C", 1), ("C", 3)])      # C's layers 2, 3 have a window
 def test_mixer_alone_over_a_prompt_and_from_the_cache(name, layer, dtype):
     """x += attention(h): two prompts of unequal length in one step, then one more token each from the
