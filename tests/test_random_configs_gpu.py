@@ -58,3 +58,49 @@ def test_random_configuration(seed, tmp_path):
         m.cache.check()
         assert m.cache.slots.held == 0
         m.check_device()
+
+
+@pytest.mark.parametrize("seed", SEEDS)
+def test_random_configuration_generates_as_the_plain_loop(seed, tmp_path):
+    """Generation through the entry point on a configuration drawn at random, in 32-bit: a random number of prompts
+    of random lengths (one prompt alone takes a recorded prompt step, more than 8 the schedule for many rows),
+    greedy or through the reference's default sampling chain, with run-ahead on or off and stop tokens taken from a
+    first run: token for token what the plain implementation generates, twice over so that slots, pages, recorded
+    steps and kept sequences are used again."""
+    from qwen2_plain import PlainXorshift, plain_sample
+    rng = random.Random(5000 + seed)
+    cfg = draw_config(rng)
+    cfg["max_position_embeddings"] = 256
+    folder = str(tmp_path / "m")
+    cima_b200.write_random_model(folder, cfg, seed=seed)
+    c, W = plain_load(folder)
+    W = {k: v.double() for k, v in W.items()}
+    n_prompts = rng.choice([1, 1, 2, 5, 9, 12])
+    prompts = [random_tokens(cfg["vocab_size"], rng.choice([1, 2, 15, 16, 17, 40, 64, 65, 70]), seed * 100 + i) for i in range(n_prompts)]
+    opts = rng.choice([dict(temperature=0.0, repeat_penalty=1.0), dict(temperature=0.8, top_k=40, top_p=0.9, repeat_penalty=1.1, seed=seed + 1)])
+    steps = 5
+
+    def plain_generate(p, stops):
+        gen, seq, out = PlainXorshift(opts.get("seed", 0)), list(p), []
+        for _ in range(steps):
+            t = plain_sample(plain_forward(W, c, seq)[-1].float().tolist(), seq, opts, gen)
+            if t in stops:
+                break
+            out.append(t)
+            seq.append(t)
+        return out
+
+    lm = cima_b200.load(folder, dtype="float32", max_tokens=4096, verbose=False, pipeline=rng.random() < 0.5,
+                        retain=rng.choice([0, 0, 2]))
+    free = [plain_generate(p, ()) for p in prompts]
+    what = (seed, cfg, [len(p) for p in prompts], opts)
+    assert [r.tokens for r in lm.generate(prompts, max_tokens=steps, **opts)] == free, what
+    stops = tuple({free[0][min(2, len(free[0]) - 1)], free[-1][0]})
+    want = [plain_generate(p, stops) for p in prompts]
+    for _ in range(2):
+        got = lm.generate(prompts, max_tokens=steps, stop=stops, **opts)
+        assert [r.tokens for r in got] == want, (what, stops)
+    lm.stepper.drop_retained()
+    lm.model.cache.check()
+    assert lm.model.cache.slots.held == 0
+    lm.model.check_device()
