@@ -3,7 +3,7 @@ into a toy architecture (also registered here) and stepped, without any change t
 The toy model also runs one layer twice (each run with storage of its own) and lets one attention
 layer read another layer's keys and values.  A second toy architecture has a feed-forward with routing
 (top-1 of three experts) and a position encoding of its own (partial rotary with scaled frequencies) in
-some layers and the package's parts in the others."""
+some layers and the package's parts in the others, and scales the embedding rows (``ModelSpec.embed_scale``)."""
 import json
 import math
 import os
@@ -213,10 +213,10 @@ def toy2_spec(cfg) -> ModelSpec:
                if i % 2 == 0 else FeedForwardSpec("gated_mlp", H, cfg["intermediate"], "silu"))
         layers.append(BlockSpec("prenorm", mixer, ffn, norm, norm, f"blocks.{i}.", names))
     return ModelSpec("ToyRoutedForCausalLM", cfg["vocab_size"], H, cfg["max_positions"], layers, list(range(cfg["layers"])),
-                     norm, False, "embed.weight", "final_norm.weight", "head.weight")
+                     norm, False, "embed.weight", "final_norm.weight", "head.weight", embed_scale=cfg["embed_scale"])
 
 
-TOY2 = dict(architectures=["ToyRoutedForCausalLM"], model_type="toyrouted", hidden_size=80, vocab_size=211, heads=5,
+TOY2 = dict(embed_scale=3.0, architectures=["ToyRoutedForCausalLM"], model_type="toyrouted", hidden_size=80, vocab_size=211, heads=5,
             kv_heads=1, head_dim=32, rotary_dim=16, factor=4.0, intermediate=120, expert_intermediate=48, experts=3,
             eps=1e-6, theta=5000.0, max_positions=256, layers=3)
 
@@ -234,7 +234,7 @@ def toy2_plain(W, cfg, tokens):
         c, s = ang.cos()[:, None], ang.sin()[:, None]
         return torch.cat([a * c - b * s, a * s + b * c, u[..., rd:]], dim=-1)
 
-    x = plain_embed(W["embed.weight"], tokens)
+    x = plain_embed(W["embed.weight"], tokens) * cfg["embed_scale"]       # the table's rows are scaled as they enter
     for i in range(cfg["layers"]):
         p = f"blocks.{i}."
         h = plain_rmsnorm(x, W[p + "norm1.weight"], cfg["eps"])

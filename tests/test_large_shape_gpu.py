@@ -286,3 +286,34 @@ def test_the_full_vocabulary_head_argmax_and_sampler():
             # may land on neighbouring tokens of the sorted order: then the draw must be one the chain can make
             assert r.tokens == [want] or (opts["top_k"] == 0 and draw_is_consistent(
                 logits[i].tolist(), list(p), opts, PlainXorshift(opts["seed"]).next_f32(), r.tokens[0])), (opts, i)
+
+
+def test_unequal_batch_of_prompts_of_1024_to_2048_tokens(folder):
+    """The benchmark's own kind of batch: prompts of 1,024, 1,500 and 2,048 tokens in one step, then eight tokens
+    each, the shortest request ending first; bfloat16 (tcgen05 attention and gated product, then the decode
+    kernels over 16 to 33 pages) against the 32-bit engine at every decoded position and at the prompts' ends."""
+    from cima_b200.engine import StepEntry
+    lens = [1024, 1500, 2048]
+    tails = [3, 8, 6]
+    seqs = [random_tokens(SHAPE["vocab_size"], n + t, seed=900 + n) for n, t in zip(lens, tails)]
+
+    def run(dtype):
+        m = load_model(folder, dtype=dtype, max_tokens=64 * 80, max_seqs=3, verbose=False)
+        slots = m.cache.open(3)
+        outs = []
+        try:
+            outs.append(m.step([StepEntry(s, q[:n], [0, n // 2, n - 1]) for s, q, n in zip(slots, seqs, lens)]).float().cpu())
+            for k in range(max(tails)):
+                live = [i for i in range(3) if k < tails[i]]
+                outs.append(m.step([StepEntry(slots[i], [seqs[i][lens[i] + k]], [0]) for i in live]).float().cpu())
+            m.check_device()
+        finally:
+            m.cache.close(slots)
+        m.cache.check()
+        del m
+        torch.cuda.empty_cache()
+        return torch.cat(outs)
+
+    got16, got32 = run("bfloat16"), run("float32")
+    assert got16.shape == got32.shape == (9 + sum(tails), SHAPE["vocab_size"])
+    assert (got16 - got32).abs().max().item() <= REL_BF16 * got32.std().item()
