@@ -87,38 +87,43 @@ class DecodeGraph:
         return self.chosen
 
 
-PROMPT_BUCKETS = (16, 32, 64)      # rows of a recorded prompt step; longer prompts hide the host's launches behind their own work
+PROMPT_BUCKETS = (16, 32, 64, 128, 256)     # rows a sequence of a recorded prompt step; longer prompts hide the host's launches
+PROMPT_ROWS = 256                           # most rows of a recorded prompt step, all sequences together
 
 
 class PromptGraph:
-    """The step of ONE short prompt recorded as a graph, for the first token's sake: a prompt of up to 64 tokens is
-    a few milliseconds of device work behind some 250 launches from the host, and the host is the slower of the two.
-    The prompt is padded at its end to the bucket's rows; the rows of the padding come after every real row, so no
-    real row sees them (attention is causal), their keys land beyond the sequence's committed length, where the
-    next tokens are written over them, and logits are gathered at the prompt's last real row only.  Padding
-    changes no result.  (The reference records its decode step only, src/models/transformer.rs:1467-1494.)"""
+    """The step of a few short prompts recorded as a graph, for the first token's sake: prompts of some tens of
+    tokens are a few milliseconds of device work behind some 250 launches from the host, and the host is the slower
+    of the two.  Every prompt is padded at its end to the bucket's rows; the rows of the padding come after the
+    sequence's real rows, so no real row sees them (attention is causal and stays inside a sequence), their keys
+    land beyond the sequence's committed length, where the next tokens are written over them, and logits are
+    gathered at each prompt's last real row only.  Padding changes no result.  (The reference records its decode
+    step only, src/models/transformer.rs:1467-1494.)"""
 
-    def __init__(self, model, rows: int):
-        self.model, self.rows = model, rows
+    def __init__(self, model, n_seqs: int, rows: int):
+        self.model, self.n_seqs, self.rows = model, n_seqs, rows
         dev = model.rt.device
-        self.batch = build_batch([StepEntry(0, [0] * rows, [rows - 1])], [0], model.spec.vocab, dev)
+        self.batch = build_batch([StepEntry(i, [0] * rows, [rows - 1]) for i in range(n_seqs)], [0] * n_seqs,
+                                 model.spec.vocab, dev)
         self.batch.host_seq_slot = self.batch.host_seq_len = None       # they change from replay to replay
-        self.host = torch.zeros(rows + 2, dtype=torch.int32).pin_memory()
+        self.host = torch.zeros(n_seqs * rows + 2 * n_seqs, dtype=torch.int32).pin_memory()
         self.graph = None
         self.logits = None
 
-    def run(self, slot: int, tokens: Sequence[int]) -> torch.Tensor:
-        """Float32 logits [1, vocab] at the prompt's last token.  The caller has reserved ``rows`` positions for the
-        slot and commits ``len(tokens)`` afterwards."""
-        n, R = len(tokens), self.rows
+    def run(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> torch.Tensor:
+        """Float32 logits [sequences, vocab] at each prompt's last token.  The caller has reserved ``rows`` positions
+        for every slot and commits the prompts' lengths afterwards."""
+        B, R = self.n_seqs, self.rows
         h = self.host.numpy()
-        h[:n] = tokens
-        h[n:R] = 0
-        h[R], h[R + 1] = slot, n - 1
+        h[:B * R] = 0
+        for i, p in enumerate(prompts):
+            h[i * R:i * R + len(p)] = p
+            h[B * R + i] = slots[i]
+            h[B * R + B + i] = i * R + len(p) - 1
         b = self.batch
-        b.tokens.copy_(self.host[:R], non_blocking=True)
-        b.seq_slot.copy_(self.host[R:R + 1], non_blocking=True)
-        b.want_rows.copy_(self.host[R + 1:R + 2], non_blocking=True)
+        b.tokens.copy_(self.host[:B * R], non_blocking=True)
+        b.seq_slot.copy_(self.host[B * R:B * R + B], non_blocking=True)
+        b.want_rows.copy_(self.host[B * R + B:B * R + 2 * B], non_blocking=True)
         if self.graph is None:
             out = self.model.forward(b)                 # a real step, eagerly; it also warms every kernel up
             torch.cuda.current_stream().synchronize()

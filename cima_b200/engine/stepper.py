@@ -39,7 +39,7 @@ class ModelStepper:
         self.use_graphs = (use_graphs and torch.device(model.rt.device).type == "cuda"
                            and getattr(model, "graph_safe", False))
         self._graphs = {}
-        self._prompt_graphs = {}      # rows of the bucket -> PromptGraph
+        self._prompt_graphs = {}      # (sequences, rows of the bucket) -> PromptGraph
         self._armed = None            # (graph, slots) whose device-side inputs are those of the next step
         cache = model.cache
         self.max_batch = max(1, min(max_batch, cache.n_slots))
@@ -124,10 +124,10 @@ class ModelStepper:
         for s, n in zip(slots, reused):
             if n:
                 cache.rewind(s, n)
-        if len(slots) == 1 and not reused[0]:
-            first = self._short_prompt(slots[0], prompts[0], options[0])
+        if not any(reused):
+            first = self._short_prompts(slots, prompts, options)
             if first is not None:
-                return [first]
+                return first
         out: List[Optional[int]] = [None] * len(slots)
         # sequences that start run as one prompt step (attention over the step's own keys), those that go on as
         # another (rows that read the cache)
@@ -141,33 +141,37 @@ class ModelStepper:
                 out[i] = t
         return out  # type: ignore[return-value]
 
-    def _short_prompt(self, slot: int, prompt: Sequence[int], option: GenOptions) -> Optional[int]:
-        """The first token of one short prompt through a recorded step (``PromptGraph``), or None where that does
-        not apply: graphs off, a prompt beyond the largest bucket, no room for the bucket's rows, or a mixer that
-        keeps state of its own per sequence (the padding's rows would pass through it)."""
-        from .graph import PROMPT_BUCKETS, PromptGraph
-        n = len(prompt)
-        if not self.use_graphs or n == 0 or n > PROMPT_BUCKETS[-1] or self.model.cache.has_mixer_state:
-            return None
-        rows = next(r for r in PROMPT_BUCKETS if r >= n)
+    def _short_prompts(self, slots, prompts, options) -> Optional[List[int]]:
+        """The first tokens of a few short prompts through a recorded step (``PromptGraph``), or None where that
+        does not apply: graphs off, prompts beyond the largest bucket or more rows than a recorded step takes, no
+        room for the bucket's rows, or a mixer that keeps state of its own per sequence (the padding's rows would
+        pass through it)."""
+        from .graph import PROMPT_BUCKETS, PROMPT_ROWS, PromptGraph
         cache = self.model.cache
-        if rows > self.max_position or cache.length(slot) != 0:
+        longest = max(len(p) for p in prompts)
+        if not self.use_graphs or min(len(p) for p in prompts) == 0 or longest > PROMPT_BUCKETS[-1] or cache.has_mixer_state:
+            return None
+        rows = next(r for r in PROMPT_BUCKETS if r >= longest)
+        if rows * len(slots) > PROMPT_ROWS or rows > self.max_position or any(cache.length(s) for s in slots):
             return None
         vocab = self.model.spec.vocab
-        if min(prompt) < 0 or max(prompt) >= vocab:
+        if min(min(p) for p in prompts) < 0 or max(max(p) for p in prompts) >= vocab:
             raise ValueError(f"token ids must lie in [0, {vocab})")
         try:
-            cache.must_fit([(slot, rows)])
+            cache.must_fit([(s, rows) for s in slots])
         except (CacheFull, CapacityError):
             return None
-        cache.reserve(slot, rows)
+        for s in slots:
+            cache.reserve(s, rows)
         cache.flush()
-        g = self._prompt_graphs.get(rows)
+        key = (len(slots), rows)
+        g = self._prompt_graphs.get(key)
         if g is None:
-            g = self._prompt_graphs[rows] = PromptGraph(self.model, rows)
-        logits = g.run(slot, prompt)
-        cache.commit(slot, n)
-        return self._choose(logits, [slot], [option], n)[0]
+            g = self._prompt_graphs[key] = PromptGraph(self.model, len(slots), rows)
+        logits = g.run(slots, prompts)
+        for s, p in zip(slots, prompts):
+            cache.commit(s, len(p))
+        return self._choose(logits, slots, options, sum(len(p) for p in prompts))
 
     def decode(self, slots, last_tokens, options) -> List[int]:
         if not self.use_graphs:

@@ -435,7 +435,22 @@ def test_short_prompts_through_recorded_prompt_steps(dtype):
                     lg = plain_forward(W, cfg, seq)[-1]
                     assert lg[t] >= lg.max() - 4e-2, (n, rep)
                     seq.append(t)
-    assert sorted(lm.stepper._prompt_graphs) == [16, 32, 64]
+    assert sorted(lm.stepper._prompt_graphs) == [(1, 16), (1, 32), (1, 64), (1, 128)]
+    # several short prompts in one recorded step: padded to the longest one's bucket, each gathered at its own end
+    for lens in ([3, 16, 9], [40, 1, 33, 64], [5, 5, 5, 5, 5, 5, 5, 5], [100, 128]):
+        ps = [random_tokens(V, n, seed=4000 + 13 * i + n) for i, n in enumerate(lens)]
+        for rep in range(2):
+            got = lm.generate(ps, temperature=0, repeat_penalty=1.0, max_tokens=4)
+            for p, r in zip(ps, got):
+                if dtype == "float32":
+                    assert r.tokens == plain_generate(name, p, dict(temperature=0.0), 4)[0], (lens, rep)
+                else:
+                    seq = list(p)
+                    for t in r.tokens:
+                        lg = plain_forward(W, cfg, seq)[-1]
+                        assert lg[t] >= lg.max() - 4e-2, (lens, rep)
+                        seq.append(t)
+    assert {(3, 16), (4, 64), (8, 16), (2, 128)} <= set(lm.stepper._prompt_graphs)
     opts = dict(temperature=0.8, top_k=40, top_p=0.9, repeat_penalty=1.1, seed=4)
     if dtype == "float32":
         p = random_tokens(V, 20, seed=1)
