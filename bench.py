@@ -198,10 +198,9 @@ def main(argv=None) -> int:
             st.decode_on_device(slots, last, opts, warmup)
             before = K.launches
             secs = timed(lambda: st.decode_on_device(slots, None, opts, steps))
-            g = st._graphs[(batch, True)]
             ctx = a.prompt + 1 + warmup + steps / 2.0
             assert K.launches == before                           # everything ran from the graph
-            return secs, g.launches_per_step, ctx
+            return secs, st.recorded_launches(batch), ctx
         finally:
             st.close(slots)
 

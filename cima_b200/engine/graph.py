@@ -21,10 +21,15 @@ class DecodeGraph:
     """One batch size's captured step.  ``load`` sets its inputs for a set of sequences; ``run``
     does one step (the first run after construction executes eagerly and captures)."""
 
-    def __init__(self, model, sampler, n_seqs: int, all_greedy: bool):
+    def __init__(self, model, sampler, n_seqs: int, all_greedy: bool, max_len: int = 0):
+        """``max_len``: the most positions that a sequence may hold after a step of this graph (0: any number).  A
+        recorded step fixes its launches; one recorded for short contexts takes the kernels' choices for them
+        (the decode attention without splits), and the stepper moves to the unbounded graph when a sequence
+        outgrows the bound."""
         self.model, self.sampler = model, sampler
         self.B = B = n_seqs
         self.all_greedy = all_greedy
+        self.max_len = max_len
         dev = model.rt.device
         self.meta = torch.zeros(6 * B + 1, dtype=torch.int32, device=dev)
         self.meta_host = torch.zeros(6 * B + 1, dtype=torch.int32).pin_memory()
@@ -35,8 +40,8 @@ class DecodeGraph:
         self.chosen = torch.zeros(B, dtype=torch.int32, device=dev)
         # What a recorded step may know on the host is what every replay shares: the number of sequences and their
         # rows (one each).  Slots, positions and lengths change from replay to replay and exist on the device only
-        # (``host_seq_slot`` / ``host_seq_len`` stay None, ``max_len`` 0 = unknown).
-        self.batch = StepBatch(prefill=False, n_rows=B, n_seqs=B, n_want=B, max_len=0, want_all_in_order=True,
+        # (``host_seq_slot`` / ``host_seq_len`` stay None; ``max_len`` is the graph's bound, 0 = unknown).
+        self.batch = StepBatch(prefill=False, n_rows=B, n_seqs=B, n_want=B, max_len=max_len, want_all_in_order=True,
                                tokens=self.tokens, row_pos=self.row_pos, row_seq=self.row_seq,
                                seq_slot=self.seq_slot, seq_first_row=self.seq_first_row, seq_len=self.seq_len,
                                want_rows=self.row_seq, max_rows=1, host_seq_first_row=np.arange(B + 1, dtype=np.int32))

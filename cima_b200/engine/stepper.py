@@ -245,11 +245,19 @@ class ModelStepper:
             self._armed = None
         self._inflight.clear()
 
+    def _context_bound(self, slots, ahead: int) -> int:
+        """The bound of the graph that may run the next ``ahead`` steps of these sequences: the short-context bound
+        while every sequence stays within it, else 0 (no bound)."""
+        from ..kernels import SHORT_CONTEXT
+        cache = self.model.cache
+        longest = max(cache.length(s) + self._inflight.get(s, 0) for s in slots) + ahead
+        return SHORT_CONTEXT if longest <= SHORT_CONTEXT else 0
+
     def _decode_pipelined(self, slots, last_tokens, options) -> List[int]:
         fl = self._flight
         if fl is not None and fl["fed"] is not None and set(slots) <= set(fl["slots"]) and \
                 all(fl["fed"][s] == t for s, t in zip(slots, last_tokens)):
-            if fl["slots"] == slots:
+            if fl["slots"] == slots and self._context_bound(slots, 1) == fl["graph"].max_len:
                 nxt = self._launch(fl["graph"], slots)           # the step after, before this one is read
                 toks = self._read(fl, slots)
                 if nxt is not None:
@@ -268,7 +276,7 @@ class ModelStepper:
             self._flight = nxt
             return toks
         self._drain()
-        graph = self._arm(slots, last_tokens, options)
+        graph = self._arm(slots, last_tokens, options, ahead=2)
         first = self._launch(graph, slots)
         if first is None:
             raise CacheFull("no room for the next position of a sequence")
@@ -280,25 +288,44 @@ class ModelStepper:
         return toks
 
     # ------------------------------------------------------------------ graph plumbing
-    def _arm(self, slots, last_tokens, options):
-        """The graph for this batch size with its inputs set: uploaded when the set of sequences
-        changed, otherwise already there (the last step fed its tokens forward on the device)."""
+    def _arm(self, slots, last_tokens, options, ahead: int = 1):
+        """The graph for this batch size (and for the lengths that the next ``ahead`` steps reach) with its inputs
+        set: uploaded when the set of sequences or the graph changed, otherwise already there (the last step fed
+        its tokens forward on the device)."""
         cache = self.model.cache
         all_greedy = all(o.greedy for o in options)
-        key = (len(slots), all_greedy)
+        bound = self._context_bound(slots, ahead)
+        key = (len(slots), all_greedy, bound)
         graph = self._graphs.get(key)
         if graph is None:
             from .graph import DecodeGraph
-            graph = self._graphs[key] = DecodeGraph(self.model, self.sampler, len(slots), all_greedy)
+            graph = self._graphs[key] = DecodeGraph(self.model, self.sampler, len(slots), all_greedy, bound)
         if self._armed != (key, tuple(slots)):
             params = np.array([[o.temperature, float(o.top_k), o.top_p, o.repeat_penalty] for o in options], dtype=np.float32)
-            graph.load(slots, last_tokens, [cache.length(s) for s in slots], params)
+            carried = None
+            if last_tokens is None:
+                # the tokens are on the device only, in the graph that ran these sequences' last step
+                before = self._graphs.get(self._armed[0]) if self._armed and self._armed[1] == tuple(slots) else None
+                if before is None:
+                    raise ValueError("the next step's tokens are needed: no recorded step of these sequences holds them")
+                carried = before.tokens.clone()
+            graph.load(slots, last_tokens if carried is None else [0] * len(slots), [cache.length(s) for s in slots], params)
+            if carried is not None:
+                graph.tokens.copy_(carried)
             self.h2d_bytes += 4 * (6 * len(slots) + 1) + params.nbytes
             self._armed = (key, tuple(slots))
         elif last_tokens is not None:
             graph.feed(last_tokens)
             self.h2d_bytes += 4 * len(slots)
         return graph
+
+    def recorded_launches(self, n_seqs: int) -> int:
+        """Kernel launches of this library in one recorded decode step of ``n_seqs`` sequences (the graph used last
+        among those of that size)."""
+        found = [g for k, g in self._graphs.items() if k[0] == n_seqs and g.graph is not None]
+        if not found:
+            raise KeyError(f"no decode step of {n_seqs} sequences has been recorded")
+        return found[-1].launches_per_step
 
     def reserve_ahead(self, slots, steps: int) -> None:
         cache = self.model.cache
@@ -315,7 +342,7 @@ class ModelStepper:
         """``steps`` decode steps without a host round trip between them (tokens are fed forward on
         the device); returns the last step's chosen tokens (device).  Used to time the device alone."""
         self._drain()
-        graph = self._arm(slots, last_tokens, options)
+        graph = self._arm(slots, last_tokens, options, ahead=steps)
         self.reserve_ahead(slots, steps)
         for _ in range(steps):
             chosen = graph.run()

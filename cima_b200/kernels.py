@@ -19,6 +19,7 @@ ABI_VERSION = 20
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
+SHORT_CONTEXT = 512         # up to this many positions a sequence's keys are one block's work: no split, no merge kernel
 
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
@@ -550,6 +551,9 @@ class Kernels:
                 n_splits = 8
             if max_len > 0:
                 n_splits = min(n_splits, -(-max_len // 64))
+                # a short context is a few pages: one block reads them in less time than the merge of splits takes
+                if max_len <= SHORT_CONTEXT:
+                    n_splits = 1
         if not self._admit(f"attention_decode[{n_splits} splits]", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
         part_o = part_ml = None
         if n_splits > 1:
