@@ -16,6 +16,7 @@ from .batch import StepEntry
 
 
 MIN_REUSE = 16     # a finished sequence is taken up again only for at least this many tokens in common
+MAX_PROMPT_GRAPHS = 12    # recorded prompt steps kept (by sequences and rows); the one used longest ago gives way
 
 
 class ModelStepper:
@@ -39,7 +40,7 @@ class ModelStepper:
         self.use_graphs = (use_graphs and torch.device(model.rt.device).type == "cuda"
                            and getattr(model, "graph_safe", False))
         self._graphs = {}
-        self._prompt_graphs = {}      # (sequences, rows of the bucket) -> PromptGraph
+        self._prompt_graphs = OrderedDict()      # (sequences, rows of the bucket) -> PromptGraph, the newest last
         self._armed = None            # (graph, slots) whose device-side inputs are those of the next step
         cache = model.cache
         self.max_batch = max(1, min(max_batch, cache.n_slots))
@@ -168,6 +169,9 @@ class ModelStepper:
         g = self._prompt_graphs.get(key)
         if g is None:
             g = self._prompt_graphs[key] = PromptGraph(self.model, len(slots), rows)
+            while len(self._prompt_graphs) > MAX_PROMPT_GRAPHS:          # each holds its step's activations
+                self._prompt_graphs.popitem(last=False)
+        self._prompt_graphs.move_to_end(key)
         logits = g.run(slots, prompts)
         for s, p in zip(slots, prompts):
             cache.commit(s, len(p))
