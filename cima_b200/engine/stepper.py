@@ -145,12 +145,15 @@ class ModelStepper:
     def _short_prompts(self, slots, prompts, options) -> Optional[List[int]]:
         """The first tokens of a few short prompts through a recorded step (``PromptGraph``), or None where that
         does not apply: graphs off, prompts beyond the largest bucket or more rows than a recorded step takes, no
-        room for the bucket's rows, or a mixer that keeps state of its own per sequence (the padding's rows would
-        pass through it)."""
+        room for the bucket's rows, a mixer that keeps state of its own per sequence (the padding's rows would pass
+        through it), or a group of layers that keeps a window's keys in a ring of pages (the padding's keys would
+        land on ring entries that real positions still need)."""
         from .graph import PROMPT_BUCKETS, PROMPT_ROWS, PromptGraph
         cache = self.model.cache
         longest = max(len(p) for p in prompts)
         if not self.use_graphs or min(len(p) for p in prompts) == 0 or longest > PROMPT_BUCKETS[-1] or cache.has_mixer_state:
+            return None
+        if any(g.ring_pages for g in cache.groups):
             return None
         rows = next(r for r in PROMPT_BUCKETS if r >= longest)
         if rows * len(slots) > PROMPT_ROWS or rows > self.max_position or any(cache.length(s) for s in slots):

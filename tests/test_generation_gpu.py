@@ -490,3 +490,18 @@ def test_sequences_that_outgrow_the_short_context_change_graphs(pipeline, tmp_pa
                 st.close(slots)
             assert last == [t[1 + 2 + 50] for t in outs[0]]
     assert outs[0] == outs[1]
+
+
+def test_short_prompts_of_a_windowed_model_keep_their_window(tmp_path):
+    """A windowed group keeps its keys in a ring of pages: rows padded onto a prompt would land on ring entries that
+    positions inside the window still need (129 tokens padded to 256 rows with a window of 40: the padding at 217..255
+    falls on the places of 89..127).  Such a model's prompts therefore run unpadded; generation from prompts of 129 to
+    200 tokens equals the plain loop's."""
+    name = "C"
+    V = TINY[name]["vocab_size"]
+    lm = cima_b200.load(model_folder(name), dtype="float32", max_tokens=4096, verbose=False)
+    for n in (129, 150, 200, 16):
+        p = random_tokens(V, n, seed=7000 + n)
+        got = lm.generate([p], temperature=0, repeat_penalty=1.0, max_tokens=8)[0]
+        assert got.tokens == plain_generate(name, p, dict(temperature=0.0), 8)[0], n
+    assert not lm.stepper._prompt_graphs

@@ -76,7 +76,7 @@ def test_random_configuration_generates_as_the_plain_loop(seed, tmp_path):
     c, W = plain_load(folder)
     W = {k: v.double() for k, v in W.items()}
     n_prompts = rng.choice([1, 1, 2, 5, 9, 12])
-    prompts = [random_tokens(cfg["vocab_size"], rng.choice([1, 2, 15, 16, 17, 40, 64, 65, 70]), seed * 100 + i) for i in range(n_prompts)]
+    prompts = [random_tokens(cfg["vocab_size"], rng.choice([1, 2, 15, 16, 17, 40, 64, 65, 70, 129, 150, 200]), seed * 100 + i) for i in range(n_prompts)]
     opts = rng.choice([dict(temperature=0.0, repeat_penalty=1.0), dict(temperature=0.8, top_k=40, top_p=0.9, repeat_penalty=1.1, seed=seed + 1)])
     steps = 5
 
