@@ -3,6 +3,7 @@
     cima run <MODEL_DIR> [TOKEN_ID ...] [--prompts FILE] [--dtype D] [--max-seq N] [--PARAM VALUE]...
     cima run --random-shape NAME [--weights-seed S] [TOKEN_ID ...] ...
     cima bench <MODEL_DIR> [-n TOKENS] [--iters N] [--batch B] [--prompt-len P]
+    cima profile <MODEL_DIR> | --random-shape NAME [--batch B] [--prompt-len P]
     cima random <OUT_DIR> --shape NAME | --config FILE [--seed S]
     cima show <MODEL_DIR>
     cima selftest
@@ -36,6 +37,8 @@ Usage:
        --PARAM VALUE                      generation parameters (see `cima run --help`)
   cima bench <MODEL_DIR> [-n TOKENS] [--iters N] [--batch B] [--prompt-len P]
                                         Greedy decode rate, stop tokens ignored, one discarded warm-up
+  cima profile <MODEL_DIR> | --random-shape NAME [--batch B] [--prompt-len P]
+                                        Every launch of a decode step and of a prompt step with its time inside the step
   cima random <OUT_DIR> --shape NAME | --config FILE [--seed S]
                                         Write a model folder with seeded random weights
   cima show <MODEL_DIR>                 Show the model's configuration and layers
@@ -154,6 +157,48 @@ def cmd_bench(args: List[str]) -> int:
     return 0
 
 
+def cmd_profile(args: List[str]) -> int:
+    """Where a step's time goes, launch by launch, without a profiler (the reference's ``cima profile`` prints
+    microseconds per launch, launches per token and the weight-streaming floor, src/selftest.rs:1201-1331)."""
+    rest = list(args)
+    shape = _flag(rest, "--random-shape")
+    batch = int(_flag(rest, "--batch", "1"))
+    plen = int(_flag(rest, "--prompt-len", "128"))
+    dtype = _flag(rest, "--dtype", "bfloat16")
+    hbm = float(_flag(rest, "--hbm-gbs", "6650"))
+    tflops = float(_flag(rest, "--tflops", "1590"))
+    if shape is None and not rest:
+        raise SystemExit("cima profile: a model folder (or --random-shape NAME) is needed")
+    import numpy as np
+    import cima_b200
+    from .engine.profile import profile_decode, profile_prompt, table
+    kw = dict(dtype=dtype, max_tokens=batch * (plen + 1024), max_batch=batch, pipeline=False)
+    if shape is not None:
+        from .config.shapes import SHAPES
+        if shape not in SHAPES:
+            raise SystemExit(f"cima profile: unknown shape '{shape}' (known: {', '.join(sorted(SHAPES))})")
+        lm = cima_b200.load(config=SHAPES[shape], seed=0, draw="device", **kw)
+    else:
+        lm = cima_b200.load(rest[0], **kw)
+    st = lm.stepper
+    if not st.use_graphs:
+        raise SystemExit("cima profile: this model's steps cannot be recorded (a part is not fit for it, or no GPU)")
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(0, lm.spec.vocab, size=plen).tolist() for _ in range(batch)]
+    o = [GenOptions(temperature=0.0, repeat_penalty=1.0, ignore_eos=True)] * batch
+    slots = st.open(batch)
+    try:
+        first = st.prefill(slots, prompts, o)
+        rows = profile_decode(st, slots, first, o)
+    finally:
+        st.close(slots)
+    print(f"decode step, batch {batch}, context {plen} (peaks given: {hbm:.0f} GB/s, {tflops:.0f} TFLOP/s):")
+    print(table(rows, hbm, tflops, tokens=batch))
+    print(f"\nprompt step, one prompt of {plen} tokens:")
+    print(table(profile_prompt(lm.model, [plen]), hbm, tflops))
+    return 0
+
+
 def cmd_random(args: List[str]) -> int:
     if not args:
         raise SystemExit("cima random: an output folder is needed")
@@ -237,6 +282,8 @@ def main(argv=None) -> int:
         return cmd_run(rest)
     if cmd == "bench":
         return cmd_bench(rest)
+    if cmd == "profile":
+        return cmd_profile(rest)
     if cmd == "random":
         return cmd_random(rest)
     if cmd == "show":

@@ -114,13 +114,13 @@ def profile_decode(stepper, slots, last_tokens, options, reps: int = 20) -> List
     stepper._drain()
     stepper._armed = None
     all_greedy = all(o.greedy for o in options)
-    graph = DecodeGraph(model, stepper.sampler, len(slots), all_greedy)
+    ahead = 8 * reps + 16                     # every replay of the whole step moves the sequences on by one position
+    graph = DecodeGraph(model, stepper.sampler, len(slots), all_greedy, stepper._context_bound(slots, ahead))
     lengths = [cache.length(s) for s in slots]
     params = np.array([[o.temperature, float(o.top_k), o.top_p, o.repeat_penalty] for o in options], dtype=np.float32)
     graph.load(slots, last_tokens, lengths, params)
-    # every replay of the whole step moves the sequences on by one position: room for all of them
-    for s, n in zip(slots, lengths):
-        cache.reserve(s, min(n + 8 * reps + 16, stepper.max_position))
+    for s, n in zip(slots, lengths):         # room for all of those positions
+        cache.reserve(s, min(n + ahead, stepper.max_position))
     cache.flush()
     torch.cuda.synchronize()
     try:

@@ -505,3 +505,13 @@ def test_short_prompts_of_a_windowed_model_keep_their_window(tmp_path):
         got = lm.generate([p], temperature=0, repeat_penalty=1.0, max_tokens=8)[0]
         assert got.tokens == plain_generate(name, p, dict(temperature=0.0), 8)[0], n
     assert not lm.stepper._prompt_graphs
+
+
+def test_cima_profile_prints_every_launch_of_a_step():
+    """``bin/cima profile``: the launches of one decode step and of one prompt step with their times, from a shape
+    with random weights in memory."""
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "cima"), "profile", "--random-shape", "tiny-b", "--batch", "2",
+                        "--prompt-len", "40"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert "decode step, batch 2, context 40" in p.stdout and "prompt step, one prompt of 40 tokens" in p.stdout
+    assert "qkv_rope_skinny" in p.stdout and "attention_decode" in p.stdout and "launches a token" in p.stdout
