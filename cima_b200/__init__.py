@@ -53,10 +53,11 @@ class LM:
         return self.model.step(entries)
 
     def generate(self, prompts: Sequence[Sequence[int]], options: Union[GenOptions, Sequence[GenOptions], None] = None,
-                 **named):
+                 on_token=None, **named):
         """Token ids in, ``GenResult`` per prompt out.  Options by the reference's names
         (temperature, top_k, top_p, repeat_penalty, seed, max_tokens, stop, ignore_eos), either as a
-        ``GenOptions`` (one for all prompts or one per prompt) or as keyword arguments."""
+        ``GenOptions`` (one for all prompts or one per prompt) or as keyword arguments.  ``on_token(i, token)`` is
+        called for every token of prompt ``i`` as soon as its step is read."""
         if named:
             if options is not None and not isinstance(options, GenOptions):
                 raise ValueError("keyword options go with at most one GenOptions")
@@ -68,7 +69,7 @@ class LM:
                 else:
                     o = o.set(k, v)
             options = o
-        return self.loop.generate(prompts, options)
+        return self.loop.generate(prompts, options, on_token=on_token)
 
     @property
     def stats(self):

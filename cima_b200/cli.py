@@ -32,6 +32,7 @@ Usage:
   cima run <MODEL_DIR> [TOKEN_ID ...]   Generate from a prompt of token ids (--prompts FILE: one per line)
        --random-shape NAME                instead of MODEL_DIR: a known shape with random weights in memory
        --weights-seed S                   seed of those weights (default 0)
+       --stream                           print every token as its step is read ("<prompt>:<token>" a line)
        --dtype bfloat16|float32           precision of the whole model (default bfloat16)
        --max-seq N                        positions the cache holds in all (default 8192)
        --PARAM VALUE                      generation parameters (see `cima run --help`)
@@ -89,6 +90,9 @@ def cmd_run(args: List[str]) -> int:
     dtype = _flag(rest, "--dtype", "bfloat16")
     max_seq = int(_flag(rest, "--max-seq", "8192"))
     prompts_file = _flag(rest, "--prompts")
+    stream = "--stream" in rest
+    if stream:
+        rest.remove("--stream")
     opts = GenOptions()
     words: List[str] = []
     i = 0
@@ -118,10 +122,12 @@ def cmd_run(args: List[str]) -> int:
         print(f"random weights of shape {shape}, seed {weights_seed} …", file=sys.stderr)
         lm = cima_b200.load(config=SHAPES[shape], seed=weights_seed, dtype=dtype, max_tokens=max_seq)
     t0 = time.perf_counter()
-    results = lm.generate(prompts, opts)
+    on_token = (lambda i, t: print(f"{i}:{t}", flush=True)) if stream else None
+    results = lm.generate(prompts, opts, on_token=on_token)
     total = time.perf_counter() - t0
-    for r in results:
-        print(" ".join(str(t) for t in r.tokens))
+    if not stream:
+        for r in results:
+            print(" ".join(str(t) for t in r.tokens))
     s = lm.stats
     rate = s.gen_tokens / total if total > 0 else 0.0
     print(f"[{s.prompt_tokens} prompt tok | {s.gen_tokens} gen tok | ttft {s.prefill_s * 1e3:.0f} ms | {rate:.1f} tok/s]",

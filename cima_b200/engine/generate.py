@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import time
 from dataclasses import dataclass
-from typing import List, Optional, Protocol, Sequence, Union
+from typing import Callable, List, Optional, Protocol, Sequence, Union
 
 from ..sampling.options import GenOptions
 
@@ -100,10 +100,16 @@ class GenerationLoop:
         self.stepper = stepper
         self.eos_ids = tuple(eos_ids)
         self.stats = GenStats()
+        self._on_token = None
 
     def generate(self, prompts: Sequence[Sequence[int]],
-                 options: Union[GenOptions, Sequence[GenOptions], None] = None) -> List[GenResult]:
+                 options: Union[GenOptions, Sequence[GenOptions], None] = None,
+                 on_token: Optional[Callable[[int, int], None]] = None) -> List[GenResult]:
+        """``on_token(i, token)`` is called for every token of request ``i`` as soon as the step that made it is
+        read, in the order of the requests within a step (the reference hands each token's text to its
+        ``on_token`` as it is generated, src/models/mod.rs:977, :1307); a stop token is not reported."""
         st = self.stepper
+        self._on_token = on_token
         n = len(prompts)
         if options is None:
             options = GenOptions()
@@ -160,6 +166,8 @@ class GenerationLoop:
                         results[i] = GenResult(out[j], "stop", len(prompts[j]), fitted[i][1])
                         continue
                     out[j].append(int(t))
+                    if self._on_token is not None:
+                        self._on_token(i, int(t))
                     if len(out[j]) >= budgets[i]:
                         results[i] = GenResult(out[j], "length", len(prompts[j]), fitted[i][1])
                         continue

@@ -368,6 +368,11 @@ def test_cima_run_generates_what_the_plain_loop_does(tmp_path):
                        capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stderr[-2000:]
     assert len(p.stdout.split()) == 5
+    # --stream: every token as its step is read, "<prompt>:<token>" a line, the same tokens
+    p = subprocess.run(exe + [folder, "5", "17", "3", "--stream", "--temp", "0", "--repeat-penalty", "1.0", "--max-tokens", "8",
+                              "--dtype", "float32"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [int(l.split(":")[1]) for l in p.stdout.split()] == plain_generate(name, [5, 17, 3], dict(temperature=0.0), 8)[0]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -113,3 +113,17 @@ def test_budget_is_capped_by_positions_and_zero_budget_needs_no_step():
     res = loop.generate([[5]], GenOptions(max_tokens=0))
     assert res[0].tokens == [] and res[0].finish_reason == "length"
     assert not [c for c in st.calls[-1:] if c[0] == "prefill"]
+
+
+def test_tokens_are_reported_as_their_steps_are_read():
+    """``on_token`` gets every emitted token with its request's index, step by step in the order of the requests;
+    a stop token is not reported; requests of a later batch follow those of the earlier one."""
+    st = Scripted(max_batch=2)
+    loop = GenerationLoop(st, eos_ids=[103])
+    seen = []
+    res = loop.generate([[100, 7], [200], [300]], GenOptions(temperature=0.0, repeat_penalty=1.0, max_tokens=3),
+                        on_token=lambda i, t: seen.append((i, t)))
+    assert seen == [(0, 101), (1, 201), (0, 102), (1, 202), (1, 203), (2, 301), (2, 302), (2, 303)]
+    assert [t for i, t in seen if i == 0] == res[0].tokens and res[0].finish_reason == "stop"
+    loop.generate([[100]], GenOptions(temperature=0.0, repeat_penalty=1.0, max_tokens=2))        # no callback: none is kept
+    assert len(seen) == 8
