@@ -195,7 +195,7 @@ def main(argv=None) -> int:
             for i in range(0, batch, 8):
                 first += st.prefill(slots[i:i + 8], prompts[i:i + 8], opts[i:i + 8])
             last = st.decode(slots, first, opts)                  # arms and captures the graph
-            st.decode_on_device(slots, last, opts, warmup)
+            st.decode_on_device(slots, last, opts, warmup, reach=warmup + steps)
             before = K.launches
             secs = timed(lambda: st.decode_on_device(slots, None, opts, steps))
             ctx = a.prompt + 1 + warmup + steps / 2.0

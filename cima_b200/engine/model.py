@@ -98,6 +98,14 @@ class Model:
         return out
 
     @property
+    def short_context(self) -> int:
+        """The bound of the context class for which decode steps are recorded apart: the smallest that a mixer
+        names (``mixer.short_context``), 0 if none does."""
+        named = [int(getattr(b.mixer, "short_context", 0) or 0) for b in self.blocks if hasattr(b, "mixer")]
+        named = [n for n in named if n > 0]
+        return min(named) if named else 0
+
+    @property
     def graph_safe(self) -> bool:
         """Whether a decode step may be recorded as a CUDA graph: every layer's parts and the final norm say so."""
         return all(getattr(b, "graph_safe", False) for b in self.blocks) and getattr(self.final_norm, "graph_safe", False)

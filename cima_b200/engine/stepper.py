@@ -40,6 +40,7 @@ class ModelStepper:
         self.use_graphs = (use_graphs and torch.device(model.rt.device).type == "cuda"
                            and getattr(model, "graph_safe", False))
         self._graphs = {}
+        self.short_context = int(getattr(model, "short_context", 0) or 0)
         self._prompt_graphs = OrderedDict()      # (sequences, rows of the bucket) -> PromptGraph, the newest last
         self._armed = None            # (graph, slots) whose device-side inputs are those of the next step
         cache = model.cache
@@ -255,10 +256,10 @@ class ModelStepper:
     def _context_bound(self, slots, ahead: int) -> int:
         """The bound of the graph that may run the next ``ahead`` steps of these sequences: the short-context bound
         while every sequence stays within it, else 0 (no bound)."""
-        from ..kernels import SHORT_CONTEXT
         cache = self.model.cache
+        short = self.short_context
         longest = max(cache.length(s) + self._inflight.get(s, 0) for s in slots) + ahead
-        return SHORT_CONTEXT if longest <= SHORT_CONTEXT else 0
+        return short if longest <= short else 0
 
     def _decode_pipelined(self, slots, last_tokens, options) -> List[int]:
         fl = self._flight
@@ -345,11 +346,13 @@ class ModelStepper:
         for s in slots:
             cache.commit(s, cache.length(s) + steps)
 
-    def decode_on_device(self, slots, last_tokens, options, steps: int) -> torch.Tensor:
+    def decode_on_device(self, slots, last_tokens, options, steps: int, reach: Optional[int] = None) -> torch.Tensor:
         """``steps`` decode steps without a host round trip between them (tokens are fed forward on
-        the device); returns the last step's chosen tokens (device).  Used to time the device alone."""
+        the device); returns the last step's chosen tokens (device).  Used to time the device alone.
+        ``reach``: how many steps the caller will run in all, this call's included; the graph is chosen for the
+        lengths they reach, so that a warm-up and the timed steps after it run the same recorded step."""
         self._drain()
-        graph = self._arm(slots, last_tokens, options, ahead=steps)
+        graph = self._arm(slots, last_tokens, options, ahead=max(steps, reach or 0))
         self.reserve_ahead(slots, steps)
         for _ in range(steps):
             chosen = graph.run()

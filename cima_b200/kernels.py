@@ -19,7 +19,18 @@ ABI_VERSION = 20
 SPLIT_BLOCKS = 296          # blocks of the decode attention that one wave holds (two per SM, 148 SMs)
 TC_ATTENTION_MIN_LEN = 256  # prompts from this length on take the tcgen05 attention (head_dim 64 or 128)
 SPLIT_FEW_BLOCKS = 148      # below this many blocks at 8 splits, more splits are taken
-SHORT_CONTEXT = 512         # up to this many positions a sequence's keys are one block's work: no split, no merge kernel
+SHORT_CONTEXT_BYTES = 96 * 1024   # up to this many bytes of keys and values (one kv head) a sequence's context is one block's
+                                  # work in the decode attention: no split, no merge kernel.  Measured at the 7B shape
+                                  # (head_dim 128: 192 positions), batch 1 and 8: up to ~190 positions 4.4 to 6.1 us against
+                                  # 6.1 to 6.6 with splits, from ~280 on 7.7 to 10 against 5.7 to 7.4; at head_dim 64 the
+                                  # same bytes are 384 positions (Qwen2.5-0.5B, batch 1, contexts 137 to 265: 0.526 ms a
+                                  # step without splits, 0.567 with)
+
+
+def short_context(head_dim: int) -> int:
+    """Positions (whole pages of 64) up to which the decode attention of this head size runs without splits."""
+    return SHORT_CONTEXT_BYTES // (4 * head_dim) // 64 * 64
+
 
 # epilogues of the skinny product
 SK_STORE, SK_ACCUM, SK_SWIGLU, SK_STORE_F32 = 0, 1, 2, 3
@@ -552,7 +563,7 @@ class Kernels:
             if max_len > 0:
                 n_splits = min(n_splits, -(-max_len // 64))
                 # a short context is a few pages: one block reads them in less time than the merge of splits takes
-                if max_len <= SHORT_CONTEXT:
+                if max_len <= short_context(head_dim):
                     n_splits = 1
         if not self._admit(f"attention_decode[{n_splits} splits]", *self._attention_work(qkv, n_heads, n_kv_heads, head_dim)): return
         part_o = part_ml = None

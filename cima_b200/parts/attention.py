@@ -78,6 +78,13 @@ class Attention:
 
     graph_safe = True              # a decode step reads nothing of the batch on the host
 
+    @property
+    def short_context(self) -> int:
+        """Positions up to which this mixer's decode kernel takes another road than for long contexts (none if 0):
+        the stepper records decode steps for such contexts apart (``StepBatch.max_len`` is their bound)."""
+        from ..kernels import short_context
+        return short_context(self.spec.head_dim)
+
     # ------------------------------------------------------------------ cache
     def cache_requests(self, site: int) -> List[object]:
         if self.spec.cache_from is not None:

@@ -466,9 +466,9 @@ def test_short_prompts_through_recorded_prompt_steps(dtype):
 
 @pytest.mark.parametrize("pipeline", [True, False])
 def test_sequences_that_outgrow_the_short_context_change_graphs(pipeline, tmp_path):
-    """Decode steps of sequences within 512 positions are recorded without splits of the attention; when a sequence
-    outgrows that bound the stepper goes on with the unbounded graph.  Generation across the bound (prompts of 470 to
-    509 tokens, 60 new ones), with run-ahead and without, in bfloat16: the same tokens as step-by-step decoding
+    """Decode steps of sequences within the short-context bound are recorded without splits of the attention; when
+    a sequence outgrows that bound the stepper goes on with the unbounded graph.  Generation across the bound (prompts
+    that end 3 to 42 tokens before it, 60 new ones), with run-ahead and without, in bfloat16: the same tokens as step-by-step decoding
     without graphs, whose every step chooses its kernels from the lengths it sees; and on the device without the
     host in between (``decode_on_device``) across the bound as well."""
     from cima_b200.sampling import GenOptions
@@ -476,13 +476,15 @@ def test_sequences_that_outgrow_the_short_context_change_graphs(pipeline, tmp_pa
     folder = str(tmp_path / "m")
     cima_b200.write_random_model(folder, cfg, seed=4)
     V = cfg["vocab_size"]
-    prompts = [random_tokens(V, n, seed=600 + n) for n in (470, 509, 500)]
+    from cima_b200.kernels import short_context
+    SHORT_CONTEXT = short_context(cfg["head_dim"])
+    prompts = [random_tokens(V, n, seed=600 + n) for n in (SHORT_CONTEXT - 42, SHORT_CONTEXT - 3, SHORT_CONTEXT - 12)]
     outs = []
     for use_graphs in (True, False):
         lm = cima_b200.load(folder, dtype="bfloat16", max_tokens=4096, verbose=False, pipeline=pipeline, use_graphs=use_graphs)
         outs.append([r.tokens for r in lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=60)])
         if use_graphs:
-            assert {k[2] for k in lm.stepper._graphs} == {512, 0}
+            assert {k[2] for k in lm.stepper._graphs} == {SHORT_CONTEXT, 0}
             st = lm.stepper
             greedy = [GenOptions(temperature=0.0, repeat_penalty=1.0)] * 3
             slots = st.open(3)
