@@ -522,3 +522,14 @@ def test_cima_profile_prints_every_launch_of_a_step():
     assert p.returncode == 0, p.stderr[-2000:]
     assert "decode step, batch 2, context 40" in p.stdout and "prompt step, one prompt of 40 tokens" in p.stdout
     assert "qkv_rope_skinny" in p.stdout and "attention_decode" in p.stdout and "launches a token" in p.stdout
+
+
+def test_cima_bench_reports_a_decode_rate():
+    """``bin/cima bench`` as the reference's bench command: greedy, stop tokens ignored, one discarded warm-up, the
+    median of the iterations' decode rates as one JSON line."""
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "cima"), "bench", model_folder("A"), "-n", "12", "--iters", "2",
+                        "--batch", "2", "--prompt-len", "9"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    line = json.loads(p.stdout.strip().split("\n")[-1])
+    assert line["batch"] == 2 and line["gen_tokens"] == 12 and line["prompt_tokens"] == 9
+    assert line["decode_tok_per_s_p50"] >= line["decode_tok_per_s_min"] > 0 and line["ttft_ms"] > 0
