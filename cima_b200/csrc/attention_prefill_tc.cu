@@ -87,9 +87,9 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
   unsigned long long* v_full = bars + 5;                       // [2]  long before V's (after P V): the two rings run
   unsigned long long* v_empty = bars + 7;                      // [2]  apart, so K is fetched two tiles ahead
   unsigned long long* s_full = bars + 9;                       // [2]
-  unsigned long long* p_full = bars + 11;                      // [1]
-  unsigned long long* pv_done = bars + 12;                     // [1]
-  unsigned* tmem_slot = (unsigned*)(bars + 13);
+  unsigned long long* p_full = bars + 11;                      // [2]  one per buffer of S, as s_full: see the softmax warps
+  unsigned long long* pv_done = bars + 13;                     // [1]
+  unsigned* tmem_slot = (unsigned*)(bars + 14);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -112,8 +112,8 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
     for (int s = 0; s < 2; s++) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 4);
     }
-    mbar_init(p_full, 4);
     mbar_init(pv_done, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -195,7 +195,7 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           issue_s(j + 1);
         }
-        ok = mbar_wait(&v_full[j & 1], (j >> 1) & 1, a.error_flag, abort_flag) && mbar_wait(p_full, j & 1, a.error_flag, abort_flag);
+        ok = mbar_wait(&v_full[j & 1], (j >> 1) & 1, a.error_flag, abort_flag) && mbar_wait(&p_full[j & 1], (j >> 1) & 1, a.error_flag, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int s = j & 1;
@@ -301,11 +301,13 @@ k_attention_prefill_tc(const __grid_constant__ CUtensorMap map_qkv, const __grid
         tmem_st32_words(tm_s[s] + lane_off, pk);
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      // a warp is at most one tile ahead of the slowest: were it to arrive for this tile before all four have arrived
-      // for the last one, that phase of the barrier would complete without the slowest warp's P
-      if (j > 0 && !mbar_wait(p_full, (j - 1) & 1, a.error_flag, abort_flag)) { ok = false; break; }
+      // P of tile j is announced on the barrier of its buffer, j & 1.  That barrier's last phase was tile j - 2, and S of
+      // tile j was issued only after P V of tile j - 2 had completed: all four warps had arrived for it and the issuing
+      // thread had seen that phase, so no waiter can be a phase behind.  (One barrier for both buffers would let the
+      // warps, when no row rescales, announce tiles j and j + 1 while the issuing thread still waits for V of tile j;
+      // its wait on the parity of tile j would then be answered by tile j + 2, which never comes.)
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[s]);
     }
     // A wait on a parity answers for the last phase of that parity.  This warp has S of tile n - 1, so P V of tile
     // n - 3 is complete, but that of tile n - 2 need not be: asked for tile n - 1 alone, the barrier would answer for
@@ -361,7 +363,7 @@ int launch_attention_tc(const void* qkv, int ld, const int* tile_seq, const int*
   if (rc) return rc;
   constexpr int NH = HD / 64;
   const size_t smem = NH * (size_t)HALF_BYTES + 2 * NH * (size_t)KHALF_BYTES + 2 * (size_t)HD * 128 + 14 * 8 + 16;
-  static_assert(13 * 8 + 8 <= 14 * 8 + 16, "barriers and flags fit their place");
+  static_assert(14 * 8 + 8 <= 14 * 8 + 16, "barriers and flags fit their place");
   static bool raised = false;
   if (!raised) {
     cudaError_t e = cudaFuncSetAttribute(k_attention_prefill_tc<HD, FROM_CACHE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

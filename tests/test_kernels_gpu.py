@@ -409,6 +409,46 @@ def test_attention_prefill_tcgen05(K, lens, nh, nkv, window, hd):
     assert err(out, want) <= TOL["bfloat16"]
 
 
+def first_launch_on_long_sequences(n_seqs=8, n=8192, nh=28, nkv=4, hd=128):
+    """Run by the test below in a process of its own, where the launch is the kernel's first: then its loads are
+    slow (nothing of the buffer is in any cache or translation buffer) and the roles of a block drift apart."""
+    from cima_b200.kernels import Kernels
+    K = Kernels(verbose=False)
+    T = n_seqs * n
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    bg = batch_of([(i, 0, n) for i in range(n_seqs)], "cuda")
+    out = torch.full((T, nh * hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    scale = 1.0 / math.sqrt(hd)
+    K.attention_prefill_tc(qkv, bg, out, nh, nkv, hd, scale, 0)
+    assert K.device_errors() == 0, "a bounded wait ran out in the kernel's first launch"
+    for seq, h in ((0, 0), (n_seqs - 1, nh - 1), (n_seqs // 2, nh // 2)):     # some heads whole, in float64
+        rows = slice(seq * n, (seq + 1) * n)
+        kvh = h // (nh // nkv)
+        q = qkv[rows, h * hd:(h + 1) * hd].double()
+        k = qkv[rows, (nh + kvh) * hd:(nh + kvh + 1) * hd].double()
+        v = qkv[rows, (nh + nkv + kvh) * hd:(nh + nkv + kvh + 1) * hd].double()
+        sc = (q @ k.T) * scale
+        sc.masked_fill_(torch.ones(n, n, dtype=torch.bool, device="cuda").triu(1), float("-inf"))
+        want = torch.softmax(sc, dim=-1) @ v
+        got = out[rows, h * hd:(h + 1) * hd].double()
+        assert (got - want).abs().max().item() <= TOL["bfloat16"], (seq, h)
+    print("first launch sound")
+
+
+@pytest.mark.parametrize("attempt", [0, 1])
+def test_attention_prefill_tcgen05_first_launch_on_long_sequences(attempt):
+    """Eight sequences of 8,192 rows at the 7B head shape as the first launch of a fresh process.  With one barrier for
+    the probabilities of both score buffers, the softmax warps could announce two tiles while the issuing thread
+    still waited for a late tile of V, and its wait was answered a phase late: about every second fresh process ran
+    into the bounded wait.  Two processes, since the drift is a matter of timing."""
+    import os, subprocess, sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    code = f"import sys; sys.path[:0] = [{here!r}, {os.path.dirname(here)!r}]; import test_kernels_gpu as t; t.first_launch_on_long_sequences()"
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "first launch sound" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 @pytest.mark.parametrize("nh,nkv,hd", [(6, 2, 48), (28, 4, 128), (4, 4, 16)])
 @pytest.mark.parametrize("window,ring", [(0, 0), (90, 0), (40, 2)])
 def test_attention_of_sequences_that_go_on(K, nh, nkv, hd, window, ring):
