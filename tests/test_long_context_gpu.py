@@ -1,0 +1,135 @@
+"""Contexts as long as the configuration allows (32,768 positions), at the 7B layer shape with 2 layers: the
+tcgen05 attention over hundreds of key tiles, prompts that go on from hundreds of pages, split decode over 512
+pages, sequences of very unequal lengths in one batch, and the last position the model may hold.  At these
+lengths the plain implementation (a loop over queries) is out of reach, so the bfloat16 engine is compared with
+the 32-bit engine, whose kernels are others (one warp per row and head, no tensor core) and which the shorter
+tests compare with the plain implementation."""
+import tempfile
+
+import pytest
+import torch
+
+import cima_b200
+from cima_b200.cache.kv import CapacityError
+from cima_b200.engine import StepEntry, load_model
+from helpers import random_tokens
+
+pytestmark = pytest.mark.gpu
+
+REL_BF16 = 2e-2 / 0.28            # the tiny models' bfloat16 tolerance as a fraction of the logits' spread
+MAXPOS = 32768
+SHAPE = dict(model_type="qwen2", architectures=["Qwen2ForCausalLM"], num_hidden_layers=2, hidden_size=3584,
+             num_attention_heads=28, num_key_value_heads=4, head_dim=128, intermediate_size=18944,
+             vocab_size=20008, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False,
+             use_sliding_window=False, max_position_embeddings=MAXPOS)
+TOKENS = random_tokens(SHAPE["vocab_size"], MAXPOS, seed=77)
+PLACES = [0, 63, 64, 4095, 16383, 16384, 24000, MAXPOS - 2, MAXPOS - 1]
+
+
+@pytest.fixture(scope="module")
+def folder():
+    d = tempfile.mkdtemp(prefix="cima_long_")
+    cima_b200.write_random_model(d, SHAPE, seed=5)
+    return d
+
+
+def whole(model, tokens, places):
+    (slot,) = model.cache.open(1)
+    try:
+        out = model.step([StepEntry(slot, tokens, places)]).float().cpu()
+        model.check_device()
+        return out
+    finally:
+        model.cache.close([slot])
+
+
+@pytest.fixture(scope="module")
+def exact(folder):
+    """The 32-bit engine's logits of the whole 32,768-token prompt at PLACES."""
+    m = load_model(folder, dtype="float32", max_tokens=MAXPOS + 64, verbose=False)
+    out = whole(m, TOKENS, PLACES)
+    del m
+    torch.cuda.empty_cache()
+    return out
+
+
+@pytest.fixture(scope="module")
+def m16(folder):
+    return load_model(folder, dtype="bfloat16", max_tokens=MAXPOS + 16384 + 4096 + 256, max_seqs=4, verbose=False)
+
+
+def test_the_longest_prompt_whole(m16, exact):
+    got = whole(m16, TOKENS, PLACES)
+    assert (got - exact).abs().max().item() <= REL_BF16 * exact.std().item()
+    again = whole(m16, TOKENS, PLACES)              # from other pages' contents left behind: the same bits
+    assert torch.equal(got, again)
+
+
+def test_the_longest_prompt_in_pieces_and_its_tail_one_by_one(m16, exact):
+    """16,384 tokens, then 16,000 that go on from 256 pages, then 380 more, then the last 4 one by one (split decode
+    over 512 pages), with the logits at the same places as the whole prompt's; the 32,769th position is refused
+    and the refusal takes nothing."""
+    cuts = [0, 16384, 32384, MAXPOS - 4]
+    (slot,) = m16.cache.open(1)
+    try:
+        outs = []
+        for lo, hi in zip(cuts, cuts[1:]):
+            want = [p - lo for p in PLACES if lo <= p < hi]
+            outs.append(m16.step([StepEntry(slot, TOKENS[lo:hi], want)]).float().cpu())
+        for p in range(MAXPOS - 4, MAXPOS):
+            o = m16.step([StepEntry(slot, [TOKENS[p]], [0])]).float().cpu()
+            if p in PLACES:
+                outs.append(o)
+        m16.check_device()
+        got = torch.cat(outs)
+        assert got.shape == exact.shape
+        assert (got - exact).abs().max().item() <= REL_BF16 * exact.std().item()
+        free = m16.cache.free_tokens()
+        with pytest.raises(CapacityError):
+            m16.step([StepEntry(slot, [1], [0])])
+        assert m16.cache.length(slot) == MAXPOS and m16.cache.free_tokens() == free
+    finally:
+        m16.cache.close([slot])
+    m16.cache.check()
+
+
+def test_sequences_of_very_unequal_lengths_decode_together(m16):
+    """Prompts of 30,000, 5,000, 130 and 1 tokens in one step, then 6 decode steps of the four together: every
+    sequence's logits as when it runs alone (the split of the keys is chosen for the longest; the shortest has
+    one page)."""
+    lens = [30000, 5000, 130, 1]
+    seqs = [TOKENS[i * 100:i * 100 + n + 6] for i, n in enumerate(lens)]
+
+    def run(idx):
+        slots = m16.cache.open(len(idx))
+        try:
+            outs = [m16.step([StepEntry(s, seqs[i][:lens[i]], [lens[i] - 1]) for s, i in zip(slots, idx)]).float().cpu()]
+            for k in range(6):
+                outs.append(m16.step([StepEntry(s, [seqs[i][lens[i] + k]], [0]) for s, i in zip(slots, idx)]).float().cpu())
+            m16.check_device()
+            return torch.stack(outs)                 # [7, sequences, vocab]
+        finally:
+            m16.cache.close(slots)
+
+    together = run([0, 1, 2, 3])
+    for i in range(4):
+        alone = run([i])[:, 0]
+        assert (together[:, i] - alone).abs().max().item() <= REL_BF16 * alone.std().item(), lens[i]
+    m16.cache.check()
+    assert m16.cache.slots.held == 0
+
+
+def test_long_tail_in_32_bit(folder, exact):
+    """The 32-bit engine: the last 3 of the 32,768 tokens one by one after the rest in two pieces give the whole
+    prompt's bits (its attention adds a row's keys in one order, however the tokens were cut)."""
+    m = load_model(folder, dtype="float32", max_tokens=MAXPOS + 64, verbose=False)
+    (slot,) = m.cache.open(1)
+    try:
+        m.step([StepEntry(slot, TOKENS[:20000], [])])
+        m.step([StepEntry(slot, TOKENS[20000:MAXPOS - 3], [])])
+        outs = [m.step([StepEntry(slot, [TOKENS[p]], [0])]).float().cpu() for p in range(MAXPOS - 3, MAXPOS)]
+        m.check_device()
+    finally:
+        m.cache.close([slot])
+    got = torch.cat(outs[1:])
+    assert torch.equal(got, exact[-2:])
