@@ -160,9 +160,7 @@ def main(argv=None) -> int:
         slots = st.open(a.batch)
         try:
             opts = [greedy] * a.batch
-            first = []
-            for i in range(0, a.batch, 8):
-                first += st.prefill(slots[i:i + 8], prompts[i:i + 8], opts[i:i + 8])
+            first = st.prefill(slots, prompts, opts)
             rows = profile_decode(st, slots, first, opts)
         finally:
             st.close(slots)
@@ -190,10 +188,7 @@ def main(argv=None) -> int:
         slots = st.open(batch)
         try:
             opts = [greedy] * batch
-            # prompts in groups of 8 sequences: bounds the activation scratch of the prefill
-            first = []
-            for i in range(0, batch, 8):
-                first += st.prefill(slots[i:i + 8], prompts[i:i + 8], opts[i:i + 8])
+            first = st.prefill(slots, prompts, opts)          # the model runs a step of many rows in parts of 16,384
             last = st.decode(slots, first, opts)                  # arms and captures the graph
             st.decode_on_device(slots, last, opts, warmup, reach=warmup + steps)
             before = K.launches

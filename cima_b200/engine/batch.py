@@ -7,7 +7,7 @@ and its length after the step.  All of it travels to the device in one copy from
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -53,15 +53,31 @@ class StepBatch:
     host_seq_len: np.ndarray = None
 
 
-def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, device) -> StepBatch:
-    """Validate and pack.  ``starts[i]`` is how many positions entry i's slot already holds."""
+def check_entries(entries: Sequence[StepEntry], vocab: Optional[int] = None) -> None:
+    """What must hold of a step's entries whatever their sizes; with ``vocab`` also the token ids and the wanted
+    places (``build_batch`` checks those while it packs; a step that is run in parts checks them before the first
+    part, so that a fault in a later part leaves nothing behind)."""
     if not entries:
         raise ValueError("a step needs at least one entry")
     if len({e.slot for e in entries}) != len(entries):
         raise ValueError("a slot appears twice in one step")
-    counts = [len(e.tokens) for e in entries]
-    if any(c <= 0 for c in counts):
+    if any(len(e.tokens) <= 0 for e in entries):
         raise ValueError("every entry of a step brings at least one token")
+    if vocab is None:
+        return
+    for i, e in enumerate(entries):
+        tk = np.asarray(e.tokens, dtype=np.int64)
+        if tk.min() < 0 or tk.max() >= vocab:
+            raise ValueError(f"entry {i}: token ids must lie in [0, {vocab})")
+        for p in e.want:
+            if not (0 <= p < len(e.tokens)):
+                raise ValueError(f"entry {i}: wanted place {p} is outside its {len(e.tokens)} tokens")
+
+
+def build_batch(entries: List[StepEntry], starts: Sequence[int], vocab: int, device) -> StepBatch:
+    """Validate and pack.  ``starts[i]`` is how many positions entry i's slot already holds."""
+    check_entries(entries)
+    counts = [len(e.tokens) for e in entries]
     if all(c == 1 for c in counts):
         prefill = False                   # one token each: attention over the cache, also at position 0
     elif all(s == 0 for s in starts):

@@ -15,6 +15,9 @@ import torch
 from ..cache import KVRequest, StateRequest
 
 
+STEP_ROWS = 16384        # the most rows that run as one step; a step that brings more is run in parts (``Model.step``)
+
+
 class DoesNotFit(RuntimeError):
     """The weights, the cache and the step's scratch together exceed the device's free memory."""
 
@@ -65,7 +68,7 @@ def forecast(plan: Dict[str, object], requests: Sequence[Sequence[object]], dtyp
     for r, sites in groups.items():
         cache += sites * n_pages * 2 * r.n_kv_heads * page_size * r.head_dim * elt
     # a step of the longest prompt: the float32 residual, the widest activation and its input, logits of a batch
-    rows = min(max_tokens, 16384)
+    rows = min(max_tokens, STEP_ROWS)
     scratch = rows * (hidden * 4 + (widest + 2 * hidden) * elt) + min(n_slots, 256) * vocab * 4 * 2
     return Forecast(weights, cache, scratch)
 

@@ -21,7 +21,8 @@ from ..parts import Linear, Runtime, build_block, build_norm
 from ..parts.linear import FOLDED_NORM_ROWS
 from ..parts.norm import RowsInfo
 from ..weights.loader import TensorSpec, tensor_names
-from .batch import StepBatch, StepEntry, build_batch
+from .batch import StepBatch, StepEntry, build_batch, check_entries
+from .fit import STEP_ROWS
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -48,6 +49,7 @@ class Model:
         self.blocks = [build_block(b, i, rt) for i, b in enumerate(spec.layers)]
         self.final_norm = build_norm(spec.final_norm, rt)
         self.config = None                                  # set by load_model
+        self.step_rows = STEP_ROWS                          # a step of more rows runs in parts
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
         self.cache: Optional[KVCache] = None
@@ -154,6 +156,12 @@ class Model:
         starts = [cache.length(e.slot) for e in entries]
         # the whole step fits or nothing is taken: a step that fails leaves the cache as it found it
         cache.must_fit([(e.slot, s + len(e.tokens)) for e, s in zip(entries, starts)])
+        if sum(len(e.tokens) for e in entries) > self.step_rows:
+            return self._step_in_parts(entries)
+        return self._step_within_bound(entries, starts)
+
+    def _step_within_bound(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
+        cache = self.cache
         limit = cache.most_tokens_going_on()
         if limit is not None and any(starts) and max(len(e.tokens) for e in entries) > limit:
             return self._step_in_rounds(entries, limit)
@@ -165,6 +173,41 @@ class Model:
         for e, s in zip(entries, starts):
             cache.commit(e.slot, s + len(e.tokens))
         return logits
+
+    def _step_in_parts(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """A step of more rows than ``step_rows`` (the number the forecast of a step's scratch counts on) as several:
+        its sequences in their order, as many at a time as stay within the bound; a sequence that alone exceeds it
+        in rounds of ``step_rows`` tokens (its later rounds go on from the cache).  Sequences do not depend on one
+        another and a sequence's logits not on how its tokens are cut, so the logits are the step's own, in the
+        order of the entries and of their ``want``.  With a window's ring of pages a prompt that starts is left
+        whole however long (it reads its own rows, while rounds that go on may add a page at most)."""
+        check_entries(entries, self.spec.vocab)
+        cache = self.cache
+        ring = cache.most_tokens_going_on() is not None
+        parts, group, rows = [], [], 0
+
+        def run_group():
+            nonlocal group, rows
+            if group:
+                parts.append(self._step_within_bound(group, [cache.length(e.slot) for e in group]))
+            group, rows = [], 0
+
+        for e in entries:
+            n = len(e.tokens)
+            if n > self.step_rows:
+                run_group()
+                if ring and cache.length(e.slot) == 0:
+                    group = [e]
+                    run_group()
+                else:
+                    parts.append(self._step_in_rounds([e], self.step_rows))
+                continue
+            if rows + n > self.step_rows:
+                run_group()
+            group.append(e)
+            rows += n
+        run_group()
+        return torch.cat(parts)
 
     def _step_in_rounds(self, entries: Sequence[StepEntry], most: int) -> torch.Tensor:
         """The same step as rounds of at most ``most`` tokens a sequence (see ``KVCache.most_tokens_going_on``);

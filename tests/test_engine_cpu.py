@@ -65,6 +65,51 @@ def test_sequences_may_go_on_by_several_tokens(name):
         model.cache.close([slot])
 
 
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_a_step_of_more_rows_than_the_bound_runs_in_parts(name):
+    """Sequences of 7, 25, 4, 11 and 30 tokens with a bound of 10 rows a step: the short ones run grouped in their
+    order, the long ones in rounds (C keeps a window's ring, so its long prompts that start stay whole); two of the
+    sequences go on from positions they hold.  The logits are those of the unbounded step, in its order; a token
+    outside the vocabulary in the last sequence is refused before any part has run."""
+    cfg = TINY[name]
+    m = cpu_model(name, max_tokens=1024)
+    lens, held = [7, 25, 4, 11, 30], [0, 3, 0, 0, 65]
+    seqs = [random_tokens(cfg["vocab_size"], h + n, seed=50 + i) for i, (n, h) in enumerate(zip(lens, held))]
+    wants = [[0, n - 1] if i != 2 else [] for i, n in enumerate(lens)]
+
+    def run(bound, spoil=False):
+        m.step_rows = bound
+        slots = m.cache.open(len(seqs))
+        try:
+            for s, q, h in zip(slots, seqs, held):
+                if h:
+                    m.step([StepEntry(s, q[:h], [])])
+            entries = [StepEntry(s, list(q[h:]), w) for s, q, h, w in zip(slots, seqs, held, wants)]
+            if spoil:
+                entries[-1].tokens[-1] = cfg["vocab_size"]
+                with pytest.raises(ValueError, match="token ids"):
+                    m.step(entries)
+                assert [m.cache.length(s) for s in slots] == held
+                return None
+            out = m.step(entries)
+            assert [m.cache.length(s) for s in slots] == [h + n for h, n in zip(held, lens)]
+            return out
+        finally:
+            m.cache.close(slots)
+            m.cache.check()
+
+    one = run(1 << 20)
+    cut = run(10)
+    assert one.shape == cut.shape == (8, cfg["vocab_size"])
+    assert (one - cut).abs().max().item() <= 2e-5
+    for i, k in ((0, 0), (1, 2), (3, 4), (4, 6)):          # and against the plain implementation, sequence by sequence
+        c, W = plain_load(model_folder(name))
+        want = plain_forward(W, c, seqs[i]).float()
+        assert (cut[k] - want[held[i]]).abs().max().item() <= 2e-5
+        assert (cut[k + 1] - want[-1]).abs().max().item() <= 2e-5
+    run(10, spoil=True)
+
+
 def test_bfloat16_plumbing_with_folded_norms():
     """The bfloat16 path's host logic (pending norms handed to the products, sums of squares handed on)
     on the stand-in kernels: one-by-one decoding agrees with whole prompts and with the plain logits."""

@@ -47,6 +47,7 @@ def whole(model, tokens, places):
 def exact(folder):
     """The 32-bit engine's logits of the whole 32,768-token prompt at PLACES."""
     m = load_model(folder, dtype="float32", max_tokens=MAXPOS + 64, verbose=False)
+    m.step_rows = MAXPOS                           # one step
     out = whole(m, TOKENS, PLACES)
     del m
     torch.cuda.empty_cache()
@@ -59,10 +60,18 @@ def m16(folder):
 
 
 def test_the_longest_prompt_whole(m16, exact):
+    """As the engine runs it (a step of more than 16,384 rows in parts: the second half goes on from 256 pages) and as
+    one step of 32,768 rows (the tcgen05 attention over up to 512 key tiles of the step's own rows)."""
     got = whole(m16, TOKENS, PLACES)
     assert (got - exact).abs().max().item() <= REL_BF16 * exact.std().item()
     again = whole(m16, TOKENS, PLACES)              # from other pages' contents left behind: the same bits
     assert torch.equal(got, again)
+    bound, m16.step_rows = m16.step_rows, MAXPOS
+    try:
+        one = whole(m16, TOKENS, PLACES)
+    finally:
+        m16.step_rows = bound
+    assert (one - exact).abs().max().item() <= REL_BF16 * exact.std().item()
 
 
 def test_the_longest_prompt_in_pieces_and_its_tail_one_by_one(m16, exact):
