@@ -200,6 +200,54 @@ def test_64_sequences_decode_together_at_the_7b_layer_shape(folder):
         assert (got - want32[:, :count]).abs().max().item() <= tol, count
 
 
+def test_256_sequences_generate_together_at_the_7b_layer_shape(folder):
+    """256 prompts of 1 to 300 tokens as ONE batch through the entry point (recorded decode steps of 256 rows, the
+    device sampler's chain and the argmax on 256 rows, sequences that stop at different steps), greedy and through
+    the default sampling chain with a generator per request: in 32-bit every request's tokens are those it gets
+    in a batch of its own; in bfloat16 every token lies within the tolerance of the 32-bit logits' best."""
+    gen = torch.Generator().manual_seed(9)
+    lens = [int(x) for x in torch.randint(1, 300, (256,), generator=gen)]
+    lens[0], lens[255] = 1, 299
+    prompts = [random_tokens(SHAPE["vocab_size"], n, seed=700 + i) for i, n in enumerate(lens)]
+    budgets = [1 + (i * 7) % 6 for i in range(256)]
+    from cima_b200.sampling import GenOptions
+    for chain in (dict(temperature=0.0, repeat_penalty=1.0), dict(temperature=0.8, top_k=40, top_p=0.9, repeat_penalty=1.1)):
+        opts = [GenOptions(max_tokens=b, ignore_eos=True, seed=i + 1, **chain) for i, b in enumerate(budgets)]
+        lm = cima_b200.load(folder, dtype="float32", max_tokens=256 * 320, max_seqs=256, max_batch=256, verbose=False)
+        got = lm.generate(prompts, opts)
+        assert lm.stats.batches == 1 and [len(r.tokens) for r in got] == budgets
+        for i in (0, 1, 77, 128, 254, 255):
+            alone = lm.generate([prompts[i]], [opts[i]])[0]
+            assert alone.tokens == got[i].tokens, (i, chain)
+        lm.model.cache.check()
+        assert lm.model.cache.slots.held == 0
+        lm.model.check_device()
+        del lm
+        torch.cuda.empty_cache()
+    # bfloat16, greedy: each token against the 32-bit logits of the same history
+    opts = [GenOptions(max_tokens=b, ignore_eos=True, temperature=0.0, repeat_penalty=1.0) for b in budgets]
+    lm = cima_b200.load(folder, dtype="bfloat16", max_tokens=256 * 320, max_seqs=256, max_batch=256, verbose=False)
+    got = lm.generate(prompts, opts)
+    assert lm.stats.batches == 1 and [len(r.tokens) for r in got] == budgets
+    lm.model.check_device()
+    del lm
+    torch.cuda.empty_cache()
+    m32 = load_model(folder, dtype="float32", max_tokens=4096, verbose=False)
+    from cima_b200.engine import StepEntry
+    for i in (0, 5, 77, 128, 200, 255):
+        seq = prompts[i] + got[i].tokens
+        (slot,) = m32.cache.open(1)
+        try:
+            places = list(range(len(prompts[i]) - 1, len(seq) - 1))
+            lg = m32.step([StepEntry(slot, seq[:-1], places)]).float().cpu()
+        finally:
+            m32.cache.close([slot])
+        tol = REL_BF16 * lg.std().item()
+        for k, t in enumerate(got[i].tokens):
+            # the chosen token's and the best token's logits are each off by at most the tolerance
+            assert lg[k, t].item() >= lg[k].max().item() - 2 * tol, (i, k)
+
+
 def test_gated_feed_forward_in_row_chunks(folder, monkeypatch):
     """A step whose [rows, 2 x intermediate] scratch would exceed its bound runs the feed-forward in row chunks: with
     the bound set so low that a 300-token prompt takes three chunks, the 32-bit logits are bit for bit those of
