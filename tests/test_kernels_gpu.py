@@ -436,6 +436,12 @@ def first_launch_on_long_sequences(n_seqs=8, n=8192, nh=28, nkv=4, hd=128):
     print("first launch sound")
 
 
+def test_attention_prefill_tcgen05_long_sequences_of_64_wide_heads():
+    """Four sequences of 8,192 rows with 14 heads of 64 in 2 groups (128 key tiles a block at the narrow head size),
+    three heads whole against float64."""
+    first_launch_on_long_sequences(n_seqs=4, n=8192, nh=14, nkv=2, hd=64)
+
+
 @pytest.mark.parametrize("attempt", [0, 1])
 def test_attention_prefill_tcgen05_first_launch_on_long_sequences(attempt):
     """Eight sequences of 8,192 rows at the 7B head shape as the first launch of a fresh process.  With one barrier for
