@@ -21,6 +21,7 @@ import statistics
 import subprocess
 import sys
 import threading
+import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -254,6 +255,13 @@ def main(argv=None) -> int:
         e2e = {"value": a.batch * stats.decode_steps / stats.decode_s, "unit": "tokens/s",
                "h2d_bytes_per_step": (st.h2d_bytes - pre_h2d) / max(stats.decode_steps, 1),
                "d2h_bytes_per_step": (st.d2h_bytes - pre_d2h) / max(stats.decode_steps, 1)}
+        # The same call with 48 more tokens, its last K steps timed on the host as their tokens arrive: after the
+        # 16k-token prefill has run at the power cap, the SM clock stays near 1.3 GHz for some 25 decode steps (a
+        # step then takes 3.8 ms instead of 3.15), which is most of what this dictionary's "value" sees at a small K.
+        stamps = []
+        lm.generate(prompts, GenOptions(temperature=0.0, repeat_penalty=1.0, max_tokens=a.steps + 48, ignore_eos=True),
+                    on_token=lambda i, t: stamps.append(time.perf_counter()) if i == 0 else None)
+        e2e["after_48_steps"] = a.batch * a.steps / (stamps[-1] - stamps[-1 - a.steps])
         st.pipeline = True
         lm.generate(prompts, GenOptions(temperature=0.0, repeat_penalty=1.0, max_tokens=a.warmup, ignore_eos=True))
         res = lm.generate(prompts, greedy)
@@ -261,7 +269,6 @@ def main(argv=None) -> int:
         st.pipeline = False
 
     # the first token of one short prompt through the entry point (host ids in, the token out), wall clock
-    import time
     first_token = {}
     if not a.no_e2e:
         one = GenOptions(temperature=0.0, repeat_penalty=1.0, max_tokens=1, ignore_eos=True)
