@@ -142,3 +142,45 @@ def test_long_tail_in_32_bit(folder, exact):
         m.cache.close([slot])
     got = torch.cat(outs[1:])
     assert torch.equal(got, exact[-2:])
+
+
+def test_a_window_of_4096_over_20000_positions(tmp_path):
+    """The second layer keeps a window of 4,096 keys in a ring of 65 pages: a 20,000-token prompt whole (the window's
+    first key tile is far from the block's own), then 700 tokens that go on (rounds of a page), then three tokens
+    one by one; bfloat16 against the 32-bit engine, and the 32-bit engine's tail against its own whole prompt."""
+    cfg = dict(SHAPE, use_sliding_window=True, sliding_window=4096, max_window_layers=1)
+    folder = str(tmp_path / "w")
+    cima_b200.write_random_model(folder, cfg, seed=6)
+    n, more, tail = 20000, 700, 3
+    toks = TOKENS[:n + more + tail]
+    places = [0, 4095, 4096, 4097, 8191, 12345, n - 1]
+
+    def run(dtype):
+        m = load_model(folder, dtype=dtype, max_tokens=MAXPOS, verbose=False)
+        assert any(g.ring_pages for g in m.cache.groups)
+        (slot,) = m.cache.open(1)
+        try:
+            outs = [m.step([StepEntry(slot, toks[:n], places)]).float().cpu()]
+            outs.append(m.step([StepEntry(slot, toks[n:n + more], [0, 63, 64, more - 1])]).float().cpu())
+            for p in range(n + more, n + more + tail):
+                outs.append(m.step([StepEntry(slot, [toks[p]], [0])]).float().cpu())
+            m.check_device()
+        finally:
+            m.cache.close([slot])
+        m.cache.check()
+        got = torch.cat(outs)
+        (slot,) = m.cache.open(1)                    # the whole sequence as one prompt: the same places
+        try:
+            allp = places + [n, n + 63, n + 64, n + more - 1] + list(range(n + more, n + more + tail))
+            one = m.step([StepEntry(slot, toks, allp)]).float().cpu()
+        finally:
+            m.cache.close([slot])
+        del m
+        torch.cuda.empty_cache()
+        return got, one
+
+    got32, one32 = run("float32")
+    assert (got32 - one32).abs().max().item() <= 1e-4          # sums of thousands of float32 terms in another order
+    got16, one16 = run("bfloat16")
+    tol = REL_BF16 * one32.std().item()
+    assert (got16 - one32).abs().max().item() <= tol and (one16 - one32).abs().max().item() <= tol
