@@ -68,6 +68,13 @@ struct PairArgs {
   int act;                    // gated epilogue: the gate's activation (CIMA_ACT_*)
 };
 
+// The rows a tile loads: its own 256, but the last tile of a matrix of at least 256 rows starts early enough to end
+// with the matrix.  A TMA box that reaches beyond the tensor is filled with zeros much more slowly than one is loaded
+// (300 rows took 151 us where 512 take 115); the rows before the tile's own are computed again and not stored.
+__device__ __forceinline__ int tile_rows(int first, int p_rows) {
+  return p_rows >= 2 * BM ? min(first, p_rows - 2 * BM) : first;
+}
+
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q, PairArgs a,
@@ -117,7 +124,7 @@ k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_cons
       int g = 0;
       bool ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += pairs) {
-        const int p0 = (tile % p_tiles) * (2 * BM) + (int)rank * BM;
+        const int p0 = tile_rows((tile % p_tiles) * (2 * BM), a.p_rows) + (int)rank * BM;
         const int qt = (tile / p_tiles) * (GATED ? QH : BN);
         const int q0 = GATED ? (rank ? a.up_offset + qt : qt) : qt + (int)rank * QH;
         for (int kb = 0; kb < kblocks; kb++, g++) {
@@ -164,7 +171,8 @@ k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_cons
     int it = 0;
     for (int tile = pair; tile < n_tiles; tile += pairs, it++) {
       const int ab = it & 1;
-      const int p0 = (tile % p_tiles) * (2 * BM) + (int)rank * BM;
+      const int p_first = (tile % p_tiles) * (2 * BM);         // the tile's own rows start here
+      const int p0 = tile_rows(p_first, a.p_rows) + (int)rank * BM;
       const int q0 = (tile / p_tiles) * OUT_COLS;              // first output column of the tile
       if (!mbar_wait(&acc_full[ab], (it >> 1) & 1, a.error_flag, abort_flag)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -180,7 +188,7 @@ k_gemm_tcgen05_pair(const __grid_constant__ CUtensorMap map_p, const __grid_cons
 #pragma unroll
           for (int e = 0; e < 32; e++) v[e] = (a.act == CIMA_ACT_SILU ? v[e] / (1.0f + expf(-v[e])) : cima_gate_act(v[e], a.act)) * u[e];
         }
-        if (i < a.p_rows) {
+        if (i >= p_first && i < a.p_rows) {
           const int jmax = GATED ? a.up_offset : a.q_rows;
           const int j0 = q0 + c0;
           const bool wide = j0 + 32 <= jmax && (a.ldo & 7) == 0 && ((uintptr_t)a.out & 15) == 0;

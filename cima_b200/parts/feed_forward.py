@@ -57,6 +57,7 @@ class GatedMLP:
     def forward(self, h, x: torch.Tensor, batch, next_norm=None):
         rows = h.shape[0]
         chunk = max(64, _SCRATCH_ELEMS // (2 * self.spec.intermediate))
+        chunk -= chunk % 256 if chunk >= 256 else 0          # whole row tiles for the tensor-core product
         if rows <= chunk:
             return self.down.accumulate(self.gate_up.activated(h), x, next_norm)
         if hasattr(h, "tensor"):

@@ -16,7 +16,7 @@ import torch
 from ..kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
 
 FOLDED_NORM_ROWS = 8     # most rows of the skinny kernel's folded RMSNorm (the kernel takes at most 8 rows)
-TCGEN05_ROWS = 256       # from this many rows on, the gated product runs on the tcgen05 kernel
+TCGEN05_ROWS = 256       # rows of a tile of the tcgen05 kernel, and the fewest rows for which the gated product runs on it
 # Measured on B200 inside a recorded decode step of the 7B shape: for 12 and 16 rows the skinny kernel with two
 # 8-row tiles took 77 us for gate|up, 43 us for down and 224 us for the head, the library product with its activation
 # and norm kernels 47 + 3, 29 + 3 and 181 us; the skinny kernel therefore serves 8 rows at most.
@@ -152,11 +152,16 @@ class GatedLinearPair:
         """Whether the tcgen05 product with the fused activation beats the library product plus the activation
         kernel.  With a short sum the tile's epilogue (256 x 256 accumulators through the activation) outlasts
         its main loop: measured at 2,048 rows, K 896 / 1,536 / 2,048 / 3,584: 55 / 93 / 136 / 366 us against
-        41 / 96 / 147 / 385; at 512 rows 31 / 36 / 54 / 101 against 17 / 32 / 52 / 105."""
+        41 / 96 / 147 / 385; at 512 rows 31 / 36 / 54 / 101 against 17 / 32 / 52 / 105.  And the kernel works in
+        tiles of 256 rows, a last tile that is mostly padding costing a whole one, where the library's time follows
+        the rows: inside a prompt step of the 7B shape (K 3,584) 300 rows took 115 us against 65 + 11 for the
+        library and the activation, 600: 163 against 103 + 16, 1,000: 209 against 167 + 25; with full tiles the two
+        are within 5 % (256: 72 / 80, 1,024: 194 / 192, 2,048: 375 / 379, 4,096: 749 / 772, 8,192: 1,576 / 1,586).
+        So the kernel takes the product when at most 2 % of its tiles' rows are padding."""
         K = self.lin.K
-        if K % 8 or K < 1536:
+        if K % 8 or K < 1536 or rows < (TCGEN05_ROWS if K >= 3072 else 1024):
             return False
-        return rows >= (TCGEN05_ROWS if K >= 3072 else 1024)
+        return rows >= 0.98 * TCGEN05_ROWS * -(-rows // TCGEN05_ROWS)
 
     def activated(self, a) -> torch.Tensor:
         """act(a Wg^T) * (a Wu^T) in the activation dtype, [M, I]."""

@@ -601,9 +601,10 @@ def test_add_rmsnorm_equals_the_two_kernels(K, dtype, T, H):
 
 
 @pytest.mark.parametrize("M,N,K_", [(256, 256, 64), (300, 328, 200), (2048, 1000, 448), (513, 3584, 192), (130, 66, 72),
-                                    (1, 8, 8)])
+                                    (1, 8, 8), (257, 264, 72), (1000, 200, 136)])
 def test_gemm_tcgen05_pair_modes(K, M, N, K_):
-    """The product on pairs of SMs (cta_group::2) against float64, every epilogue, tails in every dimension."""
+    """The product on pairs of SMs (cta_group::2) against float64, every epilogue, tails in every dimension (a last
+    tile of rows that starts early to end with the matrix must store, and above all accumulate, its own rows only)."""
     from cima_b200.kernels import SK_ACCUM, SK_STORE, SK_STORE_F32, SK_SWIGLU
     a = g(M, K_, dtype=torch.bfloat16, seed=M)
     w = g(N, K_, dtype=torch.bfloat16, seed=N, scale=1.0 / math.sqrt(K_))
