@@ -42,6 +42,8 @@ class ModelStepper:
         self._graphs = {}
         self.short_context = int(getattr(model, "short_context", 0) or 0)
         self._prompt_graphs = OrderedDict()      # (sequences, rows of the bucket) -> PromptGraph, the newest last
+        from .graph import recorded_prompt_rows
+        self.prompt_rows = recorded_prompt_rows(model) if self.use_graphs else 0
         self._armed = None            # (graph, slots) whose device-side inputs are those of the next step
         cache = model.cache
         self.max_batch = max(1, min(max_batch, cache.n_slots))
@@ -149,15 +151,15 @@ class ModelStepper:
         room for the bucket's rows, a mixer that keeps state of its own per sequence (the padding's rows would pass
         through it), or a group of layers that keeps a window's keys in a ring of pages (the padding's keys would
         land on ring entries that real positions still need)."""
-        from .graph import PROMPT_BUCKETS, PROMPT_ROWS, PromptGraph
+        from .graph import PROMPT_BUCKETS, PromptGraph
         cache = self.model.cache
         longest = max(len(p) for p in prompts)
-        if not self.use_graphs or min(len(p) for p in prompts) == 0 or longest > PROMPT_BUCKETS[-1] or cache.has_mixer_state:
+        if not self.use_graphs or min(len(p) for p in prompts) == 0 or longest > self.prompt_rows or cache.has_mixer_state:
             return None
         if any(g.ring_pages for g in cache.groups):
             return None
         rows = next(r for r in PROMPT_BUCKETS if r >= longest)
-        if rows * len(slots) > PROMPT_ROWS or rows > self.max_position or any(cache.length(s) for s in slots):
+        if rows * len(slots) > self.prompt_rows or rows > self.max_position or any(cache.length(s) for s in slots):
             return None
         vocab = self.model.spec.vocab
         if min(min(p) for p in prompts) < 0 or max(max(p) for p in prompts) >= vocab:

@@ -464,6 +464,44 @@ def test_short_prompts_through_recorded_prompt_steps(dtype):
     assert lm.model.cache.slots.held == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_longer_prompts_of_a_small_model_through_recorded_prompt_steps(dtype, tmp_path):
+    """A small model's prompt steps are recorded up to 2,048 rows (the host would be the slower side): prompts of 257
+    to 2,040 tokens at and around the buckets' edges, one at a time and two together, the second time replayed.
+    32-bit: the tokens of the plain implementation; bfloat16: maxima of the plain logits within its rounding."""
+    cfg = dict(TINY["B"], max_position_embeddings=2048)
+    folder = str(tmp_path / "m")
+    cima_b200.write_random_model(folder, cfg, seed=8)
+    c, W = plain_load(folder)
+    if dtype == "float32":
+        W = {k: v.double() for k, v in W.items()}
+    V = cfg["vocab_size"]
+    lm = cima_b200.load(folder, dtype=dtype, max_tokens=3 * 2048, verbose=False)
+    assert lm.stepper.prompt_rows == 2048
+
+    def check(prompts, tag):
+        got = lm.generate(prompts, temperature=0, repeat_penalty=1.0, max_tokens=3)
+        for p, r in zip(prompts, got):
+            seq = list(p)
+            for t in r.tokens:
+                lg = plain_forward(W, c, seq)[-1].float()
+                assert lg[t] >= lg.max() - (0.0 if dtype == "float32" else 4e-2), (tag, len(p))
+                seq.append(t)
+
+    for n in (257, 384, 385, 1000, 2040):
+        p = random_tokens(V, n, seed=5000 + n)
+        for rep in range(2):
+            check([p], rep)
+    assert {(1, 384), (1, 512), (1, 1024), (1, 2048)} <= set(lm.stepper._prompt_graphs)
+    pair = [random_tokens(V, n, seed=5100 + n) for n in (700, 300)]
+    for rep in range(2):
+        check(pair, rep)
+    assert (2, 768) in lm.stepper._prompt_graphs
+    lm.model.cache.check()
+    assert lm.model.cache.slots.held == 0
+    lm.model.check_device()
+
+
 @pytest.mark.parametrize("pipeline", [True, False])
 def test_sequences_that_outgrow_the_short_context_change_graphs(pipeline, tmp_path):
     """Decode steps of sequences within the short-context bound are recorded without splits of the attention; when
