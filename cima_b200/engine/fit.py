@@ -67,9 +67,13 @@ def forecast(plan: Dict[str, object], requests: Sequence[Sequence[object]], dtyp
     cache = state
     for r, sites in groups.items():
         cache += sites * n_pages * 2 * r.n_kv_heads * page_size * r.head_dim * elt
-    # a step of the longest prompt: the float32 residual, the widest activation and its input, logits of a batch
+    # a step of the longest prompt: the float32 residual, the widest activation and its input, logits of a batch;
+    # and the recorded prompt steps that are kept, each with the activations of its rows
+    from .graph import MAX_PROMPT_GRAPHS, recorded_prompt_rows
+    row = hidden * 4 + (widest + 2 * hidden) * elt
     rows = min(max_tokens, STEP_ROWS)
-    scratch = rows * (hidden * 4 + (widest + 2 * hidden) * elt) + min(n_slots, 256) * vocab * 4 * 2
+    scratch = rows * row + min(n_slots, 256) * vocab * 4 * 2
+    scratch += MAX_PROMPT_GRAPHS * min(max_tokens, recorded_prompt_rows(weights, len(requests), elt)) * row
     return Forecast(weights, cache, scratch)
 
 

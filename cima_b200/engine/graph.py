@@ -96,22 +96,24 @@ PROMPT_BUCKETS = (16, 32, 64, 128, 256, 384, 512, 768, 1024, 1536, 2048)    # ro
 PROMPT_ROWS = 256                           # rows (all sequences together) that every model's prompt steps are recorded for
 
 
-def recorded_prompt_rows(model) -> int:
+MAX_PROMPT_GRAPHS = 12    # recorded prompt steps kept (by sequences and rows); the one used longest ago gives way
+
+
+def recorded_prompt_rows(weight_bytes: float, sites: int, element_size: int) -> int:
     """The most rows, all sequences together, for which a prompt step is recorded rather than issued launch by launch:
-    the largest bucket whose padded step the device finishes before the host could have issued an unrecorded one.  The
-    host needs about 145 us a layer for a prompt step's launches whatever the sizes (measured: 3.8 ms for the 24
+    the largest bucket whose padded step the device finishes before the host could have issued an unrecorded one.
+    ``weight_bytes``: what a step reads of the weights; ``sites``: layers that run; ``element_size``: of a weight.
+    The host needs about 145 us a layer for a prompt step's launches whatever the sizes (measured: 3.8 ms for the 24
     layers of the 0.5B shape, 4.0 to 4.4 ms for 28 layers of the 1.5B and the 7B shape), so a small model's prompts
     of some hundred tokens wait for the host (0.5B, 300 tokens: 4.0 ms to the first token, of which the device works
     0.5), while a 7B prompt beyond 256 rows keeps the device busy longer than the host needs (300 tokens: 5.5 ms of
     device work behind 4.3 ms of launches) and would only pay for its padding.  The device's time is put at the
-    weights read once at 6 TB/s plus two operations per weight and row at 0.8 PFLOP/s (what the small shapes reach at some hundred rows)."""
-    sites = len(model.spec.schedule)
+    weights read once at 6 TB/s plus two operations per weight and row at 0.8 PFLOP/s (what the small shapes reach at
+    some hundred rows)."""
     host_s = 145e-6 * sites
-    nbytes = float(model.weight_bytes())
-    elt = 4 if model.rt.dtype is torch.float32 else 2
     best = PROMPT_ROWS
     for rows in PROMPT_BUCKETS:
-        if rows > PROMPT_ROWS and nbytes / 6e12 + 2.0 * (nbytes / elt) * rows / 0.8e15 <= host_s:
+        if rows > PROMPT_ROWS and weight_bytes / 6e12 + 2.0 * (weight_bytes / element_size) * rows / 0.8e15 <= host_s:
             best = rows
     return best
 

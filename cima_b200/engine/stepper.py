@@ -13,10 +13,10 @@ from ..cache.kv import CapacityError
 from ..sampling.options import GenOptions
 from ..sampling.sampler import DeviceSampler
 from .batch import StepEntry
+from .graph import MAX_PROMPT_GRAPHS
 
 
 MIN_REUSE = 16     # a finished sequence is taken up again only for at least this many tokens in common
-MAX_PROMPT_GRAPHS = 12    # recorded prompt steps kept (by sequences and rows); the one used longest ago gives way
 
 
 class ModelStepper:
@@ -43,7 +43,8 @@ class ModelStepper:
         self.short_context = int(getattr(model, "short_context", 0) or 0)
         self._prompt_graphs = OrderedDict()      # (sequences, rows of the bucket) -> PromptGraph, the newest last
         from .graph import recorded_prompt_rows
-        self.prompt_rows = recorded_prompt_rows(model) if self.use_graphs else 0
+        self.prompt_rows = (recorded_prompt_rows(model.weight_bytes(), len(model.spec.schedule), (4 if model.rt.dtype is torch.float32 else 2))
+                            if self.use_graphs else 0)
         self._armed = None            # (graph, slots) whose device-side inputs are those of the next step
         cache = model.cache
         self.max_batch = max(1, min(max_batch, cache.n_slots))

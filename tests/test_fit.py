@@ -40,3 +40,22 @@ def test_a_cache_that_cannot_fit_is_refused_before_allocating():
     with pytest.raises(DoesNotFit, match="does not fit"):
         load_model(model_folder("B"), dtype="bfloat16", max_tokens=10 ** 10, device="cuda:0", verbose=False)
     assert torch.cuda.memory_allocated() == before
+
+
+def test_how_far_prompt_steps_are_recorded_follows_the_model_size():
+    """A recorded prompt step pays while the device finishes its padded rows before the host could have issued the
+    launches: the known shapes land where they were measured to (0.5B wins up to 2,048 rows, 1.5B up to 768, 3B up to
+    512 or 768, 7B and larger only within the 256 rows that every model gets)."""
+    from cima_b200.config.shapes import SHAPES
+    from cima_b200.engine.graph import PROMPT_ROWS, recorded_prompt_rows
+
+    def step_bytes(c):
+        H, I, L = c["hidden_size"], c["intermediate_size"], c["num_hidden_layers"]
+        qkv = (c["num_attention_heads"] + 2 * c["num_key_value_heads"]) * c["head_dim"]
+        return 2 * (L * (H * qkv + c["num_attention_heads"] * c["head_dim"] * H + 3 * H * I) + c["vocab_size"] * H)
+
+    got = {name: recorded_prompt_rows(step_bytes(SHAPES[name]), SHAPES[name]["num_hidden_layers"], 2)
+           for name in ("qwen2.5-0.5b", "qwen2.5-1.5b", "qwen2.5-3b", "qwen2.5-7b", "qwen2.5-32b")}
+    assert got == {"qwen2.5-0.5b": 2048, "qwen2.5-1.5b": 768, "qwen2.5-3b": 512, "qwen2.5-7b": PROMPT_ROWS,
+                   "qwen2.5-32b": PROMPT_ROWS}
+    assert recorded_prompt_rows(1e6, 2, 4) == 2048 and recorded_prompt_rows(1e12, 2, 2) == PROMPT_ROWS
