@@ -96,7 +96,7 @@ PROMPT_BUCKETS = (16, 32, 64, 128, 256, 384, 512, 768, 1024, 1536, 2048)    # ro
 PROMPT_ROWS = 256                           # rows (all sequences together) that every model's prompt steps are recorded for
 
 
-MAX_PROMPT_GRAPHS = 12    # recorded prompt steps kept (by sequences and rows); the one used longest ago gives way
+MAX_PROMPT_GRAPHS = 24    # recorded prompt steps kept (by sequences and rows); the one used longest ago gives way
 
 
 def recorded_prompt_rows(weight_bytes: float, sites: int, element_size: int) -> int:
@@ -136,6 +136,7 @@ class PromptGraph:
         self.host = torch.zeros(n_seqs * rows + 2 * n_seqs, dtype=torch.int32).pin_memory()
         self.graph = None
         self.logits = None
+        self.uses = 0
 
     def run(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> torch.Tensor:
         """Float32 logits [sequences, vocab] at each prompt's last token.  The caller has reserved ``rows`` positions
@@ -152,12 +153,17 @@ class PromptGraph:
         b.seq_slot.copy_(self.host[B * R:B * R + B], non_blocking=True)
         b.want_rows.copy_(self.host[B * R + B:B * R + 2 * B], non_blocking=True)
         if self.graph is None:
-            out = self.model.forward(b)                 # a real step, eagerly; it also warms every kernel up
-            torch.cuda.current_stream().synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self.logits = self.model.forward(b)
-            self.graph = g
+            # The padded step, launch by launch.  A shape's first step is only that; its second is recorded as well
+            # (recording costs about one more step's launches, which a shape that never comes back would not
+            # repay); from the third on the graph is replayed.  What is computed is the same each time.
+            self.uses += 1
+            out = self.model.forward(b)
+            if self.uses >= 2:
+                torch.cuda.current_stream().synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self.logits = self.model.forward(b)
+                self.graph = g
             return out
         self.graph.replay()
         return self.logits

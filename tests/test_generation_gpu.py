@@ -421,7 +421,8 @@ def test_loading_holds_one_group_of_tensors_on_the_host_not_the_checkpoint():
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_short_prompts_through_recorded_prompt_steps(dtype):
     """One short prompt at a time takes a recorded prompt step whose rows are padded to 16, 32 or 64: lengths at and
-    around the buckets' edges, each twice (the second time the step is replayed), then a batch, then longer ones.
+    around the buckets' edges, each three times (a shape's first step is issued as it is, its second is recorded,
+    its third replayed), then batches, then longer ones.
     32-bit: the tokens of the plain implementation; bfloat16: maxima of the plain logits within its rounding.
     The padding's keys lie beyond the sequence's length and are written over by the tokens that follow."""
     name = "B"
@@ -429,7 +430,7 @@ def test_short_prompts_through_recorded_prompt_steps(dtype):
     cfg, W = plain_load(model_folder(name))
     lm = cima_b200.load(model_folder(name), dtype=dtype, max_tokens=2048, verbose=False)
     for n in (1, 2, 15, 16, 17, 31, 33, 64, 65, 100):
-        for rep in range(2):
+        for rep in range(3):
             p = random_tokens(V, n, seed=3000 + n + 7 * rep)
             r = lm.generate([p], temperature=0, repeat_penalty=1.0, max_tokens=6)[0]
             if dtype == "float32":
@@ -444,7 +445,7 @@ def test_short_prompts_through_recorded_prompt_steps(dtype):
     # several short prompts in one recorded step: padded to the longest one's bucket, each gathered at its own end
     for lens in ([3, 16, 9], [40, 1, 33, 64], [5, 5, 5, 5, 5, 5, 5, 5], [100, 128]):
         ps = [random_tokens(V, n, seed=4000 + 13 * i + n) for i, n in enumerate(lens)]
-        for rep in range(2):
+        for rep in range(3):
             got = lm.generate(ps, temperature=0, repeat_penalty=1.0, max_tokens=4)
             for p, r in zip(ps, got):
                 if dtype == "float32":
@@ -467,7 +468,8 @@ def test_short_prompts_through_recorded_prompt_steps(dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_longer_prompts_of_a_small_model_through_recorded_prompt_steps(dtype, tmp_path):
     """A small model's prompt steps are recorded up to 2,048 rows (the host would be the slower side): prompts of 257
-    to 2,040 tokens at and around the buckets' edges, one at a time and two together, the second time replayed.
+    to 2,040 tokens at and around the buckets' edges, one at a time and two together, each three times (issued as it
+    is, recorded, replayed).
     32-bit: the tokens of the plain implementation; bfloat16: maxima of the plain logits within its rounding."""
     cfg = dict(TINY["B"], max_position_embeddings=2048)
     folder = str(tmp_path / "m")
@@ -490,11 +492,11 @@ def test_longer_prompts_of_a_small_model_through_recorded_prompt_steps(dtype, tm
 
     for n in (257, 384, 385, 1000, 2040):
         p = random_tokens(V, n, seed=5000 + n)
-        for rep in range(2):
+        for rep in range(3):
             check([p], rep)
     assert {(1, 384), (1, 512), (1, 1024), (1, 2048)} <= set(lm.stepper._prompt_graphs)
     pair = [random_tokens(V, n, seed=5100 + n) for n in (700, 300)]
-    for rep in range(2):
+    for rep in range(3):
         check(pair, rep)
     assert (2, 768) in lm.stepper._prompt_graphs
     lm.model.cache.check()
