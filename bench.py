@@ -272,7 +272,7 @@ def main(argv=None) -> int:
     first_token = {}
     if not a.no_e2e:
         one = GenOptions(temperature=0.0, repeat_penalty=1.0, max_tokens=1, ignore_eos=True)
-        for n in (16, 128):
+        for n in (16, 128, 300):
             p = rng.integers(0, V, size=n).tolist()
             for _ in range(3):
                 lm.generate([p], one)
