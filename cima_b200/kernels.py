@@ -557,7 +557,10 @@ class Kernels:
             # place) and merging in the last block to finish (a fence and a ticket per block) were both measured
             # slower inside the decode step
             base = B * n_kv_heads * mtiles
-            n_splits = max(1, min(32, SPLIT_BLOCKS // base))
+            # 32 splits at most, 64 where even 32 leave SMs without a block (one sequence of 4 kv heads: measured at
+            # the 7B shape 19 to 25 us against 28 to 31 at 30,000 positions, 15 against 19 at 16,384, the same up to
+            # 6,000; with two sequences 32 are the best again)
+            n_splits = max(1, min(64 if base * 32 < SPLIT_FEW_BLOCKS else 32, SPLIT_BLOCKS // base))
             if n_splits > 8 and base * 8 >= SPLIT_FEW_BLOCKS:
                 n_splits = 8
             if max_len > 0:

@@ -284,6 +284,41 @@ def scattered_tables(lens, slots, page, ring=0, seed=0):
     return tables, total, max(need)
 
 
+@pytest.mark.parametrize("nh,nkv,hd", [(28, 4, 128), (14, 2, 64)])
+def test_attention_decode_with_many_live_splits(K, nh, nkv, hd):
+    """One sequence of 5,000 positions (79 pages) beside a short one: 33, 40 and 64 splits that all have pages (the
+    short sequence's blocks beyond its pages have none), and the number the wrapper chooses for one long sequence
+    alone (64), against the float64 statement; key 4,321 stands out for head 0."""
+    lens, slots, page = [5000, 70], [2, 0], 64
+    tables, n_pages, width = scattered_tables(lens, slots, page, seed=hd + 1)
+    cpu, gpu = make_kv(n_pages, nkv, page, hd, 4, width, 0, 0, torch.bfloat16, tables)
+    scale = 1.0 / math.sqrt(hd)
+    qkv = g(2, (nh + 2 * nkv) * hd, dtype=torch.bfloat16, seed=5)
+    for i, (slot, n) in enumerate(zip(slots, lens)):
+        k, v = g(n, nkv, hd, dtype=torch.bfloat16, seed=30 + i), g(n, nkv, hd, dtype=torch.bfloat16, seed=40 + i)
+        if i == 0:
+            k[4321, 0] = qkv[0, :hd] * 6.0
+        fill_cache(cpu, gpu, slot, k, v)
+    seqs = [(slots[i], lens[i] - 1, 1) for i in range(2)]
+    bc, bg = batch_of(seqs, "cpu"), batch_of(seqs, "cuda")
+    want = torch.zeros(2, nh * hd, dtype=torch.float64)
+    REF.attention_plain(qkv, cpu, bc.row_pos, bc.row_seq, bc.seq_slot, bc.seq_first_row, want, nh, nkv, hd, scale, 0, True)
+    out = torch.empty(2, nh * hd, dtype=torch.bfloat16, device="cuda")
+    for n_splits in (33, 40, 64):
+        out.fill_(7.0)
+        K.attention_decode(qkv.cuda(), gpu, bg.seq_slot, bg.seq_len, out, nh, nkv, hd, scale, 0, n_splits=n_splits)
+        assert err(out, want) <= TOL["bfloat16"], n_splits
+    from cima_b200.engine.profile import StepProfile
+    K.profile = seen = StepProfile()
+    try:
+        out.fill_(7.0)
+        K.attention_decode(qkv[:1].cuda(), gpu, bg.seq_slot[:1], bg.seq_len[:1], out[:1], nh, nkv, hd, scale, 0, max_len=5000)
+    finally:
+        K.profile = None
+    assert [l.name for l in seen.launches] == ["attention_decode[64 splits]"]
+    assert err(out[:1], want[:1]) <= TOL["bfloat16"]
+
+
 @pytest.mark.parametrize("dtype,page", [("float32", 16), ("bfloat16", 16), ("bfloat16", 64)])
 @pytest.mark.parametrize("nh,nkv,hd", [(6, 2, 48), (7, 1, 128), (4, 4, 16), (28, 4, 128), (3, 3, 80), (40, 2, 64), (2, 1, 112)])
 def test_attention_decode_over_cache(K, dtype, page, nh, nkv, hd):
