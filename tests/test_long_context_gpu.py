@@ -184,3 +184,43 @@ def test_a_window_of_4096_over_20000_positions(tmp_path):
     got16, one16 = run("bfloat16")
     tol = REL_BF16 * one32.std().item()
     assert (got16 - one32).abs().max().item() <= tol and (one16 - one32).abs().max().item() <= tol
+
+
+@pytest.mark.parametrize("dtype,max_tokens", [("bfloat16", 2_700_000), ("float32", 1_400_000)])
+def test_pages_far_into_a_large_cache(folder, dtype, max_tokens):
+    """A cache of more than 5 GB a layer (2.7 million positions in bfloat16): with the low pages taken away, sequences
+    get pages whose bytes lie beyond 4 GB of their layer's storage.  A prompt whole, one in pieces (rows that read the
+    pages through the tensor map or the block table), then decode steps of the two together: bit for bit the logits of
+    the same run on the first pages, so no kernel cuts a page's address to 32 bits."""
+    m = load_model(folder, dtype=dtype, max_tokens=max_tokens, max_seqs=4, verbose=False)
+    elt = 2 if dtype == "bfloat16" else 4
+    page_bytes = 2 * SHAPE["num_key_value_heads"] * 64 * SHAPE["head_dim"] * elt
+    a, b = TOKENS[:700], TOKENS[1000:1600]
+
+    def run():
+        slots = m.cache.open(2)
+        try:
+            outs = [m.step([StepEntry(slots[0], a, [0, 699])]).float().cpu()]
+            outs.append(m.step([StepEntry(slots[1], b[:100], [99])]).float().cpu())
+            outs.append(m.step([StepEntry(slots[1], b[100:], [0, 499])]).float().cpu())       # goes on by 500 rows
+            for k in range(3):
+                outs.append(m.step([StepEntry(slots[0], [TOKENS[2000 + k]], [0]),
+                                    StepEntry(slots[1], [TOKENS[3000 + k]], [0])]).float().cpu())
+            m.check_device()
+            pages = [p for g in m.cache.groups for s in slots for p in g.pages_of[s]]
+            return torch.cat(outs), min(pages)
+        finally:
+            m.cache.close(slots)
+
+    low, first_low = run()
+    assert first_low == 0
+    ballast = [g.pool.take(g.pool.free - 40) for g in m.cache.groups]
+    try:
+        high, first_high = run()
+    finally:
+        for g, held in zip(m.cache.groups, ballast):
+            g.pool.give(held)
+    assert first_high * page_bytes > 5 * 2 ** 30
+    assert torch.equal(low, high)
+    m.cache.check()
+    assert m.cache.slots.held == 0
