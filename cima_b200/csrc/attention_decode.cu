@@ -59,7 +59,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 constexpr int MAX_SPLITS = 64;
-constexpr int STAGES = 3;         // pages in flight per block (two blocks of 3 x 34 KB fit an SM at head_dim 128)
+// Pages in flight per block: as many as fill about 104 KB of shared memory with their padded tiles, so that two blocks
+// fit an SM whatever the head size and hold the same bytes in flight (3 pages of 34 KB at head_dim 128, 5 of 18 KB at
+// 64; with 3 at every head size a block of 64-wide heads drew half the bandwidth).
+__host__ __device__ constexpr int decode_stages(int hd) {
+  const int n = (104 * 1024) / (2 * PS * (hd + 8) * 2);
+  return n < 3 ? 3 : (n > 8 ? 8 : n);
+}
 
 // The splits that get pages of a sequence with ``len`` positions: at most one per page of the visible keys.
 __device__ __forceinline__ int live_splits(int len, int window, int n_splits) {
@@ -80,6 +86,7 @@ k_attention_decode(const __nv_bfloat16* __restrict__ qkv, int ld, const __nv_bfl
   constexpr int ROW = HD + 8;                         // padded row of a tile, in elements (16 bytes of padding)
   constexpr int TILE = PS * ROW;                      // elements of one K or V tile
   constexpr int KSTEPS = HD / 16, NTILES = HD / 8;
+  constexpr int STAGES = decode_stages(HD);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [STAGES][K|V][PS][ROW]
 
@@ -340,6 +347,7 @@ int launch_decode(const void* qkv, int ld, const void* cache, CimaPaged pg, cons
                   float* part_o, float* part_ml, void* out, int ldo, int B, int nh, int nkv, float scale, int window,
                   int n_splits, int early, cudaStream_t stream) {
   auto kern = k_attention_decode<HD>;
+  constexpr int STAGES = decode_stages(HD);
   const size_t tiles = (size_t)STAGES * 2 * PS * (HD + 8) * sizeof(__nv_bfloat16);
   const size_t merge = (size_t)WARPS * 16 * (HD + 2) * sizeof(float);
   const size_t smem = tiles > merge ? tiles : merge;
